@@ -1,0 +1,318 @@
+#!/usr/bin/env python
+"""Attention-stack decode benchmark (BASELINE.json configs[2]).
+
+One step = one token for each of 64 concurrent sequences through the 40-layer
+35B-shaped attention stack (30 gated delta-net + 10 GQA layers, 3:1), Q8_0 KV
+cache, fp32 recurrent state, bf16 activations, contexts uniform in [1k, 32k].
+Multi-GPU runs shard by sequence: every rank owns 64 sequences of its own
+(weak scaling, nothing is exchanged inside the stack).
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    torchrun ... bench.py --gpus N ...
+    python bench.py --impl reference     # the CPU path on the host cores
+
+Prints ONE JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "attn_stack_decode_tokens_per_s"
+UNIT = "tok/s"
+
+
+def draw_contexts(n, lo, hi, seed):
+    return np.random.default_rng(seed).integers(lo, hi + 1, n).astype(np.int64)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while active."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()                  # the exact process started above
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------
+# CPU path (the checker libraries, timed): a bounded sample of the same workload
+# ---------------------------------------------------------------------------------------
+def cpu_sample(contexts, n_seq_sample, seed, threads):
+    """Time one decode token of `n_seq_sample` sequences through one interleave group
+    (3 delta-net layers + 1 GQA layer) on the host, and scale to the 40-layer stack.
+    Uses the reference's own compiled objects when they were built, else the port."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import oracle as O
+    from ornithology_b200.stack import ARCHS, full_weights, linear_weights
+    a = ARCHS["35b"]
+    orc = O.Oracle()
+    kind = "port"
+    lin_layers = []
+    for i in range(3):
+        w = linear_weights(a, seed, i)
+        lin_layers.append(O.LinearLayer(a["nk"], a["nv"], a["dk"], a["dv"], w["conv_w"], w["a_coef"], w["dt_bias"], w["norm_w"]))
+    fw = full_weights(a, seed, 3)
+    full = O.FullLayer(a["nh"], a["nkv"], a["hd"], fw["q_norm_w"], fw["k_norm_w"], rope_dim=a["rope_dim"], theta=a["theta"])
+    ctx = [int(c) for c in contexts[:n_seq_sample]]
+    g = np.random.default_rng(seed + 1)
+    seqs = []
+    for L in ctx:                                # state set-up is not timed
+        kv = orc.kv(L + 1, a["nkv"], a["hd"], O.KV_Q8_0)
+        rows = (L, a["nkv"] * a["hd"])
+        Kd = g.standard_normal(rows, dtype=np.float32)        # stand-in for the decoded rows
+        Vd = g.standard_normal(rows, dtype=np.float32)
+        import ctypes as C
+        C.memmove(kv.c.K, Kd.ctypes.data, Kd.nbytes); C.memmove(kv.c.V, Vd.ctypes.data, Vd.nbytes)
+        kv.c.len = L
+        S = [(g.standard_normal((a["nv"], a["dv"], a["dk"])) * 0.05).astype(np.float32) for _ in range(3)]
+        buf = [g.standard_normal(3 * lin_layers[0].cc).astype(np.float32) for _ in range(3)]
+        ins_l = [[g.standard_normal(w).astype(np.float32) for w in (lin_layers[0].cc, a["nv"], a["nv"], lin_layers[0].vd)] for _ in range(3)]
+        ins_f = [g.standard_normal(w).astype(np.float32) for w in (a["nh"] * 2 * a["hd"], a["nkv"] * a["hd"], a["nkv"] * a["hd"])]
+        seqs.append((kv, L, S, buf, ins_l, ins_f))
+
+    def one(s):
+        kv, L, S, buf, ins_l, ins_f = s
+        for i in range(3):
+            orc.linear_attn_step(lin_layers[i], S[i], buf[i], *ins_l[i])
+        orc.full_attn_step(full, kv, L, *ins_f)
+
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        list(ex.map(one, seqs))
+    dt = time.perf_counter() - t0
+    groups = a["layers"] // a["interval"]
+    tok_s = len(seqs) / (dt * groups)            # sequence-tokens per second through all 40 layers
+    sample = (f"1 decode token for {len(seqs)} of the sequences (contexts {ctx}) through one 3+1 layer group, "
+              f"x{groups} groups, {threads} threads, {dt:.2f} s of wall time")
+    return tok_s, kind, sample, dt
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = min(os.cpu_count() or 1, 32)
+    contexts = draw_contexts(args.seqs, args.min_ctx, args.max_ctx, args.seed)
+    n_sample = min(args.seqs, max(threads, 8))
+    vals, sample, kind = [], "", "port"
+    for it in range(args.warmup + args.steps):
+        v, kind, sample, _ = cpu_sample(contexts, n_sample, args.seed, threads)
+        if it >= args.warmup:
+            vals.append(v)
+        if it >= 1 and args.steps > 2:            # bounded: the CPU path is slow by construction
+            break
+    value = float(np.mean(vals)) if vals else v
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * args.seqs / value,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, contexts, 1),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, contexts, world):
+    return {"workload": "configs[2]: batched decode, 40-layer 35B-shaped attention stack (30 delta-net + 10 GQA)",
+            "sequences_per_gpu": args.seqs, "context": f"uniform[{args.min_ctx},{args.max_ctx}] seed {args.seed}",
+            "sum_context_rank0": int(np.sum(contexts[:args.seqs])), "kv_cache": "Q8_0", "state": "fp32",
+            "activations": "bf16", "parallelism": f"sequence-sharded x{world}",
+            "l2": "inputs larger than L2 (every step streams all KV rows and all recurrent state)"}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from ornithology_b200 import device as D
+    from ornithology_b200.stack import AttnStack
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    all_ctx = draw_contexts(args.seqs * world, args.min_ctx, args.max_ctx, args.seed)
+    contexts = all_ctx[rank * args.seqs:(rank + 1) * args.seqs]
+    total_steps = 2 * (args.warmup + args.steps) + 4
+    caps = [int(c) + total_steps + 8 for c in contexts]
+    stack = AttnStack("35b", caps, kv_mode=D.KV_Q8_0, seed=args.seed, device=dev)
+    stack.fill(contexts, seed=args.seed + 17)
+    max_len = int(max(caps))
+
+    ins = stack.random_inputs(args.seed + 5, dtype=torch.bfloat16, device=dev)
+    outs = [torch.empty(stack.n_seq, stack.output_width(k), dtype=torch.bfloat16, device=dev) for k, _, _ in stack.layers]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- value: inputs resident in HBM --------------------------------------------------
+    for _ in range(args.warmup):
+        stack.decode_step(ins, outs, max_len=max_len)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    n_layers = len(stack.layers)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n_layers + 1)] for _ in range(args.steps)]
+    barrier()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for s in range(args.steps):
+        # same work as decode_step, with an event between layers (per-kernel-family timing)
+        for i, (kind, layer, state) in enumerate(stack.layers):
+            ev[s][i].record()
+            if kind == "full":
+                D.full_attn_step(layer, state, stack.pos, *ins[i], out=outs[i], max_len=max_len)
+            else:
+                D.linear_attn_step(layer, state, stack.pos, *ins[i], out=outs[i])
+        ev[s][n_layers].record()
+        D.advance(stack.pos)
+    t_end.record()
+    barrier()
+    ms_total = t_start.elapsed_time(t_end)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_lin = np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)
+                      for i, (k, _, _) in enumerate(stack.layers) if k == "linear"])
+    ms_full = np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)
+                       for i, (k, _, _) in enumerate(stack.layers) if k == "full"])
+
+    # ---- e2e: host buffers, copies inside the timed region -------------------------------
+    h_ins = stack.random_inputs(args.seed + 5, dtype=torch.bfloat16, pin=True)
+    h_outs = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+    h2d = sum(t.numel() * t.element_size() for layer in h_ins for t in layer)
+    d2h = sum(t.numel() * t.element_size() for t in h_outs)
+
+    def e2e_step():
+        for i in range(n_layers):
+            for dst, src in zip(ins[i], h_ins[i]):
+                dst.copy_(src, non_blocking=True)
+        stack.decode_step(ins, outs, max_len=max_len)
+        for dst, src in zip(h_outs, outs):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e_end.record()
+    barrier()
+    ms_e2e = e_start.elapsed_time(e_end)
+
+    times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = float(times[0]), float(times[1])
+
+    if rank == 0:
+        tokens = args.seqs * world * args.steps
+        value = tokens / (ms_total * 1e-3)
+        e2e = tokens / (ms_e2e * 1e-3)
+        ctx_now = [int(c) + args.warmup + args.steps // 2 for c in contexts]      # contexts mid-way through the timed steps
+        b_lin, b_full = stack.decode_bytes(ctx_now)
+        n_lin = sum(1 for k, _, _ in stack.layers if k == "linear")
+        n_full = n_layers - n_lin
+        peak, src = measured_peaks()
+        fam = {"linear_attn_step": {"ms_per_launch": float(ms_lin), "bytes_per_launch": b_lin / n_lin,
+                                    "gbs": b_lin / n_lin / (ms_lin * 1e-3) / 1e9, "launches_per_step": n_lin},
+               "full_attn_step": {"ms_per_launch": float(ms_full), "bytes_per_launch": b_full / n_full,
+                                  "gbs": b_full / n_full / (ms_full * 1e-3) / 1e9, "launches_per_step": n_full}}
+        dom = max(fam, key=lambda k: fam[k]["ms_per_launch"] * fam[k]["launches_per_step"])
+        roof = {"bound": "hbm", "kernel": dom, "achieved": fam[dom]["gbs"], "peak": peak, "unit": "GB/s",
+                "frac": fam[dom]["gbs"] / peak, "peak_source": f"of {src}", "traffic": None, "families": fam,
+                "whole_step_gbs": (b_lin + b_full) / (ms_total / args.steps * 1e-3) / 1e9}
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            threads = min(os.cpu_count() or 1, 32)
+            v, kind, sample, _ = cpu_sample(all_ctx, min(args.seqs, max(threads, 8)), args.seed, threads)
+            cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": workload_config(args, contexts, world),
+                "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": ms_e2e / args.steps},
+                "gpu_launches": stack.launches_per_step() * args.steps,
+                "roofline": roof, "cpu_baseline": cpu, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU")
+    ap.add_argument("--min-ctx", type=int, default=1024)
+    ap.add_argument("--max-ctx", type=int, default=32768)
+    ap.add_argument("--seed", type=int, default=3)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world == 1 and args.gpus > 1:
+        # launched without torchrun: re-launch one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,307 @@
+/* ornith_cuda.h — C ABI of the B200 attention backend for ornithology.
+ *
+ * One shared library (libornith_cuda.so) exports two tiers:
+ *
+ *  Tier 1 — the drop-in.  The seventeen functions of the engine's attention
+ *  header (reference: src/ornith_attn.h:71-147) plus the backend probe
+ *  (reference: src/ornith_cuda.cu:12), with the same names, structs, argument
+ *  meaning and error behaviour.  Host pointers in and out; every call runs the
+ *  CUDA kernels below and keeps the caller-visible struct fields valid host
+ *  images, so code that pokes `K`, `len`, `S` or `buf` directly keeps working.
+ *  Link this library instead of the engine's ornith_attn.o.
+ *
+ *  Tier 2 — the device-resident API (ornith_cuda_*).  Layer-level entry points
+ *  that take DEVICE pointers and batch descriptors, keep the KV cache, the
+ *  recurrent state and the conv history in HBM, and never touch the host on the
+ *  data path.  This is what the engine's layer wiring calls under
+ *  ORNITH_BACKEND_CUDA (reference call sites: src/ornith_rforward.c:419-618,
+ *  src/ornith_forward.c:338-531).
+ *
+ * There is no CPU fallback: every compute entry point fails with
+ * ORNITH_ERR_BACKEND (tier 2) or leaves its outputs untouched and records an
+ * error (tier 1, whose compute functions return void like the reference's) when
+ * no CUDA device is usable.
+ *
+ * All pointers are plain C pointers; `stream` is a cudaStream_t passed as void*
+ * (NULL = the default stream).  Unless stated otherwise tier-2 calls are
+ * asynchronous on `stream`.
+ */
+#ifndef ORNITH_CUDA_H
+#define ORNITH_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (reference: src/ornith.h:34-41) ------------------------- */
+#ifndef ORNITH_H
+typedef enum {
+    ORNITH_OK = 0,
+    ORNITH_ERR_IO,
+    ORNITH_ERR_FORMAT,
+    ORNITH_ERR_UNSUPPORTED,
+    ORNITH_ERR_OOM,
+    ORNITH_ERR_NOTFOUND
+} ornith_status;
+const char *ornith_last_error(void);              /* reference: src/ornith_util.c:21-23 */
+void        ornith_set_error(const char *fmt, ...);   /* reference: src/ornith_util.c:25-30 */
+#endif
+/* one code beyond the reference's enum: a CUDA runtime / launch failure */
+#define ORNITH_ERR_BACKEND 6
+
+/* 1 when a CUDA device of compute capability 10.x is usable, else 0.
+ * Replaces the stub at src/ornith_cuda.cu:12-15 (which always returns 0). */
+int ornith_backend_cuda_available(void);
+
+/* ======================================================================== */
+/* Tier 1 — drop-in for src/ornith_attn.h                                    */
+/* ======================================================================== */
+#ifndef ORNITH_ATTN_H
+
+/* reference: src/ornith_attn.h:57-69 (field order and types are ABI) */
+typedef struct {
+    float  *K, *V;
+    int8_t *Kq, *Vq;
+    float  *Ks, *Vs;
+    int     quantized;
+    int     capacity;
+    int     len;
+    int     n_kv_heads;
+    int     head_dim;
+} ornith_kv_cache;
+
+/* reference: src/ornith_attn.h:104-107 */
+typedef struct { float *S; int dk, dv; } ornith_delta_state;
+
+/* reference: src/ornith_attn.h:129-132 */
+typedef struct { float *buf; int K, C; } ornith_conv_state;
+
+/* reference: src/ornith_attn.h:72-82, src/ornith_attn.c:12-60 */
+ornith_status ornith_kv_init(ornith_kv_cache *c, int capacity, int n_kv_heads, int head_dim);
+ornith_status ornith_kv_init_ex(ornith_kv_cache *c, int capacity, int n_kv_heads, int head_dim,
+                                int quantized);
+size_t        ornith_kv_bytes_per_token(int n_kv_heads, int head_dim, int quantized);
+void          ornith_kv_free(ornith_kv_cache *c);
+void          ornith_kv_reset(ornith_kv_cache *c);
+
+/* reference: src/ornith_attn.h:89-91, src/ornith_attn.c:87-149.
+ * Appends k_new/v_new at position c->len, then attends over the whole cache.
+ * A full cache is a silent no-op, as in the reference. */
+void ornith_gqa_step(ornith_kv_cache *c, const float *q, const float *k_new, const float *v_new,
+                     int n_heads, float *out, float scale);
+/* reference: src/ornith_attn.h:97-99, src/ornith_attn.c:151-176 */
+void ornith_gqa_reference(const float *Q, const float *K, const float *V, int T, int n_heads,
+                          int n_kv_heads, int head_dim, float *O, float scale);
+
+/* reference: src/ornith_attn.h:109-123, src/ornith_attn.c:182-349 */
+ornith_status ornith_delta_init(ornith_delta_state *s, int dk, int dv);
+void          ornith_delta_free(ornith_delta_state *s);
+void          ornith_delta_reset(ornith_delta_state *s);
+void ornith_delta_step(ornith_delta_state *s, const float *q, const float *k, const float *v,
+                       float alpha, float beta, float *o);
+void ornith_delta_prefill(ornith_delta_state *s, const float *Q, const float *K, const float *V,
+                          const float *alpha, const float *beta, int T, int chunk, float *O);
+
+/* reference: src/ornith_attn.h:134-147, src/ornith_attn.c:355-397 */
+ornith_status ornith_conv_init(ornith_conv_state *cs, int K, int C);
+void          ornith_conv_free(ornith_conv_state *cs);
+void          ornith_conv_reset(ornith_conv_state *cs);
+void ornith_conv_step(ornith_conv_state *cs, const float *x_in, const float *weight,
+                      const float *bias, float *out);
+void ornith_conv_prefill(ornith_conv_state *cs, const float *X, const float *weight,
+                         const float *bias, int T, float *OUT);
+#endif /* ORNITH_ATTN_H */
+
+/* ======================================================================== */
+/* Tier 2 — device-resident API                                              */
+/* ======================================================================== */
+
+/* activation I/O format of the layer entry points (state and accumulation are
+ * always f32) */
+enum { ORNITH_ACT_F32 = 0, ORNITH_ACT_BF16 = 1 };
+
+/* KV row formats.
+ *  F32        rows of head_dim f32 (reference: src/ornith_attn.h:59)
+ *  INT8_HEAD  int8 codes + one f32 scale per (position, head), the engine's own
+ *             quantised cache (reference: src/ornith_attn.h:46-52, src/ornith_attn.c:65-77)
+ *  Q8_0       ggml Q8_0 blocks, 34 bytes per 32 values, byte-identical to the
+ *             engine's codec (reference: src/ornith_quant.c:155-175) */
+enum { ORNITH_KV_F32 = 0, ORNITH_KV_INT8_HEAD = 1, ORNITH_KV_Q8_0 = 2 };
+
+/* key-head -> value-head pairing of the delta-net layers
+ *  TILED   kh = hv % nk        (reference: src/ornith_rforward.c:491)
+ *  GROUPED kh = hv / (nv/nk)   (reference: src/ornith_forward.c:387) */
+enum { ORNITH_HEADMAP_TILED = 0, ORNITH_HEADMAP_GROUPED = 1 };
+
+/* ---- runtime helpers (synchronous; for hosts that do not link cudart) ------ */
+const char   *ornith_cuda_last_error(void);
+ornith_status ornith_cuda_set_device(int device);
+ornith_status ornith_cuda_malloc(void **dev_ptr, size_t bytes);      /* zero-filled */
+ornith_status ornith_cuda_free(void *dev_ptr);
+ornith_status ornith_cuda_memset(void *dev_ptr, int value, size_t bytes);
+ornith_status ornith_cuda_h2d(void *dev_dst, const void *host_src, size_t bytes);
+ornith_status ornith_cuda_d2h(void *host_dst, const void *dev_src, size_t bytes);
+ornith_status ornith_cuda_sync(void *stream);
+/* inverse RoPE frequencies theta^(-2i/rotary_dim), i < rotary_dim/2, computed on
+ * the host with the engine's own expression (reference: src/ornith_tensor.c:171);
+ * upload them once and pass the device copy as `rope_inv_freq`. */
+void ornith_cuda_rope_inv_freq(float theta, int rotary_dim, float *host_out);
+
+/* ---- codec entry points (reference: src/ornith_quant.c:155-184, src/ornith_attn.c:65-77) */
+/* n f32 values (multiple of 32) -> n/32 blocks of 34 bytes, and back. */
+ornith_status ornith_cuda_q8_0_encode(const float *dev_src, void *dev_dst, size_t n, void *stream);
+ornith_status ornith_cuda_q8_0_decode(const void *dev_src, float *dev_dst, size_t n, void *stream);
+
+/* ---- full (GQA) attention layers ------------------------------------------ */
+
+/* One layer's KV cache for a batch of sequences.  Sequence b owns positions
+ * [seq_off[b], seq_off[b+1]) of the pools; its capacity is the difference.
+ *   F32        K,V: float   [positions][n_kv_heads][head_dim]
+ *   INT8_HEAD  K,V: int8    [positions][n_kv_heads][head_dim]; Ks,Vs: float [positions][n_kv_heads]
+ *   Q8_0       K,V: uint8   [positions][n_kv_heads][head_dim/32][34]
+ * Within a sequence these are exactly the engine's cache images
+ * (reference: src/ornith_attn.h:57-69), so a session dump is a plain copy. */
+typedef struct {
+    int32_t mode, n_kv_heads, head_dim, n_seq;
+    void   *K, *V;                 /* device */
+    float  *Ks, *Vs;               /* device, INT8_HEAD only */
+    const int64_t *seq_off;        /* device [n_seq + 1] */
+} ornith_cuda_kv;
+
+/* reference: src/ornith_rforward.c:419-455 (weights and shape of one full layer) */
+typedef struct {
+    int32_t n_heads, n_kv_heads, head_dim, rope_dim;
+    int32_t gated;                 /* 1: q projection packs [q | gate] per head (:432-435) */
+    float   eps, scale;            /* scale <= 0: 1/sqrt(head_dim) (src/ornith_attn.c:91) */
+    const float *q_norm_w;         /* device [head_dim], NULL: q,k arrive normalised + rotated */
+    const float *k_norm_w;         /* device [head_dim] */
+    const float *rope_inv_freq;    /* device [rope_dim/2], NULL with rope_dim == 0 */
+} ornith_cuda_full_layer;
+
+/* scratch bytes ornith_cuda_full_attn_step needs for n_seq sequences whose
+ * longest context (after the append) is max_len */
+size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *layer, int n_seq, int max_len);
+
+/* One decode step of a full-attention layer for n_seq sequences, between the
+ * projections: split q|gate, q/k RMSNorm, partial RoPE, append to the cache at
+ * kv_len[b], attend over [0, kv_len[b]], sigmoid output gate.
+ * Replaces the body of full_attn() (reference: src/ornith_rforward.c:432-450).
+ *   qproj [n_seq][n_heads*(gated?2:1)*head_dim], k,v [n_seq][n_kv_heads*head_dim],
+ *   out [n_seq][n_heads*head_dim]                       (act_dtype)
+ *   kv_len  device int32 [n_seq]: positions already in the cache (not modified)
+ *   rope_pos device int32 [n_seq] or NULL (= kv_len)
+ *   max_len: host upper bound on kv_len[b] + 1
+ * A sequence whose cache is full is skipped, as the reference does. */
+ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *layer, const ornith_cuda_kv *kv,
+                                         const int32_t *kv_len, const int32_t *rope_pos,
+                                         const void *qproj, const void *k, const void *v, void *out,
+                                         int act_dtype, int max_len,
+                                         void *scratch, size_t scratch_bytes, void *stream);
+
+size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *layer, int n_seq, int T);
+
+/* Causal prefill of T tokens per sequence, appended at kv_len[b].. and attending
+ * over everything already cached plus the new tokens; quantised modes attend
+ * over the decoded rows, current token included, like T decode steps do.
+ * Replaces the body of full_attn_prefill() (reference: src/ornith_rforward.c:529-551).
+ *   qproj [n_seq][T][...], k,v [n_seq][T][...], out [n_seq][T][n_heads*head_dim] */
+ornith_status ornith_cuda_full_attn_prefill(const ornith_cuda_full_layer *layer, const ornith_cuda_kv *kv,
+                                            const int32_t *kv_len, const int32_t *rope_pos,
+                                            const void *qproj, const void *k, const void *v, void *out,
+                                            int act_dtype, int T,
+                                            void *scratch, size_t scratch_bytes, void *stream);
+
+/* The append half alone: k RMSNorm + RoPE, then f32 copy / Q8_0 / int8 encode of k
+ * and v into positions kv_len[b] .. kv_len[b]+T-1 (reference: the append part of
+ * ornith_gqa_step, src/ornith_attn.c:94-110, after src/ornith_rforward.c:443-447).
+ *   k,v [n_seq][T][n_kv_heads*head_dim] */
+ornith_status ornith_cuda_kv_append(const ornith_cuda_full_layer *layer, const ornith_cuda_kv *kv,
+                                    const int32_t *kv_len, const int32_t *rope_pos,
+                                    const void *k, const void *v, int act_dtype, int T, void *stream);
+
+/* kv_len[b] += delta for every sequence (call once per token after all layers). */
+ornith_status ornith_cuda_advance(int32_t *counters, int n, int delta, void *stream);
+
+/* ---- gated delta-net (linear attention) layers ------------------------------ */
+
+/* reference: src/ornith_rforward.c:457-503, :300-314 (weights and shape of one layer) */
+typedef struct {
+    int32_t nk, nv, dk, dv, conv_k, head_map;
+    float   out_scale;             /* 1/sqrt(dk) in the real-weights engine (:305) */
+    float   eps;
+    const float *conv_w;           /* device [Cc][conv_k], Cc = 2*nk*dk + nv*dv */
+    const float *conv_b;           /* device [Cc] or NULL */
+    const float *a_coef;           /* device [nv]: decay = exp(a_coef*softplus(a+dt_bias)) (:282-284) */
+    const float *dt_bias;          /* device [nv] */
+    const float *norm_w;           /* device [dv] */
+} ornith_cuda_linear_layer;
+
+/* One layer's recurrent state for a batch of sequences.
+ *   S     f32 [nv][dv][dk] per sequence (reference image: src/ornith_rforward.c:261)
+ *   conv  f32 [conv_k][Cc] per sequence: a ring, token t lives in slot t % conv_k.
+ *         Use ornith_cuda_conv_import/export for the engine's oldest-first
+ *         [(conv_k-1)][Cc] image (reference: src/ornith_attn.h:129-132). */
+typedef struct {
+    float  *S;
+    float  *conv;
+    int64_t S_seq_stride;          /* elements between consecutive sequences */
+    int64_t conv_seq_stride;
+} ornith_cuda_linear_state;
+
+/* One decode step of a delta-net layer for n_seq sequences, between the
+ * projections: conv + SiLU, q/k L2-norm, decay and write gates, recurrent
+ * update, output scale, per-head RMSNorm, SiLU(z) gate.
+ * Replaces the bodies of linear_attn() and linear_finish() minus their matvecs
+ * (reference: src/ornith_rforward.c:466-500, :305-314).
+ *   qkv [n_seq][Cc], a,b [n_seq][nv], z,out [n_seq][nv*dv]   (act_dtype)
+ *   pos device int32 [n_seq]: index of the token being processed (conv ring phase) */
+ornith_status ornith_cuda_linear_attn_step(const ornith_cuda_linear_layer *layer,
+                                           const ornith_cuda_linear_state *st, const int32_t *pos,
+                                           const void *qkv, const void *a, const void *b,
+                                           const void *z, void *out, int act_dtype, int n_seq,
+                                           void *stream);
+
+size_t ornith_cuda_linear_attn_prefill_scratch(const ornith_cuda_linear_layer *layer, int n_seq, int T);
+
+/* T tokens per sequence through the chunked scan; state and conv history end
+ * exactly where T decode steps would leave them.
+ * Replaces linear_attn_prefill() minus its matvecs (reference: src/ornith_rforward.c:571-616).
+ *   qkv [n_seq][T][Cc], a,b [n_seq][T][nv], z,out [n_seq][T][nv*dv]; chunk in {16,32,64} */
+ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *layer,
+                                              const ornith_cuda_linear_state *st, const int32_t *pos,
+                                              const void *qkv, const void *a, const void *b,
+                                              const void *z, void *out, int act_dtype,
+                                              int n_seq, int T, int chunk,
+                                              void *scratch, size_t scratch_bytes, void *stream);
+
+/* conv ring <-> the engine's history image [(conv_k-1)][Cc], oldest first
+ * (reference: src/ornith_attn.c:369, session dump src/ornith_rforward.c:1056-1063).
+ * `pos` is the index of the next token of that sequence. */
+ornith_status ornith_cuda_conv_export(const float *dev_ring, int conv_k, int Cc, int pos,
+                                      float *dev_image, void *stream);
+ornith_status ornith_cuda_conv_import(float *dev_ring, int conv_k, int Cc, int pos,
+                                      const float *dev_image, void *stream);
+
+/* ---- per-head primitives on device pointers (what tier 1 is built from) ---- */
+
+/* reference: src/ornith_attn.c:198-213; n_heads independent states S [h][dv][dk],
+ * q,k [h][dk], v,o [h][dv], alpha,beta [h] (device) */
+ornith_status ornith_cuda_delta_step(float *S, int n_heads, int dk, int dv, const float *q,
+                                     const float *k, const float *v, const float *alpha,
+                                     const float *beta, float *o, void *stream);
+/* reference: src/ornith_attn.c:337-349; one head, T tokens, any dk,dv; the chunk
+ * size only selects the tiling, the result is that of T steps */
+ornith_status ornith_cuda_delta_prefill(float *S, int dk, int dv, const float *Q, const float *K,
+                                        const float *V, const float *alpha, const float *beta,
+                                        int T, int chunk, float *O, void *stream);
+/* reference: src/ornith_attn.c:370-397; image = [(K-1)][C] oldest first, X,OUT [T][C] */
+ornith_status ornith_cuda_conv_image(float *image, int K, int C, const float *X, const float *w,
+                                     const float *bias, int T, float *OUT, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORNITH_CUDA_H */

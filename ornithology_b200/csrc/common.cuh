@@ -1,0 +1,80 @@
+// common.cuh — shared device helpers and host-side error plumbing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ornith_cuda.h"
+
+// ---- host side -------------------------------------------------------------
+void orn_record_error(const char *fmt, ...);          // fills both last-error buffers
+ornith_status orn_check(cudaError_t e, const char *what);
+ornith_status orn_check_launch(const char *what);     // cudaGetLastError after a launch
+ornith_status orn_require_device();                    // ORNITH_ERR_BACKEND when no usable GPU
+
+#define ORN_TRY(expr)                                   \
+    do {                                                \
+        ornith_status _s = (expr);                      \
+        if (_s != ORNITH_OK) return _s;                 \
+    } while (0)
+
+static inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---- activation I/O ----------------------------------------------------------
+template <typename T> __device__ __forceinline__ float act_ld(const T *p, size_t i);
+template <> __device__ __forceinline__ float act_ld<float>(const float *p, size_t i) { return p[i]; }
+template <> __device__ __forceinline__ float act_ld<__nv_bfloat16>(const __nv_bfloat16 *p, size_t i) {
+    return __bfloat162float(p[i]);
+}
+template <typename T> __device__ __forceinline__ void act_st(T *p, size_t i, float v);
+template <> __device__ __forceinline__ void act_st<float>(float *p, size_t i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void act_st<__nv_bfloat16>(__nv_bfloat16 *p, size_t i, float v) {
+    p[i] = __float2bfloat16_rn(v);
+}
+
+// ---- scalar math in the engine's form (reference: src/ornith_tensor.c:117-119)
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// ---- reductions ---------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide reductions over up to 32 warps. `red` is shared scratch of at least
+// 32 elements; every thread of the block must call. Result is returned to all.
+template <typename T>
+__device__ __forceinline__ T block_sum(T v, T *red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                       // protects `red` from the previous use
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    T r = (lane < nw) ? red[lane] : T(0);
+    return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float *red) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float r = (lane < nw) ? red[lane] : -INFINITY;
+    return warp_max(r);
+}

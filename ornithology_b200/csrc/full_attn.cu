@@ -1,0 +1,570 @@
+// full_attn.cu — GQA full-attention layers: q/k preparation + KV append/encode,
+// split-K decode over f32 / Q8_0 / int8-per-head rows, causal prefill.
+//
+// Reference behaviour being replaced:
+//   full_attn()          src/ornith_rforward.c:419-455
+//   full_attn_prefill()  src/ornith_rforward.c:513-556
+//   ornith_gqa_step()    src/ornith_attn.c:87-149
+#include <math.h>
+
+#include "common.cuh"
+#include "kv_rows.cuh"
+
+// =============================================================================
+// q/k preparation and KV append  (one CTA per (token, head-row))
+// =============================================================================
+
+struct PrepArgs {
+    KvView kv;
+    const int32_t *kv_len, *rope_pos;
+    const void *qproj, *k, *v;
+    float *q_prep;                       // [n_tok][nh][hd] f32
+    const float *q_norm_w, *k_norm_w, *inv_freq;
+    int nh, rope_dim, gated, T;
+    int row0;                            // first row handled (nh skips the query heads)
+    float eps;
+};
+
+// Row j of token tt: j < nh is a query head (normalise, rotate, write f32 to the
+// scratch the attention kernels read); the next nkv rows are key heads
+// (normalise, rotate, encode into the cache); the last nkv rows are value heads
+// (encode as they are).  Reference: src/ornith_rforward.c:432-447 and the append
+// half of ornith_gqa_step (src/ornith_attn.c:94-110).
+template <typename ACT>
+__global__ void __launch_bounds__(128) k_full_prep(PrepArgs a) {
+    extern __shared__ float row[];
+    __shared__ double redd[32];
+    __shared__ float redf[32];
+    const int hd = a.kv.hd, nkv = a.kv.nkv, nh = a.nh;
+    const int j = blockIdx.x + a.row0, tt = blockIdx.y, b = tt / a.T, t = tt % a.T;
+    const int64_t base = a.kv.seq_off[b];
+    const int cap = (int)(a.kv.seq_off[b + 1] - base);
+    const int slot = a.kv_len[b] + t;
+    if (slot >= cap) return;                              // full cache: silent no-op
+    const int pos = (a.rope_pos ? a.rope_pos[b] : a.kv_len[b]) + t;
+
+    int kind, h;
+    const ACT *src;
+    const float *w;
+    if (j < nh) {
+        kind = 0; h = j; w = a.q_norm_w;
+        size_t per_tok = (size_t)nh * hd * (a.gated ? 2 : 1);
+        src = (const ACT *)a.qproj + (size_t)tt * per_tok + (size_t)h * hd * (a.gated ? 2 : 1);
+    } else if (j < nh + nkv) {
+        kind = 1; h = j - nh; w = a.k_norm_w;
+        src = (const ACT *)a.k + ((size_t)tt * nkv + h) * hd;
+    } else {
+        kind = 2; h = j - nh - nkv; w = nullptr;
+        src = (const ACT *)a.v + ((size_t)tt * nkv + h) * hd;
+    }
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) row[i] = act_ld(src, i);
+    __syncthreads();
+
+    if (w) {                                              // RMSNorm, f64 sum like the engine
+        double ss = 0.0;
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) ss += (double)row[i] * (double)row[i];
+        ss = block_sum(ss, redd);
+        float inv = (float)(1.0 / sqrt(ss / (double)hd + (double)a.eps));
+        for (int i = threadIdx.x; i < hd; i += blockDim.x)
+            row[i] = __fmul_rn(__fmul_rn(row[i], inv), w[i]);
+        __syncthreads();
+    }
+    if (kind != 2 && a.rope_dim > 0) {                    // partial RoPE, rotate-half pairs
+        const int half = a.rope_dim / 2;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float ang = __fmul_rn((float)pos, a.inv_freq[i]);
+            float c = cosf(ang), s = sinf(ang);
+            float lo = row[i], hi = row[i + half];
+            row[i]        = __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s));
+            row[i + half] = __fadd_rn(__fmul_rn(lo, s), __fmul_rn(hi, c));
+        }
+        __syncthreads();
+    }
+
+    if (kind == 0) {
+        float *dst = a.q_prep + ((size_t)tt * nh + h) * hd;
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = row[i];
+        return;
+    }
+    const size_t r = (size_t)(base + slot) * nkv + h;
+    uint8_t *pool = (kind == 1) ? a.kv.K : a.kv.V;
+    if (a.kv.mode == ORNITH_KV_F32) {
+        float *dst = reinterpret_cast<float *>(pool) + r * hd;
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = row[i];
+    } else if (a.kv.mode == ORNITH_KV_Q8_0) {
+        encode_row_q8_0(row, hd, pool + r * kv_row_bytes(ORNITH_KV_Q8_0, hd));
+    } else {
+        float *sc = ((kind == 1) ? a.kv.Ks : a.kv.Vs) + r;
+        encode_row_int8(row, hd, reinterpret_cast<int8_t *>(pool) + r * hd, sc, redf);
+    }
+}
+
+// =============================================================================
+// split-K decode, generic in head_dim and group size
+// =============================================================================
+
+struct DecodeArgs {
+    KvView kv;
+    const int32_t *kv_len;
+    const float *q_prep;                 // [n_seq][nh][hd]
+    float *part;                         // [n_seq][nh][nsplit][hd + 2]
+    int nh, nsplit, tokens_per_split;
+    float scale;
+};
+
+// One CTA = one (split, query head, sequence).  Scores are one thread per token
+// with the engine's element order; the value pass is one thread per dimension.
+// Partial (m, l, o) go to scratch for k_gqa_combine.
+template <int MODE>
+__global__ void __launch_bounds__(128) k_gqa_decode_generic(DecodeArgs a) {
+    extern __shared__ float sm[];
+    const int hd = a.kv.hd, nkv = a.kv.nkv;
+    float *q_s = sm, *p_s = sm + hd;                      // [hd], [128]
+    __shared__ float red[32];
+    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
+    const int64_t base = a.kv.seq_off[b];
+    const int cap = (int)(a.kv.seq_off[b + 1] - base);
+    const int len0 = a.kv_len[b];
+    if (len0 >= cap) return;
+    const int L = len0 + 1;
+    float *part = a.part + (((size_t)b * a.nh + h) * a.nsplit + split) * (hd + 2);
+    const int t0 = split * a.tokens_per_split, t1 = min(L, t0 + a.tokens_per_split);
+    if (t0 >= L) {
+        if (tid == 0) { part[0] = -INFINITY; part[1] = 0.0f; }
+        return;
+    }
+    const int kvh = h / (a.nh / nkv);
+    const size_t rb = kv_row_bytes(MODE, hd);
+    for (int i = tid; i < hd; i += 128) q_s[i] = a.q_prep[((size_t)b * a.nh + h) * hd + i];
+    __syncthreads();
+
+    float m_run = -INFINITY, l_run = 0.0f, acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+
+    for (int tb = t0; tb < t1; tb += 128) {
+        const int tok = tb + tid;
+        const bool valid = tok < t1;
+        float s = -INFINITY, vscale = 1.0f;
+        if (valid) {
+            const size_t r = (size_t)(base + tok) * nkv + kvh;
+            const uint8_t *krow = a.kv.K + r * rb;
+            float dot = 0.0f;
+            for (int d = 0; d < hd; d++) dot += q_s[d] * kv_elem<MODE>(krow, d);
+            if (MODE == ORNITH_KV_INT8_HEAD) {
+                float ks = a.kv.Ks[r];
+                dot = (ks == 0.0f) ? 0.0f : dot * ks;
+                vscale = a.kv.Vs[r];
+            }
+            s = dot * a.scale;
+        }
+        const float m_new = fmaxf(m_run, block_max(s, red));
+        const float p = valid ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m_run - m_new);           // 0 on the first tile
+        l_run = l_run * corr + block_sum(p, red);
+        m_run = m_new;
+        p_s[tid] = p * vscale;
+        __syncthreads();
+        const int n = min(128, t1 - tb);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int d = tid + i * 128;
+            if (d < hd) {
+                float o = acc[i] * corr;
+                for (int tt = 0; tt < n; tt++) {
+                    const uint8_t *vrow = a.kv.V + ((size_t)(base + tb + tt) * nkv + kvh) * rb;
+                    o += p_s[tt] * kv_elem<MODE>(vrow, d);
+                }
+                acc[i] = o;
+            }
+        }
+        __syncthreads();
+    }
+    if (tid == 0) { part[0] = m_run; part[1] = l_run; }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int d = tid + i * 128;
+        if (d < hd) part[2 + d] = acc[i];
+    }
+}
+
+struct CombineArgs {
+    KvView kv;
+    const int32_t *kv_len;
+    const float *part;
+    const void *qproj;                   // for the gate half, when gated
+    void *out;
+    int nh, nsplit, gated;
+};
+
+// Merge the split partials of one (head, sequence), normalise, apply the sigmoid
+// output gate (reference: src/ornith_rforward.c:450) and store.
+template <typename ACT>
+__global__ void __launch_bounds__(128) k_gqa_combine(CombineArgs a) {
+    extern __shared__ float w_s[];                       // [nsplit]
+    __shared__ float red[32];
+    const int hd = a.kv.hd, h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const int cap = (int)(a.kv.seq_off[b + 1] - a.kv.seq_off[b]);
+    if (a.kv_len[b] >= cap) return;
+    const float *part = a.part + ((size_t)b * a.nh + h) * a.nsplit * (hd + 2);
+    float m = -INFINITY;
+    for (int s = tid; s < a.nsplit; s += 128)
+        if (part[(size_t)s * (hd + 2) + 1] > 0.0f) m = fmaxf(m, part[(size_t)s * (hd + 2)]);
+    const float M = block_max(m, red);
+    float lsum = 0.0f;
+    for (int s = tid; s < a.nsplit; s += 128) {
+        const float l = part[(size_t)s * (hd + 2) + 1];
+        const float w = (l > 0.0f) ? expf(part[(size_t)s * (hd + 2)] - M) : 0.0f;
+        w_s[s] = w;
+        lsum += l * w;
+    }
+    const float Lsum = block_sum(lsum, red);              // also orders the w_s writes
+    const float inv = 1.0f / Lsum;
+    const ACT *gate = nullptr;
+    if (a.gated) gate = (const ACT *)a.qproj + (size_t)b * a.nh * hd * 2 + (size_t)h * hd * 2 + hd;
+    ACT *out = (ACT *)a.out + ((size_t)b * a.nh + h) * hd;
+    for (int d = tid; d < hd; d += 128) {
+        float o = 0.0f;
+        for (int s = 0; s < a.nsplit; s++)
+            if (w_s[s] != 0.0f) o += part[(size_t)s * (hd + 2) + 2 + d] * w_s[s];
+        o *= inv;
+        if (gate) o *= sigmoid_f(act_ld(gate, d));
+        act_st(out, d, o);
+    }
+}
+
+// =============================================================================
+// causal prefill (f32 accumulate, online softmax), generic in head_dim
+// =============================================================================
+
+struct PrefillArgs {
+    KvView kv;
+    const int32_t *kv_len;
+    const float *q_prep;                 // [n_seq*T][nh][hd]
+    const void *qproj;
+    void *out;
+    int nh, T, gated, hpb, tpb;          // heads / tokens per block, hpb*tpb == 8
+    float scale;
+};
+
+constexpr int PF_KT = 32;                // keys per shared-memory tile
+
+// One CTA = 8 (token, head) pairs that share a kv head: warp w owns pair w.
+// K and V tiles are decoded to f32 in shared memory once per CTA.  Score phase:
+// lane = key; value phase: lane = dimension slice.
+template <int MODE, typename ACT>
+__global__ void __launch_bounds__(256) k_gqa_prefill(PrefillArgs a) {
+    extern __shared__ float sm[];
+    const int hd = a.kv.hd, nkv = a.kv.nkv, ldk = hd + 1;   // odd stride: lane = key reads are conflict-free
+    float *K_s = sm;                                      // [PF_KT][hd + 1]
+    float *V_s = K_s + PF_KT * ldk;                       // [PF_KT][hd]
+    float *q_s = V_s + PF_KT * hd;                        // [8][hd]
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int b = blockIdx.z;
+    const int groups_per_kv = (a.nh / nkv) / a.hpb;       // head sub-groups per kv head
+    const int kvh = blockIdx.y / groups_per_kv;
+    const int h = kvh * (a.nh / nkv) + (blockIdx.y % groups_per_kv) * a.hpb + (w % a.hpb);
+    const int t = blockIdx.x * a.tpb + (w / a.hpb);       // token of this warp
+    const int64_t base = a.kv.seq_off[b];
+    const int cap = (int)(a.kv.seq_off[b + 1] - base);
+    const int len0 = a.kv_len[b];
+    const bool live = (t < a.T) && (len0 + t < cap);      // appended tokens only
+    const int qpos = len0 + t;                            // attends keys 0..qpos
+    const int t_last = min(a.T - 1, blockIdx.x * a.tpb + a.tpb - 1);
+    const int kmax = min(len0 + t_last, cap - 1);         // last key any warp needs
+    const size_t rb = kv_row_bytes(MODE, hd);
+    const int ndim = (hd + 31) / 32;                      // dims per lane (<= 8 for hd <= 256), strided
+
+    const size_t tok = (size_t)b * a.T + min(t, a.T - 1);
+    for (int i = lane; i < hd; i += 32) q_s[w * hd + i] = a.q_prep[(tok * a.nh + h) * hd + i];
+
+    float m_run = -INFINITY, l_run = 0.0f, acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+
+    for (int kb = 0; kb <= kmax; kb += PF_KT) {
+        __syncthreads();                                  // previous tile fully consumed
+        for (int e = tid; e < PF_KT * hd; e += 256) {
+            const int kk = e / hd, d = e % hd, kp = kb + kk;
+            float kvv = 0.0f, vv = 0.0f;
+            if (kp <= kmax) {
+                const size_t r = (size_t)(base + kp) * nkv + kvh;
+                kvv = kv_elem<MODE>(a.kv.K + r * rb, d);
+                vv = kv_elem<MODE>(a.kv.V + r * rb, d);
+                if (MODE == ORNITH_KV_INT8_HEAD) vv *= a.kv.Vs[r];
+            }
+            K_s[kk * ldk + d] = kvv;
+            V_s[kk * hd + d] = vv;
+        }
+        __syncthreads();
+        if (!live) continue;
+        const int kp = kb + lane;
+        float s = -INFINITY;
+        if (kp <= qpos) {
+            float dot = 0.0f;
+            const float *kr = K_s + lane * ldk, *qr = q_s + w * hd;
+            for (int d = 0; d < hd; d++) dot += qr[d] * kr[d];
+            if (MODE == ORNITH_KV_INT8_HEAD) {
+                float ks = a.kv.Ks[(size_t)(base + kp) * nkv + kvh];
+                dot = (ks == 0.0f) ? 0.0f : dot * ks;
+            }
+            s = dot * a.scale;
+        }
+        const float tile_max = warp_max(s);
+        if (tile_max == -INFINITY) continue;              // whole tile is in the future
+        const float m_new = fmaxf(m_run, tile_max);
+        const float p = (kp <= qpos) ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m_run - m_new);
+        l_run = l_run * corr + warp_sum(p);
+        m_run = m_new;
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] *= corr;
+        for (int kk = 0; kk < PF_KT; kk++) {
+            const float pk = __shfl_sync(0xffffffffu, p, kk);
+            if (pk == 0.0f) continue;
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if (i < ndim) {
+                    const int d = lane + i * 32;
+                    if (d < hd) acc[i] += pk * V_s[kk * hd + d];
+                }
+        }
+    }
+    if (!live) return;
+    const float inv = 1.0f / l_run;
+    const ACT *gate = nullptr;
+    const size_t otok = (size_t)b * a.T + t;
+    if (a.gated) gate = (const ACT *)a.qproj + otok * a.nh * hd * 2 + (size_t)h * hd * 2 + hd;
+    ACT *out = (ACT *)a.out + (otok * a.nh + h) * hd;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int d = lane + i * 32;
+        if (i < ndim && d < hd) {
+            float o = acc[i] * inv;
+            if (gate) o *= sigmoid_f(act_ld(gate, d));
+            act_st(out, d, o);
+        }
+    }
+}
+
+// =============================================================================
+// host entry points
+// =============================================================================
+
+static float attn_scale(const ornith_cuda_full_layer *l) {
+    return l->scale > 0.0f ? l->scale : 1.0f / sqrtf((float)l->head_dim);
+}
+
+static ornith_status check_full(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv) {
+    if (!l || !kv || l->n_heads <= 0 || l->n_kv_heads <= 0 || l->head_dim <= 0 ||
+        l->n_heads % l->n_kv_heads || kv->n_kv_heads != l->n_kv_heads || kv->head_dim != l->head_dim) {
+        orn_record_error("full attention: inconsistent layer / cache geometry");
+        return ORNITH_ERR_FORMAT;
+    }
+    if (l->head_dim > 1024) { orn_record_error("full attention: head_dim > 1024 unsupported"); return ORNITH_ERR_UNSUPPORTED; }
+    if (kv->mode == ORNITH_KV_Q8_0 && l->head_dim % 32) {
+        orn_record_error("Q8_0 KV rows need head_dim to be a multiple of 32");
+        return ORNITH_ERR_FORMAT;
+    }
+    if (kv->mode < 0 || kv->mode > 2) { orn_record_error("unknown KV mode %d", kv->mode); return ORNITH_ERR_FORMAT; }
+    if (l->rope_dim > 0 && (!l->rope_inv_freq || l->rope_dim > l->head_dim || (l->rope_dim & 1))) {
+        orn_record_error("full attention: bad rope_dim %d or missing inverse-frequency table", l->rope_dim);
+        return ORNITH_ERR_FORMAT;
+    }
+    return ORNITH_OK;
+}
+
+static int split_tokens(int max_len) {
+    // tokens per split: long contexts use 512-token splits; short ones fewer CTAs
+    return max_len <= 512 ? 128 : 512;
+}
+
+template <typename ACT>
+static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
+                                 const int32_t *kv_len, const int32_t *rope_pos, const void *qproj,
+                                 const void *k, const void *v, float *q_prep, int n_tok, int T,
+                                 cudaStream_t st, bool kv_only = false) {
+    PrepArgs a;
+    a.kv = make_view(kv); a.kv_len = kv_len; a.rope_pos = rope_pos;
+    a.qproj = qproj; a.k = k; a.v = v; a.q_prep = q_prep;
+    a.q_norm_w = l->q_norm_w; a.k_norm_w = l->k_norm_w; a.inv_freq = l->rope_inv_freq;
+    a.nh = l->n_heads; a.rope_dim = l->rope_dim; a.gated = l->gated; a.T = T; a.eps = l->eps;
+    a.row0 = kv_only ? l->n_heads : 0;
+    dim3 grid((kv_only ? 0 : l->n_heads) + 2 * l->n_kv_heads, n_tok);
+    k_full_prep<ACT><<<grid, 128, l->head_dim * sizeof(float), st>>>(a);
+    return orn_check_launch("k_full_prep");
+}
+
+extern "C" {
+
+size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *l, int n_seq, int max_len) {
+    if (!l || n_seq <= 0) return 0;
+    if (max_len < 1) max_len = 1;
+    const int tps = split_tokens(max_len), nsplit = (max_len + tps - 1) / tps;
+    size_t qp = align_up((size_t)n_seq * l->n_heads * l->head_dim * sizeof(float), 256);
+    size_t part = (size_t)n_seq * l->n_heads * nsplit * (l->head_dim + 2) * sizeof(float);
+    return qp + align_up(part, 256);
+}
+
+ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
+                                         const int32_t *kv_len, const int32_t *rope_pos,
+                                         const void *qproj, const void *k, const void *v, void *out,
+                                         int act_dtype, int max_len, void *scratch, size_t scratch_bytes,
+                                         void *stream) {
+    ORN_TRY(orn_require_device());
+    ORN_TRY(check_full(l, kv));
+    const int B = kv->n_seq;
+    if (B <= 0) return ORNITH_OK;
+    if (max_len < 1) max_len = 1;
+    if (scratch_bytes < ornith_cuda_full_attn_step_scratch(l, B, max_len) || !scratch) {
+        orn_record_error("full_attn_step: scratch too small (%zu bytes given)", scratch_bytes);
+        return ORNITH_ERR_FORMAT;
+    }
+    cudaStream_t st = as_stream(stream);
+    const int hd = l->head_dim, nh = l->n_heads;
+    const int tps = split_tokens(max_len), nsplit = (max_len + tps - 1) / tps;
+    float *q_prep = (float *)scratch;
+    float *part = (float *)((char *)scratch + align_up((size_t)B * nh * hd * sizeof(float), 256));
+
+    if (act_dtype == ORNITH_ACT_BF16)
+        ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B, 1, st));
+    else
+        ORN_TRY(launch_prep<float>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B, 1, st));
+
+    DecodeArgs d;
+    d.kv = make_view(kv); d.kv_len = kv_len; d.q_prep = q_prep; d.part = part;
+    d.nh = nh; d.nsplit = nsplit; d.tokens_per_split = tps; d.scale = attn_scale(l);
+    dim3 grid(nsplit, nh, B);
+    const size_t smem = (size_t)(hd + 128) * sizeof(float);
+    switch (kv->mode) {
+    case ORNITH_KV_F32:       k_gqa_decode_generic<ORNITH_KV_F32><<<grid, 128, smem, st>>>(d); break;
+    case ORNITH_KV_INT8_HEAD: k_gqa_decode_generic<ORNITH_KV_INT8_HEAD><<<grid, 128, smem, st>>>(d); break;
+    default:                  k_gqa_decode_generic<ORNITH_KV_Q8_0><<<grid, 128, smem, st>>>(d); break;
+    }
+    ORN_TRY(orn_check_launch("k_gqa_decode_generic"));
+
+    CombineArgs c;
+    c.kv = d.kv; c.kv_len = kv_len; c.part = part; c.qproj = qproj; c.out = out;
+    c.nh = nh; c.nsplit = nsplit; c.gated = l->gated;
+    dim3 cgrid(nh, B);
+    if (act_dtype == ORNITH_ACT_BF16)
+        k_gqa_combine<__nv_bfloat16><<<cgrid, 128, nsplit * sizeof(float), st>>>(c);
+    else
+        k_gqa_combine<float><<<cgrid, 128, nsplit * sizeof(float), st>>>(c);
+    return orn_check_launch("k_gqa_combine");
+}
+
+size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *l, int n_seq, int T) {
+    if (!l || n_seq <= 0 || T <= 0) return 0;
+    return align_up((size_t)n_seq * T * l->n_heads * l->head_dim * sizeof(float), 256);
+}
+
+}  // extern "C"
+
+template <int MODE, typename ACT>
+static ornith_status launch_prefill(const PrefillArgs &a, dim3 grid, size_t smem, cudaStream_t st) {
+    static bool configured = false;                      // per instantiation
+    if (!configured) {
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill<MODE, ACT>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024),
+                          "prefill smem opt-in"));
+        configured = true;
+    }
+    k_gqa_prefill<MODE, ACT><<<grid, 256, smem, st>>>(a);
+    return orn_check_launch("k_gqa_prefill");
+}
+
+extern "C" {
+
+ornith_status ornith_cuda_full_attn_prefill(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
+                                            const int32_t *kv_len, const int32_t *rope_pos,
+                                            const void *qproj, const void *k, const void *v, void *out,
+                                            int act_dtype, int T, void *scratch, size_t scratch_bytes,
+                                            void *stream) {
+    ORN_TRY(orn_require_device());
+    ORN_TRY(check_full(l, kv));
+    const int B = kv->n_seq;
+    if (B <= 0 || T <= 0) return ORNITH_OK;
+    if (l->head_dim > 256) { orn_record_error("prefill: head_dim > 256 unsupported"); return ORNITH_ERR_UNSUPPORTED; }
+    if (scratch_bytes < ornith_cuda_full_attn_prefill_scratch(l, B, T) || !scratch) {
+        orn_record_error("full_attn_prefill: scratch too small (%zu bytes given)", scratch_bytes);
+        return ORNITH_ERR_FORMAT;
+    }
+    cudaStream_t st = as_stream(stream);
+    const int hd = l->head_dim, nh = l->n_heads, G = nh / l->n_kv_heads;
+    float *q_prep = (float *)scratch;
+    const bool bf = act_dtype == ORNITH_ACT_BF16;
+    if (bf) ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st));
+    else    ORN_TRY(launch_prep<float>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st));
+
+    PrefillArgs a;
+    a.kv = make_view(kv); a.kv_len = kv_len; a.q_prep = q_prep; a.qproj = qproj; a.out = out;
+    a.nh = nh; a.T = T; a.gated = l->gated; a.scale = attn_scale(l);
+    a.hpb = (G % 8 == 0) ? 8 : (8 % G == 0 ? G : 1);
+    a.tpb = 8 / a.hpb;
+    dim3 grid((T + a.tpb - 1) / a.tpb, nh / a.hpb, B);
+    const size_t smem = ((size_t)PF_KT * (hd + 1) + (size_t)PF_KT * hd + 8 * (size_t)hd) * sizeof(float);
+#define PF_LAUNCH(M)                                                                    \
+    (bf ? launch_prefill<M, __nv_bfloat16>(a, grid, smem, st) : launch_prefill<M, float>(a, grid, smem, st))
+    switch (kv->mode) {
+    case ORNITH_KV_F32:       return PF_LAUNCH(ORNITH_KV_F32);
+    case ORNITH_KV_INT8_HEAD: return PF_LAUNCH(ORNITH_KV_INT8_HEAD);
+    default:                  return PF_LAUNCH(ORNITH_KV_Q8_0);
+    }
+#undef PF_LAUNCH
+}
+
+// K/V rows only: normalise + rotate k, encode k and v into the cache (no attention).
+ornith_status ornith_cuda_kv_append(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
+                                    const int32_t *kv_len, const int32_t *rope_pos, const void *k,
+                                    const void *v, int act_dtype, int T, void *stream) {
+    ORN_TRY(orn_require_device());
+    ORN_TRY(check_full(l, kv));
+    if (kv->n_seq <= 0 || T <= 0) return ORNITH_OK;
+    cudaStream_t st = as_stream(stream);
+    if (act_dtype == ORNITH_ACT_BF16)
+        return launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, nullptr, k, v, nullptr, kv->n_seq * T, T, st, true);
+    return launch_prep<float>(l, kv, kv_len, rope_pos, nullptr, k, v, nullptr, kv->n_seq * T, T, st, true);
+}
+
+// ---- standalone Q8_0 codec on flat arrays ---------------------------------------
+__global__ void __launch_bounds__(128) k_q8_0_encode(const float *src, uint8_t *dst, size_t nblk) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const size_t blk = (size_t)blockIdx.x * 4 + w;
+    if (blk >= nblk) return;                             // whole warp leaves together
+    float x = src[blk * 32 + lane];
+    float amax = warp_max(fabsf(x));
+    float d = __fdiv_rn(amax, 127.0f);
+    float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+    int q = (int)roundf(__fmul_rn(x, id));
+    q = max(-127, min(127, q));
+    uint8_t *o = dst + blk * 34;
+    if (lane == 0) *reinterpret_cast<unsigned short *>(o) = __half_as_ushort(__float2half_rn(d));
+    o[2 + lane] = (uint8_t)(int8_t)q;
+}
+
+__global__ void k_q8_0_decode(const uint8_t *src, float *dst, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint8_t *blk = src + (i >> 5) * 34;
+    dst[i] = __fmul_rn((float)(int8_t)blk[2 + (i & 31)], q8_0_block_scale(blk));
+}
+
+ornith_status ornith_cuda_q8_0_encode(const float *src, void *dst, size_t n, void *stream) {
+    ORN_TRY(orn_require_device());
+    if (n % 32) { orn_record_error("Q8_0 needs a multiple of 32 values"); return ORNITH_ERR_FORMAT; }
+    if (!n) return ORNITH_OK;
+    const size_t nblk = n / 32;
+    k_q8_0_encode<<<(unsigned)((nblk + 3) / 4), 128, 0, as_stream(stream)>>>(src, (uint8_t *)dst, nblk);
+    return orn_check_launch("k_q8_0_encode");
+}
+
+ornith_status ornith_cuda_q8_0_decode(const void *src, float *dst, size_t n, void *stream) {
+    ORN_TRY(orn_require_device());
+    if (n % 32) { orn_record_error("Q8_0 needs a multiple of 32 values"); return ORNITH_ERR_FORMAT; }
+    if (!n) return ORNITH_OK;
+    k_q8_0_decode<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>((const uint8_t *)src, dst, n);
+    return orn_check_launch("k_q8_0_decode");
+}
+
+}  // extern "C"

@@ -1,0 +1,167 @@
+"""Full-attention layers on the GPU (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+
+from tests._cases import TOL, device_full, full_case, full_inputs, rel_err
+
+pytestmark = pytest.mark.gpu
+
+MODES = ["f32", "q8_0", "int8"]
+# With bf16 activations the result itself is stored as bf16: half a bf16 ulp (2^-9) of
+# output rounding comes on top of the 2e-3 arithmetic bar.
+TOL_BF16_IO = TOL + 2.0 ** -9 + 5e-4
+
+
+def _modes(name):
+    from ornithology_b200 import device as D
+    from oracle import oracle as O
+    return {"f32": (D.KV_F32, O.KV_F32), "q8_0": (D.KV_Q8_0, O.KV_Q8_0), "int8": (D.KV_INT8_HEAD, O.KV_INT8_HEAD)}[name]
+
+
+@pytest.mark.parametrize("name,mode", [("full_layer_f32.npz", "f32"), ("full_layer_int8.npz", "int8")])
+def test_golden_full_layer_steps(golden, name, mode):
+    """Fixtures produced by the reference's own code (tests/golden/make_golden.py)."""
+    import torch
+    from ornithology_b200 import device as D
+    g = golden(name)
+    nh, nkv, hd, T, base = int(g["nh"]), int(g["nkv"]), int(g["hd"]), g["QP"].shape[0], int(g["base"])
+    layer = D.FullLayer(nh, nkv, hd, g["q_norm_w"], g["k_norm_w"], rope_dim=int(g["rope_dim"]), theta=float(g["theta"]))
+    kv = D.KvBatch(_modes(mode)[0], nkv, hd, [T])
+    kv_len = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rope = torch.full((1,), base, dtype=torch.int32, device="cuda")
+    for t in range(T):
+        out = D.full_attn_step(layer, kv, kv_len, torch.from_numpy(g["QP"][t:t + 1]).cuda(),
+                               torch.from_numpy(g["K"][t:t + 1]).cuda(), torch.from_numpy(g["V"][t:t + 1]).cuda(),
+                               rope_pos=rope)
+        assert rel_err(out.cpu().numpy()[0], g["OUT"][t]) < TOL, t
+        D.advance(kv_len); D.advance(rope)
+    # prefill of the same tokens from an empty cache
+    kv2 = D.KvBatch(_modes(mode)[0], nkv, hd, [T])
+    kv_len.zero_(); rope.fill_(base)
+    out = D.full_attn_prefill(layer, kv2, kv_len, torch.from_numpy(g["QP"])[None].cuda(),
+                              torch.from_numpy(g["K"])[None].cuda(), torch.from_numpy(g["V"])[None].cuda(), T, rope_pos=rope)
+    assert rel_err(out.cpu().numpy()[0], g["OUT"]) < TOL
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("bf16", [False, True])
+def test_35b_shape_batched_decode(oracle, mode, bf16):
+    """16 query / 2 KV heads x 256, ragged batch: prefill then decode, each sequence
+    checked against the oracle at every step; Q8_0 rows checked byte for byte."""
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(1)
+    dl = device_full(layer)
+    ctx = [37, 130, 1, 300]                      # prompt lengths, ragged
+    steps = 5
+    caps = [c + steps for c in ctx]
+    caps[2] = ctx[2] + 2                         # this one fills up: later steps must be no-ops
+    dm, om = _modes(mode)
+    kv = D.KvBatch(dm, layer.nkv, layer.hd, caps)
+    dt = torch.bfloat16 if bf16 else torch.float32
+    okvs, data = [], []
+    for b, c in enumerate(ctx):
+        QP, K, V = full_inputs(100 + b, layer, c + steps, bf16)
+        data.append((QP, K, V))
+        okv = oracle.kv(caps[b], layer.nkv, layer.hd, om)
+        ref = oracle.full_attn_prefill(layer, okv, 0, QP[:c], K[:c], V[:c])
+        okvs.append(okv)
+        # prefill one sequence at a time through a single-sequence view of the same pools
+        one = D.KvBatch.__new__(D.KvBatch)
+        one.__dict__.update(kv.__dict__)
+        import ctypes as C
+        from ornithology_b200._lib import CudaKv
+        off = kv.seq_off[b:b + 2].clone()
+        one.n_seq = 1
+        one.c = CudaKv(dm, layer.nkv, layer.hd, 1, kv.c.K, kv.c.V, kv.c.Ks, kv.c.Vs, C.c_void_p(off.data_ptr()))
+        z = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = D.full_attn_prefill(dl, one, z, torch.from_numpy(QP[:c])[None].cuda().to(dt),
+                                  torch.from_numpy(K[:c])[None].cuda().to(dt),
+                                  torch.from_numpy(V[:c])[None].cuda().to(dt), c)
+        torch.cuda.synchronize()
+        tol = TOL if not bf16 else TOL_BF16_IO
+        assert rel_err(out.float().cpu().numpy()[0], ref) < tol, ("prefill", b)
+    kv_len = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    for s in range(steps):
+        qp = np.stack([data[b][0][ctx[b] + s] for b in range(len(ctx))])
+        k = np.stack([data[b][1][ctx[b] + s] for b in range(len(ctx))])
+        v = np.stack([data[b][2][ctx[b] + s] for b in range(len(ctx))])
+        out = D.full_attn_step(dl, kv, kv_len, torch.from_numpy(qp).cuda().to(dt), torch.from_numpy(k).cuda().to(dt),
+                               torch.from_numpy(v).cuda().to(dt), max_len=max(caps)).float().cpu().numpy()
+        for b in range(len(ctx)):
+            if ctx[b] + s >= caps[b]:
+                continue                          # full cache: output untouched, nothing appended
+            ref = oracle.full_attn_step(layer, okvs[b], ctx[b] + s, qp[b], k[b], v[b])
+            tol = TOL if not bf16 else TOL_BF16_IO
+            assert rel_err(out[b], ref) < tol, (s, b)
+        D.advance(kv_len)
+    if mode == "q8_0" and not bf16:
+        # rows were built from GPU-side norm+RoPE values; re-encode those on the CPU and compare bytes
+        f32kv = D.KvBatch(D.KV_F32, layer.nkv, layer.hd, caps)
+        z = torch.zeros(len(ctx), dtype=torch.int32, device="cuda")
+        for s in range(2):
+            qp = np.stack([data[b][0][s] for b in range(len(ctx))])
+            k = np.stack([data[b][1][s] for b in range(len(ctx))])
+            v = np.stack([data[b][2][s] for b in range(len(ctx))])
+            D.full_attn_step(dl, f32kv, z, torch.from_numpy(qp).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(), max_len=8)
+            D.advance(z)
+        for b in range(len(ctx)):
+            n = min(2, caps[b])
+            Kf, Vf = f32kv.rows(b, n)
+            Kb, Vb = kv.rows(b, n)
+            for t in range(n):
+                for h in range(layer.nkv):
+                    assert (oracle.q8_0_encode(Kf[t, h]) == Kb[t, h]).all()
+                    assert (oracle.q8_0_encode(Vf[t, h]) == Vb[t, h]).all()
+
+
+def test_prefill_equals_decode_on_gpu():
+    """The engine's own contract (prefill == T decode steps) on the CUDA path."""
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(3, nh=8, nkv=2, hd=128, rope_dim=32)
+    dl = device_full(layer)
+    T = 70
+    QP, K, V = full_inputs(7, layer, T)
+    for mode in (D.KV_F32, D.KV_Q8_0):
+        kv_a, kv_b = D.KvBatch(mode, 2, 128, [T]), D.KvBatch(mode, 2, 128, [T])
+        z = torch.zeros(1, dtype=torch.int32, device="cuda")
+        pre = D.full_attn_prefill(dl, kv_a, z, torch.from_numpy(QP)[None].cuda(), torch.from_numpy(K)[None].cuda(),
+                                  torch.from_numpy(V)[None].cuda(), T).cpu().numpy()[0]
+        outs = []
+        for t in range(T):
+            outs.append(D.full_attn_step(dl, kv_b, z, torch.from_numpy(QP[t:t + 1]).cuda(), torch.from_numpy(K[t:t + 1]).cuda(),
+                                         torch.from_numpy(V[t:t + 1]).cuda()).cpu().numpy()[0])
+            D.advance(z)
+        assert rel_err(pre, np.stack(outs)) < 1e-4
+        assert (kv_a.K.cpu().numpy() == kv_b.K.cpu().numpy()).all() and (kv_a.V.cpu().numpy() == kv_b.V.cpu().numpy()).all()
+
+
+def test_long_context_split_k(oracle):
+    """A context long enough for several splits (and a ragged last one)."""
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(5)
+    dl = device_full(layer)
+    L = 1500
+    rng = np.random.default_rng(8)
+    kv = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [L + 1])
+    okv = oracle.kv(L + 1, layer.nkv, layer.hd, 2)
+    # fill both caches with the same already-encoded rows (skips an O(L^2) CPU prefill)
+    Kraw = rng.standard_normal((L, layer.nkv * layer.hd)).astype(np.float32)
+    Vraw = rng.standard_normal((L, layer.nkv * layer.hd)).astype(np.float32)
+    Kb = np.stack([oracle.q8_0_encode(r.reshape(layer.nkv, layer.hd)[h]) for r in Kraw for h in range(layer.nkv)])
+    Vb = np.stack([oracle.q8_0_encode(r.reshape(layer.nkv, layer.hd)[h]) for r in Vraw for h in range(layer.nkv)])
+    kv.K[:Kb.size] = torch.from_numpy(Kb.ravel()).cuda()
+    kv.V[:Vb.size] = torch.from_numpy(Vb.ravel()).cuda()
+    import ctypes as C
+    C.memmove(okv.c.Kb, Kb.ctypes.data, Kb.size); C.memmove(okv.c.Vb, Vb.ctypes.data, Vb.size)
+    Kd = np.stack([oracle.q8_0_decode(r) for r in Kb]).astype(np.float32)
+    Vd = np.stack([oracle.q8_0_decode(r) for r in Vb]).astype(np.float32)
+    C.memmove(okv.c.K, Kd.ctypes.data, Kd.nbytes); C.memmove(okv.c.V, Vd.ctypes.data, Vd.nbytes)
+    okv.c.len = L
+    QP, K, V = full_inputs(9, layer, 1)
+    kv_len = torch.tensor([L], dtype=torch.int32, device="cuda")
+    out = D.full_attn_step(dl, kv, kv_len, torch.from_numpy(QP).cuda(), torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
+    ref = oracle.full_attn_step(layer, okv, L, QP[0], K[0], V[0])
+    assert rel_err(out.cpu().numpy()[0], ref) < TOL

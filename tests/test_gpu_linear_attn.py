@@ -1,0 +1,147 @@
+"""Gated delta-net layers on the GPU (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests._cases import TOL, device_linear, linear_case, linear_inputs, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL_BF16_IO = TOL + 2.0 ** -9 + 5e-4     # bf16-stored outputs: half an ulp on top of the bar
+
+
+def _t(x, dt=None):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    return t if dt is None else t.to(dt)
+
+
+@pytest.mark.parametrize("name", ["linear_layer_tiled.npz", "linear_layer_grouped.npz"])
+def test_golden_linear_layer(golden, name):
+    """Fixtures produced by the reference's own code; small heads (generic kernels)."""
+    import torch
+    from ornithology_b200 import device as D
+    g = golden(name)
+    nk, nv, dk, dv = int(g["nk"]), int(g["nv"]), int(g["dk"]), int(g["dv"])
+    layer = D.LinearLayer(nk, nv, dk, dv, g["conv_w"], g["a_coef"], g["dt_bias"], g["norm_w"],
+                          conv_b=g["conv_b"] if g["conv_b"].size else None, head_map=int(g["head_map"]),
+                          out_scale=None if int(g["scaled"]) else 1.0)
+    T = g["QKV"].shape[0]
+    st = D.LinearState(layer, 1)
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for t in range(T):
+        out = D.linear_attn_step(layer, st, pos, _t(g["QKV"][t:t + 1]), _t(g["A"][t:t + 1]), _t(g["B"][t:t + 1]),
+                                 _t(g["Z"][t:t + 1]))
+        assert rel_err(out.cpu().numpy()[0], g["OUT"][t]) < TOL, t
+        D.advance(pos)
+    assert rel_err(st.S.cpu().numpy()[0], g["S_final"]) < TOL
+    img = st.conv_image(0, T).cpu().numpy()
+    assert (img.view(np.uint32) == g["conv_final"].view(np.uint32)).all()      # conv history is exact
+    # prefill of the same tokens
+    st2 = D.LinearState(layer, 1)
+    pos.zero_()
+    out = D.linear_attn_prefill(layer, st2, pos, _t(g["QKV"])[None], _t(g["A"])[None], _t(g["B"])[None], _t(g["Z"])[None], T)
+    assert rel_err(out.cpu().numpy()[0], g["OUT"]) < TOL
+    assert rel_err(st2.S.cpu().numpy()[0], g["S_final"]) < TOL
+    assert (st2.conv_image(0, T).cpu().numpy().view(np.uint32) == g["conv_final"].view(np.uint32)).all()
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("head_map,bias,scaled", [(O.HEADMAP_TILED, False, True), (O.HEADMAP_GROUPED, True, False)])
+def test_35b_shape_decode_steps(oracle, bf16, head_map, bias, scaled):
+    """16 key / 32 value heads x 128, 3 sequences, 24 steps: outputs at every step, then
+    the recurrent state and the conv history, against the oracle."""
+    import torch
+    from ornithology_b200 import device as D
+    layer, kw = linear_case(2, head_map=head_map, bias=bias, scaled=scaled)
+    dl = device_linear(layer, kw)
+    B, T = 3, 24
+    dt = torch.bfloat16 if bf16 else torch.float32
+    ins = [linear_inputs(50 + b, layer, T, bf16) for b in range(B)]
+    S = [np.zeros((layer.nv, layer.dv, layer.dk), np.float32) for _ in range(B)]
+    buf = [np.zeros(3 * layer.cc, np.float32) for _ in range(B)]
+    st = D.LinearState(dl, B)
+    pos = torch.zeros(B, dtype=torch.int32, device="cuda")
+    tol = TOL_BF16_IO if bf16 else TOL
+    for t in range(T):
+        stack = [np.stack([ins[b][i][t] for b in range(B)]) for i in range(4)]
+        out = D.linear_attn_step(dl, st, pos, *[_t(x, dt) for x in stack]).float().cpu().numpy()
+        for b in range(B):
+            ref = oracle.linear_attn_step(layer, S[b], buf[b], *[ins[b][i][t] for i in range(4)])
+            assert rel_err(out[b], ref) < tol, (t, b)
+        D.advance(pos)
+    for b in range(B):
+        assert rel_err(st.S[b].cpu().numpy(), S[b]) < TOL
+        assert (st.conv_image(b, T).cpu().numpy().ravel().view(np.uint32) == buf[b].view(np.uint32)).all()
+
+
+def test_512_decode_steps_stay_within_tolerance(oracle):
+    """The stated parity bar: outputs and recurrent state within 2e-3 over 512 decode steps."""
+    import torch
+    from ornithology_b200 import device as D
+    layer, kw = linear_case(4, nk=4, nv=8)               # 35B head shape, fewer heads (CPU time)
+    dl = device_linear(layer, kw)
+    T = 512
+    QKV, A, Bm, Z = linear_inputs(60, layer, T)
+    S = np.zeros((layer.nv, 128, 128), np.float32); buf = np.zeros(3 * layer.cc, np.float32)
+    st = D.LinearState(dl, 1)
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dQ, dA, dB, dZ = _t(QKV), _t(A), _t(Bm), _t(Z)
+    worst = 0.0
+    for t in range(T):
+        out = D.linear_attn_step(dl, st, pos, dQ[t:t + 1], dA[t:t + 1], dB[t:t + 1], dZ[t:t + 1])
+        ref = oracle.linear_attn_step(layer, S, buf, QKV[t], A[t], Bm[t], Z[t])
+        worst = max(worst, rel_err(out.cpu().numpy()[0], ref))
+        D.advance(pos)
+    assert worst < TOL, worst
+    assert rel_err(st.S.cpu().numpy()[0], S) < TOL
+
+
+@pytest.mark.parametrize("T,chunk", [(77, 32), (64, 16), (5, 32), (200, 32)])
+def test_35b_shape_prefill_then_decode(oracle, T, chunk):
+    """Chunked prefill (ragged tail, carried state) then decode steps; the oracle runs
+    the engine's own chunked scan for the prefill part."""
+    import torch
+    from ornithology_b200 import device as D
+    layer, kw = linear_case(6, nk=4, nv=8)
+    dl = device_linear(layer, kw)
+    extra = 4
+    QKV, A, Bm, Z = linear_inputs(70, layer, 2 * T + extra)
+    S = np.zeros((layer.nv, 128, 128), np.float32); buf = np.zeros(3 * layer.cc, np.float32)
+    st = D.LinearState(dl, 1)
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for part in range(2):                                  # second call starts from a non-zero state
+        sl = slice(part * T, (part + 1) * T)
+        ref = oracle.linear_attn_prefill(layer, S, buf, QKV[sl], A[sl], Bm[sl], Z[sl], chunk=32)
+        out = D.linear_attn_prefill(dl, st, pos, _t(QKV[sl])[None], _t(A[sl])[None], _t(Bm[sl])[None], _t(Z[sl])[None],
+                                    T, chunk=chunk)
+        assert rel_err(out.cpu().numpy()[0], ref) < TOL, part
+        assert rel_err(st.S.cpu().numpy()[0], S) < TOL, part
+        D.advance(pos, T)
+        assert (st.conv_image(0, (part + 1) * T).cpu().numpy().ravel().view(np.uint32) == buf.view(np.uint32)).all()
+    for t in range(2 * T, 2 * T + extra):
+        out = D.linear_attn_step(dl, st, pos, _t(QKV[t:t + 1]), _t(A[t:t + 1]), _t(Bm[t:t + 1]), _t(Z[t:t + 1]))
+        ref = oracle.linear_attn_step(layer, S, buf, QKV[t], A[t], Bm[t], Z[t])
+        assert rel_err(out.cpu().numpy()[0], ref) < TOL, t
+        D.advance(pos)
+
+
+def test_prefill_equals_decode_on_gpu_bf16_batch():
+    """prefill == T decode steps on the CUDA path itself, batch of 2, bf16 activations."""
+    import torch
+    from ornithology_b200 import device as D
+    layer, kw = linear_case(8, nk=4, nv=8)
+    dl = device_linear(layer, kw)
+    B, T = 2, 45
+    ins = [np.stack([linear_inputs(80 + b, layer, T, True)[i] for b in range(B)]) for i in range(4)]
+    dins = [_t(x, torch.bfloat16) for x in ins]
+    sa, sb = D.LinearState(dl, B), D.LinearState(dl, B)
+    pos = torch.zeros(B, dtype=torch.int32, device="cuda")
+    pre = D.linear_attn_prefill(dl, sa, pos, *dins, T, chunk=32).float().cpu().numpy()
+    outs = []
+    for t in range(T):
+        outs.append(D.linear_attn_step(dl, sb, pos, *[x[:, t].contiguous() for x in dins]).float().cpu().numpy())
+        D.advance(pos)
+    dec = np.stack(outs, axis=1)
+    assert rel_err(pre, dec) < TOL_BF16_IO
+    assert rel_err(sa.S.cpu().numpy(), sb.S.cpu().numpy()) < 2e-4
+    assert (sa.conv.cpu().numpy() == sb.conv.cpu().numpy()).all()
