@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(128) k_full_prep(PrepArgs a) {
     __shared__ double redd[32];
     __shared__ float redf[32];
     const int hd = a.kv.hd, nkv = a.kv.nkv, nh = a.nh;
-    const int j = blockIdx.x + a.row0, tt = blockIdx.y, b = tt / a.T, t = tt % a.T;
+    const int j = blockIdx.y + a.row0, tt = blockIdx.x, b = tt / a.T, t = tt % a.T;
     const int64_t base = a.kv.seq_off[b];
     const int cap = (int)(a.kv.seq_off[b + 1] - base);
     const int slot = a.kv_len[b] + t;
@@ -390,7 +390,7 @@ static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_c
     a.q_norm_w = l->q_norm_w; a.k_norm_w = l->k_norm_w; a.inv_freq = l->rope_inv_freq;
     a.nh = l->n_heads; a.rope_dim = l->rope_dim; a.gated = l->gated; a.T = T; a.eps = l->eps;
     a.row0 = kv_only ? l->n_heads : 0;
-    dim3 grid((kv_only ? 0 : l->n_heads) + 2 * l->n_kv_heads, n_tok);
+    dim3 grid(n_tok, (kv_only ? 0 : l->n_heads) + 2 * l->n_kv_heads);
     k_full_prep<ACT><<<grid, 128, l->head_dim * sizeof(float), st>>>(a);
     return orn_check_launch("k_full_prep");
 }
