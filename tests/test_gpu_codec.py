@@ -22,7 +22,10 @@ def test_q8_0_encode_decode_bit_exact(oracle, golden):
         bad = np.flatnonzero(got != ref)
         assert bad.size == 0, f"{bad.size} bytes differ, first at {bad[:5]}"
         dec = D.q8_0_decode(b).cpu().numpy()
-        assert (dec.view(np.uint32) == oracle.q8_0_decode(ref).view(np.uint32)).all()
+        want = oracle.q8_0_decode(ref)
+        nan = np.isnan(want)                      # 0 * inf blocks: NaN on both sides, payload unspecified
+        assert (np.isnan(dec) == nan).all()
+        assert (dec.view(np.uint32)[~nan] == want.view(np.uint32)[~nan]).all()
     assert (D.q8_0_encode(torch.from_numpy(g["x"]).cuda()).cpu().numpy() == g["bytes"]).all()
 
 
