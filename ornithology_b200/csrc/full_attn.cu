@@ -6,8 +6,10 @@
 //   full_attn_prefill()  src/ornith_rforward.c:513-556
 //   ornith_gqa_step()    src/ornith_attn.c:87-149
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
+#include "full_attn.cuh"
 #include "kv_rows.cuh"
 
 // =============================================================================
@@ -102,15 +104,6 @@ __global__ void __launch_bounds__(128) k_full_prep(PrepArgs a) {
 // =============================================================================
 // split-K decode, generic in head_dim and group size
 // =============================================================================
-
-struct DecodeArgs {
-    KvView kv;
-    const int32_t *kv_len;
-    const float *q_prep;                 // [n_seq][nh][hd]
-    float *part;                         // [n_seq][nh][nsplit][hd + 2]
-    int nh, nsplit, tokens_per_split;
-    float scale;
-};
 
 // One CTA = one (split, query head, sequence).  Scores are one thread per token
 // with the engine's element order; the value pass is one thread per dimension.
@@ -374,6 +367,14 @@ static ornith_status check_full(const ornith_cuda_full_layer *l, const ornith_cu
     return ORNITH_OK;
 }
 
+// ORNITH_CUDA_GENERIC_DECODE=1 routes Q8_0 decode through the generic CUDA-core
+// kernel (A/B comparison of the two device paths; both run on the GPU).
+static bool force_generic_decode() {
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("ORNITH_CUDA_GENERIC_DECODE"); v = (e && e[0] == '1') ? 1 : 0; }
+    return v == 1;
+}
+
 static int split_tokens(int max_len) {
     // tokens per split: long contexts use 512-token splits; short ones fewer CTAs
     return max_len <= 512 ? 128 : 512;
@@ -433,24 +434,33 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
 
     DecodeArgs d;
     d.kv = make_view(kv); d.kv_len = kv_len; d.q_prep = q_prep; d.part = part;
-    d.nh = nh; d.nsplit = nsplit; d.tokens_per_split = tps; d.scale = attn_scale(l);
-    dim3 grid(nsplit, nh, B);
-    const size_t smem = (size_t)(hd + 128) * sizeof(float);
-    switch (kv->mode) {
-    case ORNITH_KV_F32:       k_gqa_decode_generic<ORNITH_KV_F32><<<grid, 128, smem, st>>>(d); break;
-    case ORNITH_KV_INT8_HEAD: k_gqa_decode_generic<ORNITH_KV_INT8_HEAD><<<grid, 128, smem, st>>>(d); break;
-    default:                  k_gqa_decode_generic<ORNITH_KV_Q8_0><<<grid, 128, smem, st>>>(d); break;
+    d.nh = nh; d.scale = attn_scale(l);
+    int nsplit_used;
+    if (gqa_decode_q8_mma_supported(d.kv, nh) && !force_generic_decode()) {
+        // tensor-core path: larger splits (fewer partials); never more splits than the scratch was sized for
+        const int tps_mma = max_len > 8192 ? 1024 : (max_len > 1024 ? 512 : 256);
+        d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
+        ORN_TRY(launch_gqa_decode_q8_mma(d, B, st));
+    } else {
+        d.tokens_per_split = tps; d.nsplit = nsplit_used = nsplit;
+        dim3 grid(nsplit, nh, B);
+        const size_t smem = (size_t)(hd + 128) * sizeof(float);
+        switch (kv->mode) {
+        case ORNITH_KV_F32:       k_gqa_decode_generic<ORNITH_KV_F32><<<grid, 128, smem, st>>>(d); break;
+        case ORNITH_KV_INT8_HEAD: k_gqa_decode_generic<ORNITH_KV_INT8_HEAD><<<grid, 128, smem, st>>>(d); break;
+        default:                  k_gqa_decode_generic<ORNITH_KV_Q8_0><<<grid, 128, smem, st>>>(d); break;
+        }
+        ORN_TRY(orn_check_launch("k_gqa_decode_generic"));
     }
-    ORN_TRY(orn_check_launch("k_gqa_decode_generic"));
 
     CombineArgs c;
     c.kv = d.kv; c.kv_len = kv_len; c.part = part; c.qproj = qproj; c.out = out;
-    c.nh = nh; c.nsplit = nsplit; c.gated = l->gated;
+    c.nh = nh; c.nsplit = nsplit_used; c.gated = l->gated;
     dim3 cgrid(nh, B);
     if (act_dtype == ORNITH_ACT_BF16)
-        k_gqa_combine<__nv_bfloat16><<<cgrid, 128, nsplit * sizeof(float), st>>>(c);
+        k_gqa_combine<__nv_bfloat16><<<cgrid, 128, nsplit_used * sizeof(float), st>>>(c);
     else
-        k_gqa_combine<float><<<cgrid, 128, nsplit * sizeof(float), st>>>(c);
+        k_gqa_combine<float><<<cgrid, 128, nsplit_used * sizeof(float), st>>>(c);
     return orn_check_launch("k_gqa_combine");
 }
 

@@ -1,0 +1,18 @@
+// full_attn.cuh — argument block shared by the split-K decode kernels.
+#pragma once
+#include "common.cuh"
+#include "kv_rows.cuh"
+
+struct DecodeArgs {
+    KvView kv;
+    const int32_t *kv_len;
+    const float *q_prep;                 // [n_seq][nh][hd] f32, normalised + rotated
+    float *part;                         // [n_seq][nh][nsplit][hd + 2]: m, l, o[hd]
+    int nh, nsplit, tokens_per_split;
+    float scale;
+};
+
+// Tensor-core split-K decode over Q8_0 rows, head_dim 256, up to 16 query heads
+// per KV head.  Writes the same partials as the generic kernel.
+bool gqa_decode_q8_mma_supported(const KvView &kv, int nh);
+ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st);

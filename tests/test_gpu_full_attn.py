@@ -137,13 +137,13 @@ def test_prefill_equals_decode_on_gpu():
         assert (kv_a.K.cpu().numpy() == kv_b.K.cpu().numpy()).all() and (kv_a.V.cpu().numpy() == kv_b.V.cpu().numpy()).all()
 
 
-def test_long_context_split_k(oracle):
+@pytest.mark.parametrize("L", [1500, 9001])
+def test_long_context_split_k(oracle, L):
     """A context long enough for several splits (and a ragged last one)."""
     import torch
     from ornithology_b200 import device as D
     layer = full_case(5)
     dl = device_full(layer)
-    L = 1500
     rng = np.random.default_rng(8)
     kv = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [L + 1])
     okv = oracle.kv(L + 1, layer.nkv, layer.hd, 2)
