@@ -61,17 +61,19 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 }
 
 // Decode one staged tile (16 rows x 8 blocks of {f16 scale, 32 int8}) to f16.
-// A lane handles 4 (row, block) units; its block index is lane & 7, so the
-// 2-byte misalignment of the codes (even blocks) is a per-lane constant shift.
+// A lane handles 4 (row, block) units; its block index is lane >> 2, so the
+// 2-byte misalignment of the codes (even blocks) is a per-lane constant shift,
+// and the 8 lanes of one 128-bit store phase hit 8 distinct 16-byte bank groups
+// (rows 0-3 x two neighbouring blocks).
 __device__ __forceinline__ void decode_tile(const unsigned char *raw, __half *th, int lane) {
-    const int blk = lane & 7;
+    const int blk = lane >> 2;
     const bool even = (blk & 1) == 0;
     const int start = 34 * blk - (even ? 0 : 2);          // 4-byte aligned
     const uint32_t sh = even ? 16u : 32u;
     const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const int row = (lane >> 3) + 4 * i;
+        const int row = (lane & 3) + 4 * i;
         const uint32_t *w = reinterpret_cast<const uint32_t *>(raw + row * ROWB + start);
         uint32_t wd[9];
 #pragma unroll
@@ -187,13 +189,22 @@ __global__ void __launch_bounds__(128, 2) k_gqa_decode_q8_mma(DecodeArgs a) {
         decode_tile(rawK, th, lane);
         __syncwarp();
         float s0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        {   // four independent accumulator chains (even / odd k-steps), summed at the end
+            float e0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, e1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-            uint32_t A[4], B[4];
-            ldsm_x4(A, q_addr + ks * 32);
-            ldsm_x4(B, k_addr + ks * 32);
-            mma16816(s0, A, B[0], B[1]);
-            mma16816(s1, A, B[2], B[3]);
+            for (int ks = 0; ks < 16; ks += 2) {
+                uint32_t A[4], B[4], A2[4], B2[4];
+                ldsm_x4(A, q_addr + ks * 32);
+                ldsm_x4(B, k_addr + ks * 32);
+                ldsm_x4(A2, q_addr + ks * 32 + 32);
+                ldsm_x4(B2, k_addr + ks * 32 + 32);
+                mma16816(s0, A, B[0], B[1]);
+                mma16816(s1, A, B[2], B[3]);
+                mma16816(e0, A2, B2[0], B2[1]);
+                mma16816(e1, A2, B2[2], B2[3]);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; c++) { s0[c] += e0[c]; s1[c] += e1[c]; }
         }
         // ---- online softmax, log2 domain; rows r = lane/4 and r + 8 ----------------------
         const bool ok0 = tok0 + j2 < t1, ok1 = tok0 + j2 + 1 < t1, ok2 = tok0 + 8 + j2 < t1, ok3 = tok0 + 9 + j2 < t1;
