@@ -84,8 +84,8 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------
 # CPU path (the checker libraries, timed): a bounded sample of the same workload
 # ---------------------------------------------------------------------------------------
-def cpu_sample(contexts, n_seq_sample, seed, threads):
-    """Time one decode token of `n_seq_sample` sequences through one interleave group
+def cpu_sample(contexts, n_seq_sample, seed, threads, passes=3):
+    """Time `passes` interleave groups of one decode token for `n_seq_sample` sequences
     (3 delta-net layers + 1 GQA layer) on the host, and scale to the 40-layer stack.
     Uses the reference's own compiled objects when they were built, else the port."""
     from concurrent.futures import ThreadPoolExecutor
@@ -93,7 +93,8 @@ def cpu_sample(contexts, n_seq_sample, seed, threads):
     from ornithology_b200.stack import ARCHS, full_weights, linear_weights
     a = ARCHS["35b"]
     orc = O.Oracle()
-    kind = "port"
+    ref = O.Ref() if O.Ref.available() else None
+    kind = "reference" if ref is not None else "port"
     lin_layers = []
     for i in range(3):
         w = linear_weights(a, seed, i)
@@ -103,34 +104,48 @@ def cpu_sample(contexts, n_seq_sample, seed, threads):
     ctx = [int(c) for c in contexts[:n_seq_sample]]
     g = np.random.default_rng(seed + 1)
     seqs = []
-    for L in ctx:                                # state set-up is not timed
-        kv = orc.kv(L + 1, a["nkv"], a["hd"], O.KV_Q8_0)
-        rows = (L, a["nkv"] * a["hd"])
-        Kd = g.standard_normal(rows, dtype=np.float32)        # stand-in for the decoded rows
-        Vd = g.standard_normal(rows, dtype=np.float32)
-        import ctypes as C
-        C.memmove(kv.c.K, Kd.ctypes.data, Kd.nbytes); C.memmove(kv.c.V, Vd.ctypes.data, Vd.nbytes)
-        kv.c.len = L
+    import ctypes as C
+    pool = g.standard_normal((max(ctx) + 64, a["nkv"] * a["hd"]), dtype=np.float32)   # stand-in for decoded rows
+    for n, L in enumerate(ctx):                  # state set-up is not timed
+        Kd = pool[n % 32:n % 32 + L]
+        Vd = pool[32 + n % 32:32 + n % 32 + L]
+        if ref is not None:                      # the reference's own f32 cache (src/ornith_attn.h:57-69)
+            kv = ref.kv_init(L + 1, a["nkv"], a["hd"], 0)
+            C.memmove(kv.K, Kd.ctypes.data, Kd.nbytes); C.memmove(kv.V, Vd.ctypes.data, Vd.nbytes)
+            kv.len = L
+        else:
+            kv = orc.kv(L + 1, a["nkv"], a["hd"], O.KV_Q8_0)
+            C.memmove(kv.c.K, Kd.ctypes.data, Kd.nbytes); C.memmove(kv.c.V, Vd.ctypes.data, Vd.nbytes)
+            kv.c.len = L
         S = [(g.standard_normal((a["nv"], a["dv"], a["dk"])) * 0.05).astype(np.float32) for _ in range(3)]
-        buf = [g.standard_normal(3 * lin_layers[0].cc).astype(np.float32) for _ in range(3)]
+        buf = [g.standard_normal(3 * lin_layers[0].cc + 1).astype(np.float32) for _ in range(3)]
         ins_l = [[g.standard_normal(w).astype(np.float32) for w in (lin_layers[0].cc, a["nv"], a["nv"], lin_layers[0].vd)] for _ in range(3)]
         ins_f = [g.standard_normal(w).astype(np.float32) for w in (a["nh"] * 2 * a["hd"], a["nkv"] * a["hd"], a["nkv"] * a["hd"])]
         seqs.append((kv, L, S, buf, ins_l, ins_f))
 
     def one(s):
         kv, L, S, buf, ins_l, ins_f = s
-        for i in range(3):
-            orc.linear_attn_step(lin_layers[i], S[i], buf[i], *ins_l[i])
-        orc.full_attn_step(full, kv, L, *ins_f)
+        if ref is not None:                      # the reference's own functions, Q8_0 rows via its codec
+            for i in range(3):
+                O.ref_linear_step(ref, lin_layers[i], S[i], buf[i], *ins_l[i])
+            kv.len = L                           # every pass appends at the same position
+            O.ref_full_step(ref, full, kv, L, *ins_f, q8_0=True)
+        else:
+            for i in range(3):
+                orc.linear_attn_step(lin_layers[i], S[i], buf[i], *ins_l[i])
+            kv.c.len = L
+            orc.full_attn_step(full, kv, L, *ins_f)
 
     t0 = time.perf_counter()
     with ThreadPoolExecutor(max_workers=threads) as ex:
-        list(ex.map(one, seqs))
+        for _ in range(passes):
+            list(ex.map(one, seqs))
     dt = time.perf_counter() - t0
     groups = a["layers"] // a["interval"]
-    tok_s = len(seqs) / (dt * groups)            # sequence-tokens per second through all 40 layers
-    sample = (f"1 decode token for {len(seqs)} of the sequences (contexts {ctx}) through one 3+1 layer group, "
-              f"x{groups} groups, {threads} threads, {dt:.2f} s of wall time")
+    tok_s = len(seqs) * passes / (dt * groups)   # sequence-tokens per second through all 40 layers
+    sample = (f"{passes} of the {groups} 3+1 layer groups of one decode step, {len(seqs)} sequences "
+              f"(contexts sum {sum(ctx)}), scaled x{groups}/{passes}; {threads} threads, one sequence per thread; "
+              f"{dt:.2f} s wall = {dt * threads:.0f} s of CPU work")
     return tok_s, kind, sample, dt
 
 
@@ -139,7 +154,7 @@ def run_reference(args, rank, world):
         return
     threads = min(os.cpu_count() or 1, 32)
     contexts = draw_contexts(args.seqs, args.min_ctx, args.max_ctx, args.seed)
-    n_sample = min(args.seqs, max(threads, 8))
+    n_sample = args.seqs
     vals, sample, kind = [], "", "port"
     for it in range(args.warmup + args.steps):
         v, kind, sample, _ = cpu_sample(contexts, n_sample, args.seed, threads)
@@ -272,7 +287,7 @@ def run_ours(args, rank, world, local_rank):
         cpu = None
         if world == 1 and not args.no_cpu:
             threads = min(os.cpu_count() or 1, 32)
-            v, kind, sample, _ = cpu_sample(all_ctx, min(args.seqs, max(threads, 8)), args.seed, threads)
+            v, kind, sample, _ = cpu_sample(all_ctx, args.seqs, args.seed, threads)
             cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,

@@ -442,3 +442,36 @@ class Ref:
         OUT = np.empty_like(X)
         self.lib.ornith_conv_prefill(C.byref(cs), _fp(X), _fp(w), _fp(bias), T, _fp(OUT))
         return OUT
+
+
+# ---- the reference's functions driven through whole layer steps (ref_driver.c) -----------
+class _RefDrvLinear(C.Structure):
+    _fields_ = [("nk", C.c_int), ("nv", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("conv_k", C.c_int),
+                ("eps", C.c_float), ("conv_w", _f32p), ("a_coef", _f32p), ("dt_bias", _f32p), ("norm_w", _f32p)]
+
+
+class _RefDrvFull(C.Structure):
+    _fields_ = [("nh", C.c_int), ("nkv", C.c_int), ("hd", C.c_int), ("rope_dim", C.c_int),
+                ("theta", C.c_float), ("eps", C.c_float), ("q_norm_w", _f32p), ("k_norm_w", _f32p),
+                ("q8_0", C.c_int)]
+
+
+def ref_linear_step(ref: "Ref", layer: LinearLayer, S, conv_buf, qkv, a, b, z):
+    """One token of a delta-net layer through the reference's own functions
+    (real-weights conventions: tiled head map, no conv bias, 1/sqrt(dk) scale)."""
+    assert layer.head_map == HEADMAP_TILED and layer.conv_b is None
+    p = _RefDrvLinear(layer.nk, layer.nv, layer.dk, layer.dv, layer.conv_k, layer.eps,
+                      _fp(layer.conv_w), _fp(layer.a_coef), _fp(layer.dt_bias), _fp(layer.norm_w))
+    out = np.empty(layer.vd, np.float32)
+    ref.lib.refdrv_linear_step(C.byref(p), _fp(S), _fp(conv_buf), _fp(qkv), _fp(a), _fp(b), _fp(z), _fp(out))
+    return out
+
+
+def ref_full_step(ref: "Ref", layer: FullLayer, kv_struct, pos, qproj, k, v, q8_0=False):
+    """One token of a full-attention layer through the reference's own functions over
+    its f32 cache; q8_0 passes the appended rows through the reference's Q8_0 codec."""
+    p = _RefDrvFull(layer.nh, layer.nkv, layer.hd, layer.rope_dim, layer.theta, layer.eps,
+                    _fp(layer.q_norm_w), _fp(layer.k_norm_w), int(q8_0))
+    out = np.zeros(layer.nh * layer.hd, np.float32)
+    ref.lib.refdrv_full_step(C.byref(p), C.byref(kv_struct), int(pos), _fp(qproj), _fp(k), _fp(v), _fp(out))
+    return out

@@ -293,6 +293,253 @@ __global__ void __launch_bounds__(128, 2) k_gqa_decode_q8_mma(DecodeArgs a) {
     }
 }
 
+// =============================================================================
+// Variant for groups of up to 8 query heads: tokens on the MMA M axis
+// =============================================================================
+//
+// S^T[token, head] = K Q^T and O^T[dim, head] += V^T P^T, so the 8 heads fill the
+// N = 8 axis exactly (no padded rows), the output accumulator is 64 registers and
+// the whole query group lives in registers as B fragments.  K never touches a
+// second buffer: each lane converts the 8 consecutive codes it needs per 32-value
+// block straight into A fragments (the contraction index is permuted the same
+// way on the query side, which leaves the dot product unchanged).  V is decoded
+// into the warp's f16 tile and read back transposed with ldmatrix.  One raw stage
+// per warp (17 KB of shared memory in all) lets three CTAs share an SM; the next
+// tile's K rows are requested right after the score loop and its V rows right
+// after the V decode.
+constexpr int W3_RAW = 2 * RAW_TILE;                    // K rows, V rows
+constexpr int W3_BYTES = W3_RAW + TILE * LDH * 2;       // + f16 tile = 17152
+constexpr int SMEM3_BYTES = NWARP * W3_BYTES;
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// 4 int8 codes (one word) -> two f16x2 words scaled by d2
+__device__ __forceinline__ void cvt4(uint32_t w, __half2 d2, uint32_t &x01, uint32_t &x23) {
+    const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+    const uint32_t cw = w ^ 0x80808080u;
+    uint32_t h01 = __byte_perm(cw, 0x64646464u, 0x4140), h23 = __byte_perm(cw, 0x64646464u, 0x4342);
+    __half2 a = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h01), bias), d2);
+    __half2 b = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&h23), bias), d2);
+    x01 = *reinterpret_cast<uint32_t *>(&a);
+    x23 = *reinterpret_cast<uint32_t *>(&b);
+}
+
+// the 8 codes at in-block offset 8j of block B of one staged row, and the block scale
+template <int B>
+__device__ __forceinline__ void load_block8(const unsigned char *row, int j, uint32_t &lo, uint32_t &hi, __half2 &d2) {
+    const __half d = __ushort_as_half(*reinterpret_cast<const unsigned short *>(row + 34 * B));
+    d2 = __halves2half2(d, d);
+    if (B % 2 == 0) {            // codes start 2 bytes past a word boundary
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(row + 34 * B + 8 * j);
+        const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+        lo = __funnelshift_r(w0, w1, 16);
+        hi = __funnelshift_r(w1, w2, 16);
+    } else {
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(row + 34 * B + 2 + 8 * j);
+        lo = w[0];
+        hi = w[1];
+    }
+}
+
+template <int B>
+__device__ __forceinline__ void qk_block(const unsigned char *r0p, const unsigned char *r1p, int j,
+                                         const uint32_t (&qf)[8][4], float (&s)[4], float (&e)[4]) {
+    uint32_t lo0, hi0, lo1, hi1;
+    __half2 d0, d1;
+    load_block8<B>(r0p, j, lo0, hi0, d0);
+    load_block8<B>(r1p, j, lo1, hi1, d1);
+    uint32_t A0[4], A1[4];
+    cvt4(lo0, d0, A0[0], A0[2]);     // row r:   k = 2j,2j+1 | 2j+8,2j+9 of the first k-step
+    cvt4(lo1, d1, A0[1], A0[3]);     // row r+8
+    cvt4(hi0, d0, A1[0], A1[2]);     // second k-step of the block
+    cvt4(hi1, d1, A1[1], A1[3]);
+    mma16816(s, A0, qf[B][0], qf[B][1]);
+    mma16816(e, A1, qf[B][2], qf[B][3]);
+}
+
+__device__ __forceinline__ void issue_rows(unsigned char *dst, const unsigned char *src_base, size_t row_stride,
+                                           int tok0, int t1, int lane) {
+    // lane pair (2r, 2r+1) copies row r: 9 + 8 chunks of 16 bytes
+    const int row = lane >> 1, first = (lane & 1) * 9, cnt = 9 - (lane & 1);
+    const int tok = tok0 + row;
+    const bool ok = tok < t1;
+    const unsigned char *src = src_base + (ok ? (size_t)tok * row_stride : 0) + first * 16;
+    uint32_t d = smem_u32(dst + row * ROWB + first * 16);
+    for (int c = 0; c < cnt; c++) cp_async16(d + c * 16, src + (ok ? c * 16 : 0), ok ? 16 : 0);
+}
+
+__global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_tok(DecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float m_s[NWARP][8], l_s[NWARP][8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned char *wbase = smem + warp * W3_BYTES;
+    unsigned char *rawK = wbase, *rawV = wbase + RAW_TILE;
+    __half *th = reinterpret_cast<__half *>(wbase + W3_RAW);
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, nkv = a.kv.nkv;
+    const int G = a.nh / nkv;
+    const int64_t base = a.kv.seq_off[b];
+    const int cap = (int)(a.kv.seq_off[b + 1] - base);
+    const int len0 = a.kv_len[b];
+    if (len0 >= cap) return;
+    const int L = len0 + 1;
+    const int t0 = split * a.tokens_per_split, t1 = min(L, t0 + a.tokens_per_split);
+    float *part0 = a.part + (((size_t)b * a.nh + (size_t)kvh * G) * a.nsplit + split) * (HD + 2);
+    const size_t part_stride = (size_t)a.nsplit * (HD + 2);
+    if (t0 >= L) {
+        if (tid < G) { part0[tid * part_stride] = -INFINITY; part0[tid * part_stride + 1] = 0.0f; }
+        return;
+    }
+    const int r = lane >> 2, j = lane & 3;
+
+    // ---- query group -> B fragments in registers: lane (head r, quarter j) keeps q[r][32b + 8j .. +7]
+    uint32_t qf[8][4];
+    float rs_mine;
+    {
+        float v[8][8];
+        float mx = 0.0f;
+        const float *q = a.q_prep + ((size_t)b * a.nh + (size_t)kvh * G + r) * HD + 8 * j;
+#pragma unroll
+        for (int bb = 0; bb < 8; bb++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                v[bb][i] = (r < G) ? q[32 * bb + i] : 0.0f;
+                mx = fmaxf(mx, fabsf(v[bb][i]));
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        int e = 0;
+        if (mx > 0.0f && mx < INFINITY) (void)frexpf(mx, &e);
+        const float down = exp2f((float)-e);
+#pragma unroll
+        for (int bb = 0; bb < 8; bb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) qf[bb][i] = pack_h2(v[bb][2 * i] * down, v[bb][2 * i + 1] * down);
+        rs_mine = (r < G) ? a.scale * exp2f((float)e) * LOG2E : 0.0f;
+    }
+    // score scale of the two heads this lane sees as accumulator columns (2j, 2j+1)
+    const float rsA = __shfl_sync(0xffffffffu, rs_mine, (2 * j) * 4);
+    const float rsB = __shfl_sync(0xffffffffu, rs_mine, (2 * j + 1) * 4);
+
+    const int ntiles = (t1 - t0 + TILE - 1) / TILE;
+    const size_t row_stride = (size_t)nkv * ROWB;
+    const unsigned char *Kbase = a.kv.K + ((size_t)base * nkv + kvh) * ROWB;
+    const unsigned char *Vbase = a.kv.V + ((size_t)base * nkv + kvh) * ROWB;
+
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
+    const unsigned char *r0p = rawK + r * ROWB, *r1p = r0p + 8 * ROWB;
+    const uint32_t v_addr = smem_u32(th) + (((lane & 7) + (lane >> 4) * 8) * LDH) * 2 + ((lane >> 3) & 1) * 16;
+
+    int it = warp;
+    if (it < ntiles) issue_rows(rawK, Kbase, row_stride, t0 + it * TILE, t1, lane);
+    cp_async_commit();
+    if (it < ntiles) issue_rows(rawV, Vbase, row_stride, t0 + it * TILE, t1, lane);
+    cp_async_commit();
+    for (; it < ntiles; it += NWARP) {
+        const int tok0 = t0 + it * TILE;
+        const bool more = it + NWARP < ntiles;
+        cp_async_wait<1>();                                   // this tile's K rows have landed
+        __syncwarp();
+        // ---- S^T = K Q^T, two accumulator chains ---------------------------------------
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f}, e2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        qk_block<0>(r0p, r1p, j, qf, s, e2); qk_block<1>(r0p, r1p, j, qf, s, e2);
+        qk_block<2>(r0p, r1p, j, qf, s, e2); qk_block<3>(r0p, r1p, j, qf, s, e2);
+        qk_block<4>(r0p, r1p, j, qf, s, e2); qk_block<5>(r0p, r1p, j, qf, s, e2);
+        qk_block<6>(r0p, r1p, j, qf, s, e2); qk_block<7>(r0p, r1p, j, qf, s, e2);
+        __syncwarp();                                         // every lane is done with the K rows
+        if (more) issue_rows(rawK, Kbase, row_stride, tok0 + NWARP * TILE, t1, lane);
+        cp_async_commit();
+
+        // ---- online softmax over tokens (rows r, r+8); columns = heads 2j, 2j+1 -----------
+        const bool ok0 = tok0 + r < t1, ok1 = tok0 + r + 8 < t1;
+        float x00 = ok0 ? (s[0] + e2[0]) * rsA : -INFINITY, x01 = ok0 ? (s[1] + e2[1]) * rsB : -INFINITY;
+        float x10 = ok1 ? (s[2] + e2[2]) * rsA : -INFINITY, x11 = ok1 ? (s[3] + e2[3]) * rsB : -INFINITY;
+        float cA = fmaxf(x00, x10), cB = fmaxf(x01, x11);
+#pragma unroll
+        for (int sft = 4; sft <= 16; sft <<= 1) {
+            cA = fmaxf(cA, __shfl_xor_sync(0xffffffffu, cA, sft));
+            cB = fmaxf(cB, __shfl_xor_sync(0xffffffffu, cB, sft));
+        }
+        const float nA = fmaxf(mA, cA), nB = fmaxf(mB, cB);   // finite: token tok0 is valid
+        const float corrA = exp2f(mA - nA), corrB = exp2f(mB - nB);
+        mA = nA; mB = nB;
+        x00 = exp2f(x00 - nA); x10 = exp2f(x10 - nA); x01 = exp2f(x01 - nB); x11 = exp2f(x11 - nB);
+        lA = lA * corrA + x00 + x10;                          // per-lane partial over its two rows
+        lB = lB * corrB + x01 + x11;
+        if (__any_sync(0xffffffffu, corrA != 1.0f || corrB != 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) { o[i][0] *= corrA; o[i][1] *= corrB; o[i][2] *= corrA; o[i][3] *= corrB; }
+        }
+        // P^T as the B operand: transpose the two 8x8 (token x head) blocks across the warp
+        const uint32_t pb0 = movmatrix_trans(pack_h2(x00 * 256.0f, x01 * 256.0f));
+        const uint32_t pb1 = movmatrix_trans(pack_h2(x10 * 256.0f, x11 * 256.0f));
+
+        // ---- O^T += V^T P^T -----------------------------------------------------------------
+        cp_async_wait<1>();                                   // this tile's V rows have landed
+        __syncwarp();
+        decode_tile(rawV, th, lane);
+        __syncwarp();
+        if (more) issue_rows(rawV, Vbase, row_stride, tok0 + NWARP * TILE, t1, lane);
+        cp_async_commit();
+#pragma unroll
+        for (int mt = 0; mt < 16; mt++) {
+            uint32_t A[4];
+            ldsm_x4_trans(A, v_addr + mt * 32);
+            mma16816(o[mt], A, pb0, pb1);
+        }
+        __syncwarp();                                         // f16 tile free for the next round
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+
+    // ---- merge the four warps, one partial per (head, split) -------------------------------
+#pragma unroll
+    for (int sft = 4; sft <= 16; sft <<= 1) {
+        lA += __shfl_xor_sync(0xffffffffu, lA, sft);
+        lB += __shfl_xor_sync(0xffffffffu, lB, sft);
+    }
+    float *Ow = reinterpret_cast<float *>(wbase);             // [8 heads][256] f32 over this warp's buffers
+#pragma unroll
+    for (int mt = 0; mt < 16; mt++) {
+        Ow[(2 * j) * HD + mt * 16 + r] = o[mt][0];
+        Ow[(2 * j + 1) * HD + mt * 16 + r] = o[mt][1];
+        Ow[(2 * j) * HD + mt * 16 + r + 8] = o[mt][2];
+        Ow[(2 * j + 1) * HD + mt * 16 + r + 8] = o[mt][3];
+    }
+    if (r == 0) {
+        m_s[warp][2 * j] = mA; m_s[warp][2 * j + 1] = mB;
+        l_s[warp][2 * j] = lA; l_s[warp][2 * j + 1] = lB;
+    }
+    __syncthreads();
+    for (int h = 0; h < G; h++) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARP; w++) if (l_s[w][h] > 0.0f) M = fmaxf(M, m_s[w][h]);
+        float ww[NWARP], Lt = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NWARP; w++) {
+            ww[w] = (l_s[w][h] > 0.0f) ? exp2f(m_s[w][h] - M) : 0.0f;
+            Lt += l_s[w][h] * ww[w];
+        }
+        float *part = part0 + h * part_stride;
+        if (tid == 0) { part[0] = M * LN2; part[1] = Lt; }
+        for (int d = tid; d < HD; d += 128) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int w = 0; w < NWARP; w++)
+                acc += ww[w] * reinterpret_cast<const float *>(smem + w * W3_BYTES)[h * HD + d];
+            part[2 + d] = acc * (1.0f / 256.0f);
+        }
+    }
+}
+
 }  // namespace
 
 bool gqa_decode_q8_mma_supported(const KvView &kv, int nh) {
@@ -307,7 +554,17 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
                                                SMEM_BYTES), "gqa decode smem opt-in"));
         configured = true;
     }
+    static bool configured3 = false;
+    if (!configured3) {
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_tok, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               SMEM3_BYTES), "gqa decode smem opt-in"));
+        configured3 = true;
+    }
     dim3 grid(a.nsplit, a.kv.nkv, n_seq);
+    if (a.nh / a.kv.nkv <= 8) {
+        k_gqa_decode_q8_tok<<<grid, 128, SMEM3_BYTES, st>>>(a);
+        return orn_check_launch("k_gqa_decode_q8_tok");
+    }
     k_gqa_decode_q8_mma<<<grid, 128, SMEM_BYTES, st>>>(a);
     return orn_check_launch("k_gqa_decode_q8_mma");
 }
