@@ -16,3 +16,7 @@ struct DecodeArgs {
 // per KV head.  Writes the same partials as the generic kernel.
 bool gqa_decode_q8_mma_supported(const KvView &kv, int nh);
 ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st);
+
+// Variant for groups of up to 8 query heads that builds its MMA fragments straight
+// from the staged raw rows (gqa_decode_q8_raw.cu).
+ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st);

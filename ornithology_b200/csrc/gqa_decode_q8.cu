@@ -18,6 +18,8 @@
 // to f16 (11-bit significand, the same as tf32); decoded K/V elements carry one
 // f16 rounding; probabilities are scaled by 2^8 before the f16 rounding so small
 // weights stay in the normal range.  Accumulation is f32.
+#include <stdlib.h>
+
 #include "full_attn.cuh"
 
 namespace {
@@ -562,6 +564,10 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
     }
     dim3 grid(a.nsplit, a.kv.nkv, n_seq);
     if (a.nh / a.kv.nkv <= 8) {
+        // ORNITH_CUDA_DECODE_VARIANT=tile selects the variant that decodes V into an f16 tile
+        static int use_tile = -1;
+        if (use_tile < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); use_tile = (e && e[0] == 't') ? 1 : 0; }
+        if (!use_tile) return launch_gqa_decode_q8_raw(a, n_seq, st);
         k_gqa_decode_q8_tok<<<grid, 128, SMEM3_BYTES, st>>>(a);
         return orn_check_launch("k_gqa_decode_q8_tok");
     }

@@ -1,0 +1,354 @@
+// gqa_decode_q8_raw.cu — split-K GQA decode over Q8_0 rows, fragments taken straight
+// from the staged raw bytes (groups of up to 8 query heads, head_dim 256).
+//
+// Replaces the attend half of ornith_gqa_step (reference: src/ornith_attn.c:111-148).
+//
+// A Q8_0 row of 256 values is 8 blocks of {f16 scale, 32 int8} = 272 bytes.  Read
+// as a stream of 136 16-bit elements it is  [scale, 16 code pairs] x 8, and the
+// 17 aligned 16-byte chunks of the row are exactly what ldmatrix moves:
+//
+//   K (A operand, tokens on M): plain ldmatrix hands lane (token r, quarter j) the
+//     elements 8c+2j and 8c+2j+1 of chunk c — four codes, i.e. the two f16 pairs
+//     one k-step needs.  The contraction index is whatever order the stream has;
+//     the query B fragments are built in the same order once per CTA, with zeros
+//     where the stream holds a scale.  One chunk = one k-step, 17 per tile.
+//   V (A operand of O^T = V^T P^T): ldmatrix.trans hands lane (element r, token
+//     pair j) one stream element for two tokens: codes (d, d+1) x (t, t+1).  The
+//     int8 -> f16 byte permute picks (t, t+1) of dim d and of dim d+1, which are
+//     the rows of two 8-row halves of one m-tile.  One chunk = one m-tile; the
+//     lane whose element is the block's scale holds both tokens' scales as an
+//     f16 pair and broadcasts it with one shuffle.
+//
+// Nothing is decoded into a second shared-memory buffer: per 16-token tile the
+// shared-memory pipe moves the staged bytes once in (cp.async) and once out
+// (ldmatrix), plus 16 two-byte scale loads for K.
+//
+// Precision: as the other tensor-core decode kernel — q scaled per head by a
+// power of two and rounded to f16, decoded K/V elements carry one f16 rounding,
+// probabilities scaled by 2^8 before the f16 rounding, f32 accumulation.
+#include "full_attn.cuh"
+
+namespace {
+
+constexpr int HD = 256;
+constexpr int ROWB = 272;
+constexpr int TILE = 16;
+constexpr int NWARP = 4;
+constexpr int NCHUNK = 17;                         // 16-byte chunks per row
+constexpr int RAW_TILE = TILE * ROWB;              // 4352
+constexpr int STAGE_BYTES = 2 * RAW_TILE;          // K rows + V rows
+constexpr int WARP_BYTES = 2 * STAGE_BYTES;        // two stages = 17408
+constexpr int SMEM_BYTES = NWARP * WARP_BYTES;     // 69632
+constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ uint32_t h2_mul_sub(uint32_t biased, uint32_t scale) {   // (x - 1152) * scale
+    const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+    __half2 v = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&biased), bias), *reinterpret_cast<__half2 *>(&scale));
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// stream element e of a row: block e / 17; index 0 of a block is its scale, index i > 0
+// is the code pair of dims 2(i-1), 2(i-1)+1.  Returns the first dim, or -1 for a scale.
+__host__ __device__ constexpr int elem_block(int e) { return e / 17; }
+__host__ __device__ constexpr int elem_dim(int e) { return (e % 17 == 0) ? -1 : 32 * (e / 17) + 2 * (e % 17 - 1); }
+
+// ---- one k-step of S^T = K Q^T from chunk C of the staged K rows -------------------------
+// raw0 / raw1: the lane's ldmatrix registers for token rows r and r + 8 (elements
+// 8C+2j and 8C+2j+1); dk0 / dk1: that row's block scales as f16 pairs.
+template <int C>
+__device__ __forceinline__ void qk_chunk(uint32_t raw0, uint32_t raw1, const uint32_t (&dk0)[8], const uint32_t (&dk1)[8],
+                                         int j, const uint32_t (&qf)[NCHUNK][2], float (&acc)[4]) {
+    constexpr int BLO = elem_block(8 * C), BHI = elem_block(8 * C + 7) > 7 ? 7 : elem_block(8 * C + 7);
+    // block of element 8C+2j+h: BHI once the element index reaches 17*BHI
+    const bool hi0 = (BHI != BLO) && (8 * C + 2 * j >= 17 * BHI);
+    const bool hi1 = (BHI != BLO) && (8 * C + 2 * j + 1 >= 17 * BHI);
+    const uint32_t s00 = hi0 ? dk0[BHI] : dk0[BLO], s01 = hi1 ? dk0[BHI] : dk0[BLO];
+    const uint32_t s10 = hi0 ? dk1[BHI] : dk1[BLO], s11 = hi1 ? dk1[BHI] : dk1[BLO];
+    const uint32_t x0 = raw0 ^ 0x80808080u, x1 = raw1 ^ 0x80808080u;
+    uint32_t A[4];
+    A[0] = h2_mul_sub(__byte_perm(x0, 0x64646464u, 0x4140), s00);    // row r,   element 8C+2j   -> k = 2j, 2j+1
+    A[1] = h2_mul_sub(__byte_perm(x1, 0x64646464u, 0x4140), s10);    // row r+8
+    A[2] = h2_mul_sub(__byte_perm(x0, 0x64646464u, 0x4342), s01);    // row r,   element 8C+2j+1 -> k = 2j+8, 2j+9
+    A[3] = h2_mul_sub(__byte_perm(x1, 0x64646464u, 0x4342), s11);
+    mma16816(acc, A, qf[C][0], qf[C][1]);
+}
+
+// ---- one m-tile of O^T += V^T P^T from chunk C of the staged V rows ------------------------
+// raw0 / raw1: transposed-ldmatrix registers: element 8C+r for tokens (2j, 2j+1) and
+// (2j+8, 2j+9).  sc*: the f16 scale pairs of the two candidate blocks for those tokens.
+template <int C>
+__device__ __forceinline__ void pv_chunk(uint32_t raw0, uint32_t raw1, uint32_t sc_lo0, uint32_t sc_lo1,
+                                         uint32_t sc_hi0, uint32_t sc_hi1, int r, uint32_t pb0, uint32_t pb1,
+                                         float (&acc)[4]) {
+    constexpr int BLO = elem_block(8 * C), BHI = elem_block(8 * C + 7) > 7 ? 7 : elem_block(8 * C + 7);
+    const bool hi = (BHI != BLO) && (8 * C + r >= 17 * BHI);
+    const uint32_t s0 = hi ? sc_hi0 : sc_lo0, s1 = hi ? sc_hi1 : sc_lo1;
+    const uint32_t x0 = raw0 ^ 0x80808080u, x1 = raw1 ^ 0x80808080u;
+    uint32_t A[4];
+    A[0] = h2_mul_sub(__byte_perm(x0, 0x64646464u, 0x4240), s0);     // even dim, tokens 2j, 2j+1
+    A[1] = h2_mul_sub(__byte_perm(x0, 0x64646464u, 0x4341), s0);     // odd dim (rows 8..15 of the m-tile)
+    A[2] = h2_mul_sub(__byte_perm(x1, 0x64646464u, 0x4240), s1);     // even dim, tokens 2j+8, 2j+9
+    A[3] = h2_mul_sub(__byte_perm(x1, 0x64646464u, 0x4341), s1);
+    mma16816(acc, A, pb0, pb1);
+}
+
+__device__ __forceinline__ void issue_rows(unsigned char *dst, const unsigned char *src_base, size_t row_stride,
+                                           int tok0, int t1, int lane) {
+    // chunk id = lane + 32 i over the tile's 16 x 17 chunks: neighbouring lanes copy
+    // neighbouring 16-byte pieces, so a sector is requested by one instruction
+    for (int c = lane; c < TILE * NCHUNK; c += 32) {
+        const int row = c / NCHUNK, ch = c - row * NCHUNK, tok = tok0 + row;
+        const bool ok = tok < t1;
+        cp_async16(smem_u32(dst + row * ROWB + ch * 16), src_base + (ok ? (size_t)tok * row_stride + ch * 16 : 0),
+                   ok ? 16 : 0);
+    }
+}
+
+template <int C>
+__device__ __forceinline__ void store_chunk(float *Ow, const float (&acc)[4], int r, int j) {
+    const int e = 8 * C + r;
+    if (e % 17 == 0 || e >= 136) return;          // this lane's rows of the m-tile were a scale, not values
+    const int dim = 32 * (e / 17) + 2 * (e % 17 - 1);
+    Ow[(2 * j) * HD + dim] = acc[0];
+    Ow[(2 * j + 1) * HD + dim] = acc[1];
+    Ow[(2 * j) * HD + dim + 1] = acc[2];
+    Ow[(2 * j + 1) * HD + dim + 1] = acc[3];
+}
+
+__global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float m_s[NWARP][8], l_s[NWARP][8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned char *wbase = smem + warp * WARP_BYTES;
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, nkv = a.kv.nkv;
+    const int G = a.nh / nkv;
+    const int64_t base = a.kv.seq_off[b];
+    const int cap = (int)(a.kv.seq_off[b + 1] - base);
+    const int len0 = a.kv_len[b];
+    if (len0 >= cap) return;
+    const int L = len0 + 1;
+    const int t0 = split * a.tokens_per_split, t1 = min(L, t0 + a.tokens_per_split);
+    float *part0 = a.part + (((size_t)b * a.nh + (size_t)kvh * G) * a.nsplit + split) * (HD + 2);
+    const size_t part_stride = (size_t)a.nsplit * (HD + 2);
+    if (t0 >= L) {
+        if (tid < G) { part0[tid * part_stride] = -INFINITY; part0[tid * part_stride + 1] = 0.0f; }
+        return;
+    }
+    const int r = lane >> 2, j = lane & 3;
+
+    // ---- query group -> B fragments in stream order: lane (head r, quarter j), k-step c
+    //      holds q at the dims of elements 8c+2j and 8c+2j+1 (zeros where the stream has a scale)
+    uint32_t qf[NCHUNK][2];
+    float rs_mine;
+    {
+        const float *q = a.q_prep + ((size_t)b * a.nh + (size_t)kvh * G + (r < G ? r : 0)) * HD;
+        float mx = 0.0f;
+        for (int i = j * 64; i < j * 64 + 64; i++) mx = fmaxf(mx, fabsf(q[i]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        int e = 0;
+        if (mx > 0.0f && mx < INFINITY) (void)frexpf(mx, &e);
+        const float down = (r < G) ? exp2f((float)-e) : 0.0f;
+#pragma unroll
+        for (int c = 0; c < NCHUNK; c++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int el = 8 * c + 2 * j + h;
+                const int bl = el / 17, idx = el - 17 * bl;
+                float lo = 0.0f, hi = 0.0f;
+                if (idx != 0) { const int d = 32 * bl + 2 * (idx - 1); lo = q[d] * down; hi = q[d + 1] * down; }
+                qf[c][h] = pack_h2(lo, hi);
+            }
+        rs_mine = (r < G) ? a.scale * exp2f((float)e) * LOG2E : 0.0f;
+    }
+    const float rsA = __shfl_sync(0xffffffffu, rs_mine, (2 * j) * 4);
+    const float rsB = __shfl_sync(0xffffffffu, rs_mine, (2 * j + 1) * 4);
+
+    const int ntiles = (t1 - t0 + TILE - 1) / TILE;
+    const size_t row_stride = (size_t)nkv * ROWB;
+    const unsigned char *Kbase = a.kv.K + ((size_t)base * nkv + kvh) * ROWB;
+    const unsigned char *Vbase = a.kv.V + ((size_t)base * nkv + kvh) * ROWB;
+
+    float o[NCHUNK][4];
+#pragma unroll
+    for (int i = 0; i < NCHUNK; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
+    // ldmatrix row address of this lane inside a staged tile: matrices 0,1 = chunk c (tokens 0-7, 8-15),
+    // matrices 2,3 = chunk c + 1
+    const uint32_t lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+
+    int it = warp;
+    if (it < ntiles) {
+        issue_rows(wbase, Kbase, row_stride, t0 + it * TILE, t1, lane);
+        issue_rows(wbase + RAW_TILE, Vbase, row_stride, t0 + it * TILE, t1, lane);
+    }
+    cp_async_commit();
+    for (int n = 0; it < ntiles; it += NWARP, n++) {
+        const int tok0 = t0 + it * TILE;
+        if (it + NWARP < ntiles) {
+            unsigned char *nxt = wbase + ((n + 1) & 1) * STAGE_BYTES;
+            issue_rows(nxt, Kbase, row_stride, tok0 + NWARP * TILE, t1, lane);
+            issue_rows(nxt + RAW_TILE, Vbase, row_stride, tok0 + NWARP * TILE, t1, lane);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const unsigned char *rawK = wbase + (n & 1) * STAGE_BYTES, *rawV = rawK + RAW_TILE;
+
+        // ---- S^T = K Q^T: 17 k-steps in two accumulator chains -----------------------------
+        uint32_t dk0[8], dk1[8];
+#pragma unroll
+        for (int bb = 0; bb < 8; bb++) {
+            const unsigned short u0 = *reinterpret_cast<const unsigned short *>(rawK + r * ROWB + 34 * bb);
+            const unsigned short u1 = *reinterpret_cast<const unsigned short *>(rawK + (r + 8) * ROWB + 34 * bb);
+            dk0[bb] = (uint32_t)u0 | ((uint32_t)u0 << 16);
+            dk1[bb] = (uint32_t)u1 | ((uint32_t)u1 << 16);
+        }
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint32_t k_addr = smem_u32(rawK) + lane_off;
+        {
+            uint32_t R[4];
+#define QK_PAIR(C)                                                \
+            ldsm_x4(R, k_addr + (C) * 16);                        \
+            qk_chunk<(C)>(R[0], R[1], dk0, dk1, j, qf, s);        \
+            qk_chunk<(C) + 1>(R[2], R[3], dk0, dk1, j, qf, s2);
+            QK_PAIR(0) QK_PAIR(2) QK_PAIR(4) QK_PAIR(6) QK_PAIR(8) QK_PAIR(10) QK_PAIR(12) QK_PAIR(14)
+#undef QK_PAIR
+            ldsm_x2(R, k_addr + 16 * 16);                         // lanes 0-15 address chunk 16
+            qk_chunk<16>(R[0], R[1], dk0, dk1, j, qf, s);
+        }
+
+        // ---- online softmax over tokens (rows r, r+8); columns = heads 2j, 2j+1 -------------
+        const bool ok0 = tok0 + r < t1, ok1 = tok0 + r + 8 < t1;
+        float x00 = ok0 ? (s[0] + s2[0]) * rsA : -INFINITY, x01 = ok0 ? (s[1] + s2[1]) * rsB : -INFINITY;
+        float x10 = ok1 ? (s[2] + s2[2]) * rsA : -INFINITY, x11 = ok1 ? (s[3] + s2[3]) * rsB : -INFINITY;
+        float cA = fmaxf(x00, x10), cB = fmaxf(x01, x11);
+#pragma unroll
+        for (int sft = 4; sft <= 16; sft <<= 1) {
+            cA = fmaxf(cA, __shfl_xor_sync(0xffffffffu, cA, sft));
+            cB = fmaxf(cB, __shfl_xor_sync(0xffffffffu, cB, sft));
+        }
+        const float nA = fmaxf(mA, cA), nB = fmaxf(mB, cB);       // finite: token tok0 is valid
+        const float corrA = exp2f(mA - nA), corrB = exp2f(mB - nB);
+        mA = nA; mB = nB;
+        x00 = exp2f(x00 - nA); x10 = exp2f(x10 - nA); x01 = exp2f(x01 - nB); x11 = exp2f(x11 - nB);
+        lA = lA * corrA + x00 + x10;
+        lB = lB * corrB + x01 + x11;
+        if (__any_sync(0xffffffffu, corrA != 1.0f || corrB != 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < NCHUNK; i++) { o[i][0] *= corrA; o[i][1] *= corrB; o[i][2] *= corrA; o[i][3] *= corrB; }
+        }
+        const uint32_t pb0 = movmatrix_trans(pack_h2(x00 * 256.0f, x01 * 256.0f));
+        const uint32_t pb1 = movmatrix_trans(pack_h2(x10 * 256.0f, x11 * 256.0f));
+
+        // ---- O^T += V^T P^T: one m-tile per chunk; block scales arrive with chunk 2b ---------
+        const uint32_t v_addr = smem_u32(rawV) + lane_off;
+        {
+            uint32_t R[4];
+            uint32_t lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;          // scale pairs of the current two blocks
+#define PV_PAIR(C)                                                                         \
+            ldsm_x4_trans(R, v_addr + (C) * 16);                                           \
+            lo0 = hi0; lo1 = hi1;                                                          \
+            hi0 = __shfl_sync(0xffffffffu, R[0], ((C) / 2) * 4 + j);   /* scale of block C/2 */ \
+            hi1 = __shfl_sync(0xffffffffu, R[1], ((C) / 2) * 4 + j);                        \
+            if ((C) == 0) { lo0 = hi0; lo1 = hi1; }                                         \
+            pv_chunk<(C)>(R[0], R[1], lo0, lo1, hi0, hi1, r, pb0, pb1, o[(C)]);             \
+            pv_chunk<(C) + 1>(R[2], R[3], hi0, hi1, hi0, hi1, r, pb0, pb1, o[(C) + 1]);
+            PV_PAIR(0) PV_PAIR(2) PV_PAIR(4) PV_PAIR(6) PV_PAIR(8) PV_PAIR(10) PV_PAIR(12) PV_PAIR(14)
+#undef PV_PAIR
+            ldsm_x2_trans(R, v_addr + 16 * 16);
+            pv_chunk<16>(R[0], R[1], hi0, hi1, hi0, hi1, r, pb0, pb1, o[16]);
+        }
+        __syncwarp();                                             // stage free for the copy after next
+    }
+    cp_async_wait<0>();
+    __syncwarp();
+
+    // ---- merge the four warps, one partial per (head, split) -----------------------------------
+#pragma unroll
+    for (int sft = 4; sft <= 16; sft <<= 1) {
+        lA += __shfl_xor_sync(0xffffffffu, lA, sft);
+        lB += __shfl_xor_sync(0xffffffffu, lB, sft);
+    }
+    float *Ow = reinterpret_cast<float *>(wbase);                 // [8 heads][256] f32 over this warp's stages
+    store_chunk<0>(Ow, o[0], r, j);   store_chunk<1>(Ow, o[1], r, j);   store_chunk<2>(Ow, o[2], r, j);
+    store_chunk<3>(Ow, o[3], r, j);   store_chunk<4>(Ow, o[4], r, j);   store_chunk<5>(Ow, o[5], r, j);
+    store_chunk<6>(Ow, o[6], r, j);   store_chunk<7>(Ow, o[7], r, j);   store_chunk<8>(Ow, o[8], r, j);
+    store_chunk<9>(Ow, o[9], r, j);   store_chunk<10>(Ow, o[10], r, j); store_chunk<11>(Ow, o[11], r, j);
+    store_chunk<12>(Ow, o[12], r, j); store_chunk<13>(Ow, o[13], r, j); store_chunk<14>(Ow, o[14], r, j);
+    store_chunk<15>(Ow, o[15], r, j); store_chunk<16>(Ow, o[16], r, j);
+    if (r == 0) {
+        m_s[warp][2 * j] = mA; m_s[warp][2 * j + 1] = mB;
+        l_s[warp][2 * j] = lA; l_s[warp][2 * j + 1] = lB;
+    }
+    __syncthreads();
+    for (int h = 0; h < G; h++) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARP; w++) if (l_s[w][h] > 0.0f) M = fmaxf(M, m_s[w][h]);
+        float ww[NWARP], Lt = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NWARP; w++) {
+            ww[w] = (l_s[w][h] > 0.0f) ? exp2f(m_s[w][h] - M) : 0.0f;
+            Lt += l_s[w][h] * ww[w];
+        }
+        float *part = part0 + h * part_stride;
+        if (tid == 0) { part[0] = M * LN2; part[1] = Lt; }
+        for (int d = tid; d < HD; d += 128) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int w = 0; w < NWARP; w++)
+                acc += ww[w] * reinterpret_cast<const float *>(smem + w * WARP_BYTES)[h * HD + d];
+            part[2 + d] = acc * (1.0f / 256.0f);
+        }
+    }
+}
+
+}  // namespace
+
+ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st) {
+    static bool configured = false;
+    if (!configured) {
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_raw, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               SMEM_BYTES), "gqa decode smem opt-in"));
+        configured = true;
+    }
+    dim3 grid(a.nsplit, a.kv.nkv, n_seq);
+    k_gqa_decode_q8_raw<<<grid, 128, SMEM_BYTES, st>>>(a);
+    return orn_check_launch("k_gqa_decode_q8_raw");
+}
