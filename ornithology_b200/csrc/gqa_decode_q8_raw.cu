@@ -126,15 +126,43 @@ __device__ __forceinline__ void pv_chunk(uint32_t raw0, uint32_t raw1, uint32_t 
     mma16816(acc, A, pb0, pb1);
 }
 
-__device__ __forceinline__ void issue_rows(unsigned char *dst, const unsigned char *src_base, size_t row_stride,
-                                           int tok0, int t1, int lane) {
-    // chunk id = lane + 32 i over the tile's 16 x 17 chunks: neighbouring lanes copy
-    // neighbouring 16-byte pieces, so a sector is requested by one instruction
-    for (int c = lane; c < TILE * NCHUNK; c += 32) {
-        const int row = c / NCHUNK, ch = c - row * NCHUNK, tok = tok0 + row;
-        const bool ok = tok < t1;
-        cp_async16(smem_u32(dst + row * ROWB + ch * 16), src_base + (ok ? (size_t)tok * row_stride + ch * 16 : 0),
-                   ok ? 16 : 0);
+// ---- bulk-copy staging: one 272-byte cp.async.bulk per row, completion on an mbarrier ------
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: gives up (returns false) instead of spinning for ever
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < (1 << 22); i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_row(uint32_t dst, const void *src, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(ROWB), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// Stage the K rows (lanes 0-15) and V rows (lanes 16-31) of one 16-token tile.  Rows past
+// the end of the split are not copied: the slot keeps earlier (finite) contents and the
+// token is masked in the softmax.
+__device__ __forceinline__ void issue_tile(unsigned char *stage, uint32_t bar, const unsigned char *Kbase,
+                                           const unsigned char *Vbase, size_t row_stride, int tok0, int t1, int lane) {
+    const int valid = min(TILE, t1 - tok0);
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(2 * valid * ROWB));
+    __syncwarp();
+    const int row = lane & 15;
+    if (row < valid) {
+        const unsigned char *src = (lane < 16 ? Kbase : Vbase) + (size_t)(tok0 + row) * row_stride;
+        bulk_copy_row(smem_u32(stage + (lane >> 4) * RAW_TILE + row * ROWB), src, bar);
     }
 }
 
@@ -152,10 +180,15 @@ __device__ __forceinline__ void store_chunk(float *Ow, const float (&acc)[4], in
 __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float m_s[NWARP][8], l_s[NWARP][8];
+    __shared__ __align__(8) unsigned long long bars[NWARP][2];
+    __shared__ int pipe_failed;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     unsigned char *wbase = smem + warp * WARP_BYTES;
+    if (tid == 0) pipe_failed = 0;
 
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, nkv = a.kv.nkv;
+    // KV head on the fastest grid axis: the CTAs that read the two interleaved halves of the
+    // same token rows are launched side by side and share DRAM pages while they are open
+    const int kvh = blockIdx.x, split = blockIdx.y, b = blockIdx.z, nkv = a.kv.nkv;
     const int G = a.nh / nkv;
     const int64_t base = a.kv.seq_off[b];
     const int cap = (int)(a.kv.seq_off[b + 1] - base);
@@ -212,24 +245,46 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
     // matrices 2,3 = chunk c + 1
     const uint32_t lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
 
-    int it = warp;
-    if (it < ntiles) {
-        issue_rows(wbase, Kbase, row_stride, t0 + it * TILE, t1, lane);
-        issue_rows(wbase + RAW_TILE, Vbase, row_stride, t0 + it * TILE, t1, lane);
-    }
-    cp_async_commit();
-    for (int n = 0; it < ntiles; it += NWARP, n++) {
-        const int tok0 = t0 + it * TILE;
-        if (it + NWARP < ntiles) {
-            unsigned char *nxt = wbase + ((n + 1) & 1) * STAGE_BYTES;
-            issue_rows(nxt, Kbase, row_stride, tok0 + NWARP * TILE, t1, lane);
-            issue_rows(nxt + RAW_TILE, Vbase, row_stride, tok0 + NWARP * TILE, t1, lane);
+    // ---- per-warp two-stage ring: zero it once (skipped tail rows must stay finite), one
+    //      mbarrier per stage
+    {
+        uint4 *z = reinterpret_cast<uint4 *>(wbase);
+        for (int i = lane; i < WARP_BYTES / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (lane == 0) {
+            mbar_init(smem_u32(&bars[warp][0]), 1);
+            mbar_init(smem_u32(&bars[warp][1]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         }
-        cp_async_commit();
-        cp_async_wait<1>();
+        fence_proxy_async();                                      // generic-proxy zeros before async-proxy copies
         __syncwarp();
+    }
+    const uint32_t bar0 = smem_u32(&bars[warp][0]), bar1 = smem_u32(&bars[warp][1]);
+    bool pipe_ok = true;
+
+    int it = warp;
+    if (it < ntiles) issue_tile(wbase, bar0, Kbase, Vbase, row_stride, t0 + it * TILE, t1, lane);
+    for (uint32_t n = 0; it < ntiles; it += NWARP, n++) {
+        const int tok0 = t0 + it * TILE;
+        const bool more = it + NWARP < ntiles;
+        if (more) {
+            // the other stage was last read one iteration ago, which ended with __syncwarp()
+            fence_proxy_async();
+            issue_tile(wbase + ((n + 1) & 1) * STAGE_BYTES, ((n + 1) & 1) ? bar1 : bar0, Kbase, Vbase, row_stride,
+                       tok0 + NWARP * TILE, t1, lane);
+        }
+        if (!mbar_wait((n & 1) ? bar1 : bar0, (n >> 1) & 1)) {
+            // copies never landed: give the other stage a bounded chance to drain, then report
+            if (more) (void)mbar_wait(((n + 1) & 1) ? bar1 : bar0, ((n + 1) >> 1) & 1);
+            pipe_ok = false;
+            break;
+        }
         const unsigned char *rawK = wbase + (n & 1) * STAGE_BYTES, *rawV = rawK + RAW_TILE;
 
+#ifdef ORN_PROBE_COPY_ONLY
+        lA += *reinterpret_cast<const float *>(rawK + lane * 4) + *reinterpret_cast<const float *>(rawV + lane * 4);
+        __syncwarp();
+        continue;
+#endif
         // ---- S^T = K Q^T: 17 k-steps in two accumulator chains -----------------------------
         uint32_t dk0[8], dk1[8];
 #pragma unroll
@@ -296,7 +351,7 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
         }
         __syncwarp();                                             // stage free for the copy after next
     }
-    cp_async_wait<0>();
+    if (!pipe_ok && lane == 0) pipe_failed = 1;
     __syncwarp();
 
     // ---- merge the four warps, one partial per (head, split) -----------------------------------
@@ -328,13 +383,15 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
             Lt += l_s[w][h] * ww[w];
         }
         float *part = part0 + h * part_stride;
-        if (tid == 0) { part[0] = M * LN2; part[1] = Lt; }
+        // a staging copy that never completed poisons the partial (the result becomes NaN, not silently wrong)
+        const float poison = pipe_failed ? NAN : 0.0f;
+        if (tid == 0) { part[0] = M * LN2; part[1] = pipe_failed ? 1.0f : Lt; }
         for (int d = tid; d < HD; d += 128) {
             float acc = 0.0f;
 #pragma unroll
             for (int w = 0; w < NWARP; w++)
                 acc += ww[w] * reinterpret_cast<const float *>(smem + w * WARP_BYTES)[h * HD + d];
-            part[2 + d] = acc * (1.0f / 256.0f);
+            part[2 + d] = acc * (1.0f / 256.0f) + poison;
         }
     }
 }
@@ -348,7 +405,7 @@ ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStrea
                                                SMEM_BYTES), "gqa decode smem opt-in"));
         configured = true;
     }
-    dim3 grid(a.nsplit, a.kv.nkv, n_seq);
+    dim3 grid(a.kv.nkv, a.nsplit, n_seq);
     k_gqa_decode_q8_raw<<<grid, 128, SMEM_BYTES, st>>>(a);
     return orn_check_launch("k_gqa_decode_q8_raw");
 }
