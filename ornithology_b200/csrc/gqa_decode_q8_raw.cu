@@ -211,7 +211,15 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
     {
         const float *q = a.q_prep + ((size_t)b * a.nh + (size_t)kvh * G + (r < G ? r : 0)) * HD;
         float mx = 0.0f;
-        for (int i = j * 64; i < j * 64 + 64; i++) mx = fmaxf(mx, fabsf(q[i]));
+        {   // 16 independent 128-bit loads: the prologue is per CTA, keep it off the latency path
+            const float4 *q4 = reinterpret_cast<const float4 *>(q + j * 64);
+            float4 t[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) t[i] = q4[i];
+#pragma unroll
+            for (int i = 0; i < 16; i++)
+                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(t[i].x), fabsf(t[i].y)), fmaxf(fabsf(t[i].z), fabsf(t[i].w))));
+        }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         int e = 0;
@@ -223,9 +231,11 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
             for (int h = 0; h < 2; h++) {
                 const int el = 8 * c + 2 * j + h;
                 const int bl = el / 17, idx = el - 17 * bl;
-                float lo = 0.0f, hi = 0.0f;
-                if (idx != 0) { const int d = 32 * bl + 2 * (idx - 1); lo = q[d] * down; hi = q[d + 1] * down; }
-                qf[c][h] = pack_h2(lo, hi);
+                // scale slots read dims 0,1 (any valid address) and are zeroed by the multiplier
+                const int d = (idx != 0) ? 32 * bl + 2 * (idx - 1) : 0;
+                const float2 v = *reinterpret_cast<const float2 *>(q + d);
+                const float mul = (idx != 0) ? down : 0.0f;
+                qf[c][h] = pack_h2(v.x * mul, v.y * mul);
             }
         rs_mine = (r < G) ? a.scale * exp2f((float)e) * LOG2E : 0.0f;
     }
