@@ -438,7 +438,12 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     int nsplit_used;
     if (gqa_decode_q8_mma_supported(d.kv, nh) && !force_generic_decode()) {
         // tensor-core path: larger splits (fewer partials); never more splits than the scratch was sized for
-        const int tps_mma = max_len > 8192 ? 1024 : (max_len > 1024 ? 512 : 256);
+        int tps_mma = max_len > 8192 ? 1024 : (max_len > 1024 ? 512 : 256);
+        {   // ORNITH_CUDA_DECODE_SPLIT=<tokens> overrides the split length for long contexts (tuning knob)
+            static int forced = -1;
+            if (forced < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_SPLIT"); forced = e ? atoi(e) : 0; }
+            if (forced >= 512 && max_len > 1024) tps_mma = forced / 16 * 16;
+        }
         d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
         ORN_TRY(launch_gqa_decode_q8_mma(d, B, st));
     } else {

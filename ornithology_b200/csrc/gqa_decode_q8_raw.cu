@@ -36,9 +36,9 @@ constexpr int TILE = 16;
 constexpr int NWARP = 4;
 constexpr int NCHUNK = 17;                         // 16-byte chunks per row
 constexpr int RAW_TILE = TILE * ROWB;              // 4352
-constexpr int STAGE_BYTES = 2 * RAW_TILE;          // K rows + V rows
-constexpr int WARP_BYTES = 2 * STAGE_BYTES;        // two stages = 17408
-constexpr int SMEM_BYTES = NWARP * WARP_BYTES;     // 69632
+constexpr int QS_BYTES = NCHUNK * 32 * 8;          // query B fragments, [k-step][lane] x 2 words = 4352
+constexpr int WARP_BYTES = 2 * RAW_TILE;           // one slot of K rows + one of V rows = 8704
+constexpr int SMEM_BYTES = QS_BYTES + NWARP * WARP_BYTES;     // 39168: four CTAs per SM
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -91,7 +91,7 @@ __host__ __device__ constexpr int elem_dim(int e) { return (e % 17 == 0) ? -1 : 
 // 8C+2j and 8C+2j+1); dk0 / dk1: that row's block scales as f16 pairs.
 template <int C>
 __device__ __forceinline__ void qk_chunk(uint32_t raw0, uint32_t raw1, const uint32_t (&dk0)[8], const uint32_t (&dk1)[8],
-                                         int j, const uint32_t (&qf)[NCHUNK][2], float (&acc)[4]) {
+                                         int j, const uint2 *q_frag, float (&acc)[4]) {
     constexpr int BLO = elem_block(8 * C), BHI = elem_block(8 * C + 7) > 7 ? 7 : elem_block(8 * C + 7);
     // block of element 8C+2j+h: BHI once the element index reaches 17*BHI
     const bool hi0 = (BHI != BLO) && (8 * C + 2 * j >= 17 * BHI);
@@ -104,7 +104,8 @@ __device__ __forceinline__ void qk_chunk(uint32_t raw0, uint32_t raw1, const uin
     A[1] = h2_mul_sub(__byte_perm(x1, 0x64646464u, 0x4140), s10);    // row r+8
     A[2] = h2_mul_sub(__byte_perm(x0, 0x64646464u, 0x4342), s01);    // row r,   element 8C+2j+1 -> k = 2j+8, 2j+9
     A[3] = h2_mul_sub(__byte_perm(x1, 0x64646464u, 0x4342), s11);
-    mma16816(acc, A, qf[C][0], qf[C][1]);
+    const uint2 qv = q_frag[C * 32];                                 // this lane's B fragment of k-step C
+    mma16816(acc, A, qv.x, qv.y);
 }
 
 // ---- one m-tile of O^T += V^T P^T from chunk C of the staged V rows ------------------------
@@ -151,19 +152,15 @@ __device__ __forceinline__ void bulk_copy_row(uint32_t dst, const void *src, uin
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-// Stage the K rows (lanes 0-15) and V rows (lanes 16-31) of one 16-token tile.  Rows past
-// the end of the split are not copied: the slot keeps earlier (finite) contents and the
-// token is masked in the softmax.
-__device__ __forceinline__ void issue_tile(unsigned char *stage, uint32_t bar, const unsigned char *Kbase,
-                                           const unsigned char *Vbase, size_t row_stride, int tok0, int t1, int lane) {
+// Stage the 16 rows of one tile of K (or V): lanes 0-15 copy one row each.  Rows past the
+// end of the split are not copied: the slot keeps earlier (finite) contents and the token
+// is masked in the softmax.
+__device__ __forceinline__ void issue_rows16(unsigned char *slot, uint32_t bar, const unsigned char *src_base,
+                                             size_t row_stride, int tok0, int t1, int lane) {
     const int valid = min(TILE, t1 - tok0);
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(2 * valid * ROWB));
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(valid * ROWB));
     __syncwarp();
-    const int row = lane & 15;
-    if (row < valid) {
-        const unsigned char *src = (lane < 16 ? Kbase : Vbase) + (size_t)(tok0 + row) * row_stride;
-        bulk_copy_row(smem_u32(stage + (lane >> 4) * RAW_TILE + row * ROWB), src, bar);
-    }
+    if (lane < valid) bulk_copy_row(smem_u32(slot + lane * ROWB), src_base + (size_t)(tok0 + lane) * row_stride, bar);
 }
 
 template <int C>
@@ -177,13 +174,14 @@ __device__ __forceinline__ void store_chunk(float *Ow, const float (&acc)[4], in
     Ow[(2 * j + 1) * HD + dim + 1] = acc[3];
 }
 
-__global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
+__global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ float m_s[NWARP][8], l_s[NWARP][8];
     __shared__ __align__(8) unsigned long long bars[NWARP][2];
     __shared__ int pipe_failed;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    unsigned char *wbase = smem + warp * WARP_BYTES;
+    unsigned char *wbase = smem + QS_BYTES + warp * WARP_BYTES;
+    uint2 *Q_s = reinterpret_cast<uint2 *>(smem);               // [k-step][lane]
     if (tid == 0) pipe_failed = 0;
 
     // KV head on the fastest grid axis: the CTAs that read the two interleaved halves of the
@@ -206,7 +204,6 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
 
     // ---- query group -> B fragments in stream order: lane (head r, quarter j), k-step c
     //      holds q at the dims of elements 8c+2j and 8c+2j+1 (zeros where the stream has a scale)
-    uint32_t qf[NCHUNK][2];
     float rs_mine;
     {
         const float *q = a.q_prep + ((size_t)b * a.nh + (size_t)kvh * G + (r < G ? r : 0)) * HD;
@@ -225,8 +222,8 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
         int e = 0;
         if (mx > 0.0f && mx < INFINITY) (void)frexpf(mx, &e);
         const float down = (r < G) ? exp2f((float)-e) : 0.0f;
-#pragma unroll
-        for (int c = 0; c < NCHUNK; c++)
+        for (int c = warp; c < NCHUNK; c += NWARP) {      // the four warps share the work; identical per warp otherwise
+            uint32_t pk[2];
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const int el = 8 * c + 2 * j + h;
@@ -235,8 +232,10 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
                 const int d = (idx != 0) ? 32 * bl + 2 * (idx - 1) : 0;
                 const float2 v = *reinterpret_cast<const float2 *>(q + d);
                 const float mul = (idx != 0) ? down : 0.0f;
-                qf[c][h] = pack_h2(v.x * mul, v.y * mul);
+                pk[h] = pack_h2(v.x * mul, v.y * mul);
             }
+            Q_s[c * 32 + lane] = make_uint2(pk[0], pk[1]);
+        }
         rs_mine = (r < G) ? a.scale * exp2f((float)e) * LOG2E : 0.0f;
     }
     const float rsA = __shfl_sync(0xffffffffu, rs_mine, (2 * j) * 4);
@@ -255,8 +254,10 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
     // matrices 2,3 = chunk c + 1
     const uint32_t lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
 
-    // ---- per-warp two-stage ring: zero it once (skipped tail rows must stay finite), one
-    //      mbarrier per stage
+    // ---- per-warp staging slots (K rows, V rows): zero them once (skipped tail rows must stay
+    //      finite), one mbarrier each.  K of the next tile is requested as soon as the score
+    //      loop is done with the slot, V right after the value loop.
+    unsigned char *rawK = wbase, *rawV = wbase + RAW_TILE;
     {
         uint4 *z = reinterpret_cast<uint4 *>(wbase);
         for (int i = lane; i < WARP_BYTES / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -266,35 +267,26 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
             asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         }
         fence_proxy_async();                                      // generic-proxy zeros before async-proxy copies
-        __syncwarp();
     }
-    const uint32_t bar0 = smem_u32(&bars[warp][0]), bar1 = smem_u32(&bars[warp][1]);
+    __syncthreads();                                              // also publishes Q_s
+    const uint32_t barK = smem_u32(&bars[warp][0]), barV = smem_u32(&bars[warp][1]);
+    const uint2 *q_frag = Q_s + lane;
     bool pipe_ok = true;
 
     int it = warp;
-    if (it < ntiles) issue_tile(wbase, bar0, Kbase, Vbase, row_stride, t0 + it * TILE, t1, lane);
+    if (it < ntiles) {
+        issue_rows16(rawK, barK, Kbase, row_stride, t0 + it * TILE, t1, lane);
+        issue_rows16(rawV, barV, Vbase, row_stride, t0 + it * TILE, t1, lane);
+    }
     for (uint32_t n = 0; it < ntiles; it += NWARP, n++) {
         const int tok0 = t0 + it * TILE;
         const bool more = it + NWARP < ntiles;
-        if (more) {
-            // the other stage was last read one iteration ago, which ended with __syncwarp()
-            fence_proxy_async();
-            issue_tile(wbase + ((n + 1) & 1) * STAGE_BYTES, ((n + 1) & 1) ? bar1 : bar0, Kbase, Vbase, row_stride,
-                       tok0 + NWARP * TILE, t1, lane);
-        }
-        if (!mbar_wait((n & 1) ? bar1 : bar0, (n >> 1) & 1)) {
-            // copies never landed: give the other stage a bounded chance to drain, then report
-            if (more) (void)mbar_wait(((n + 1) & 1) ? bar1 : bar0, ((n + 1) >> 1) & 1);
+        if (!mbar_wait(barK, n & 1)) {
+            (void)mbar_wait(barV, n & 1);                         // bounded chance for the other copy to drain
             pipe_ok = false;
             break;
         }
-        const unsigned char *rawK = wbase + (n & 1) * STAGE_BYTES, *rawV = rawK + RAW_TILE;
 
-#ifdef ORN_PROBE_COPY_ONLY
-        lA += *reinterpret_cast<const float *>(rawK + lane * 4) + *reinterpret_cast<const float *>(rawV + lane * 4);
-        __syncwarp();
-        continue;
-#endif
         // ---- S^T = K Q^T: 17 k-steps in two accumulator chains -----------------------------
         uint32_t dk0[8], dk1[8];
 #pragma unroll
@@ -310,12 +302,17 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
             uint32_t R[4];
 #define QK_PAIR(C)                                                \
             ldsm_x4(R, k_addr + (C) * 16);                        \
-            qk_chunk<(C)>(R[0], R[1], dk0, dk1, j, qf, s);        \
-            qk_chunk<(C) + 1>(R[2], R[3], dk0, dk1, j, qf, s2);
+            qk_chunk<(C)>(R[0], R[1], dk0, dk1, j, q_frag, s);    \
+            qk_chunk<(C) + 1>(R[2], R[3], dk0, dk1, j, q_frag, s2);
             QK_PAIR(0) QK_PAIR(2) QK_PAIR(4) QK_PAIR(6) QK_PAIR(8) QK_PAIR(10) QK_PAIR(12) QK_PAIR(14)
 #undef QK_PAIR
             ldsm_x2(R, k_addr + 16 * 16);                         // lanes 0-15 address chunk 16
-            qk_chunk<16>(R[0], R[1], dk0, dk1, j, qf, s);
+            qk_chunk<16>(R[0], R[1], dk0, dk1, j, q_frag, s);
+        }
+        __syncwarp();                                             // every lane is done with the K slot
+        if (more) {
+            fence_proxy_async();
+            issue_rows16(rawK, barK, Kbase, row_stride, tok0 + NWARP * TILE, t1, lane);
         }
 
         // ---- online softmax over tokens (rows r, r+8); columns = heads 2j, 2j+1 -------------
@@ -342,6 +339,11 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
         const uint32_t pb1 = movmatrix_trans(pack_h2(x10 * 256.0f, x11 * 256.0f));
 
         // ---- O^T += V^T P^T: one m-tile per chunk; block scales arrive with chunk 2b ---------
+        if (!mbar_wait(barV, n & 1)) {
+            if (more) (void)mbar_wait(barK, (n + 1) & 1);
+            pipe_ok = false;
+            break;
+        }
         const uint32_t v_addr = smem_u32(rawV) + lane_off;
         {
             uint32_t R[4];
@@ -359,7 +361,11 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
             ldsm_x2_trans(R, v_addr + 16 * 16);
             pv_chunk<16>(R[0], R[1], hi0, hi1, hi0, hi1, r, pb0, pb1, o[16]);
         }
-        __syncwarp();                                             // stage free for the copy after next
+        __syncwarp();                                             // every lane is done with the V slot
+        if (more) {
+            fence_proxy_async();
+            issue_rows16(rawV, barV, Vbase, row_stride, tok0 + NWARP * TILE, t1, lane);
+        }
     }
     if (!pipe_ok && lane == 0) pipe_failed = 1;
     __syncwarp();
@@ -370,7 +376,7 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
         lA += __shfl_xor_sync(0xffffffffu, lA, sft);
         lB += __shfl_xor_sync(0xffffffffu, lB, sft);
     }
-    float *Ow = reinterpret_cast<float *>(wbase);                 // [8 heads][256] f32 over this warp's stages
+    float *Ow = reinterpret_cast<float *>(wbase);                 // [8 heads][256] f32 over this warp's slots
     store_chunk<0>(Ow, o[0], r, j);   store_chunk<1>(Ow, o[1], r, j);   store_chunk<2>(Ow, o[2], r, j);
     store_chunk<3>(Ow, o[3], r, j);   store_chunk<4>(Ow, o[4], r, j);   store_chunk<5>(Ow, o[5], r, j);
     store_chunk<6>(Ow, o[6], r, j);   store_chunk<7>(Ow, o[7], r, j);   store_chunk<8>(Ow, o[8], r, j);
@@ -400,7 +406,7 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_q8_raw(DecodeArgs a) {
             float acc = 0.0f;
 #pragma unroll
             for (int w = 0; w < NWARP; w++)
-                acc += ww[w] * reinterpret_cast<const float *>(smem + w * WARP_BYTES)[h * HD + d];
+                acc += ww[w] * reinterpret_cast<const float *>(smem + QS_BYTES + w * WARP_BYTES)[h * HD + d];
             part[2 + d] = acc * (1.0f / 256.0f) + poison;
         }
     }
