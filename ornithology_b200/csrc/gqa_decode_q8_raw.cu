@@ -136,13 +136,15 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    // the suspend-time hint lets the hardware park the thread (no issue slots burnt on polling)
+    // until the phase completes or ~10 us pass
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(10000u) : "memory");
     return ok != 0;
 }
-// bounded wait: gives up (returns false) instead of spinning for ever
+// bounded wait: gives up (returns false) after ~1 s instead of waiting for ever
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < (1 << 22); i++)
+    for (int i = 0; i < (1 << 18); i++)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
