@@ -53,12 +53,43 @@ __device__ __forceinline__ float conv_channel(const LinArgs &a, const float *rin
 // =============================================================================
 //
 // The 64 KiB state of the head is read once into registers (16 x float4 per
-// thread, all loads issued before the prologue's arithmetic), updated and
-// written back once.  Rows are split 16 per warp; within a warp 8 lanes share a
-// row (4 x float4 each), so the two dot products per row reduce over 3 shuffles.
+// thread) and written back once.  Every load the step needs is issued before the
+// first dependent instruction: the state, and — independent of the token index —
+// all four ring slots, the input and the taps of each conv channel, the gate
+// inputs and the z / norm weights of the epilogue, so the step pays one memory
+// latency.  Rows are split 16 per warp; within a warp 8 lanes share a row
+// (4 x float4 each), so the two dot products per row reduce over 3 shuffles.
+// Three block barriers in all.
+
+__device__ __forceinline__ float4 lds128(const float *p) {        // not hoisted: keeps k/q out of registers
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return v;
+}
+
+// conv of one channel from its four ring slots (slot of token t' is t' & 3); taps are the
+// tokens t-3, t-2, t-1 = slots sb, sb+1, sb+2 with sb = (t + 1) & 3.  Same operation order
+// and rounding as the engine (reference: src/ornith_attn.c:373-381), then SiLU.
+__device__ __forceinline__ float conv4_silu(const float (&h)[4], float xin, float4 w, float bias, int sb) {
+    float t0, t1, t2;
+    switch (sb) {                                                  // uniform over the CTA
+    case 0:  t0 = h[0]; t1 = h[1]; t2 = h[2]; break;
+    case 1:  t0 = h[1]; t1 = h[2]; t2 = h[3]; break;
+    case 2:  t0 = h[2]; t1 = h[3]; t2 = h[0]; break;
+    default: t0 = h[3]; t1 = h[0]; t2 = h[1]; break;
+    }
+    float acc = bias;
+    acc = __fadd_rn(acc, __fmul_rn(w.x, t0));
+    acc = __fadd_rn(acc, __fmul_rn(w.y, t1));
+    acc = __fadd_rn(acc, __fmul_rn(w.z, t2));
+    acc = __fadd_rn(acc, __fmul_rn(w.w, xin));
+    return silu_f(acc);
+}
+
 template <typename ACT>
 __global__ void __launch_bounds__(256, 2) k_linear_decode_128(LinArgs a) {
-    __shared__ __align__(16) float q_s[128], k_s[128], v_s[128], o_s[128];
+    __shared__ __align__(16) float q_s[128], k_s[128], v_s[128];
     __shared__ double redd[32];
     __shared__ float gates[2];
     const int hv = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -73,48 +104,83 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_128(LinArgs a) {
         for (int j = 0; j < 4; j++)
             s[i][j] = __ldcs(reinterpret_cast<const float4 *>(S + (size_t)(w * 16 + i * 4 + sr) * 128) + cc + j * 8);
 
-    // conv + SiLU for this head's 128 q, 128 k and 128 v channels
-    const int t = a.pos[b];
+    // ---- all remaining loads, none of which depends on another ------------------------------
     float *ring = a.conv + (size_t)b * a.conv_stride;
     const ACT *x = (const ACT *)a.qkv + (size_t)b * Cc;
-    float yq = 0.0f, yk = 0.0f;
-    if (tid < 128) {
-        const bool own = owns_key_head(a, hv);
-        yq = conv_channel(a, ring, ring, x, Cc, t, kh * 128 + tid, own);
-        yk = conv_channel(a, ring, ring, x, Cc, t, qd + kh * 128 + tid, own);
-    } else {
-        v_s[tid - 128] = conv_channel(a, ring, ring, x, Cc, t, 2 * qd + hv * 128 + (tid - 128), true);
+    const bool qk_thread = tid < 128;
+    const int c0 = qk_thread ? kh * 128 + tid : 2 * qd + hv * 128 + (tid - 128);      // q channel | v channel
+    const int c1 = qd + kh * 128 + (tid & 127);                                       // k channel (qk threads)
+    float h0[4], h1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int sl = 0; sl < 4; sl++) h0[sl] = ring[(size_t)sl * Cc + c0];
+    const float x0 = act_ld(x, c0);
+    const float4 w0 = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)c0 * 4);
+    const float bias0 = a.conv_b ? a.conv_b[c0] : 0.0f;
+    float x1 = 0.0f, bias1 = 0.0f;
+    float4 w1 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (qk_thread) {
+#pragma unroll
+        for (int sl = 0; sl < 4; sl++) h1[sl] = ring[(size_t)sl * Cc + c1];
+        x1 = act_ld(x, c1);
+        w1 = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)c1 * 4);
+        bias1 = a.conv_b ? a.conv_b[c1] : 0.0f;
     }
-    // q/k L2-norm (reference: src/ornith_tensor.c:155-160, eps inside the sqrt)
-    const double ssq = block_sum((double)yq * (double)yq, redd);
-    const double ssk = block_sum((double)yk * (double)yk, redd);
-    if (tid < 128) {
-        q_s[tid] = yq * (float)(1.0 / sqrt(ssq + (double)1e-6f));
-        k_s[tid] = yk * (float)(1.0 / sqrt(ssk + (double)1e-6f));
+    const int t = a.pos[b];
+    const float ain = act_ld((const ACT *)a.a, (size_t)b * a.nv + hv);
+    const float bin = act_ld((const ACT *)a.b, (size_t)b * a.nv + hv);
+    const float acoef = a.a_coef[hv], dtb = a.dt_bias[hv];
+    // epilogue operands of the rows whose result this lane will hold (lanes with cc == 0)
+    const size_t out_base = (size_t)b * vd + (size_t)hv * 128;
+    float zin[4], nw[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = w * 16 + i * 4 + sr;
+        zin[i] = (cc == 0) ? act_ld((const ACT *)a.z, out_base + r) : 0.0f;
+        nw[i] = (cc == 0) ? a.norm_w[r] : 0.0f;
+    }
+
+    // ---- conv + SiLU, q/k L2-norm (reference: src/ornith_tensor.c:155-160), gates ------------
+    const int sb = (t + 1) & 3;
+    const bool own = owns_key_head(a, hv);
+    const float y0 = conv4_silu(h0, x0, w0, bias0, sb);
+    float y1 = 0.0f;
+    if (qk_thread) {
+        y1 = conv4_silu(h1, x1, w1, bias1, sb);
+        if (own) { ring[(size_t)(t & 3) * Cc + c0] = x0; ring[(size_t)(t & 3) * Cc + c1] = x1; }
+    } else {
+        ring[(size_t)(t & 3) * Cc + c0] = x0;
+        v_s[tid - 128] = y0;
+    }
+    {
+        double sq = qk_thread ? (double)y0 * (double)y0 : 0.0, sk = (double)y1 * (double)y1;
+        sq = warp_sum(sq); sk = warp_sum(sk);
+        if (lane == 0) { redd[w] = sq; redd[8 + w] = sk; }
+    }
+    __syncthreads();
+    if (qk_thread) {
+        const double ssq = redd[0] + redd[1] + redd[2] + redd[3], ssk = redd[8] + redd[9] + redd[10] + redd[11];
+        q_s[tid] = y0 * (float)(1.0 / sqrt(ssq + (double)1e-6f));
+        k_s[tid] = y1 * (float)(1.0 / sqrt(ssk + (double)1e-6f));
     }
     if (tid == 0) {   // decay and write gates (reference: src/ornith_rforward.c:282-284, :493-496)
-        const float ain = act_ld((const ACT *)a.a, (size_t)b * a.nv + hv);
-        const float bin = act_ld((const ACT *)a.b, (size_t)b * a.nv + hv);
-        gates[0] = expf(a.a_coef[hv] * softplus_f(ain + a.dt_bias[hv]));
+        gates[0] = expf(acoef * softplus_f(ain + dtb));
         gates[1] = sigmoid_f(bin);
     }
     __syncthreads();
 
+    // ---- S <- alpha S; u = beta (v - S k); S += u k^T; o = S q  (reference: src/ornith_attn.c:203-212)
     const float alpha = gates[0], beta = gates[1];
-    float4 kr[4], qr[4];
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        kr[j] = reinterpret_cast<const float4 *>(k_s)[cc + j * 8];
-        qr[j] = reinterpret_cast<const float4 *>(q_s)[cc + j * 8];
-    }
+    float orow[4];
+    double ss = 0.0;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int r = w * 16 + i * 4 + sr;
         float recall = 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
+            const float4 kr = lds128(k_s + (cc + j * 8) * 4);
             s[i][j].x *= alpha; s[i][j].y *= alpha; s[i][j].z *= alpha; s[i][j].w *= alpha;
-            recall += s[i][j].x * kr[j].x + s[i][j].y * kr[j].y + s[i][j].z * kr[j].z + s[i][j].w * kr[j].w;
+            recall += s[i][j].x * kr.x + s[i][j].y * kr.y + s[i][j].z * kr.z + s[i][j].w * kr.w;
         }
         recall += __shfl_xor_sync(0xffffffffu, recall, 1);
         recall += __shfl_xor_sync(0xffffffffu, recall, 2);
@@ -123,29 +189,35 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_128(LinArgs a) {
         float read = 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            s[i][j].x += u * kr[j].x; s[i][j].y += u * kr[j].y; s[i][j].z += u * kr[j].z; s[i][j].w += u * kr[j].w;
-            read += s[i][j].x * qr[j].x + s[i][j].y * qr[j].y + s[i][j].z * qr[j].z + s[i][j].w * qr[j].w;
+            const float4 kr = lds128(k_s + (cc + j * 8) * 4);
+            const float4 qr = lds128(q_s + (cc + j * 8) * 4);
+            s[i][j].x += u * kr.x; s[i][j].y += u * kr.y; s[i][j].z += u * kr.z; s[i][j].w += u * kr.w;
+            read += s[i][j].x * qr.x + s[i][j].y * qr.y + s[i][j].z * qr.z + s[i][j].w * qr.w;
+            __stcs(reinterpret_cast<float4 *>(S + (size_t)r * 128) + cc + j * 8, s[i][j]);
         }
         read += __shfl_xor_sync(0xffffffffu, read, 1);
         read += __shfl_xor_sync(0xffffffffu, read, 2);
         read += __shfl_xor_sync(0xffffffffu, read, 4);
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-            __stcs(reinterpret_cast<float4 *>(S + (size_t)r * 128) + cc + j * 8, s[i][j]);
-        if (cc == 0) o_s[r] = read;
+        orow[i] = read * a.out_scale;                      // scaled head output of row r (all 8 lanes agree)
+        if (cc == 0) ss += (double)orow[i] * (double)orow[i];
     }
-    __syncthreads();
 
-    // scale, per-head RMSNorm, SiLU(z) gate (reference: src/ornith_rforward.c:305-314)
-    float o = 0.0f;
-    if (tid < 128) o = o_s[tid] * a.out_scale;
-    const double ss = block_sum((double)o * (double)o, redd);
-    if (tid < 128) {
-        const float inv = (float)(1.0 / sqrt(ss / 128.0 + (double)a.eps));
-        const size_t idx = (size_t)b * vd + (size_t)hv * 128 + tid;
-        float y = o * inv * a.norm_w[tid];
-        y *= silu_f(act_ld((const ACT *)a.z, idx));
-        act_st((ACT *)a.out, idx, y);
+    // ---- per-head RMSNorm and SiLU(z) gate (reference: src/ornith_rforward.c:305-314) ---------
+    ss = warp_sum(ss);
+    if (lane == 0) redd[16 + w] = ss;
+    __syncthreads();
+    if (cc == 0) {
+        double tot = 0.0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) tot += redd[16 + i];
+        const float inv = (float)(1.0 / sqrt(tot / 128.0 + (double)a.eps));
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = w * 16 + i * 4 + sr;
+            float y = orow[i] * inv * nw[i];
+            y *= silu_f(zin[i]);
+            act_st((ACT *)a.out, out_base + r, y);
+        }
     }
 }
 
@@ -642,7 +714,7 @@ ornith_status ornith_cuda_linear_attn_step(const ornith_cuda_linear_layer *l, co
     cudaStream_t s = as_stream(stream);
     const bool bf = act_dtype == ORNITH_ACT_BF16;
     if (l->dk == 128 && l->dv == 128 && l->conv_k == 4 && (st->S_seq_stride % 4) == 0 &&
-        ((uintptr_t)st->S % 16) == 0) {
+        ((uintptr_t)st->S % 16) == 0 && ((uintptr_t)l->conv_w % 16) == 0) {
         if (bf) k_linear_decode_128<__nv_bfloat16><<<grid, 256, 0, s>>>(x);
         else    k_linear_decode_128<float><<<grid, 256, 0, s>>>(x);
         return orn_check_launch("k_linear_decode_128");
