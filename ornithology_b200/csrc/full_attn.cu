@@ -379,6 +379,13 @@ static int split_tokens(int max_len) {
     // tokens per split: long contexts use 512-token splits; short ones fewer CTAs
     return max_len <= 512 ? 128 : 512;
 }
+// split length of the tensor-core decode kernels (larger splits, fewer partials)
+static int split_tokens_mma(int max_len) { return max_len > 8192 ? 1024 : (max_len > 1024 ? 512 : 256); }
+// the largest split count either decode path may use: what the scratch is sized for
+static int max_splits(int max_len) {
+    const int a = split_tokens(max_len), b = split_tokens_mma(max_len), t = a < b ? a : b;
+    return (max_len + t - 1) / t;
+}
 
 template <typename ACT>
 static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
@@ -401,7 +408,7 @@ extern "C" {
 size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *l, int n_seq, int max_len) {
     if (!l || n_seq <= 0) return 0;
     if (max_len < 1) max_len = 1;
-    const int tps = split_tokens(max_len), nsplit = (max_len + tps - 1) / tps;
+    const int nsplit = max_splits(max_len);
     size_t qp = align_up((size_t)n_seq * l->n_heads * l->head_dim * sizeof(float), 256);
     size_t part = (size_t)n_seq * l->n_heads * nsplit * (l->head_dim + 2) * sizeof(float);
     return qp + align_up(part, 256);
@@ -438,7 +445,7 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     int nsplit_used;
     if (gqa_decode_q8_mma_supported(d.kv, nh) && !force_generic_decode()) {
         // tensor-core path: larger splits (fewer partials); never more splits than the scratch was sized for
-        int tps_mma = max_len > 8192 ? 1024 : (max_len > 1024 ? 512 : 256);
+        int tps_mma = split_tokens_mma(max_len);
         {   // ORNITH_CUDA_DECODE_SPLIT=<tokens> overrides the split length for long contexts (tuning knob)
             static int forced = -1;
             if (forced < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_SPLIT"); forced = e ? atoi(e) : 0; }
