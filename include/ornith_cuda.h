@@ -222,6 +222,33 @@ ornith_status ornith_cuda_kv_append(const ornith_cuda_full_layer *layer, const o
                                     const int32_t *kv_len, const int32_t *rope_pos,
                                     const void *k, const void *v, int act_dtype, int T, void *stream);
 
+/* The same decode step for hosts that are not allowed to allocate device memory.
+ * (No counterpart in the reference: its attention code is CPU-only and mallocs its
+ * score buffer per call, src/ornith_attn.c:114.)
+ *
+ * Who needs it: an engine that split its device memory among its subsystems once at
+ * start-up and has no allocator left to ask on the token path; a serving loop that
+ * cannot afford cudaMalloc's device-wide synchronisation (or its failure) between
+ * two tokens; an embedding host that gives this library no allocator at all.  The
+ * caller still passes every input and the output; only the scratch (prepared query
+ * rows + split-K partials) comes from a fixed array inside the library image, which
+ * every GPU that loads the library keeps resident until the process exits.
+ *
+ *  - Limit: ornith_cuda_full_attn_step_scratch(layer, n_seq, max_len) must not exceed
+ *    ORNITH_CUDA_STATIC_SCRATCH_BYTES (8 MiB; e.g. 8 sequences x 16 heads x 256 at an
+ *    8k context).  Larger requests return ORNITH_ERR_UNSUPPORTED with a message.
+ *  - The first call on each device looks up the array's device address (with that
+ *    device current); make that call before starting any stream capture.
+ *  - Calls never call cudaMalloc/cudaFree or any allocating library routine.
+ *  - All calls share the array and it keeps the previous call's contents; a step
+ *    rewrites every word before reading it, so nothing needs clearing, but two calls
+ *    whose kernels overlap on the GPU race — keep them on one stream. */
+#define ORNITH_CUDA_STATIC_SCRATCH_BYTES (8u << 20)
+ornith_status ornith_cuda_full_attn_step_static(const ornith_cuda_full_layer *layer, const ornith_cuda_kv *kv,
+                                                const int32_t *kv_len, const int32_t *rope_pos,
+                                                const void *qproj, const void *k, const void *v, void *out,
+                                                int act_dtype, int max_len, void *stream);
+
 /* kv_len[b] += delta for every sequence (call once per token after all layers). */
 ornith_status ornith_cuda_advance(int32_t *counters, int n, int delta, void *stream);
 

@@ -549,6 +549,50 @@ ornith_status ornith_cuda_kv_append(const ornith_cuda_full_layer *l, const ornit
     return launch_prep<float>(l, kv, kv_len, rope_pos, nullptr, k, v, nullptr, kv->n_seq * T, T, st, true);
 }
 
+// ---- decode step for hosts that must not allocate device memory -----------------------
+//
+// Some callers cannot call cudaMalloc on the token path: an engine whose device memory
+// was carved up once at start-up and handed to other subsystems, a serving loop where an
+// allocation (which synchronises the device and may fail) is not acceptable in the middle
+// of a generation, or an embedding host that simply gives this library no allocator.  For
+// them the split-K partials and the prepared query rows live in a fixed array that is part
+// of the library image: every GPU that loads the library carries these 8 MiB until exit.
+//
+// In host code `g_static_scratch` is only a handle; the address kernels can use is looked
+// up with cudaGetSymbolAddress the first time a device calls in, with that device current.
+// That first call per device should therefore happen before any stream capture begins.
+// All calls share the one array: it still holds what the previous call left (every word a
+// step reads is rewritten by that step first, so nothing has to be cleared), and two calls
+// whose kernels overlap on the GPU would race on it — issue them on one stream.
+static __device__ __align__(256) unsigned char g_static_scratch[ORNITH_CUDA_STATIC_SCRATCH_BYTES];
+static void *g_static_scratch_dev[64];                   // device address, per CUDA device
+
+ornith_status ornith_cuda_full_attn_step_static(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
+                                                const int32_t *kv_len, const int32_t *rope_pos,
+                                                const void *qproj, const void *k, const void *v, void *out,
+                                                int act_dtype, int max_len, void *stream) {
+    ORN_TRY(orn_require_device());
+    ORN_TRY(check_full(l, kv));
+    if (kv->n_seq <= 0) return ORNITH_OK;
+    const size_t need = ornith_cuda_full_attn_step_scratch(l, kv->n_seq, max_len);
+    if (need > (size_t)ORNITH_CUDA_STATIC_SCRATCH_BYTES) {
+        orn_record_error("full_attn_step_static: %d sequences x context %d need %zu bytes of scratch, the built-in "
+                         "array holds %u; use ornith_cuda_full_attn_step with caller scratch",
+                         kv->n_seq, max_len, need, (unsigned)ORNITH_CUDA_STATIC_SCRATCH_BYTES);
+        return ORNITH_ERR_UNSUPPORTED;
+    }
+    int dev = -1;
+    ORN_TRY(orn_check(cudaGetDevice(&dev), "cudaGetDevice"));
+    if (dev < 0 || dev >= 64) { orn_record_error("full_attn_step_static: device index %d out of range", dev); return ORNITH_ERR_UNSUPPORTED; }
+    if (!g_static_scratch_dev[dev]) {
+        void *p = nullptr;
+        ORN_TRY(orn_check(cudaGetSymbolAddress(&p, g_static_scratch), "cudaGetSymbolAddress(static scratch)"));
+        g_static_scratch_dev[dev] = p;
+    }
+    return ornith_cuda_full_attn_step(l, kv, kv_len, rope_pos, qproj, k, v, out, act_dtype, max_len,
+                                      g_static_scratch_dev[dev], (size_t)ORNITH_CUDA_STATIC_SCRATCH_BYTES, stream);
+}
+
 // ---- standalone Q8_0 codec on flat arrays ---------------------------------------
 __global__ void __launch_bounds__(128) k_q8_0_encode(const float *src, uint8_t *dst, size_t nblk) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
