@@ -28,6 +28,12 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM bytes (read + write) per launch over algorithmic bytes, from the ncu captures summarised in
+# profiles/gqa_decode_q8_raw_24seq_8k-16k.txt (308.4 MB moved for 303.8 MB) and
+# profiles/linear_decode_128_64seq.txt (the state a launch writes is partly still dirty in L2 when
+# it ends, so DRAM writes are undercounted there; 1.0 = the algorithmic bytes are what moves).
+DRAM_OVER_ALGORITHMIC = {"full_attn_step": 1.015, "linear_attn_step": 1.0}
+
 METRIC = "attn_stack_decode_tokens_per_s"
 UNIT = "tok/s"
 
@@ -45,7 +51,7 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled every 200 ms while active."""
+    """nvidia-smi clocks and throttle reasons sampled every 50 ms while active."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -55,7 +61,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -208,11 +214,11 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize(dev)
 
     # ---- value: inputs resident in HBM --------------------------------------------------
-    for _ in range(args.warmup):
-        stack.decode_step(ins, outs, max_len=max_len)
     sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.start()                   # runs from the warm-up to the end of the host-fed timed region
+    for _ in range(args.warmup):
+        stack.decode_step(ins, outs, max_len=max_len)
     n_layers = len(stack.layers)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n_layers + 1)] for _ in range(args.steps)]
     barrier()
@@ -231,7 +237,6 @@ def run_ours(args, rank, world, local_rank):
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
-    clocks = sampler.stop() if rank == 0 else None
     ms_lin = np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)
                       for i, (k, _, _) in enumerate(stack.layers) if k == "linear"])
     ms_full = np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)
@@ -243,24 +248,54 @@ def run_ours(args, rank, world, local_rank):
     h2d = sum(t.numel() * t.element_size() for layer in h_ins for t in layer)
     d2h = sum(t.numel() * t.element_size() for t in h_outs)
 
+    # Every step copies every layer's inputs up and every layer's output down.  The copies run on
+    # their own streams and are ordered against the kernels with per-layer events, so a layer's
+    # upload overlaps the layers before it and its download the layers after it.
+    s_main = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(n_layers)]
+    ev_done = [torch.cuda.Event() for _ in range(n_layers)]
+    ev_out = [torch.cuda.Event() for _ in range(n_layers)]
+    for e in ev_done + ev_out:
+        e.record(s_main)
+
     def e2e_step():
-        for i in range(n_layers):
-            for dst, src in zip(ins[i], h_ins[i]):
-                dst.copy_(src, non_blocking=True)
-        stack.decode_step(ins, outs, max_len=max_len)
-        for dst, src in zip(h_outs, outs):
-            dst.copy_(src, non_blocking=True)
+        for i, (kind, layer, state) in enumerate(stack.layers):
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_done[i])           # the previous step has finished reading ins[i]
+                for dst, src in zip(ins[i], h_ins[i]):
+                    dst.copy_(src, non_blocking=True)
+                ev_in[i].record(s_in)
+            s_main.wait_event(ev_in[i])
+            s_main.wait_event(ev_out[i])              # the previous step's outs[i] has been downloaded
+            if kind == "full":
+                D.full_attn_step(layer, state, stack.pos, *ins[i], out=outs[i], max_len=max_len)
+            else:
+                D.linear_attn_step(layer, state, stack.pos, *ins[i], out=outs[i])
+            ev_done[i].record(s_main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[i])
+                h_outs[i].copy_(outs[i], non_blocking=True)
+                ev_out[i].record(s_out)
+        D.advance(stack.pos)
+
+    def e2e_drain():
+        s_main.wait_stream(s_in)
+        s_main.wait_stream(s_out)
 
     for _ in range(args.warmup):
         e2e_step()
+    e2e_drain()
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
     for _ in range(args.steps):
         e2e_step()
+    e2e_drain()                               # the last downloads are inside the timed region
     e_end.record()
     barrier()
     ms_e2e = e_start.elapsed_time(e_end)
+    clocks = sampler.stop() if rank == 0 else None
 
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
@@ -282,7 +317,8 @@ def run_ours(args, rank, world, local_rank):
                                   "gbs": b_full / n_full / (ms_full * 1e-3) / 1e9, "launches_per_step": n_full}}
         dom = max(fam, key=lambda k: fam[k]["ms_per_launch"] * fam[k]["launches_per_step"])
         roof = {"bound": "hbm", "kernel": dom, "achieved": fam[dom]["gbs"], "peak": peak, "unit": "GB/s",
-                "frac": fam[dom]["gbs"] / peak, "peak_source": f"of {src}", "traffic": None, "families": fam,
+                "frac": fam[dom]["gbs"] / peak, "peak_source": f"of {src}",
+                "traffic": fam[dom]["bytes_per_launch"] * DRAM_OVER_ALGORITHMIC[dom], "families": fam,
                 "whole_step_gbs": (b_lin + b_full) / (ms_total / args.steps * 1e-3) / 1e9}
         cpu = None
         if world == 1 and not args.no_cpu:
