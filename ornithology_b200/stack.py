@@ -65,6 +65,36 @@ def head_shard(arch: dict, rank: int, world: int) -> HeadShard:
                      range(kv_lo, kv_hi + 1))
 
 
+def sequence_shard(contexts, rank: int, world: int):
+    """Indices of the sequences rank `rank` owns under sequence sharding: equal counts per
+    rank, balanced by total context (longest first onto the least loaded rank with room)."""
+    contexts = np.asarray(contexts)
+    n = len(contexts)
+    cap = -(-n // world)
+    load = [0] * world
+    owned = [[] for _ in range(world)]
+    for i in sorted(range(n), key=lambda i: (-int(contexts[i]), i)):
+        r = min((r for r in range(world) if len(owned[r]) < cap), key=lambda r: (load[r], r))
+        owned[r].append(i)
+        load[r] += int(contexts[i])
+    return sorted(owned[rank])
+
+
+def gather_heads(local: torch.Tensor, world: int) -> torch.Tensor:
+    """All-gather of per-rank head outputs [..., width/world] -> [..., width] (rank r owns the
+    r-th block of heads), the one collective of the head-sharded plan; it runs before the
+    output projection (reference call sites: src/ornith_rforward.c:452, :316)."""
+    import torch.distributed as dist
+    if world == 1:
+        return local
+    local = local.contiguous()
+    flat = local.reshape(-1, local.shape[-1])
+    buf = torch.empty((world * flat.shape[0], flat.shape[1]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(buf, flat)                      # rank blocks stacked along dim 0
+    out = buf.view(world, flat.shape[0], flat.shape[1]).movedim(0, 1).reshape(flat.shape[0], -1)
+    return out.reshape(*local.shape[:-1], world * local.shape[-1])
+
+
 def linear_weights(arch: dict, seed: int, layer: int):
     """Seeded synthetic weights of one delta-net layer (value ranges as in the
     reference's fixture model, tests/test_session.c:76, :121-126)."""
@@ -98,8 +128,8 @@ class AttnStack:
     """All attention layers of one model for `n_seq` sequences on one device."""
 
     def __init__(self, arch_name: str, capacities, kv_mode=D.KV_Q8_0, seed=0, device="cuda:0",
-                 shard: HeadShard | None = None):
-        self.arch = arch = ARCHS[arch_name]
+                 shard: HeadShard | None = None, n_layers: int | None = None):
+        self.arch = arch = ARCHS[arch_name] if isinstance(arch_name, str) else arch_name
         self.n_seq = len(capacities)
         self.device = torch.device(device)
         self.shard = shard
@@ -108,7 +138,7 @@ class AttnStack:
         if shard is not None:
             nk, nv, nh, nkv = len(shard.k_heads), len(shard.v_heads), len(shard.q_heads), len(shard.kv_heads)
         self.nk, self.nv, self.nh, self.nkv = nk, nv, nh, nkv
-        for i in range(arch["layers"]):
+        for i in range(arch["layers"] if n_layers is None else n_layers):
             if is_full_layer(arch, i):
                 w = full_weights(arch, seed, i)
                 layer = D.FullLayer(nh, nkv, arch["hd"], w["q_norm_w"], w["k_norm_w"], rope_dim=arch["rope_dim"],
@@ -165,6 +195,34 @@ class AttnStack:
                 outs.append(D.linear_attn_step(layer, state, self.pos, *inputs[i], out=out))
         D.advance(self.pos)
         return outs
+
+    def decode_step_gathered(self, inputs, world, max_len=None):
+        """Head-sharded decode step: every layer's local head outputs are all-gathered (NCCL
+        over NVLink) into the full-width row the output projection consumes."""
+        outs = self.decode_step(inputs, max_len=max_len)
+        return [gather_heads(o, world) for o in outs]
+
+    def shard_inputs(self, full_inputs):
+        """Slice full-width per-layer inputs (as an unsharded stack takes them) down to this
+        rank's heads."""
+        if self.shard is None:
+            return full_inputs
+        a, sh = self.arch, self.shard
+        dev = self.device
+        qcols = torch.tensor(np.concatenate([np.arange(h * 2 * a["hd"], (h + 1) * 2 * a["hd"]) for h in sh.q_heads]), device=dev)
+        kcols = torch.tensor(np.concatenate([np.arange(h * a["hd"], (h + 1) * a["hd"]) for h in sh.kv_heads]), device=dev)
+        _, chan = shard_linear_weights(a, linear_weights(a, 0, 0), sh)
+        chan = torch.tensor(chan, device=dev)
+        heads = torch.tensor(list(sh.v_heads), device=dev)
+        vcols = torch.tensor(np.concatenate([np.arange(h * a["dv"], (h + 1) * a["dv"]) for h in sh.v_heads]), device=dev)
+        out = []
+        for (kind, _, _), ins in zip(self.layers, full_inputs):
+            if kind == "full":
+                out.append([ins[0][..., qcols].contiguous(), ins[1][..., kcols].contiguous(), ins[2][..., kcols].contiguous()])
+            else:
+                out.append([ins[0][..., chan].contiguous(), ins[1][..., heads].contiguous(), ins[2][..., heads].contiguous(),
+                            ins[3][..., vcols].contiguous()])
+        return out
 
     def launches_per_step(self):
         n_full = sum(1 for k, _, _ in self.layers if k == "full")
