@@ -188,6 +188,7 @@ struct CombineArgs {
     const void *qproj;                   // for the gate half, when gated
     void *out;
     int nh, nsplit, gated;
+    int tokens_per_split;                // splits past the sequence's context hold nothing
 };
 
 // Merge the split partials of one (head, sequence), normalise, apply the sigmoid
@@ -198,14 +199,16 @@ __global__ void __launch_bounds__(128) k_gqa_combine(CombineArgs a) {
     __shared__ float red[32];
     const int hd = a.kv.hd, h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
     const int cap = (int)(a.kv.seq_off[b + 1] - a.kv.seq_off[b]);
-    if (a.kv_len[b] >= cap) return;
+    const int len0 = a.kv_len[b];
+    if (len0 >= cap) return;
     const float *part = a.part + ((size_t)b * a.nh + h) * a.nsplit * (hd + 2);
+    const int nlive = min(a.nsplit, (len0 + a.tokens_per_split) / a.tokens_per_split);   // ceil((len0+1)/tps)
     float m = -INFINITY;
-    for (int s = tid; s < a.nsplit; s += 128)
+    for (int s = tid; s < nlive; s += 128)
         if (part[(size_t)s * (hd + 2) + 1] > 0.0f) m = fmaxf(m, part[(size_t)s * (hd + 2)]);
     const float M = block_max(m, red);
     float lsum = 0.0f;
-    for (int s = tid; s < a.nsplit; s += 128) {
+    for (int s = tid; s < nlive; s += 128) {
         const float l = part[(size_t)s * (hd + 2) + 1];
         const float w = (l > 0.0f) ? expf(part[(size_t)s * (hd + 2)] - M) : 0.0f;
         w_s[s] = w;
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(128) k_gqa_combine(CombineArgs a) {
     ACT *out = (ACT *)a.out + ((size_t)b * a.nh + h) * hd;
     for (int d = tid; d < hd; d += 128) {
         float o = 0.0f;
-        for (int s = 0; s < a.nsplit; s++)
+        for (int s = 0; s < nlive; s++)
             if (w_s[s] != 0.0f) o += part[(size_t)s * (hd + 2) + 2 + d] * w_s[s];
         o *= inv;
         if (gate) o *= sigmoid_f(act_ld(gate, d));
@@ -380,7 +383,9 @@ static int split_tokens(int max_len) {
     return max_len <= 512 ? 128 : 512;
 }
 // split length of the tensor-core decode kernels (larger splits, fewer partials)
-static int split_tokens_mma(int max_len) { return max_len > 8192 ? 1024 : (max_len > 1024 ? 512 : 256); }
+static int split_tokens_mma(int max_len) {
+    return max_len > 16384 ? 2048 : (max_len > 8192 ? 1024 : (max_len > 1024 ? 512 : 256));
+}
 // the largest split count either decode path may use: what the scratch is sized for
 static int max_splits(int max_len) {
     const int a = split_tokens(max_len), b = split_tokens_mma(max_len), t = a < b ? a : b;
@@ -467,7 +472,7 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
 
     CombineArgs c;
     c.kv = d.kv; c.kv_len = kv_len; c.part = part; c.qproj = qproj; c.out = out;
-    c.nh = nh; c.nsplit = nsplit_used; c.gated = l->gated;
+    c.nh = nh; c.nsplit = nsplit_used; c.gated = l->gated; c.tokens_per_split = d.tokens_per_split;
     dim3 cgrid(nh, B);
     if (act_dtype == ORNITH_ACT_BF16)
         k_gqa_combine<__nv_bfloat16><<<cgrid, 128, nsplit_used * sizeof(float), st>>>(c);
