@@ -201,17 +201,18 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *layer, co
                                          int act_dtype, int max_len,
                                          void *scratch, size_t scratch_bytes, void *stream);
 
-size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *layer, int n_seq, int T);
+size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *layer, int n_seq, int T, int max_len);
 
 /* Causal prefill of T tokens per sequence, appended at kv_len[b].. and attending
  * over everything already cached plus the new tokens; quantised modes attend
  * over the decoded rows, current token included, like T decode steps do.
  * Replaces the body of full_attn_prefill() (reference: src/ornith_rforward.c:529-551).
- *   qproj [n_seq][T][...], k,v [n_seq][T][...], out [n_seq][T][n_heads*head_dim] */
+ *   qproj [n_seq][T][...], k,v [n_seq][T][...], out [n_seq][T][n_heads*head_dim]
+ *   max_len: host upper bound on kv_len[b] + T (sizes the decoded-row image in the scratch) */
 ornith_status ornith_cuda_full_attn_prefill(const ornith_cuda_full_layer *layer, const ornith_cuda_kv *kv,
                                             const int32_t *kv_len, const int32_t *rope_pos,
                                             const void *qproj, const void *k, const void *v, void *out,
-                                            int act_dtype, int T,
+                                            int act_dtype, int T, int max_len,
                                             void *scratch, size_t scratch_bytes, void *stream);
 
 /* The append half alone: k RMSNorm + RoPE, then f32 copy / Q8_0 / int8 encode of k

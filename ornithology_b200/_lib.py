@@ -97,8 +97,8 @@ SYMBOLS = {
     "ornith_cuda_full_attn_step_scratch": (_SZ, [vp, _I, _I]),
     "ornith_cuda_full_attn_step": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, vp, _SZ, vp]),
     "ornith_cuda_full_attn_step_static": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, vp]),
-    "ornith_cuda_full_attn_prefill_scratch": (_SZ, [vp, _I, _I]),
-    "ornith_cuda_full_attn_prefill": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, vp, _SZ, vp]),
+    "ornith_cuda_full_attn_prefill_scratch": (_SZ, [vp, _I, _I, _I]),
+    "ornith_cuda_full_attn_prefill": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, _I, vp, _SZ, vp]),
     "ornith_cuda_kv_append": (_I, [vp, vp, vp, vp, vp, vp, _I, _I, vp]),
     "ornith_cuda_advance": (_I, [vp, _I, _I, vp]),
     "ornith_cuda_linear_attn_step": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, vp]),

@@ -481,9 +481,13 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     return orn_check_launch("k_gqa_combine");
 }
 
-size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *l, int n_seq, int T) {
+size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *l, int n_seq, int T, int max_len) {
     if (!l || n_seq <= 0 || T <= 0) return 0;
-    return align_up((size_t)n_seq * T * l->n_heads * l->head_dim * sizeof(float), 256);
+    if (max_len < T) max_len = T;
+    size_t q = align_up((size_t)n_seq * T * l->n_heads * l->head_dim * sizeof(float), 256);
+    // decoded f16 image of the visible cache rows, used by the tensor-core path
+    if (l->head_dim == 256) q += gqa_prefill_mma_scratch(n_seq, l->n_kv_heads, max_len);
+    return q;
 }
 
 }  // extern "C"
@@ -506,14 +510,15 @@ extern "C" {
 ornith_status ornith_cuda_full_attn_prefill(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
                                             const int32_t *kv_len, const int32_t *rope_pos,
                                             const void *qproj, const void *k, const void *v, void *out,
-                                            int act_dtype, int T, void *scratch, size_t scratch_bytes,
-                                            void *stream) {
+                                            int act_dtype, int T, int max_len, void *scratch,
+                                            size_t scratch_bytes, void *stream) {
     ORN_TRY(orn_require_device());
     ORN_TRY(check_full(l, kv));
     const int B = kv->n_seq;
     if (B <= 0 || T <= 0) return ORNITH_OK;
+    if (max_len < T) max_len = T;
     if (l->head_dim > 256) { orn_record_error("prefill: head_dim > 256 unsupported"); return ORNITH_ERR_UNSUPPORTED; }
-    if (scratch_bytes < ornith_cuda_full_attn_prefill_scratch(l, B, T) || !scratch) {
+    if (scratch_bytes < ornith_cuda_full_attn_prefill_scratch(l, B, T, max_len) || !scratch) {
         orn_record_error("full_attn_prefill: scratch too small (%zu bytes given)", scratch_bytes);
         return ORNITH_ERR_FORMAT;
     }
@@ -524,6 +529,11 @@ ornith_status ornith_cuda_full_attn_prefill(const ornith_cuda_full_layer *l, con
     if (bf) ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st));
     else    ORN_TRY(launch_prep<float>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st));
 
+    if (gqa_prefill_mma_supported(make_view(kv)) && !force_generic_decode()) {
+        void *kvh = (char *)scratch + align_up((size_t)B * T * nh * hd * sizeof(float), 256);
+        return launch_gqa_prefill_mma(make_view(kv), kv_len, q_prep, kvh, qproj, out, nh, T, max_len, l->gated,
+                                      attn_scale(l), B, bf, st);
+    }
     PrefillArgs a;
     a.kv = make_view(kv); a.kv_len = kv_len; a.q_prep = q_prep; a.qproj = qproj; a.out = out;
     a.nh = nh; a.T = T; a.gated = l->gated; a.scale = attn_scale(l);

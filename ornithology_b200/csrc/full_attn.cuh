@@ -20,3 +20,11 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
 // Variant for groups of up to 8 query heads that builds its MMA fragments straight
 // from the staged raw rows (gqa_decode_q8_raw.cu).
 ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st);
+
+// Tensor-core causal prefill for head_dim 256 (gqa_prefill_mma.cu): decodes the visible cache
+// rows into an f16 image in `kvh_scratch` (gqa_prefill_mma_scratch bytes), then attends.
+bool gqa_prefill_mma_supported(const KvView &kv);
+size_t gqa_prefill_mma_scratch(int n_seq, int nkv, int Lmax);
+ornith_status launch_gqa_prefill_mma(const KvView &kv, const int32_t *kv_len, const float *q_prep, void *kvh_scratch,
+                                     const void *qproj, void *out, int nh, int T, int Lmax, int gated, float scale,
+                                     int n_seq, bool bf16_act, cudaStream_t st);

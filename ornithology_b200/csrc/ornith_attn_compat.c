@@ -247,7 +247,7 @@ void ornith_gqa_reference(const float *Q, const float *K, const float *V, int T,
     ornith_cuda_full_layer L;
     memset(&L, 0, sizeof(L));
     L.n_heads = n_heads; L.n_kv_heads = n_kv_heads; L.head_dim = head_dim; L.scale = scale; L.eps = 1e-6f;
-    const size_t sb = ornith_cuda_full_attn_prefill_scratch(&L, 1, T);
+    const size_t sb = ornith_cuda_full_attn_prefill_scratch(&L, 1, T, T);
     const size_t need = up256(qn) * 2 + up256(kn) * 4 + up256(sb) + 512;
     if (!ws_reserve(need)) goto done;
     {
@@ -264,7 +264,7 @@ void ornith_gqa_reference(const float *Q, const float *K, const float *V, int T,
             ornith_cuda_h2d(dv, V, kn) != ORNITH_OK || ornith_cuda_h2d(meta, off, sizeof(off)) != ORNITH_OK ||
             ornith_cuda_h2d(dlen, &zero, sizeof(zero)) != ORNITH_OK)
             goto done;
-        if (ornith_cuda_full_attn_prefill(&L, &kv, dlen, NULL, dq, dk, dv, dout, ORNITH_ACT_F32, T, ds, sb, NULL)
+        if (ornith_cuda_full_attn_prefill(&L, &kv, dlen, NULL, dq, dk, dv, dout, ORNITH_ACT_F32, T, T, ds, sb, NULL)
             != ORNITH_OK)
             goto done;
         ornith_cuda_d2h(O, dout, qn);

@@ -186,16 +186,19 @@ def full_attn_step(layer: FullLayer, kv: KvBatch, kv_len, qproj, k, v, out=None,
     return out
 
 
-def full_attn_prefill(layer: FullLayer, kv: KvBatch, kv_len, qproj, k, v, T, out=None, rope_pos=None):
+def full_attn_prefill(layer: FullLayer, kv: KvBatch, kv_len, qproj, k, v, T, out=None, rope_pos=None, max_len=None):
+    """T new tokens per sequence; `max_len` bounds kv_len[b] + T (default: the largest capacity)."""
     lib = _lib.load()
+    if max_len is None:
+        max_len = max(kv.capacities)
     B = kv.n_seq
     act = _act(qproj)
     if out is None:
         out = torch.empty(B, T, layer.nh * layer.hd, dtype=qproj.dtype, device=qproj.device)
-    need = lib.ornith_cuda_full_attn_prefill_scratch(C.byref(layer.c), B, int(T))
+    need = lib.ornith_cuda_full_attn_prefill_scratch(C.byref(layer.c), B, int(T), int(max_len))
     scr = layer.scratch.get(need, qproj.device)
     check(lib.ornith_cuda_full_attn_prefill(C.byref(layer.c), C.byref(kv.c), _ptr(kv_len), _ptr(rope_pos),
-                                            _ptr(qproj), _ptr(k), _ptr(v), _ptr(out), act, int(T),
+                                            _ptr(qproj), _ptr(k), _ptr(v), _ptr(out), act, int(T), int(max_len),
                                             _ptr(scr), scr.numel(), _stream()), "full_attn_prefill")
     return out
 
