@@ -8,27 +8,9 @@
 //   ornith_conv_step / _prefill       src/ornith_attn.c:370-397
 #include <math.h>
 
-#include "common.cuh"
+#include <stdlib.h>
 
-struct LinArgs {
-    int nk, nv, dk, dv, conv_k, head_map;
-    float out_scale, eps;
-    const float *conv_w, *conv_b, *a_coef, *dt_bias, *norm_w;
-    float *S, *conv;
-    int64_t S_stride, conv_stride;
-    const int32_t *pos;
-    const void *qkv, *a, *b, *z;
-    void *out;
-    int T;                               // tokens per sequence (prefill kernels)
-};
-
-__device__ __forceinline__ int key_head_of(const LinArgs &a, int hv) {
-    return a.head_map == ORNITH_HEADMAP_GROUPED ? hv / (a.nv / a.nk) : hv % a.nk;
-}
-// exactly one value head per key head stores that key head's q/k conv inputs
-__device__ __forceinline__ bool owns_key_head(const LinArgs &a, int hv) {
-    return a.head_map == ORNITH_HEADMAP_GROUPED ? (hv % (a.nv / a.nk)) == 0 : hv < a.nk;
-}
+#include "linear_attn.cuh"
 
 // One channel of the causal conv at token t, history in a ring of conv_k slots
 // (token t' lives in slot t' % conv_k).  Sum order and rounding follow the
@@ -728,7 +710,9 @@ ornith_status ornith_cuda_linear_attn_step(const ornith_cuda_linear_layer *l, co
 size_t ornith_cuda_linear_attn_prefill_scratch(const ornith_cuda_linear_layer *l, int n_seq, int T) {
     if (!l || n_seq <= 0 || T <= 0) return 0;
     const size_t n_tok = (size_t)n_seq * T, Cc = 2 * (size_t)l->nk * l->dk + (size_t)l->nv * l->dv;
-    return align_up(n_tok * Cc * 4, 256) + 2 * align_up(n_tok * l->nk * 4, 256) + 2 * align_up(n_tok * l->nv * 4, 256);
+    size_t bytes = align_up(n_tok * Cc * 4, 256) + 2 * align_up(n_tok * l->nk * 4, 256) + 2 * align_up(n_tok * l->nv * 4, 256);
+    if (l->dk == 128 && l->dv == 128) bytes += align_up(linear_prefill_tc_blocks_bytes(l->nv, n_seq, T), 256);
+    return bytes;
 }
 
 }  // extern "C"
@@ -769,7 +753,9 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     float *rq = (float *)p; p += align_up(n_tok * l->nk * 4, 256);
     float *rk = (float *)p; p += align_up(n_tok * l->nk * 4, 256);
     float *la = (float *)p; p += align_up(n_tok * l->nv * 4, 256);
-    float *be = (float *)p;
+    float *be = (float *)p; p += align_up(n_tok * l->nv * 4, 256);
+    float *blocks = (float *)p;          // only the tensor-core scan uses this part
+    if (((uintptr_t)scratch % 256) != 0) { orn_record_error("linear_attn_prefill: scratch must be 256-byte aligned"); return ORNITH_ERR_FORMAT; }
     LinArgs x = make_args(l, st, pos, qkv, a, b, z, out, T);
 
     dim3 cgrid((unsigned)((Cc + 127) / 128), (T + CONV_TOK - 1) / CONV_TOK, n_seq);
@@ -786,6 +772,9 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
 
     dim3 grid(l->nv, n_seq);
     if (l->dk == 128 && l->dv == 128) {
+        // default: tf32 tensor-core scan; ORNITH_CUDA_PREFILL_FP32=1 keeps every product in fp32
+        const char *exact = getenv("ORNITH_CUDA_PREFILL_FP32");
+        if (!exact || exact[0] != '1') return launch_linear_prefill_tc(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, s);
         if (chunk >= 32) return bf ? launch_chunk<32, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)
                                    : launch_chunk<32, float>(x, grid, Y, rq, rk, la, be, s);
         return bf ? launch_chunk<16, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)

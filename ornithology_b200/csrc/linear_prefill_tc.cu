@@ -1,0 +1,519 @@
+// linear_prefill_tc.cu — gated delta-net prefill scan for dk = dv = 128 with the
+// chunk contractions on the tensor cores (tf32 operands, fp32 accumulation).
+//
+// Reference behaviour being replaced: the chunked scan of ornith_delta_prefill
+// (src/ornith_attn.c:215-349) inside linear_attn_prefill (src/ornith_rforward.c:563-618).
+//
+// Per chunk of 32 tokens with incoming state S, G_i the running sum of the
+// log-decay inside the chunk, p_i = exp(G_i), Gamma_ij = exp(G_i - G_j):
+//   M = diag(beta) strictLower(Gamma o K K^T),  A = (I + M)^-1,  P = lower(Gamma o Q K^T)
+//   T = diag(beta) (V - diag(p) K S^T)
+//   U = A T
+//   O = diag(p) Q S^T + P U
+//   S <- p_31 S + sum_j Gamma_31,j u_j k_j^T
+// A and P do not depend on the state, so they are produced for every chunk at
+// once by k_delta_chunk_prep (Gram matrices on the tensor cores, the triangular
+// inverse by fp32 substitution).  What remains sequential, k_delta_chunk_scan,
+// is five small contractions per chunk.  Columns r of the state are independent
+// of one another, so one (value head, sequence) is spread over a thread-block
+// cluster of 128/NR CTAs owning NR columns each; the only thing they exchange
+// is the per-token sum of squares for the output RMSNorm, through distributed
+// shared memory.  The fp32 master copy of the state stays in registers (it is
+// the accumulator of the state update); a tf32 image of it in shared memory is
+// the B operand of the next chunk's K S^T / Q S^T.
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "bulk_copy.cuh"
+#include "linear_attn.cuh"
+
+namespace {
+
+constexpr int TC = 32;                   // tokens per chunk
+constexpr int LDK = 132;                 // K / Q rows: stride = 4 mod 32 keeps A fragments conflict-free
+constexpr int LDP = 36;                  // A / P rows
+constexpr int LDG = 33;
+constexpr int BLK_P = TC * LDP, BLK_AUX = 2 * TC * LDP;
+constexpr int BLK_FLOATS = BLK_AUX + 4 * TC;              // A, P, then p | beta | w_end | beta*p
+constexpr uint32_t BLK_BYTES = BLK_FLOATS * 4;
+
+__device__ __forceinline__ float tf32r(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+
+// D(16x8) += A(16x8) B(8x8).  Fragment owners, g = lane / 4, j = lane % 4:
+//   a0 (g, j) a1 (g+8, j) a2 (g, j+4) a3 (g+8, j+4);  b0 (k=j, n=g) b1 (k=j+4, n=g);
+//   d0 (g, 2j) d1 (g, 2j+1) d2 (g+8, 2j) d3 (g+8, 2j+1).
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const float (&a)[4], float b0, float b1) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(__float_as_uint(a[0])), "r"(__float_as_uint(a[1])), "r"(__float_as_uint(a[2])),
+          "r"(__float_as_uint(a[3])), "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+
+// A fragment of a row-major [m][k] tile whose (0, 0) element is at base
+__device__ __forceinline__ void frag_a(float (&a)[4], const float *base, int ld, int g, int j) {
+    a[0] = base[g * ld + j];
+    a[1] = base[(g + 8) * ld + j];
+    a[2] = base[g * ld + j + 4];
+    a[3] = base[(g + 8) * ld + j + 4];
+}
+
+// =============================================================================
+// state-independent part: one CTA per (chunk, key head, sequence)
+// =============================================================================
+// Normalises the chunk's q / k rows in place in Y (tf32-rounded), then for every
+// value head that reads this key head writes one block of BLK_FLOATS floats:
+// A [32][36], P [32][36] (both tf32), p, beta, w_end, beta*p [32 each].
+struct PrepSmem {
+    float Ks[TC * LDK];
+    float Qs[TC * LDK];
+    float GK[TC * LDG];                  // raw k_i.k_j
+    float GQ[TC * LDG];                  // raw q_i.k_j
+    float Mw[4][TC * LDG];               // per warp: beta_i Gamma_ij k_i.k_j, j < i
+    float Gw[4][TC], Bw[4][TC];
+};
+
+__global__ void __launch_bounds__(128) k_delta_chunk_prep(LinArgs a, float *Y, const float *rq, const float *rk,
+                                                          const float *la, const float *be, float *blocks,
+                                                          int n_chunks) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    PrepSmem &sm = *reinterpret_cast<PrepSmem *>(smraw);
+    const int chunk = blockIdx.x, kh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int g = lane >> 2, j = lane & 3;
+    const int qd = a.nk * 128, Cc = 2 * qd + a.nv * 128;
+    const int t0 = chunk * TC, n = min(TC, a.T - t0);
+    const size_t tok0 = (size_t)b * a.T + t0;
+
+    for (int e = tid; e < TC * 32; e += 128) {            // rows past the end are zero
+        const int i = e >> 5, c = (e & 31) * 4;
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f), k = q;
+        if (i < n) {
+            float *y = Y + (tok0 + i) * Cc + kh * 128 + c;
+            const float sq = rq[(tok0 + i) * a.nk + kh], sk = rk[(tok0 + i) * a.nk + kh];
+            q = *reinterpret_cast<const float4 *>(y);
+            k = *reinterpret_cast<const float4 *>(y + qd);
+            q.x = tf32r(q.x * sq); q.y = tf32r(q.y * sq); q.z = tf32r(q.z * sq); q.w = tf32r(q.w * sq);
+            k.x = tf32r(k.x * sk); k.y = tf32r(k.y * sk); k.z = tf32r(k.z * sk); k.w = tf32r(k.w * sk);
+            *reinterpret_cast<float4 *>(y) = q;
+            *reinterpret_cast<float4 *>(y + qd) = k;
+        }
+        *reinterpret_cast<float4 *>(&sm.Qs[i * LDK + c]) = q;
+        *reinterpret_cast<float4 *>(&sm.Ks[i * LDK + c]) = k;
+    }
+    __syncthreads();
+    {   // Gram tiles on or below the diagonal: warps 0-1 K K^T, warps 2-3 Q K^T; mt = w & 1
+        const int which = w >> 1, mt = w & 1, ntn = 2 * mt + 2;
+        float acc[4][4];
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int x = 0; x < 4; x++) acc[t][x] = 0.0f;
+        const float *A = (which ? sm.Qs : sm.Ks) + 16 * mt * LDK;
+#pragma unroll 4
+        for (int k0 = 0; k0 < 128; k0 += 8) {
+            float af[4];
+            frag_a(af, A + k0, LDK, g, j);
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                if (t < ntn) {
+                    const float *kr = sm.Ks + (8 * t + g) * LDK + k0 + j;
+                    mma_tf32(acc[t], af, kr[0], kr[4]);
+                }
+            }
+        }
+        float *G = which ? sm.GQ : sm.GK;
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+                G[(16 * mt + g + 8 * (x >> 1)) * LDG + 8 * t + 2 * j + (x & 1)] = acc[t][x];
+    }
+    __syncthreads();
+    const int nvk = a.nv / a.nk;
+    for (int m = w; m < nvk; m += 4) {                    // one warp per value head of this key head
+        const int hv = a.head_map == ORNITH_HEADMAP_GROUPED ? kh * nvk + m : kh + m * a.nk;
+        float gg = 0.0f, bb = 0.0f;
+        if (lane < n) { gg = la[(tok0 + lane) * a.nv + hv]; bb = be[(tok0 + lane) * a.nv + hv]; }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, gg, o);
+            if (lane >= o) gg += up;
+        }
+        const float gl = __shfl_sync(0xffffffffu, gg, 31);
+        float *blk = blocks + (((size_t)b * a.nv + hv) * n_chunks + chunk) * BLK_FLOATS;
+        const float pp = expf(gg);
+        blk[BLK_AUX + lane] = pp;
+        blk[BLK_AUX + TC + lane] = bb;
+        blk[BLK_AUX + 2 * TC + lane] = expf(gl - gg);
+        blk[BLK_AUX + 3 * TC + lane] = bb * pp;
+        __syncwarp();
+        sm.Gw[w][lane] = gg; sm.Bw[w][lane] = bb;
+        __syncwarp();
+        float *Mw = sm.Mw[w];
+#pragma unroll 4
+        for (int i = 0; i < TC; i++) {                    // lane = column l of row i
+            const float gam = (lane <= i) ? expf(sm.Gw[w][i] - gg) : 0.0f;
+            Mw[i * LDG + lane] = (lane < i) ? sm.Bw[w][i] * gam * sm.GK[i * LDG + lane] : 0.0f;
+            blk[BLK_P + i * LDP + lane] = (lane <= i) ? tf32r(gam * sm.GQ[i * LDG + lane]) : 0.0f;
+        }
+        __syncwarp();
+        float x[TC];                                      // lane = column of the inverse
+#pragma unroll
+        for (int i = 0; i < TC; i++) {
+            float acc = (i == lane) ? 1.0f : 0.0f;
+#pragma unroll
+            for (int l = 0; l < i; l++) acc -= Mw[i * LDG + l] * x[l];
+            x[i] = acc;
+        }
+#pragma unroll
+        for (int i = 0; i < TC; i++) blk[i * LDP + lane] = tf32r(x[i]);
+        __syncwarp();
+    }
+}
+
+// =============================================================================
+// sequential part: a cluster of 128/NR CTAs per (value head, sequence)
+// =============================================================================
+template <int NR>
+struct ScanSmem {
+    static constexpr int LDN = NR + 8;   // stride = 8 mod 32 keeps B fragments conflict-free
+    struct Stage {
+        float Ks[TC * LDK];
+        float Qs[TC * LDK];
+        float Vs[TC * LDN];
+        float blk[BLK_FLOATS];           // A, P, p, beta, w_end, beta*p
+    } stage[2];
+    float St[128 * LDN];                 // St[c][r] = tf32(S[col0 + r][c])
+    float Ts[TC * LDN];
+    float Us[TC * LDN];
+    double red[2][TC][16];               // [chunk parity][token][4 * cluster rank + warp pair]
+    unsigned long long bar[2];
+    int failed;
+};
+
+template <int NR>
+__device__ __forceinline__ void issue_chunk(typename ScanSmem<NR>::Stage &st, uint32_t bar, const float *Y,
+                                            size_t tok0, int nvalid, int Cc, int koff, int qoff, int voff,
+                                            const float *blk, int lane) {
+    constexpr int LDN = ScanSmem<NR>::LDN;
+    if (lane >= nvalid) {                                 // rows past the end of the sequence are zero
+        for (int c = 0; c < 128; c += 4) {
+            *reinterpret_cast<float4 *>(&st.Ks[lane * LDK + c]) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(&st.Qs[lane * LDK + c]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int c = 0; c < NR; c += 4) *reinterpret_cast<float4 *>(&st.Vs[lane * LDN + c]) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __syncwarp();
+    if (lane == 0) {
+        bc_fence_proxy_async();
+        bc_mbar_expect_tx(bar, (uint32_t)nvalid * (512u + 512u + NR * 4u) + BLK_BYTES);
+    }
+    __syncwarp();
+    if (lane < nvalid) {
+        const float *y = Y + (tok0 + lane) * Cc;
+        bc_copy(bc_smem_u32(&st.Ks[lane * LDK]), y + koff, 512u, bar);
+        bc_copy(bc_smem_u32(&st.Qs[lane * LDK]), y + qoff, 512u, bar);
+        bc_copy(bc_smem_u32(&st.Vs[lane * LDN]), y + voff, NR * 4u, bar);
+    }
+    if (lane == 0) bc_copy(bc_smem_u32(st.blk), blk, BLK_BYTES, bar);
+}
+
+template <int NR, typename ACT>
+__global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const float *Y, const float *blocks,
+                                                             int n_chunks) {
+    using SM = ScanSmem<NR>;
+    constexpr int LDN = SM::LDN, CS = 128 / NR, NT = NR / 8, NTW = NR / 32;
+    extern __shared__ __align__(128) unsigned char smraw[];
+    SM &sm = *reinterpret_cast<SM *>(smraw);
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, j = lane & 3;
+    const int rank = (int)bc_cluster_rank(), hv = blockIdx.x / CS, b = blockIdx.y;
+    const int kh = key_head_of(a, hv), qd = a.nk * 128, vd = a.nv * 128, Cc = 2 * qd + vd;
+    const int col0 = rank * NR;
+    const int qoff = kh * 128, koff = qd + kh * 128, voff = 2 * qd + hv * 128 + col0;
+    float *S = a.S + (size_t)b * a.S_stride + (size_t)hv * 128 * 128 + (size_t)col0 * 128;
+    const float *blk0 = blocks + ((size_t)b * a.nv + hv) * n_chunks * BLK_FLOATS;
+    const int mt = w & 1, wp = w >> 1, ntb = wp * NTW;   // [token][r] tiles: rows 16 mt.., n-tiles ntb..
+    const int m0 = 16 * w;                                // rows c of S^T in the state update
+
+    if (tid == 0) {
+        bc_mbar_init(bc_smem_u32(&sm.bar[0]), 1);
+        bc_mbar_init(bc_smem_u32(&sm.bar[1]), 1);
+        bc_mbar_init_fence();
+        sm.failed = 0;
+    }
+    // state: st[nt][.] = S^T[m0 + g (+8)][8 nt + 2j (+1)] (columns local to this CTA)
+    float st[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int r = 8 * nt + 2 * j, c = m0 + g;
+        st[nt][0] = S[r * 128 + c];
+        st[nt][1] = S[(r + 1) * 128 + c];
+        st[nt][2] = S[r * 128 + c + 8];
+        st[nt][3] = S[(r + 1) * 128 + c + 8];
+        *reinterpret_cast<float2 *>(&sm.St[c * LDN + r]) = make_float2(tf32r(st[nt][0]), tf32r(st[nt][1]));
+        *reinterpret_cast<float2 *>(&sm.St[(c + 8) * LDN + r]) = make_float2(tf32r(st[nt][2]), tf32r(st[nt][3]));
+    }
+    float nw[NTW][2];
+#pragma unroll
+    for (int t = 0; t < NTW; t++) {
+        nw[t][0] = a.norm_w[col0 + 8 * (ntb + t) + 2 * j];
+        nw[t][1] = a.norm_w[col0 + 8 * (ntb + t) + 2 * j + 1];
+    }
+    __syncthreads();
+    bc_cluster_arrive();                                  // every CTA of the cluster is resident
+    bc_cluster_wait();
+    if (w == 0) issue_chunk<NR>(sm.stage[0], bc_smem_u32(&sm.bar[0]), Y, (size_t)b * a.T, min(TC, a.T), Cc, koff, qoff,
+                                voff, blk0, lane);
+    bool ok = true;
+
+    for (int n = 0; n < n_chunks; n++) {
+        const int buf = n & 1, t0 = n * TC, nvalid = min(TC, a.T - t0);
+        const size_t tok0 = (size_t)b * a.T + t0;
+        typename SM::Stage &sg = sm.stage[buf];
+        __syncthreads();                                  // chunk n-1 is finished with the other stage, Ts, Us, St
+        if (w == 0 && n + 1 < n_chunks)
+            issue_chunk<NR>(sm.stage[buf ^ 1], bc_smem_u32(&sm.bar[buf ^ 1]), Y, tok0 + TC, min(TC, a.T - t0 - TC), Cc,
+                            koff, qoff, voff, blk0 + (size_t)(n + 1) * BLK_FLOATS, lane);
+        // z of this thread's outputs, requested now and used at the end of the chunk
+        float zv[2][NTW][2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int i = 16 * mt + g + 8 * h;
+#pragma unroll
+            for (int t = 0; t < NTW; t++) {
+                zv[h][t][0] = 0.0f; zv[h][t][1] = 0.0f;
+                if (i < nvalid) {
+                    const size_t off = (tok0 + i) * vd + (size_t)hv * 128 + col0 + 8 * (ntb + t) + 2 * j;
+                    zv[h][t][0] = act_ld((const ACT *)a.z, off);
+                    zv[h][t][1] = act_ld((const ACT *)a.z, off + 1);
+                }
+            }
+        }
+        ok = ok && bc_mbar_wait(bc_smem_u32(&sm.bar[buf]), (uint32_t)(n >> 1) & 1u);   // one timeout at most
+        const float *aux = sg.blk + BLK_AUX;
+
+        // ---- K S^T and Q S^T; two accumulators per product shorten the dependent chain
+        float sk[2][NTW][4], sq[2][NTW][4];
+#pragma unroll
+        for (int e = 0; e < 2; e++)
+#pragma unroll
+            for (int t = 0; t < NTW; t++)
+#pragma unroll
+                for (int x = 0; x < 4; x++) { sk[e][t][x] = 0.0f; sq[e][t][x] = 0.0f; }
+#pragma unroll 2
+        for (int k0 = 0; k0 < 128; k0 += 16) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int kk = k0 + 8 * e;
+                float ak[4], aq[4];
+                frag_a(ak, sg.Ks + 16 * mt * LDK + kk, LDK, g, j);
+                frag_a(aq, sg.Qs + 16 * mt * LDK + kk, LDK, g, j);
+#pragma unroll
+                for (int t = 0; t < NTW; t++) {
+                    const float b0 = sm.St[(kk + j) * LDN + 8 * (ntb + t) + g];
+                    const float b1 = sm.St[(kk + j + 4) * LDN + 8 * (ntb + t) + g];
+                    mma_tf32(sk[e][t], ak, b0, b1);
+                    mma_tf32(sq[e][t], aq, b0, b1);
+                }
+            }
+        }
+        // ---- T = beta V - (beta p) K S^T
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int i = 16 * mt + g + 8 * h;
+            const float bi = aux[TC + i], bp = aux[3 * TC + i];
+#pragma unroll
+            for (int t = 0; t < NTW; t++) {
+                const int r = 8 * (ntb + t) + 2 * j;
+                const float2 v = *reinterpret_cast<const float2 *>(&sg.Vs[i * LDN + r]);
+                float2 tt;
+                tt.x = tf32r(bi * v.x - bp * (sk[0][t][2 * h] + sk[1][t][2 * h]));
+                tt.y = tf32r(bi * v.y - bp * (sk[0][t][2 * h + 1] + sk[1][t][2 * h + 1]));
+                *reinterpret_cast<float2 *>(&sm.Ts[i * LDN + r]) = tt;
+            }
+        }
+        __syncthreads();
+        // ---- U = A T (A is unit lower triangular)
+        {
+            float u[NTW][4];
+#pragma unroll
+            for (int t = 0; t < NTW; t++)
+#pragma unroll
+                for (int x = 0; x < 4; x++) u[t][x] = 0.0f;
+#pragma unroll
+            for (int k0 = 0; k0 < TC; k0 += 8) {
+                if (mt == 0 && k0 >= 16) continue;
+                float af[4];
+                frag_a(af, sg.blk + 16 * mt * LDP + k0, LDP, g, j);
+#pragma unroll
+                for (int t = 0; t < NTW; t++)
+                    mma_tf32(u[t], af, sm.Ts[(k0 + j) * LDN + 8 * (ntb + t) + g],
+                             sm.Ts[(k0 + j + 4) * LDN + 8 * (ntb + t) + g]);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int t = 0; t < NTW; t++)
+                    *reinterpret_cast<float2 *>(&sm.Us[(16 * mt + g + 8 * h) * LDN + 8 * (ntb + t) + 2 * j]) =
+                        make_float2(tf32r(u[t][2 * h]), tf32r(u[t][2 * h + 1]));
+        }
+        __syncthreads();
+        // ---- O = p Q S^T + P U, scaled; this CTA's part of each token's sum of squares
+        float o[NTW][4];
+        {
+            const float p0 = aux[16 * mt + g], p1 = aux[16 * mt + g + 8];
+#pragma unroll
+            for (int t = 0; t < NTW; t++) {
+                o[t][0] = p0 * (sq[0][t][0] + sq[1][t][0]); o[t][1] = p0 * (sq[0][t][1] + sq[1][t][1]);
+                o[t][2] = p1 * (sq[0][t][2] + sq[1][t][2]); o[t][3] = p1 * (sq[0][t][3] + sq[1][t][3]);
+            }
+#pragma unroll
+            for (int k0 = 0; k0 < TC; k0 += 8) {
+                if (mt == 0 && k0 >= 16) continue;
+                float af[4];
+                frag_a(af, sg.blk + BLK_P + 16 * mt * LDP + k0, LDP, g, j);
+#pragma unroll
+                for (int t = 0; t < NTW; t++)
+                    mma_tf32(o[t], af, sm.Us[(k0 + j) * LDN + 8 * (ntb + t) + g],
+                             sm.Us[(k0 + j + 4) * LDN + 8 * (ntb + t) + g]);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                double ss = 0.0;
+#pragma unroll
+                for (int t = 0; t < NTW; t++)
+#pragma unroll
+                    for (int x = 0; x < 2; x++) {
+                        const float v = o[t][2 * h + x] * a.out_scale;
+                        o[t][2 * h + x] = v;
+                        ss += (double)v * (double)v;
+                    }
+                ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                if (j == 0) {
+                    const double *slot = &sm.red[buf][16 * mt + g + 8 * h][4 * rank + wp];
+#pragma unroll
+                    for (int rr = 0; rr < CS; rr++) bc_st_cluster_f64(bc_map_rank(slot, (uint32_t)rr), ss);
+                }
+            }
+        }
+        bc_cluster_arrive();
+        // ---- S^T <- p_end S^T + (diag(w_end) K)^T U, rows m0 .. m0+15
+        {
+            const float pend = aux[TC - 1];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int x = 0; x < 4; x++) st[nt][x] *= pend;
+#pragma unroll
+            for (int k0 = 0; k0 < TC; k0 += 8) {
+                const float w0 = aux[2 * TC + k0 + j], w1 = aux[2 * TC + k0 + j + 4];
+                float af[4];
+                af[0] = tf32r(sg.Ks[(k0 + j) * LDK + m0 + g] * w0);
+                af[1] = tf32r(sg.Ks[(k0 + j) * LDK + m0 + g + 8] * w0);
+                af[2] = tf32r(sg.Ks[(k0 + j + 4) * LDK + m0 + g] * w1);
+                af[3] = tf32r(sg.Ks[(k0 + j + 4) * LDK + m0 + g + 8] * w1);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    mma_tf32(st[nt], af, sm.Us[(k0 + j) * LDN + 8 * nt + g], sm.Us[(k0 + j + 4) * LDN + 8 * nt + g]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int r = 8 * nt + 2 * j, c = m0 + g;
+                *reinterpret_cast<float2 *>(&sm.St[c * LDN + r]) = make_float2(tf32r(st[nt][0]), tf32r(st[nt][1]));
+                *reinterpret_cast<float2 *>(&sm.St[(c + 8) * LDN + r]) =
+                    make_float2(tf32r(st[nt][2]), tf32r(st[nt][3]));
+            }
+        }
+        bc_cluster_wait();
+        // ---- RMSNorm over the head row, SiLU(z) gate, store
+        const bool bad = !ok || *(volatile int *)&sm.failed;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int i = 16 * mt + g + 8 * h;
+            if (i >= nvalid) continue;
+            double ss = 0.0;
+#pragma unroll
+            for (int q = 0; q < 4 * CS; q++) ss += sm.red[buf][i][q];
+            const float inv = bad ? NAN : (float)(1.0 / sqrt(ss / 128.0 + (double)a.eps));
+            const size_t off = (tok0 + i) * vd + (size_t)hv * 128 + col0;
+#pragma unroll
+            for (int t = 0; t < NTW; t++)
+#pragma unroll
+                for (int x = 0; x < 2; x++) {
+                    const float y = o[t][2 * h + x] * inv * nw[t][x] * silu_f(zv[h][t][x]);
+                    act_st((ACT *)a.out, off + 8 * (ntb + t) + 2 * j + x, y);
+                }
+        }
+        if (!ok) sm.failed = 1;
+    }
+    __syncthreads();
+    const bool bad = !ok || sm.failed;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int r = 8 * nt + 2 * j, c = m0 + g;
+        S[r * 128 + c] = bad ? NAN : st[nt][0];
+        S[(r + 1) * 128 + c] = bad ? NAN : st[nt][1];
+        S[r * 128 + c + 8] = bad ? NAN : st[nt][2];
+        S[(r + 1) * 128 + c + 8] = bad ? NAN : st[nt][3];
+    }
+}
+
+template <int NR, typename ACT>
+ornith_status launch_scan(const LinArgs &x, int n_seq, const float *Y, const float *blocks, int n_chunks,
+                          cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_chunk_scan<NR, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)sizeof(ScanSmem<NR>)),
+                          "delta chunk scan smem opt-in"));
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(x.nv * (128 / NR)), (unsigned)n_seq);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = sizeof(ScanSmem<NR>);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 128 / NR;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ORN_TRY(orn_check(cudaLaunchKernelEx(&cfg, k_delta_chunk_scan<NR, ACT>, x, Y, blocks, n_chunks),
+                      "k_delta_chunk_scan launch"));
+    return orn_check_launch("k_delta_chunk_scan");
+}
+
+}  // namespace
+
+size_t linear_prefill_tc_blocks_bytes(int nv, int n_seq, int T) {
+    return (size_t)n_seq * nv * ((T + TC - 1) / TC) * BLK_BYTES;
+}
+
+ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtype, float *Y, const float *rq,
+                                       const float *rk, const float *la, const float *be, float *blocks,
+                                       cudaStream_t s) {
+    const int n_chunks = (x.T + TC - 1) / TC;
+    static bool configured = false;
+    if (!configured) {
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_chunk_prep, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)sizeof(PrepSmem)),
+                          "delta chunk prep smem opt-in"));
+        configured = true;
+    }
+    k_delta_chunk_prep<<<dim3((unsigned)n_chunks, (unsigned)x.nk, (unsigned)n_seq), 128, sizeof(PrepSmem), s>>>(
+        x, Y, rq, rk, la, be, blocks, n_chunks);
+    ORN_TRY(orn_check_launch("k_delta_chunk_prep"));
+    const bool bf = act_dtype == ORNITH_ACT_BF16;
+    // 32-column CTAs (clusters of 4) while they all fit on the SMs at once, else 64-column (clusters of 2)
+    if ((long long)x.nv * n_seq * 4 <= 148)
+        return bf ? launch_scan<32, __nv_bfloat16>(x, n_seq, Y, blocks, n_chunks, s)
+                  : launch_scan<32, float>(x, n_seq, Y, blocks, n_chunks, s);
+    return bf ? launch_scan<64, __nv_bfloat16>(x, n_seq, Y, blocks, n_chunks, s)
+              : launch_scan<64, float>(x, n_seq, Y, blocks, n_chunks, s);
+}
