@@ -1,4 +1,4 @@
-// linear_prefill_tc.cu — gated delta-net prefill scan for dk = dv = 128 with the
+// delta_prefill_tc.cu — gated delta-net prefill scan for dk = dv = 128 with the
 // chunk contractions on the tensor cores (tf32 operands, fp32 accumulation).
 //
 // Reference behaviour being replaced: the chunked scan of ornith_delta_prefill
@@ -177,22 +177,47 @@ __global__ void __launch_bounds__(128) k_delta_chunk_prep(LinArgs a, float *Y, c
 // =============================================================================
 // sequential part: a cluster of 128/NR CTAs per (value head, sequence)
 // =============================================================================
+// Every MMA operand that is re-read lives in shared memory with its contraction
+// index contiguous and a row stride of 4 mod 32 words, so that one ldmatrix.x4
+// (8x8 tiles of b16 pairs = 8 rows x 4 tf32 words) fetches a whole A fragment,
+// or the B fragments of two k-steps, without bank conflicts.
 template <int NR>
 struct ScanSmem {
-    static constexpr int LDN = NR + 8;   // stride = 8 mod 32 keeps B fragments conflict-free
+    static constexpr int LDN = NR + 8;
     struct Stage {
         float Ks[TC * LDK];
         float Qs[TC * LDK];
         float Vs[TC * LDN];
         float blk[BLK_FLOATS];           // A, P, p, beta, w_end, beta*p
     } stage[2];
-    float St[128 * LDN];                 // St[c][r] = tf32(S[col0 + r][c])
-    float Ts[TC * LDN];
-    float Us[TC * LDN];
-    double red[2][TC][16];               // [chunk parity][token][4 * cluster rank + warp pair]
+    float Sn[NR * LDK];                  // Sn[r][c] = tf32(S[col0 + r][c])
+    float Tt[NR * LDP];                  // Tt[r][token]
+    float Ut[NR * LDP];                  // Ut[r][token]
+    float red[2][TC][16];                // [chunk parity][token][4 * cluster rank + warp pair]
     unsigned long long bar[2];
     int failed;
 };
+
+__device__ __forceinline__ void ldsm4(float (&r)[4], uint32_t addr) {
+    uint32_t x0, x1, x2, x3;
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
+    r[0] = __uint_as_float(x0); r[1] = __uint_as_float(x1); r[2] = __uint_as_float(x2); r[3] = __uint_as_float(x3);
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float2 ld2(const float *p, size_t i) { return *reinterpret_cast<const float2 *>(p + i); }
+__device__ __forceinline__ float2 ld2(const __nv_bfloat16 *p, size_t i) {
+    const uint32_t u = *reinterpret_cast<const uint32_t *>(p + i);
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+__device__ __forceinline__ void st2(float *p, size_t i, float x, float y) {
+    *reinterpret_cast<float2 *>(p + i) = make_float2(x, y);
+}
+__device__ __forceinline__ void st2(__nv_bfloat16 *p, size_t i, float x, float y) {
+    *reinterpret_cast<__nv_bfloat162 *>(p + i) = __floats2bfloat162_rn(x, y);
+}
 
 template <int NR>
 __device__ __forceinline__ void issue_chunk(typename ScanSmem<NR>::Stage &st, uint32_t bar, const float *Y,
@@ -237,6 +262,14 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
     const float *blk0 = blocks + ((size_t)b * a.nv + hv) * n_chunks * BLK_FLOATS;
     const int mt = w & 1, wp = w >> 1, ntb = wp * NTW;   // [token][r] tiles: rows 16 mt.., n-tiles ntb..
     const int m0 = 16 * w;                                // rows c of S^T in the state update
+    // ldmatrix lane offsets in words: A fragment of a [m][k] tile (rows +0/+8, k +0/+4),
+    // B fragments of two k-steps of an [n][k] tile (k +0/+4/+8/+12)
+    const int arow = (lane & 7) + 8 * ((lane >> 3) & 1), acol = 4 * (lane >> 4);
+    const int brow = lane & 7, bcol = 4 * (lane >> 3);
+    const uint32_t sn_b = bc_smem_u32(sm.Sn) + 4u * (uint32_t)((8 * ntb + brow) * LDK + bcol);
+    const uint32_t tt_b = bc_smem_u32(sm.Tt) + 4u * (uint32_t)((8 * ntb + brow) * LDP + bcol);
+    const uint32_t ut_b = bc_smem_u32(sm.Ut) + 4u * (uint32_t)((8 * ntb + brow) * LDP + bcol);
+    const uint32_t ut_all = bc_smem_u32(sm.Ut) + 4u * (uint32_t)(brow * LDP + bcol);
 
     if (tid == 0) {
         bc_mbar_init(bc_smem_u32(&sm.bar[0]), 1);
@@ -244,18 +277,13 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
         bc_mbar_init_fence();
         sm.failed = 0;
     }
-    // state: st[nt][.] = S^T[m0 + g (+8)][8 nt + 2j (+1)] (columns local to this CTA)
+    // state: st[nt][x] = S[8 nt + 2j + (x & 1)][m0 + g + 8 (x >> 1)] (rows local to this CTA)
     float st[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        const int r = 8 * nt + 2 * j, c = m0 + g;
-        st[nt][0] = S[r * 128 + c];
-        st[nt][1] = S[(r + 1) * 128 + c];
-        st[nt][2] = S[r * 128 + c + 8];
-        st[nt][3] = S[(r + 1) * 128 + c + 8];
-        *reinterpret_cast<float2 *>(&sm.St[c * LDN + r]) = make_float2(tf32r(st[nt][0]), tf32r(st[nt][1]));
-        *reinterpret_cast<float2 *>(&sm.St[(c + 8) * LDN + r]) = make_float2(tf32r(st[nt][2]), tf32r(st[nt][3]));
-    }
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int x = 0; x < 4; x++) st[nt][x] = S[(8 * nt + 2 * j + (x & 1)) * 128 + m0 + g + 8 * (x >> 1)];
+    for (int e = tid; e < NR * 128; e += 256) sm.Sn[(e >> 7) * LDK + (e & 127)] = tf32r(S[e]);
     float nw[NTW][2];
 #pragma unroll
     for (int t = 0; t < NTW; t++) {
@@ -273,27 +301,28 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
         const int buf = n & 1, t0 = n * TC, nvalid = min(TC, a.T - t0);
         const size_t tok0 = (size_t)b * a.T + t0;
         typename SM::Stage &sg = sm.stage[buf];
-        __syncthreads();                                  // chunk n-1 is finished with the other stage, Ts, Us, St
-        if (w == 0 && n + 1 < n_chunks)
+        __syncthreads();                                  // chunk n-1 is finished with the other stage, Tt, Ut, Sn
+        if (w == (n & 7) && n + 1 < n_chunks)
             issue_chunk<NR>(sm.stage[buf ^ 1], bc_smem_u32(&sm.bar[buf ^ 1]), Y, tok0 + TC, min(TC, a.T - t0 - TC), Cc,
                             koff, qoff, voff, blk0 + (size_t)(n + 1) * BLK_FLOATS, lane);
         // z of this thread's outputs, requested now and used at the end of the chunk
-        float zv[2][NTW][2];
+        float2 zv[2][NTW];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int i = 16 * mt + g + 8 * h;
 #pragma unroll
             for (int t = 0; t < NTW; t++) {
-                zv[h][t][0] = 0.0f; zv[h][t][1] = 0.0f;
-                if (i < nvalid) {
-                    const size_t off = (tok0 + i) * vd + (size_t)hv * 128 + col0 + 8 * (ntb + t) + 2 * j;
-                    zv[h][t][0] = act_ld((const ACT *)a.z, off);
-                    zv[h][t][1] = act_ld((const ACT *)a.z, off + 1);
-                }
+                zv[h][t] = make_float2(0.0f, 0.0f);
+                if (i < nvalid)
+                    zv[h][t] = ld2((const ACT *)a.z, (tok0 + i) * vd + (size_t)hv * 128 + col0 + 8 * (ntb + t) + 2 * j);
             }
         }
         ok = ok && bc_mbar_wait(bc_smem_u32(&sm.bar[buf]), (uint32_t)(n >> 1) & 1u);   // one timeout at most
         const float *aux = sg.blk + BLK_AUX;
+        const uint32_t ks_a = bc_smem_u32(sg.Ks) + 4u * (uint32_t)((16 * mt + arow) * LDK + acol);
+        const uint32_t qs_a = bc_smem_u32(sg.Qs) + 4u * (uint32_t)((16 * mt + arow) * LDK + acol);
+        const uint32_t as_a = bc_smem_u32(sg.blk) + 4u * (uint32_t)((16 * mt + arow) * LDP + acol);
+        const uint32_t ps_a = as_a + 4u * BLK_P;
 
         // ---- K S^T and Q S^T; two accumulators per product shorten the dependent chain
         float sk[2][NTW][4], sq[2][NTW][4];
@@ -303,24 +332,22 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
             for (int t = 0; t < NTW; t++)
 #pragma unroll
                 for (int x = 0; x < 4; x++) { sk[e][t][x] = 0.0f; sq[e][t][x] = 0.0f; }
-#pragma unroll 2
-        for (int k0 = 0; k0 < 128; k0 += 16) {
 #pragma unroll
-            for (int e = 0; e < 2; e++) {
-                const int kk = k0 + 8 * e;
-                float ak[4], aq[4];
-                frag_a(ak, sg.Ks + 16 * mt * LDK + kk, LDK, g, j);
-                frag_a(aq, sg.Qs + 16 * mt * LDK + kk, LDK, g, j);
+        for (int kb = 0; kb < 8; kb++) {                  // 16 contraction indices per step
+            float ak[2][4], aq[2][4];
+            ldsm4(ak[0], ks_a + 64u * kb); ldsm4(ak[1], ks_a + 64u * kb + 32u);
+            ldsm4(aq[0], qs_a + 64u * kb); ldsm4(aq[1], qs_a + 64u * kb + 32u);
 #pragma unroll
-                for (int t = 0; t < NTW; t++) {
-                    const float b0 = sm.St[(kk + j) * LDN + 8 * (ntb + t) + g];
-                    const float b1 = sm.St[(kk + j + 4) * LDN + 8 * (ntb + t) + g];
-                    mma_tf32(sk[e][t], ak, b0, b1);
-                    mma_tf32(sq[e][t], aq, b0, b1);
-                }
+            for (int t = 0; t < NTW; t++) {
+                float bs[4];
+                ldsm4(bs, sn_b + 4u * (uint32_t)(8 * t * LDK) + 64u * kb);
+                mma_tf32(sk[0][t], ak[0], bs[0], bs[1]);
+                mma_tf32(sq[0][t], aq[0], bs[0], bs[1]);
+                mma_tf32(sk[1][t], ak[1], bs[2], bs[3]);
+                mma_tf32(sq[1][t], aq[1], bs[2], bs[3]);
             }
         }
-        // ---- T = beta V - (beta p) K S^T
+        // ---- T = beta V - (beta p) K S^T, stored transposed
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int i = 16 * mt + g + 8 * h;
@@ -329,14 +356,12 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
             for (int t = 0; t < NTW; t++) {
                 const int r = 8 * (ntb + t) + 2 * j;
                 const float2 v = *reinterpret_cast<const float2 *>(&sg.Vs[i * LDN + r]);
-                float2 tt;
-                tt.x = tf32r(bi * v.x - bp * (sk[0][t][2 * h] + sk[1][t][2 * h]));
-                tt.y = tf32r(bi * v.y - bp * (sk[0][t][2 * h + 1] + sk[1][t][2 * h + 1]));
-                *reinterpret_cast<float2 *>(&sm.Ts[i * LDN + r]) = tt;
+                sm.Tt[r * LDP + i] = tf32r(bi * v.x - bp * (sk[0][t][2 * h] + sk[1][t][2 * h]));
+                sm.Tt[(r + 1) * LDP + i] = tf32r(bi * v.y - bp * (sk[0][t][2 * h + 1] + sk[1][t][2 * h + 1]));
             }
         }
         __syncthreads();
-        // ---- U = A T (A is unit lower triangular)
+        // ---- U = A T (A is unit lower triangular), stored transposed
         {
             float u[NTW][4];
 #pragma unroll
@@ -344,21 +369,26 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
 #pragma unroll
                 for (int x = 0; x < 4; x++) u[t][x] = 0.0f;
 #pragma unroll
-            for (int k0 = 0; k0 < TC; k0 += 8) {
-                if (mt == 0 && k0 >= 16) continue;
-                float af[4];
-                frag_a(af, sg.blk + 16 * mt * LDP + k0, LDP, g, j);
+            for (int kb = 0; kb < 2; kb++) {
+                if (mt == 0 && kb == 1) continue;
+                float af[2][4];
+                ldsm4(af[0], as_a + 64u * kb); ldsm4(af[1], as_a + 64u * kb + 32u);
 #pragma unroll
-                for (int t = 0; t < NTW; t++)
-                    mma_tf32(u[t], af, sm.Ts[(k0 + j) * LDN + 8 * (ntb + t) + g],
-                             sm.Ts[(k0 + j + 4) * LDN + 8 * (ntb + t) + g]);
+                for (int t = 0; t < NTW; t++) {
+                    float bt[4];
+                    ldsm4(bt, tt_b + 4u * (uint32_t)(8 * t * LDP) + 64u * kb);
+                    mma_tf32(u[t], af[0], bt[0], bt[1]);
+                    mma_tf32(u[t], af[1], bt[2], bt[3]);
+                }
             }
 #pragma unroll
             for (int h = 0; h < 2; h++)
 #pragma unroll
-                for (int t = 0; t < NTW; t++)
-                    *reinterpret_cast<float2 *>(&sm.Us[(16 * mt + g + 8 * h) * LDN + 8 * (ntb + t) + 2 * j]) =
-                        make_float2(tf32r(u[t][2 * h]), tf32r(u[t][2 * h + 1]));
+                for (int t = 0; t < NTW; t++) {
+                    const int r = 8 * (ntb + t) + 2 * j, i = 16 * mt + g + 8 * h;
+                    sm.Ut[r * LDP + i] = tf32r(u[t][2 * h]);
+                    sm.Ut[(r + 1) * LDP + i] = tf32r(u[t][2 * h + 1]);
+                }
         }
         __syncthreads();
         // ---- O = p Q S^T + P U, scaled; this CTA's part of each token's sum of squares
@@ -371,32 +401,35 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
                 o[t][2] = p1 * (sq[0][t][2] + sq[1][t][2]); o[t][3] = p1 * (sq[0][t][3] + sq[1][t][3]);
             }
 #pragma unroll
-            for (int k0 = 0; k0 < TC; k0 += 8) {
-                if (mt == 0 && k0 >= 16) continue;
-                float af[4];
-                frag_a(af, sg.blk + BLK_P + 16 * mt * LDP + k0, LDP, g, j);
+            for (int kb = 0; kb < 2; kb++) {
+                if (mt == 0 && kb == 1) continue;
+                float af[2][4];
+                ldsm4(af[0], ps_a + 64u * kb); ldsm4(af[1], ps_a + 64u * kb + 32u);
 #pragma unroll
-                for (int t = 0; t < NTW; t++)
-                    mma_tf32(o[t], af, sm.Us[(k0 + j) * LDN + 8 * (ntb + t) + g],
-                             sm.Us[(k0 + j + 4) * LDN + 8 * (ntb + t) + g]);
+                for (int t = 0; t < NTW; t++) {
+                    float bu[4];
+                    ldsm4(bu, ut_b + 4u * (uint32_t)(8 * t * LDP) + 64u * kb);
+                    mma_tf32(o[t], af[0], bu[0], bu[1]);
+                    mma_tf32(o[t], af[1], bu[2], bu[3]);
+                }
             }
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                double ss = 0.0;
+                float ss = 0.0f;
 #pragma unroll
                 for (int t = 0; t < NTW; t++)
 #pragma unroll
                     for (int x = 0; x < 2; x++) {
                         const float v = o[t][2 * h + x] * a.out_scale;
                         o[t][2 * h + x] = v;
-                        ss += (double)v * (double)v;
+                        ss += v * v;
                     }
                 ss += __shfl_xor_sync(0xffffffffu, ss, 1);
                 ss += __shfl_xor_sync(0xffffffffu, ss, 2);
                 if (j == 0) {
-                    const double *slot = &sm.red[buf][16 * mt + g + 8 * h][4 * rank + wp];
+                    const float *slot = &sm.red[buf][16 * mt + g + 8 * h][4 * rank + wp];
 #pragma unroll
-                    for (int rr = 0; rr < CS; rr++) bc_st_cluster_f64(bc_map_rank(slot, (uint32_t)rr), ss);
+                    for (int rr = 0; rr < CS; rr++) st_cluster_f32(bc_map_rank(slot, (uint32_t)rr), ss);
                 }
             }
         }
@@ -409,24 +442,30 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
 #pragma unroll
                 for (int x = 0; x < 4; x++) st[nt][x] *= pend;
 #pragma unroll
-            for (int k0 = 0; k0 < TC; k0 += 8) {
-                const float w0 = aux[2 * TC + k0 + j], w1 = aux[2 * TC + k0 + j + 4];
-                float af[4];
-                af[0] = tf32r(sg.Ks[(k0 + j) * LDK + m0 + g] * w0);
-                af[1] = tf32r(sg.Ks[(k0 + j) * LDK + m0 + g + 8] * w0);
-                af[2] = tf32r(sg.Ks[(k0 + j + 4) * LDK + m0 + g] * w1);
-                af[3] = tf32r(sg.Ks[(k0 + j + 4) * LDK + m0 + g + 8] * w1);
+            for (int kb = 0; kb < 2; kb++) {
+                float af[2][4];
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-                    mma_tf32(st[nt], af, sm.Us[(k0 + j) * LDN + 8 * nt + g], sm.Us[(k0 + j + 4) * LDN + 8 * nt + g]);
+                for (int e = 0; e < 2; e++) {
+                    const int k0 = 16 * kb + 8 * e;
+                    const float w0 = aux[2 * TC + k0 + j], w1 = aux[2 * TC + k0 + j + 4];
+                    af[e][0] = tf32r(sg.Ks[(k0 + j) * LDK + m0 + g] * w0);
+                    af[e][1] = tf32r(sg.Ks[(k0 + j) * LDK + m0 + g + 8] * w0);
+                    af[e][2] = tf32r(sg.Ks[(k0 + j + 4) * LDK + m0 + g] * w1);
+                    af[e][3] = tf32r(sg.Ks[(k0 + j + 4) * LDK + m0 + g + 8] * w1);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    float bu[4];
+                    ldsm4(bu, ut_all + 4u * (uint32_t)(8 * nt * LDP) + 64u * kb);
+                    mma_tf32(st[nt], af[0], bu[0], bu[1]);
+                    mma_tf32(st[nt], af[1], bu[2], bu[3]);
+                }
             }
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                const int r = 8 * nt + 2 * j, c = m0 + g;
-                *reinterpret_cast<float2 *>(&sm.St[c * LDN + r]) = make_float2(tf32r(st[nt][0]), tf32r(st[nt][1]));
-                *reinterpret_cast<float2 *>(&sm.St[(c + 8) * LDN + r]) =
-                    make_float2(tf32r(st[nt][2]), tf32r(st[nt][3]));
-            }
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int x = 0; x < 4; x++)
+                    sm.Sn[(8 * nt + 2 * j + (x & 1)) * LDK + m0 + g + 8 * (x >> 1)] = tf32r(st[nt][x]);
         }
         bc_cluster_wait();
         // ---- RMSNorm over the head row, SiLU(z) gate, store
@@ -435,31 +474,28 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
         for (int h = 0; h < 2; h++) {
             const int i = 16 * mt + g + 8 * h;
             if (i >= nvalid) continue;
-            double ss = 0.0;
+            float ss = 0.0f;
 #pragma unroll
-            for (int q = 0; q < 4 * CS; q++) ss += sm.red[buf][i][q];
-            const float inv = bad ? NAN : (float)(1.0 / sqrt(ss / 128.0 + (double)a.eps));
+            for (int q = 0; q < CS; q++) {
+                const float4 r4 = *reinterpret_cast<const float4 *>(&sm.red[buf][i][4 * q]);
+                ss += (r4.x + r4.y) + (r4.z + r4.w);
+            }
+            const float inv = bad ? NAN : 1.0f / sqrtf(ss * (1.0f / 128.0f) + a.eps);
             const size_t off = (tok0 + i) * vd + (size_t)hv * 128 + col0;
 #pragma unroll
             for (int t = 0; t < NTW; t++)
-#pragma unroll
-                for (int x = 0; x < 2; x++) {
-                    const float y = o[t][2 * h + x] * inv * nw[t][x] * silu_f(zv[h][t][x]);
-                    act_st((ACT *)a.out, off + 8 * (ntb + t) + 2 * j + x, y);
-                }
+                st2((ACT *)a.out, off + 8 * (ntb + t) + 2 * j, o[t][2 * h] * inv * nw[t][0] * silu_f(zv[h][t].x),
+                    o[t][2 * h + 1] * inv * nw[t][1] * silu_f(zv[h][t].y));
         }
         if (!ok) sm.failed = 1;
     }
     __syncthreads();
     const bool bad = !ok || sm.failed;
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        const int r = 8 * nt + 2 * j, c = m0 + g;
-        S[r * 128 + c] = bad ? NAN : st[nt][0];
-        S[(r + 1) * 128 + c] = bad ? NAN : st[nt][1];
-        S[r * 128 + c + 8] = bad ? NAN : st[nt][2];
-        S[(r + 1) * 128 + c + 8] = bad ? NAN : st[nt][3];
-    }
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int x = 0; x < 4; x++)
+            S[(8 * nt + 2 * j + (x & 1)) * 128 + m0 + g + 8 * (x >> 1)] = bad ? NAN : st[nt][x];
 }
 
 template <int NR, typename ACT>

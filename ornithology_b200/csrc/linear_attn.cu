@@ -391,6 +391,54 @@ __global__ void __launch_bounds__(128) k_conv_silu_prefill(LinArgs a, float *Y) 
     }
 }
 
+__device__ __forceinline__ float4 act_ld4(const float *p, size_t i) { return *reinterpret_cast<const float4 *>(p + i); }
+__device__ __forceinline__ float4 act_ld4(const __nv_bfloat16 *p, size_t i) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p + i);
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                       __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
+
+// conv_k = 4, Cc a multiple of 4: one thread owns 4 adjacent channels over CONV4_TOK
+// tokens and requests all its inputs before the first use.  Same products, sums and
+// rounding as k_conv_silu_prefill.  grid (ceil(Cc/512), ceil(T/CONV4_TOK), n_seq).
+constexpr int CONV4_TOK = 16;
+
+template <typename ACT>
+__global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y) {
+    const int qd = a.nk * a.dk, Cc = 2 * qd + a.nv * a.dv;
+    const int ch = (blockIdx.x * 128 + threadIdx.x) * 4, b = blockIdx.z, t0 = blockIdx.y * CONV4_TOK;
+    if (ch >= Cc) return;
+    const int pos0 = a.pos[b];
+    const float *ring = a.conv + (size_t)b * a.conv_stride;
+    const ACT *X = (const ACT *)a.qkv + (size_t)b * a.T * Cc;
+    float4 x[CONV4_TOK + 3];
+#pragma unroll
+    for (int i = 0; i < CONV4_TOK + 3; i++) {             // token t0 - 3 + i
+        const int t = t0 - 3 + i;
+        if (t >= a.T) x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        else if (t >= 0) x[i] = act_ld4(X, (size_t)t * Cc + ch);
+        else x[i] = *reinterpret_cast<const float4 *>(ring + (size_t)(((pos0 + t) % 4 + 4) % 4) * Cc + ch);
+    }
+    float4 w[4];                                          // w[c] = taps of channel ch + c
+#pragma unroll
+    for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)(ch + c) * 4);
+    float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (a.conv_b) bias = *reinterpret_cast<const float4 *>(a.conv_b + ch);
+#pragma unroll
+    for (int i = 0; i < CONV4_TOK; i++) {
+        if (t0 + i >= a.T) break;
+        float4 y;
+#define ORN_CONV4(F, WC, B)                                                                               \
+        y.F = silu_f(__fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(B, __fmul_rn(WC.x, x[i].F)),                 \
+                                                             __fmul_rn(WC.y, x[i + 1].F)),                \
+                                                   __fmul_rn(WC.z, x[i + 2].F)),                          \
+                                         __fmul_rn(WC.w, x[i + 3].F)))
+        ORN_CONV4(x, w[0], bias.x); ORN_CONV4(y, w[1], bias.y); ORN_CONV4(z, w[2], bias.z); ORN_CONV4(w, w[3], bias.w);
+#undef ORN_CONV4
+        *reinterpret_cast<float4 *>(Y + ((size_t)b * a.T + t0 + i) * Cc + ch) = y;
+    }
+}
+
 // store the last min(T, conv_k) inputs of each sequence into their ring slots
 template <typename ACT>
 __global__ void k_conv_ring_refresh(LinArgs a) {
@@ -758,10 +806,18 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     if (((uintptr_t)scratch % 256) != 0) { orn_record_error("linear_attn_prefill: scratch must be 256-byte aligned"); return ORNITH_ERR_FORMAT; }
     LinArgs x = make_args(l, st, pos, qkv, a, b, z, out, T);
 
-    dim3 cgrid((unsigned)((Cc + 127) / 128), (T + CONV_TOK - 1) / CONV_TOK, n_seq);
-    if (bf) k_conv_silu_prefill<__nv_bfloat16><<<cgrid, 128, 0, s>>>(x, Y);
-    else    k_conv_silu_prefill<float><<<cgrid, 128, 0, s>>>(x, Y);
-    ORN_TRY(orn_check_launch("k_conv_silu_prefill"));
+    if (l->conv_k == 4 && Cc % 4 == 0 && st->conv_seq_stride % 4 == 0 && ((uintptr_t)qkv % 16) == 0 &&
+        ((uintptr_t)st->conv % 16) == 0 && ((uintptr_t)l->conv_w % 16) == 0 && ((uintptr_t)l->conv_b % 16) == 0) {
+        dim3 cgrid((unsigned)((Cc + 511) / 512), (T + CONV4_TOK - 1) / CONV4_TOK, n_seq);
+        if (bf) k_conv4_silu_prefill<__nv_bfloat16><<<cgrid, 128, 0, s>>>(x, Y);
+        else    k_conv4_silu_prefill<float><<<cgrid, 128, 0, s>>>(x, Y);
+        ORN_TRY(orn_check_launch("k_conv4_silu_prefill"));
+    } else {
+        dim3 cgrid((unsigned)((Cc + 127) / 128), (T + CONV_TOK - 1) / CONV_TOK, n_seq);
+        if (bf) k_conv_silu_prefill<__nv_bfloat16><<<cgrid, 128, 0, s>>>(x, Y);
+        else    k_conv_silu_prefill<float><<<cgrid, 128, 0, s>>>(x, Y);
+        ORN_TRY(orn_check_launch("k_conv_silu_prefill"));
+    }
     dim3 rgrid((unsigned)((Cc + 255) / 256), n_seq);
     if (bf) k_conv_ring_refresh<__nv_bfloat16><<<rgrid, 256, 0, s>>>(x);
     else    k_conv_ring_refresh<float><<<rgrid, 256, 0, s>>>(x);

@@ -22,7 +22,7 @@ __device__ __forceinline__ bool owns_key_head(const LinArgs &a, int hv) {
     return a.head_map == ORNITH_HEADMAP_GROUPED ? (hv % (a.nv / a.nk)) == 0 : hv < a.nk;
 }
 
-// Tensor-core chunked scan for dk = dv = 128 (linear_prefill_tc.cu).  Y holds the
+// Tensor-core chunked scan for dk = dv = 128 (delta_prefill_tc.cu).  Y holds the
 // conv + SiLU image of qkv (its q / k parts are normalised in place), rq / rk the
 // per-(token, key head) inverse norms, la / be the per-(token, value head) log-decay
 // and write gate, blocks a work area of linear_prefill_tc_blocks_bytes() bytes.
