@@ -193,8 +193,10 @@ struct ScanSmem {
     float Sn[NR * LDK];                  // Sn[r][c] = tf32(S[col0 + r][c])
     float Tt[NR * LDP];                  // Tt[r][token]
     float Ut[NR * LDP];                  // Ut[r][token]
+    float Uw[NR * LDP];                  // Uw[r][token] = w_end[token] * U
     float red[2][TC][16];                // [chunk parity][token][4 * cluster rank + warp pair]
-    unsigned long long bar[2];
+    unsigned long long bar[2];           // stage filled
+    unsigned long long rbar[2];          // red[parity] complete (all CTAs of the cluster have stored their sums)
     int failed;
 };
 
@@ -204,8 +206,15 @@ __device__ __forceinline__ void ldsm4(float (&r)[4], uint32_t addr) {
                  : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
     r[0] = __uint_as_float(x0); r[1] = __uint_as_float(x1); r[2] = __uint_as_float(x2); r[3] = __uint_as_float(x3);
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+// round to tf32 (ties away from zero) in two integer instructions; finite inputs only
+__device__ __forceinline__ float tf32q(float x) {
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+}
+// store into another CTA of the cluster; the 4 bytes are credited to that CTA's mbarrier,
+// and are visible to whoever sees the phase complete
+__device__ __forceinline__ void st_async_f32(uint32_t addr, float v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];\n"
+                 ::"r"(addr), "r"(__float_as_uint(v)), "r"(bar) : "memory");
 }
 __device__ __forceinline__ float2 ld2(const float *p, size_t i) { return *reinterpret_cast<const float2 *>(p + i); }
 __device__ __forceinline__ float2 ld2(const __nv_bfloat16 *p, size_t i) {
@@ -219,31 +228,28 @@ __device__ __forceinline__ void st2(__nv_bfloat16 *p, size_t i, float x, float y
     *reinterpret_cast<__nv_bfloat162 *>(p + i) = __floats2bfloat162_rn(x, y);
 }
 
+// Request one chunk: warp w copies rows 4w .. 4w+3 of K, Q and V (one lane per row and
+// matrix), thread 0 arms the barrier and copies the A / P / gate block.  Rows past the
+// end of the sequence are not copied; they keep finite leftovers, which beta = 0 cancels.
 template <int NR>
 __device__ __forceinline__ void issue_chunk(typename ScanSmem<NR>::Stage &st, uint32_t bar, const float *Y,
                                             size_t tok0, int nvalid, int Cc, int koff, int qoff, int voff,
-                                            const float *blk, int lane) {
+                                            const float *blk, int w, int lane) {
     constexpr int LDN = ScanSmem<NR>::LDN;
-    if (lane >= nvalid) {                                 // rows past the end of the sequence are zero
-        for (int c = 0; c < 128; c += 4) {
-            *reinterpret_cast<float4 *>(&st.Ks[lane * LDK + c]) = make_float4(0.f, 0.f, 0.f, 0.f);
-            *reinterpret_cast<float4 *>(&st.Qs[lane * LDK + c]) = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        for (int c = 0; c < NR; c += 4) *reinterpret_cast<float4 *>(&st.Vs[lane * LDN + c]) = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    __syncwarp();
-    if (lane == 0) {
+    if (lane < 12) {                                      // row = 4w + lane / 3, matrix = lane % 3
         bc_fence_proxy_async();
-        bc_mbar_expect_tx(bar, (uint32_t)nvalid * (512u + 512u + NR * 4u) + BLK_BYTES);
+        if (w == 0 && lane == 0) {
+            bc_mbar_expect_tx(bar, (uint32_t)nvalid * (512u + 512u + NR * 4u) + BLK_BYTES);
+            bc_copy(bc_smem_u32(st.blk), blk, BLK_BYTES, bar);
+        }
+        const int row = 4 * w + lane / 3, which = lane % 3;
+        if (row < nvalid) {
+            const float *y = Y + (tok0 + row) * Cc;
+            if (which == 0) bc_copy(bc_smem_u32(&st.Ks[row * LDK]), y + koff, 512u, bar);
+            else if (which == 1) bc_copy(bc_smem_u32(&st.Qs[row * LDK]), y + qoff, 512u, bar);
+            else bc_copy(bc_smem_u32(&st.Vs[row * LDN]), y + voff, NR * 4u, bar);
+        }
     }
-    __syncwarp();
-    if (lane < nvalid) {
-        const float *y = Y + (tok0 + lane) * Cc;
-        bc_copy(bc_smem_u32(&st.Ks[lane * LDK]), y + koff, 512u, bar);
-        bc_copy(bc_smem_u32(&st.Qs[lane * LDK]), y + qoff, 512u, bar);
-        bc_copy(bc_smem_u32(&st.Vs[lane * LDN]), y + voff, NR * 4u, bar);
-    }
-    if (lane == 0) bc_copy(bc_smem_u32(st.blk), blk, BLK_BYTES, bar);
 }
 
 template <int NR, typename ACT>
@@ -269,14 +275,22 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
     const uint32_t sn_b = bc_smem_u32(sm.Sn) + 4u * (uint32_t)((8 * ntb + brow) * LDK + bcol);
     const uint32_t tt_b = bc_smem_u32(sm.Tt) + 4u * (uint32_t)((8 * ntb + brow) * LDP + bcol);
     const uint32_t ut_b = bc_smem_u32(sm.Ut) + 4u * (uint32_t)((8 * ntb + brow) * LDP + bcol);
-    const uint32_t ut_all = bc_smem_u32(sm.Ut) + 4u * (uint32_t)(brow * LDP + bcol);
+    const uint32_t uw_all = bc_smem_u32(sm.Uw) + 4u * (uint32_t)(brow * LDP + bcol);
 
     if (tid == 0) {
         bc_mbar_init(bc_smem_u32(&sm.bar[0]), 1);
         bc_mbar_init(bc_smem_u32(&sm.bar[1]), 1);
+        bc_mbar_init(bc_smem_u32(&sm.rbar[0]), 1);
+        bc_mbar_init(bc_smem_u32(&sm.rbar[1]), 1);
         bc_mbar_init_fence();
         sm.failed = 0;
     }
+    // rows of a stage that a short last chunk does not fill must hold finite values
+    for (int e = tid; e < TC * LDK; e += 256) {
+        sm.stage[0].Ks[e] = 0.0f; sm.stage[1].Ks[e] = 0.0f;
+        sm.stage[0].Qs[e] = 0.0f; sm.stage[1].Qs[e] = 0.0f;
+    }
+    for (int e = tid; e < TC * LDN; e += 256) { sm.stage[0].Vs[e] = 0.0f; sm.stage[1].Vs[e] = 0.0f; }
     // state: st[nt][x] = S[8 nt + 2j + (x & 1)][m0 + g + 8 (x >> 1)] (rows local to this CTA)
     float st[NT][4];
 #pragma unroll
@@ -293,18 +307,26 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
     __syncthreads();
     bc_cluster_arrive();                                  // every CTA of the cluster is resident
     bc_cluster_wait();
-    if (w == 0) issue_chunk<NR>(sm.stage[0], bc_smem_u32(&sm.bar[0]), Y, (size_t)b * a.T, min(TC, a.T), Cc, koff, qoff,
-                                voff, blk0, lane);
+    issue_chunk<NR>(sm.stage[0], bc_smem_u32(&sm.bar[0]), Y, (size_t)b * a.T, min(TC, a.T), Cc, koff, qoff, voff, blk0,
+                    w, lane);
     bool ok = true;
+    // where this thread's sums of squares go: slot [token][4 rank + wp] in every CTA of the cluster
+    uint32_t red_peer[CS], rbar_peer[CS];
+#pragma unroll
+    for (int rr = 0; rr < CS; rr++) {
+        red_peer[rr] = bc_map_rank(&sm.red[0][16 * mt + g][4 * rank + wp], (uint32_t)rr);
+        rbar_peer[rr] = bc_map_rank(&sm.rbar[0], (uint32_t)rr);
+    }
 
     for (int n = 0; n < n_chunks; n++) {
         const int buf = n & 1, t0 = n * TC, nvalid = min(TC, a.T - t0);
         const size_t tok0 = (size_t)b * a.T + t0;
         typename SM::Stage &sg = sm.stage[buf];
         __syncthreads();                                  // chunk n-1 is finished with the other stage, Tt, Ut, Sn
-        if (w == (n & 7) && n + 1 < n_chunks)
+        if (n + 1 < n_chunks)
             issue_chunk<NR>(sm.stage[buf ^ 1], bc_smem_u32(&sm.bar[buf ^ 1]), Y, tok0 + TC, min(TC, a.T - t0 - TC), Cc,
-                            koff, qoff, voff, blk0 + (size_t)(n + 1) * BLK_FLOATS, lane);
+                            koff, qoff, voff, blk0 + (size_t)(n + 1) * BLK_FLOATS, w, lane);
+        if (tid == 32) bc_mbar_expect_tx(bc_smem_u32(&sm.rbar[buf]), (uint32_t)(TC * 4 * CS * 4));
         // z of this thread's outputs, requested now and used at the end of the chunk
         float2 zv[2][NTW];
 #pragma unroll
@@ -356,8 +378,8 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
             for (int t = 0; t < NTW; t++) {
                 const int r = 8 * (ntb + t) + 2 * j;
                 const float2 v = *reinterpret_cast<const float2 *>(&sg.Vs[i * LDN + r]);
-                sm.Tt[r * LDP + i] = tf32r(bi * v.x - bp * (sk[0][t][2 * h] + sk[1][t][2 * h]));
-                sm.Tt[(r + 1) * LDP + i] = tf32r(bi * v.y - bp * (sk[0][t][2 * h + 1] + sk[1][t][2 * h + 1]));
+                sm.Tt[r * LDP + i] = tf32q(bi * v.x - bp * (sk[0][t][2 * h] + sk[1][t][2 * h]));
+                sm.Tt[(r + 1) * LDP + i] = tf32q(bi * v.y - bp * (sk[0][t][2 * h + 1] + sk[1][t][2 * h + 1]));
             }
         }
         __syncthreads();
@@ -382,13 +404,18 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
                 }
             }
 #pragma unroll
-            for (int h = 0; h < 2; h++)
+            for (int h = 0; h < 2; h++) {
+                const int i = 16 * mt + g + 8 * h;
+                const float we = aux[2 * TC + i];
 #pragma unroll
                 for (int t = 0; t < NTW; t++) {
-                    const int r = 8 * (ntb + t) + 2 * j, i = 16 * mt + g + 8 * h;
-                    sm.Ut[r * LDP + i] = tf32r(u[t][2 * h]);
-                    sm.Ut[(r + 1) * LDP + i] = tf32r(u[t][2 * h + 1]);
+                    const int r = 8 * (ntb + t) + 2 * j;
+                    sm.Ut[r * LDP + i] = tf32q(u[t][2 * h]);
+                    sm.Ut[(r + 1) * LDP + i] = tf32q(u[t][2 * h + 1]);
+                    sm.Uw[r * LDP + i] = tf32q(we * u[t][2 * h]);
+                    sm.Uw[(r + 1) * LDP + i] = tf32q(we * u[t][2 * h + 1]);
                 }
+            }
         }
         __syncthreads();
         // ---- O = p Q S^T + P U, scaled; this CTA's part of each token's sum of squares
@@ -427,13 +454,13 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
                 ss += __shfl_xor_sync(0xffffffffu, ss, 1);
                 ss += __shfl_xor_sync(0xffffffffu, ss, 2);
                 if (j == 0) {
-                    const float *slot = &sm.red[buf][16 * mt + g + 8 * h][4 * rank + wp];
 #pragma unroll
-                    for (int rr = 0; rr < CS; rr++) st_cluster_f32(bc_map_rank(slot, (uint32_t)rr), ss);
+                    for (int rr = 0; rr < CS; rr++)
+                        st_async_f32(red_peer[rr] + 4u * (uint32_t)(buf * TC * 16 + 8 * h * 16), ss,
+                                     rbar_peer[rr] + 8u * (uint32_t)buf);
                 }
             }
         }
-        bc_cluster_arrive();
         // ---- S^T <- p_end S^T + (diag(w_end) K)^T U, rows m0 .. m0+15
         {
             const float pend = aux[TC - 1];
@@ -447,16 +474,15 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
                     const int k0 = 16 * kb + 8 * e;
-                    const float w0 = aux[2 * TC + k0 + j], w1 = aux[2 * TC + k0 + j + 4];
-                    af[e][0] = tf32r(sg.Ks[(k0 + j) * LDK + m0 + g] * w0);
-                    af[e][1] = tf32r(sg.Ks[(k0 + j) * LDK + m0 + g + 8] * w0);
-                    af[e][2] = tf32r(sg.Ks[(k0 + j + 4) * LDK + m0 + g] * w1);
-                    af[e][3] = tf32r(sg.Ks[(k0 + j + 4) * LDK + m0 + g + 8] * w1);
+                    af[e][0] = sg.Ks[(k0 + j) * LDK + m0 + g];
+                    af[e][1] = sg.Ks[(k0 + j) * LDK + m0 + g + 8];
+                    af[e][2] = sg.Ks[(k0 + j + 4) * LDK + m0 + g];
+                    af[e][3] = sg.Ks[(k0 + j + 4) * LDK + m0 + g + 8];
                 }
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
                     float bu[4];
-                    ldsm4(bu, ut_all + 4u * (uint32_t)(8 * nt * LDP) + 64u * kb);
+                    ldsm4(bu, uw_all + 4u * (uint32_t)(8 * nt * LDP) + 64u * kb);
                     mma_tf32(st[nt], af[0], bu[0], bu[1]);
                     mma_tf32(st[nt], af[1], bu[2], bu[3]);
                 }
@@ -465,9 +491,9 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
                 for (int x = 0; x < 4; x++)
-                    sm.Sn[(8 * nt + 2 * j + (x & 1)) * LDK + m0 + g + 8 * (x >> 1)] = tf32r(st[nt][x]);
+                    sm.Sn[(8 * nt + 2 * j + (x & 1)) * LDK + m0 + g + 8 * (x >> 1)] = tf32q(st[nt][x]);
         }
-        bc_cluster_wait();
+        ok = ok && bc_mbar_wait(bc_smem_u32(&sm.rbar[buf]), (uint32_t)(n >> 1) & 1u);
         // ---- RMSNorm over the head row, SiLU(z) gate, store
         const bool bad = !ok || *(volatile int *)&sm.failed;
 #pragma unroll
@@ -490,6 +516,8 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
         if (!ok) sm.failed = 1;
     }
     __syncthreads();
+    bc_cluster_arrive();                                  // no CTA leaves while a peer may still store into it
+    bc_cluster_wait();
     const bool bad = !ok || sm.failed;
 #pragma unroll
     for (int nt = 0; nt < NT; nt++)
