@@ -39,6 +39,9 @@ template <> __device__ __forceinline__ void act_st<__nv_bfloat16>(__nv_bfloat16 
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+// SiLU with the hardware exponential and reciprocal (a few ulp); for the tensor-core
+// prefill paths, whose products are already rounded to tf32 / f16
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // ---- reductions ---------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {

@@ -206,10 +206,10 @@ __device__ __forceinline__ void ldsm4(float (&r)[4], uint32_t addr) {
                  : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
     r[0] = __uint_as_float(x0); r[1] = __uint_as_float(x1); r[2] = __uint_as_float(x2); r[3] = __uint_as_float(x3);
 }
-// round to tf32 (ties away from zero) in two integer instructions; finite inputs only
-__device__ __forceinline__ float tf32q(float x) {
-    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
-}
+// Round to tf32 for an MMA operand in one integer add (finite inputs): the tensor core
+// ignores the 13 low mantissa bits, so adding half a tf32 ulp to the magnitude first
+// turns its truncation into round-to-nearest (ties away from zero).
+__device__ __forceinline__ float tf32q(float x) { return __uint_as_float(__float_as_uint(x) + 0x1000u); }
 // store into another CTA of the cluster; the 4 bytes are credited to that CTA's mbarrier,
 // and are visible to whoever sees the phase complete
 __device__ __forceinline__ void st_async_f32(uint32_t addr, float v, uint32_t bar) {
@@ -506,12 +506,12 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
                 const float4 r4 = *reinterpret_cast<const float4 *>(&sm.red[buf][i][4 * q]);
                 ss += (r4.x + r4.y) + (r4.z + r4.w);
             }
-            const float inv = bad ? NAN : 1.0f / sqrtf(ss * (1.0f / 128.0f) + a.eps);
+            const float inv = bad ? NAN : rsqrtf(ss * (1.0f / 128.0f) + a.eps);
             const size_t off = (tok0 + i) * vd + (size_t)hv * 128 + col0;
 #pragma unroll
             for (int t = 0; t < NTW; t++)
-                st2((ACT *)a.out, off + 8 * (ntb + t) + 2 * j, o[t][2 * h] * inv * nw[t][0] * silu_f(zv[h][t].x),
-                    o[t][2 * h + 1] * inv * nw[t][1] * silu_f(zv[h][t].y));
+                st2((ACT *)a.out, off + 8 * (ntb + t) + 2 * j, o[t][2 * h] * inv * nw[t][0] * silu_fast(zv[h][t].x),
+                    o[t][2 * h + 1] * inv * nw[t][1] * silu_fast(zv[h][t].y));
         }
         if (!ok) sm.failed = 1;
     }

@@ -398,12 +398,15 @@ __device__ __forceinline__ float4 act_ld4(const __nv_bfloat16 *p, size_t i) {
                        __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
 }
 
+template <bool FAST>
+__device__ __forceinline__ float silu_sel(float x) { return FAST ? silu_fast(x) : silu_f(x); }
+
 // conv_k = 4, Cc a multiple of 4: one thread owns 4 adjacent channels over CONV4_TOK
 // tokens and requests all its inputs before the first use.  Same products, sums and
 // rounding as k_conv_silu_prefill.  grid (ceil(Cc/512), ceil(T/CONV4_TOK), n_seq).
 constexpr int CONV4_TOK = 16;
 
-template <typename ACT>
+template <typename ACT, bool FAST>
 __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y) {
     const int qd = a.nk * a.dk, Cc = 2 * qd + a.nv * a.dv;
     const int ch = (blockIdx.x * 128 + threadIdx.x) * 4, b = blockIdx.z, t0 = blockIdx.y * CONV4_TOK;
@@ -429,7 +432,7 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y)
         if (t0 + i >= a.T) break;
         float4 y;
 #define ORN_CONV4(F, WC, B)                                                                               \
-        y.F = silu_f(__fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(B, __fmul_rn(WC.x, x[i].F)),                 \
+        y.F = silu_sel<FAST>(__fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(B, __fmul_rn(WC.x, x[i].F)),                 \
                                                              __fmul_rn(WC.y, x[i + 1].F)),                \
                                                    __fmul_rn(WC.z, x[i + 2].F)),                          \
                                          __fmul_rn(WC.w, x[i + 3].F)))
@@ -806,11 +809,16 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     if (((uintptr_t)scratch % 256) != 0) { orn_record_error("linear_attn_prefill: scratch must be 256-byte aligned"); return ORNITH_ERR_FORMAT; }
     LinArgs x = make_args(l, st, pos, qkv, a, b, z, out, T);
 
+    // dk = dv = 128 scans on the tensor cores in tf32 unless ORNITH_CUDA_PREFILL_FP32=1 asks for fp32 products
+    const char *exact = getenv("ORNITH_CUDA_PREFILL_FP32");
+    const bool tc = l->dk == 128 && l->dv == 128 && !(exact && exact[0] == '1');
     if (l->conv_k == 4 && Cc % 4 == 0 && st->conv_seq_stride % 4 == 0 && ((uintptr_t)qkv % 16) == 0 &&
         ((uintptr_t)st->conv % 16) == 0 && ((uintptr_t)l->conv_w % 16) == 0 && ((uintptr_t)l->conv_b % 16) == 0) {
         dim3 cgrid((unsigned)((Cc + 511) / 512), (T + CONV4_TOK - 1) / CONV4_TOK, n_seq);
-        if (bf) k_conv4_silu_prefill<__nv_bfloat16><<<cgrid, 128, 0, s>>>(x, Y);
-        else    k_conv4_silu_prefill<float><<<cgrid, 128, 0, s>>>(x, Y);
+        if (bf && tc)  k_conv4_silu_prefill<__nv_bfloat16, true><<<cgrid, 128, 0, s>>>(x, Y);
+        else if (bf)   k_conv4_silu_prefill<__nv_bfloat16, false><<<cgrid, 128, 0, s>>>(x, Y);
+        else if (tc)   k_conv4_silu_prefill<float, true><<<cgrid, 128, 0, s>>>(x, Y);
+        else           k_conv4_silu_prefill<float, false><<<cgrid, 128, 0, s>>>(x, Y);
         ORN_TRY(orn_check_launch("k_conv4_silu_prefill"));
     } else {
         dim3 cgrid((unsigned)((Cc + 127) / 128), (T + CONV_TOK - 1) / CONV_TOK, n_seq);
@@ -829,8 +837,7 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     dim3 grid(l->nv, n_seq);
     if (l->dk == 128 && l->dv == 128) {
         // default: tf32 tensor-core scan; ORNITH_CUDA_PREFILL_FP32=1 keeps every product in fp32
-        const char *exact = getenv("ORNITH_CUDA_PREFILL_FP32");
-        if (!exact || exact[0] != '1') return launch_linear_prefill_tc(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, s);
+        if (tc) return launch_linear_prefill_tc(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, s);
         if (chunk >= 32) return bf ? launch_chunk<32, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)
                                    : launch_chunk<32, float>(x, grid, Y, rq, rk, la, be, s);
         return bf ? launch_chunk<16, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)
