@@ -486,7 +486,7 @@ size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *l, in
     if (max_len < T) max_len = T;
     size_t q = align_up((size_t)n_seq * T * l->n_heads * l->head_dim * sizeof(float), 256);
     // decoded f16 image of the visible cache rows, used by the tensor-core path
-    if (l->head_dim == 256) q += gqa_prefill_mma_scratch(n_seq, l->n_kv_heads, max_len);
+    if (l->head_dim == 256) q += gqa_prefill_mma_scratch(n_seq, l->n_kv_heads, l->n_heads, T, max_len);
     return q;
 }
 

@@ -22,9 +22,18 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
 ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st);
 
 // Tensor-core causal prefill for head_dim 256 (gqa_prefill_mma.cu): decodes the visible cache
-// rows into an f16 image in `kvh_scratch` (gqa_prefill_mma_scratch bytes), then attends.
+// rows into an f16 image in `kvh_scratch` (gqa_prefill_mma_scratch bytes), then attends with
+// the tcgen05 kernel (gqa_prefill_tc.cu) or, on request, the mma.sync one.
 bool gqa_prefill_mma_supported(const KvView &kv);
-size_t gqa_prefill_mma_scratch(int n_seq, int nkv, int Lmax);
+size_t gqa_prefill_mma_scratch(int n_seq, int nkv, int nh, int T, int Lmax);
 ornith_status launch_gqa_prefill_mma(const KvView &kv, const int32_t *kv_len, const float *q_prep, void *kvh_scratch,
                                      const void *qproj, void *out, int nh, int T, int Lmax, int gated, float scale,
                                      int n_seq, bool bf16_act, cudaStream_t st);
+
+// tcgen05 / TMEM / TMA causal prefill (gqa_prefill_tc.cu).  Kh / Vh: decoded f16 rows
+// [n_seq][nkv][Lp][256], zero past the rows the prefill sees, Lp a multiple of 64;
+// q_scratch: gqa_prefill_tc_scratch bytes for the f16 query image and its row factors.
+size_t gqa_prefill_tc_scratch(int n_seq, int nh, int T);
+ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, const float *q_prep, const __half *Kh,
+                                    const __half *Vh, void *q_scratch, const void *qproj, void *out, int nh, int T,
+                                    int Lmax, int Lp, int gated, float scale, int n_seq, bool bf16_act, cudaStream_t st);

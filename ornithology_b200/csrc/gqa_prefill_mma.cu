@@ -56,10 +56,11 @@ struct PrefillMmaArgs {
     KvView kv;
     const int32_t *kv_len;
     const float *q_prep;            // [n_seq*T][nh][256] f32, normalised + rotated
-    __half *Kh, *Vh;                // [n_seq][nkv][Lmax][256] decoded rows
+    __half *Kh, *Vh;                // [n_seq][nkv][Lp][256] decoded rows, zero past the rows the prefill sees
     const void *qproj;
     void *out;
     int nh, T, Lmax, gated;
+    int Lp;                         // row pitch of the images: Lmax rounded up to a multiple of 64
     float scale;
 };
 
@@ -71,7 +72,13 @@ __global__ void __launch_bounds__(128) k_kv_rows_to_f16(PrefillMmaArgs a) {
     const int64_t base = a.kv.seq_off[b];
     const int cap = (int)(a.kv.seq_off[b + 1] - base);
     const int seen = min(min(a.kv_len[b] + a.T, cap), a.Lmax);
-    if (pos >= seen) return;
+    if (pos >= a.Lp) return;
+    const size_t o = (((size_t)b * nkv + kvh) * a.Lp + pos) * HD + lane * 8;
+    if (pos >= seen) {                                    // whole 64-key tiles are read: keep the tail finite
+        *reinterpret_cast<uint4 *>(a.Kh + o) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4 *>(a.Vh + o) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
     const size_t r = (size_t)(base + pos) * nkv + kvh;
     const size_t rb = kv_row_bytes(MODE, HD);
     const uint8_t *krow = a.kv.K + r * rb, *vrow = a.kv.V + r * rb;
@@ -84,7 +91,6 @@ __global__ void __launch_bounds__(128) k_kv_rows_to_f16(PrefillMmaArgs a) {
         ko[i] = pack_h2(kv_elem<MODE>(krow, d) * ks, kv_elem<MODE>(krow, d + 1) * ks);
         vo[i] = pack_h2(kv_elem<MODE>(vrow, d) * vs, kv_elem<MODE>(vrow, d + 1) * vs);
     }
-    const size_t o = (((size_t)b * nkv + kvh) * a.Lmax + pos) * HD + lane * 8;
     *reinterpret_cast<uint4 *>(a.Kh + o) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
     *reinterpret_cast<uint4 *>(a.Vh + o) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
 }
@@ -149,8 +155,8 @@ __global__ void __launch_bounds__(128, 2) k_gqa_prefill_mma(PrefillMmaArgs a) {
         __syncthreads();
     }
 
-    const __half *Kg = a.Kh + (((size_t)b * nkv + kvh) * a.Lmax) * HD;
-    const __half *Vg = a.Vh + (((size_t)b * nkv + kvh) * a.Lmax) * HD;
+    const __half *Kg = a.Kh + (((size_t)b * nkv + kvh) * a.Lp) * HD;
+    const __half *Vg = a.Vh + (((size_t)b * nkv + kvh) * a.Lp) * HD;
     stage_tile(K_s, Kg, min(BN, kmax + 1), tid);
     cp_async_commit();
     stage_tile(V_s, Vg, min(BN, kmax + 1), tid);
@@ -282,8 +288,19 @@ __global__ void __launch_bounds__(128, 2) k_gqa_prefill_mma(PrefillMmaArgs a) {
 
 bool gqa_prefill_mma_supported(const KvView &kv) { return kv.hd == HD; }
 
-size_t gqa_prefill_mma_scratch(int n_seq, int nkv, int Lmax) {
-    return 2 * align_up((size_t)n_seq * nkv * Lmax * HD * sizeof(__half), 256);
+static int image_pitch(int Lmax) { return (Lmax + 63) / 64 * 64; }
+static size_t image_bytes(int n_seq, int nkv, int Lmax) {   // one of the two images; 1 KiB keeps TMA bases aligned
+    return align_up((size_t)n_seq * nkv * image_pitch(Lmax) * HD * sizeof(__half), 1024);
+}
+
+size_t gqa_prefill_mma_scratch(int n_seq, int nkv, int nh, int T, int Lmax) {
+    return 2 * image_bytes(n_seq, nkv, Lmax) + gqa_prefill_tc_scratch(n_seq, nh, T);
+}
+
+// ORNITH_CUDA_PREFILL_VARIANT=mma keeps the mma.sync kernel; the default is the tcgen05 kernel
+static bool prefer_mma_sync() {
+    const char *v = getenv("ORNITH_CUDA_PREFILL_VARIANT");
+    return v && v[0] == 'm';
 }
 
 ornith_status launch_gqa_prefill_mma(const KvView &kv, const int32_t *kv_len, const float *q_prep, void *kvh_scratch,
@@ -292,16 +309,20 @@ ornith_status launch_gqa_prefill_mma(const KvView &kv, const int32_t *kv_len, co
     PrefillMmaArgs a;
     a.kv = kv; a.kv_len = kv_len; a.q_prep = q_prep; a.qproj = qproj; a.out = out;
     a.nh = nh; a.T = T; a.Lmax = Lmax; a.gated = gated; a.scale = scale;
-    const size_t half_bytes = align_up((size_t)n_seq * kv.nkv * Lmax * HD * sizeof(__half), 256);
+    a.Lp = image_pitch(Lmax);
+    const size_t half_bytes = image_bytes(n_seq, kv.nkv, Lmax);
     a.Kh = (__half *)kvh_scratch;
     a.Vh = (__half *)((char *)kvh_scratch + half_bytes);
-    dim3 cgrid((Lmax + 3) / 4, kv.nkv, n_seq);
+    dim3 cgrid((a.Lp + 3) / 4, kv.nkv, n_seq);
     switch (kv.mode) {
     case ORNITH_KV_F32:       k_kv_rows_to_f16<ORNITH_KV_F32><<<cgrid, 128, 0, st>>>(a); break;
     case ORNITH_KV_INT8_HEAD: k_kv_rows_to_f16<ORNITH_KV_INT8_HEAD><<<cgrid, 128, 0, st>>>(a); break;
     default:                  k_kv_rows_to_f16<ORNITH_KV_Q8_0><<<cgrid, 128, 0, st>>>(a); break;
     }
     ORN_TRY(orn_check_launch("k_kv_rows_to_f16"));
+    if (!prefer_mma_sync() && ((uintptr_t)kvh_scratch % 16) == 0)
+        return launch_gqa_prefill_tc(kv, kv_len, q_prep, a.Kh, a.Vh, (char *)kvh_scratch + 2 * half_bytes, qproj, out, nh,
+                                     T, Lmax, a.Lp, gated, scale, n_seq, bf16_act, st);
     static bool configured = false;
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_mma<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -1,0 +1,420 @@
+// gqa_prefill_tc.cu — causal GQA prefill (head_dim 256) on the 5th-generation tensor cores:
+// TMA-staged operands, tcgen05.mma with the score and output accumulators in tensor memory.
+//
+// Replaces the core of full_attn_prefill() (reference: src/ornith_rforward.c:529-551, which
+// runs ornith_gqa_step once per token).  Inputs are the f16 images the front end prepares:
+// query rows (k_q_rows_to_f16, each row scaled by a power of two into [-1, 1]) and the decoded
+// rows of the cache (k_kv_rows_to_f16), so quantised caches are attended over in their decoded
+// form, the current token included, exactly as the reference does.
+//
+// One CTA = 128 query tokens of one head, 6 warps:
+//   warp 4  producer   one lane issues the TMA loads (128B-swizzled boxes of 64 dims):
+//                      the query tile once, then 64-key K and V tiles through two stages each
+//   warp 5  MMA        one lane issues tcgen05.mma: S_j = Q K_j^T (16 x M128 N64 K16) into one
+//                      of two score buffers, then O += P_{j-1} V_{j-1} (4 x M128 N256 K16);
+//                      the scores of tile j+1 are queued before the value product of tile j,
+//                      so the tensor pipe works while the softmax of tile j runs
+//   warps 0-3  softmax one thread per query row (= TMEM lane): tcgen05.ld the 64 scores,
+//                      online softmax in the log2 domain against a reference maximum that is
+//                      only moved (and O rescaled through tcgen05.ld/st) when a row maximum
+//                      exceeds it by 2^8, probabilities rounded to f16 into a swizzled smem
+//                      tile that is the A operand of the value product; finally the epilogue
+//                      (1/l, sigmoid output gate, store).
+// Tensor memory: columns 0-63 and 64-127 the two score buffers, 128-383 the output tile.
+// Every wait on an mbarrier is bounded; a wait that gives up poisons the CTA's outputs.
+#include <cuda.h>
+
+#include "full_attn.cuh"
+
+namespace {
+
+constexpr int HD = 256, BM = 128, BN = 64;
+constexpr int SM_Q = 0, SM_K = 65536, SM_V = 131072, SM_P = 196608, SM_BYTES = 212992;   // + 1 KiB alignment slack
+constexpr int TM_S = 0, TM_O = 128, TM_COLS = 512;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float GROW = 8.0f;               // move the reference maximum when exceeded by 2^8
+
+struct TcArgs {
+    const int64_t *seq_off;
+    const int32_t *kv_len;
+    const float *rs;                       // [n_seq*nh*T] per-row factor: scale * 2^e * log2(e)
+    const void *qproj;
+    void *out;
+    int nh, nkv, T, Lmax, Lp, gated;
+};
+
+__device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(10000u) : "memory");
+    return ok != 0;
+}
+// bounded: gives up after ~1 s
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < (1 << 17); i++)
+        if (mbar_try(bar, parity)) return true;
+    return false;
+}
+// x (innermost coordinate, elements) must be a multiple of 8 for f16
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// shared-memory matrix descriptor, 128-byte swizzle; offsets in bytes
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
+    uint32_t u[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
+                   "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
+                   "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
+                   "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+                 : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) r[i] = __uint_as_float(u[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr),
+                   "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])), "r"(__float_as_uint(r[3])),
+                   "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])), "r"(__float_as_uint(r[6])), "r"(__float_as_uint(r[7])),
+                   "r"(__float_as_uint(r[8])), "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])), "r"(__float_as_uint(r[11])),
+                   "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])), "r"(__float_as_uint(r[15])),
+                   "r"(__float_as_uint(r[16])), "r"(__float_as_uint(r[17])), "r"(__float_as_uint(r[18])), "r"(__float_as_uint(r[19])),
+                   "r"(__float_as_uint(r[20])), "r"(__float_as_uint(r[21])), "r"(__float_as_uint(r[22])), "r"(__float_as_uint(r[23])),
+                   "r"(__float_as_uint(r[24])), "r"(__float_as_uint(r[25])), "r"(__float_as_uint(r[26])), "r"(__float_as_uint(r[27])),
+                   "r"(__float_as_uint(r[28])), "r"(__float_as_uint(r[29])), "r"(__float_as_uint(r[30])), "r"(__float_as_uint(r[31]))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// ---- f16 image of the query rows: one warp per (token, head); rows scaled by 2^-e --------
+__global__ void __launch_bounds__(128) k_q_rows_to_f16(const float *q_prep, __half *Qh, float *rs, int n_seq, int T,
+                                                       int nh, float scale) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const size_t row = (size_t)blockIdx.x * 4 + w;       // (b*T + t)*nh + h
+    if (row >= (size_t)n_seq * T * nh) return;
+    const int h = (int)(row % nh);
+    const size_t tok = row / nh;
+    const int b = (int)(tok / T), t = (int)(tok % T);
+    const float *q = q_prep + row * HD + lane * 8;
+    const float4 v0 = *reinterpret_cast<const float4 *>(q), v1 = *reinterpret_cast<const float4 *>(q + 4);
+    float mx = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                     fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    int e = 0;
+    if (mx > 0.0f && mx < INFINITY) (void)frexpf(mx, &e);
+    const float down = exp2f((float)-e);
+    const size_t orow = ((size_t)b * nh + h) * T + t;
+    *reinterpret_cast<uint4 *>(Qh + orow * HD + lane * 8) =
+        make_uint4(pack_h2(v0.x * down, v0.y * down), pack_h2(v0.z * down, v0.w * down),
+                   pack_h2(v1.x * down, v1.y * down), pack_h2(v1.z * down, v1.w * down));
+    if (lane == 0) rs[orow] = scale * exp2f((float)e) * LOG2E;
+}
+
+struct TcBars {
+    unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, p_empty, o_done;
+};
+
+template <typename ACT>
+__global__ void __launch_bounds__(192, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mq,
+                                                           const __grid_constant__ CUtensorMap mk,
+                                                           const __grid_constant__ CUtensorMap mv, TcArgs a) {
+    extern __shared__ unsigned char smraw[];
+    __shared__ TcBars bars;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int failed_s;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y, b = blockIdx.z, kvh = h / (a.nh / a.nkv);
+    const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * BM;     // long rows first
+    const int cap = (int)(a.seq_off[b + 1] - a.seq_off[b]);
+    const int len0 = a.kv_len[b];
+    // tokens that were really appended: the engine stops appending when the cache is full
+    const int t_end = min(a.T, max(0, min(cap, a.Lmax) - len0));
+    if (q0 >= t_end) return;
+    const int rows_here = min(BM, t_end - q0);
+    const int kmax = len0 + q0 + rows_here - 1;                // last key any row of the CTA sees
+    const int n_tiles = kmax / BN + 1;
+    const uint32_t base = (su32(smraw) + 1023u) & ~1023u;      // 128B-swizzle atoms are 1 KiB aligned
+    unsigned char *smg = smraw + (base - su32(smraw));
+
+    if (tid == 0) {
+        mbar_init(su32(&bars.q_full), 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(su32(&bars.k_full[s]), 1); mbar_init(su32(&bars.k_empty[s]), 1);
+            mbar_init(su32(&bars.v_full[s]), 1); mbar_init(su32(&bars.v_empty[s]), 1);
+            mbar_init(su32(&bars.s_full[s]), 1);
+        }
+        mbar_init(su32(&bars.p_full), 128); mbar_init(su32(&bars.p_empty), 1); mbar_init(su32(&bars.o_done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        failed_s = 0;
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(su32(&tmem_base_s)), "r"((uint32_t)TM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+    bool ok = true;
+
+    if (warp == 4) {
+        // ================= producer =================
+        if (lane == 0) {
+            mbar_expect_tx(su32(&bars.q_full), 65536u);
+            const int qrow = (b * a.nh + h) * a.T + q0;
+            for (int s = 0; s < 4; s++) tma_load_2d(base + SM_Q + s * 16384, &mq, s * 64, qrow, su32(&bars.q_full));
+            const int krow = (b * a.nkv + kvh) * a.Lp;
+            for (int j = 0; j < n_tiles && ok; j++) {
+                const int st = j & 1;
+                if (j >= 2) ok = mbar_wait(su32(&bars.k_empty[st]), (uint32_t)((j >> 1) - 1) & 1u);
+                if (!ok) break;
+                mbar_expect_tx(su32(&bars.k_full[st]), 32768u);
+                for (int s = 0; s < 4; s++)
+                    tma_load_2d(base + SM_K + st * 32768 + s * 8192, &mk, s * 64, krow + j * BN, su32(&bars.k_full[st]));
+                if (j >= 2) ok = mbar_wait(su32(&bars.v_empty[st]), (uint32_t)((j >> 1) - 1) & 1u);
+                if (!ok) break;
+                mbar_expect_tx(su32(&bars.v_full[st]), 32768u);
+                for (int s = 0; s < 4; s++)
+                    tma_load_2d(base + SM_V + st * 32768 + s * 8192, &mv, s * 64, krow + j * BN, su32(&bars.v_full[st]));
+            }
+        }
+    } else if (warp == 5) {
+        // ================= MMA issue =================
+        if (lane == 0) {
+            const uint32_t idesc_qk = (1u << 4) | (8u << 17) | (8u << 24);                 // f16 x f16 -> f32, N 64, M 128
+            const uint32_t idesc_pv = (1u << 4) | (1u << 16) | (32u << 17) | (8u << 24);   // B MN-major, N 256, M 128
+            ok = mbar_wait(su32(&bars.q_full), 0);
+            for (int j = 0; j <= n_tiles && ok; j++) {
+                if (j < n_tiles) {
+                    const int st = j & 1;
+                    ok = mbar_wait(su32(&bars.k_full[st]), (uint32_t)(j >> 1) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 16; ks++) {
+                        const uint64_t ad = smem_desc(base + SM_Q + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+                        const uint64_t bd = smem_desc(base + SM_K + st * 32768 + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024);
+                        mma_f16_ss(tmem + TM_S + st * BN, ad, bd, idesc_qk, ks > 0);
+                    }
+                    mma_commit(su32(&bars.k_empty[st]));
+                    mma_commit(su32(&bars.s_full[st]));
+                }
+                if (j >= 1) {
+                    const int jj = j - 1, st = jj & 1;
+                    ok = mbar_wait(su32(&bars.p_full), (uint32_t)jj & 1u) &&
+                         mbar_wait(su32(&bars.v_full[st]), (uint32_t)(jj >> 1) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        const uint64_t ad = smem_desc(base + SM_P + ks * 32, 16, 1024);
+                        const uint64_t bd = smem_desc(base + SM_V + st * 32768 + ks * 2048, 8192, 1024);
+                        mma_f16_ss(tmem + TM_O, ad, bd, idesc_pv, (jj > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    mma_commit(su32(&bars.v_empty[st]));
+                    mma_commit(su32(&bars.p_empty));
+                    if (jj == n_tiles - 1) mma_commit(su32(&bars.o_done));
+                }
+            }
+        }
+    } else {
+        // ================= softmax + epilogue: one thread per query row =================
+        const int row = warp * 32 + lane;
+        const bool live = row < rows_here;
+        const int qpos = live ? len0 + q0 + row : 0x7fffffff;  // rows past the end mask nothing and are not stored
+        const float rscale = live ? a.rs[((size_t)b * a.nh + h) * a.T + q0 + row] : 0.0f;
+        const uint32_t lane_t = tmem + ((uint32_t)(warp * 32) << 16);
+        unsigned char *prow = smg + SM_P + row * 128;
+        float m_ref = -INFINITY, l = 0.0f;
+        for (int j = 0; j < n_tiles; j++) {
+            const int st = j & 1, key0 = j * BN;
+            ok = ok && mbar_wait(su32(&bars.s_full[st]), (uint32_t)(j >> 1) & 1u);
+            tc_fence_after();
+            float s0[32], s1[32];
+            tmem_ld32(lane_t + TM_S + st * BN, s0);
+            tmem_ld32(lane_t + TM_S + st * BN + 32, s1);
+            tmem_wait_ld();
+            float mx = -INFINITY;
+            if (key0 + BN - 1 > qpos) {                        // the tile reaches past this row's diagonal
+#pragma unroll
+                for (int c = 0; c < 32; c++) {
+                    if (key0 + c > qpos) s0[c] = -INFINITY;
+                    if (key0 + 32 + c > qpos) s1[c] = -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 32; c++) mx = fmaxf(mx, fmaxf(s0[c], s1[c]));
+            mx = live ? mx * rscale : 0.0f;                    // rscale > 0 on live rows
+            float corr = 1.0f;
+            const bool grow = mx > m_ref + GROW || m_ref == -INFINITY;
+            if (grow && mx > -INFINITY) {
+                corr = exp2f(m_ref - mx);                      // 0 on the first tile
+                m_ref = mx;
+                l *= corr;
+            }
+            const float msafe = (m_ref == -INFINITY) ? 0.0f : m_ref;
+            uint32_t pk[32];
+            float ps = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+                const float p0 = exp2f(s0[2 * c] * rscale - msafe), p1 = exp2f(s0[2 * c + 1] * rscale - msafe);
+                const float p2 = exp2f(s1[2 * c] * rscale - msafe), p3 = exp2f(s1[2 * c + 1] * rscale - msafe);
+                ps += (p0 + p1) + (p2 + p3);
+                pk[c] = pack_h2(p0, p1);
+                pk[16 + c] = pack_h2(p2, p3);
+            }
+            l += ps;
+            // the value product of the previous tile must be done before P is overwritten or O rescaled
+            if (j > 0) ok = ok && mbar_wait(su32(&bars.p_empty), (uint32_t)(j - 1) & 1u);
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 32) {
+                    float o[32];
+                    tmem_ld32(lane_t + TM_O + c, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] *= corr;
+                    tmem_st32(lane_t + TM_O + c, o);
+                }
+                tmem_wait_st();
+            }
+            // P row: 8 chunks of 8 halves, chunk c at ((c ^ (row & 7)) * 16) inside the row's 128 bytes
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) * 16)) =
+                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(su32(&bars.p_full));
+        }
+        ok = ok && mbar_wait(su32(&bars.o_done), 0);
+        tc_fence_after();
+        if (!ok) failed_s = 1;
+        const float inv = ok ? 1.0f / l : NAN;
+        const size_t tok = (size_t)b * a.T + q0 + row;
+        const ACT *gate = (a.gated && live) ? (const ACT *)a.qproj + tok * a.nh * HD * 2 + (size_t)h * HD * 2 + HD : nullptr;
+        ACT *out = (ACT *)a.out + (tok * a.nh + h) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+            float o[32];
+            tmem_ld32(lane_t + TM_O + c, o);
+            tmem_wait_ld();
+            if (live) {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float y = o[i] * inv;
+                    if (gate) y *= sigmoid_f(act_ld(gate, c + i));
+                    act_st(out, c + i, y);
+                }
+            }
+        }
+    }
+    if (!ok) failed_s = 1;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn tensor_map_encoder() {
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        cudaDriverEntryPointQueryResult q;
+        void *p = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeFn)p;
+    }
+    return fn;
+}
+
+// [rows][256] f16, boxes of 64 dims x box_rows rows, 128-byte swizzle
+ornith_status f16_rows_map(CUtensorMap *m, const void *basep, uint64_t rows, uint32_t box_rows) {
+    EncodeFn enc = tensor_map_encoder();
+    if (!enc) { orn_record_error("prefill: cuTensorMapEncodeTiled is not available"); return (ornith_status)ORNITH_ERR_BACKEND; }
+    cuuint64_t dims[2] = {(cuuint64_t)HD, rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t es[2] = {1, 1};
+    const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(basep), dims, strides, box, es,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { orn_record_error("prefill: cuTensorMapEncodeTiled failed (%d)", (int)r); return (ornith_status)ORNITH_ERR_BACKEND; }
+    return ORNITH_OK;
+}
+
+}  // namespace
+
+size_t gqa_prefill_tc_scratch(int n_seq, int nh, int T) {
+    return align_up((size_t)n_seq * nh * T * HD * sizeof(__half), 256) + align_up((size_t)n_seq * nh * T * sizeof(float), 256);
+}
+
+ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, const float *q_prep, const __half *Kh,
+                                    const __half *Vh, void *q_scratch, const void *qproj, void *out, int nh, int T,
+                                    int Lmax, int Lp, int gated, float scale, int n_seq, bool bf16_act, cudaStream_t st) {
+    __half *Qh = (__half *)q_scratch;
+    float *rs = (float *)((char *)q_scratch + align_up((size_t)n_seq * nh * T * HD * sizeof(__half), 256));
+    const size_t qrows = (size_t)n_seq * nh * T;
+    k_q_rows_to_f16<<<(unsigned)((qrows + 3) / 4), 128, 0, st>>>(q_prep, Qh, rs, n_seq, T, nh, scale);
+    ORN_TRY(orn_check_launch("k_q_rows_to_f16"));
+    CUtensorMap mq, mk, mv;
+    ORN_TRY(f16_rows_map(&mq, Qh, qrows, BM));
+    ORN_TRY(f16_rows_map(&mk, Kh, (uint64_t)n_seq * kv.nkv * Lp, BN));
+    ORN_TRY(f16_rows_map(&mv, Vh, (uint64_t)n_seq * kv.nkv * Lp, BN));
+    TcArgs a;
+    a.seq_off = kv.seq_off; a.kv_len = kv_len; a.rs = rs; a.qproj = qproj; a.out = out;
+    a.nh = nh; a.nkv = kv.nkv; a.T = T; a.Lmax = Lmax; a.Lp = Lp; a.gated = gated;
+    static bool configured = false;
+    if (!configured) {
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               SM_BYTES + 1024), "tcgen05 prefill smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               SM_BYTES + 1024), "tcgen05 prefill smem opt-in"));
+        configured = true;
+    }
+    dim3 grid((T + BM - 1) / BM, nh, n_seq);
+    if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16><<<grid, 192, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    else          k_gqa_prefill_tc<float><<<grid, 192, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    return orn_check_launch("k_gqa_prefill_tc");
+}
