@@ -7,20 +7,25 @@
 // rows of the cache (k_kv_rows_to_f16), so quantised caches are attended over in their decoded
 // form, the current token included, exactly as the reference does.
 //
-// One CTA = 128 query tokens of one head, 6 warps:
-//   warp 4  producer   one lane issues the TMA loads (128B-swizzled boxes of 64 dims):
-//                      the query tile once, then 64-key K and V tiles through two stages each
-//   warp 5  MMA        one lane issues tcgen05.mma: S_j = Q K_j^T (16 x M128 N64 K16) into one
-//                      of two score buffers, then O += P_{j-1} V_{j-1} (4 x M128 N256 K16);
-//                      the scores of tile j+1 are queued before the value product of tile j,
-//                      so the tensor pipe works while the softmax of tile j runs
-//   warps 0-3  softmax one thread per query row (= TMEM lane): tcgen05.ld the 64 scores,
-//                      online softmax in the log2 domain against a reference maximum that is
-//                      only moved (and O rescaled through tcgen05.ld/st) when a row maximum
-//                      exceeds it by 2^8, probabilities rounded to f16 into a swizzled smem
-//                      tile that is the A operand of the value product; finally the epilogue
-//                      (1/l, sigmoid output gate, store).
-// Tensor memory: columns 0-63 and 64-127 the two score buffers, 128-383 the output tile.
+// One CTA = 128 query tokens of one head, 12 warps:
+//   warp 8      producer  one lane issues the TMA loads (128B-swizzled boxes of 64 dims) of the
+//                         64-key K and V tiles, three stages each
+//   warps 9,10  scores    one lane each issues S_j = Q K_j^T (16 x tcgen05.mma M128 N64 K16) for
+//                         the even / the odd tiles into its own score buffer
+//   warp 11     values    one lane issues O += P_j V_j (4 x M128 N256 K16)
+//                         Three issuing threads because one thread issues at most one MMA per
+//                         64-96 cycles, several times what an N = 64 product occupies the pipe.
+//                         Both A operands are in tensor memory, so shared memory only feeds K
+//                         and V (its bandwidth bounded a version that also kept Q and P there).
+//   warps 0-7   softmax   two threads per query row (= TMEM lane), 32 of the 64 scores each:
+//                         they first put the query tile into tensor memory (tcgen05.st), then
+//                         per tile tcgen05.ld the scores, online softmax in the log2 domain
+//                         against a reference maximum that is only moved (and O rescaled through
+//                         tcgen05.ld/st) when a row maximum exceeds it by 2^8, and store the f16
+//                         probabilities over the scores they came from; finally the epilogue
+//                         (1/l, sigmoid output gate, store).
+// Tensor memory columns: 0-255 the output tile, 256-319 and 320-383 the two score /
+// probability buffers, 384-511 the query tile (two f16 per column).
 // Every wait on an mbarrier is bounded; a wait that gives up poisons the CTA's outputs.
 #include <cuda.h>
 
@@ -29,14 +34,15 @@
 namespace {
 
 constexpr int HD = 256, BM = 128, BN = 64;
-constexpr int SM_Q = 0, SM_K = 65536, SM_V = 131072, SM_P = 196608, SM_BYTES = 212992;   // + 1 KiB alignment slack
-constexpr int TM_S = 0, TM_O = 128, TM_COLS = 512;
+constexpr int SM_K = 0, SM_V = 98304, SM_BYTES = 196608;      // 3 + 3 stages of 32 KiB, + 1 KiB alignment slack
+constexpr int TM_O = 0, TM_S = 256, TM_Q = 384, TM_COLS = 512;   // tensor-memory columns
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float GROW = 8.0f;               // move the reference maximum when exceeded by 2^8
 
 struct TcArgs {
     const int64_t *seq_off;
     const int32_t *kv_len;
+    const __half *Qh;                      // [n_seq*nh*T][256] query rows, each scaled by a power of two
     const float *rs;                       // [n_seq*nh*T] per-row factor: scale * 2^e * log2(e)
     const void *qproj;
     void *out;
@@ -53,15 +59,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// No suspend-time hint: every hand-off in this kernel is on the critical path of the tensor pipe.
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(10000u) : "memory");
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// bounded: gives up after ~1 s
+// bounded: gives up after about a second of polling
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < (1 << 17); i++)
+    for (int i = 0; i < (1 << 24); i++)
         if (mbar_try(bar, parity)) return true;
     return false;
 }
@@ -78,6 +85,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint
 __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// A operand in tensor memory: row m in lane m, elements 2c and 2c+1 of the row in column c
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -112,6 +124,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) 
                    "r"(__float_as_uint(r[28])), "r"(__float_as_uint(r[29])), "r"(__float_as_uint(r[30])), "r"(__float_as_uint(r[31]))
                  : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr),
+                   "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])), "r"(__float_as_uint(r[3])),
+                   "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])), "r"(__float_as_uint(r[6])), "r"(__float_as_uint(r[7])),
+                   "r"(__float_as_uint(r[8])), "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])), "r"(__float_as_uint(r[11])),
+                   "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])), "r"(__float_as_uint(r[15]))
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
@@ -144,18 +166,28 @@ __global__ void __launch_bounds__(128) k_q_rows_to_f16(const float *q_prep, __ha
     if (lane == 0) rs[orow] = scale * exp2f((float)e) * LOG2E;
 }
 
+constexpr int NS = 3;                      // K and V stages
+
 struct TcBars {
-    unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, p_empty, o_done;
+    unsigned long long q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS], s_full[2], pv_done[2], p_full;
 };
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// barrier among the two softmax warps that share 32 query rows
+__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+
 template <typename ACT>
-__global__ void __launch_bounds__(192, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mq,
-                                                           const __grid_constant__ CUtensorMap mk,
+__global__ void __launch_bounds__(384, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mk,
                                                            const __grid_constant__ CUtensorMap mv, TcArgs a) {
     extern __shared__ unsigned char smraw[];
     __shared__ TcBars bars;
+    __shared__ float xch[2][2][BM];                            // [tile parity][column half][row]: partial row maxima
+    __shared__ float lx[2][BM];                                // [column half][row]: partial row sums
     __shared__ uint32_t tmem_base_s;
-    __shared__ int failed_s;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / (a.nh / a.nkv);
     const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * BM;     // long rows first
@@ -168,20 +200,19 @@ __global__ void __launch_bounds__(192, 1) k_gqa_prefill_tc(const __grid_constant
     const int kmax = len0 + q0 + rows_here - 1;                // last key any row of the CTA sees
     const int n_tiles = kmax / BN + 1;
     const uint32_t base = (su32(smraw) + 1023u) & ~1023u;      // 128B-swizzle atoms are 1 KiB aligned
-    unsigned char *smg = smraw + (base - su32(smraw));
 
     if (tid == 0) {
-        mbar_init(su32(&bars.q_full), 1);
-        for (int s = 0; s < 2; s++) {
+        mbar_init(su32(&bars.q_full), 256);
+        for (int s = 0; s < NS; s++) {
             mbar_init(su32(&bars.k_full[s]), 1); mbar_init(su32(&bars.k_empty[s]), 1);
             mbar_init(su32(&bars.v_full[s]), 1); mbar_init(su32(&bars.v_empty[s]), 1);
-            mbar_init(su32(&bars.s_full[s]), 1);
         }
-        mbar_init(su32(&bars.p_full), 128); mbar_init(su32(&bars.p_empty), 1); mbar_init(su32(&bars.o_done), 1);
+        mbar_init(su32(&bars.s_full[0]), 1); mbar_init(su32(&bars.s_full[1]), 1);
+        mbar_init(su32(&bars.pv_done[0]), 1); mbar_init(su32(&bars.pv_done[1]), 1);
+        mbar_init(su32(&bars.p_full), 256);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        failed_s = 0;
     }
-    if (warp == 5) {
+    if (warp == 11) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(su32(&tmem_base_s)), "r"((uint32_t)TM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -192,146 +223,171 @@ __global__ void __launch_bounds__(192, 1) k_gqa_prefill_tc(const __grid_constant
     const uint32_t tmem = tmem_base_s;
     bool ok = true;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ================= producer =================
         if (lane == 0) {
-            mbar_expect_tx(su32(&bars.q_full), 65536u);
-            const int qrow = (b * a.nh + h) * a.T + q0;
-            for (int s = 0; s < 4; s++) tma_load_2d(base + SM_Q + s * 16384, &mq, s * 64, qrow, su32(&bars.q_full));
             const int krow = (b * a.nkv + kvh) * a.Lp;
-            for (int j = 0; j < n_tiles && ok; j++) {
-                const int st = j & 1;
-                if (j >= 2) ok = mbar_wait(su32(&bars.k_empty[st]), (uint32_t)((j >> 1) - 1) & 1u);
+            for (int j = 0; j < n_tiles; j++) {
+                const int st = j % NS;
+                const uint32_t par = (uint32_t)(j / NS - 1) & 1u;
+                if (j >= NS) ok = mbar_wait(su32(&bars.k_empty[st]), par);
                 if (!ok) break;
                 mbar_expect_tx(su32(&bars.k_full[st]), 32768u);
                 for (int s = 0; s < 4; s++)
                     tma_load_2d(base + SM_K + st * 32768 + s * 8192, &mk, s * 64, krow + j * BN, su32(&bars.k_full[st]));
-                if (j >= 2) ok = mbar_wait(su32(&bars.v_empty[st]), (uint32_t)((j >> 1) - 1) & 1u);
+                if (j >= NS) ok = mbar_wait(su32(&bars.v_empty[st]), par);
                 if (!ok) break;
                 mbar_expect_tx(su32(&bars.v_full[st]), 32768u);
                 for (int s = 0; s < 4; s++)
                     tma_load_2d(base + SM_V + st * 32768 + s * 8192, &mv, s * 64, krow + j * BN, su32(&bars.v_full[st]));
             }
         }
-    } else if (warp == 5) {
-        // ================= MMA issue =================
+    } else if (warp == 9 || warp == 10) {
+        // ================= score MMAs: warp 9 the even tiles, warp 10 the odd ones =================
+        // One thread cannot issue tcgen05.mma faster than one per ~64-96 cycles, which is two to
+        // three times the 32 cycles an M128 N64 K16 product occupies the pipe; several issuing
+        // threads do overlap.  Both A operands come from tensor memory (the query tile, and the
+        // probabilities written over the scores they came from): shared memory only feeds K and V.
         if (lane == 0) {
+            const int e = warp - 9;
             const uint32_t idesc_qk = (1u << 4) | (8u << 17) | (8u << 24);                 // f16 x f16 -> f32, N 64, M 128
-            const uint32_t idesc_pv = (1u << 4) | (1u << 16) | (32u << 17) | (8u << 24);   // B MN-major, N 256, M 128
             ok = mbar_wait(su32(&bars.q_full), 0);
-            for (int j = 0; j <= n_tiles && ok; j++) {
-                if (j < n_tiles) {
-                    const int st = j & 1;
-                    ok = mbar_wait(su32(&bars.k_full[st]), (uint32_t)(j >> 1) & 1u);
-                    if (!ok) break;
-                    tc_fence_after();
+            for (int j = e; j < n_tiles && ok; j += 2) {
+                const int st = j % NS;
+                ok = mbar_wait(su32(&bars.k_full[st]), (uint32_t)(j / NS) & 1u);
+                // this buffer still holds the probabilities of tile j-2 until their value product is done
+                if (ok && j >= 2) ok = mbar_wait(su32(&bars.pv_done[e]), (uint32_t)((j >> 1) - 1) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t kd = smem_desc(base + SM_K + st * 32768, 16, 1024);
 #pragma unroll
-                    for (int ks = 0; ks < 16; ks++) {
-                        const uint64_t ad = smem_desc(base + SM_Q + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-                        const uint64_t bd = smem_desc(base + SM_K + st * 32768 + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024);
-                        mma_f16_ss(tmem + TM_S + st * BN, ad, bd, idesc_qk, ks > 0);
-                    }
-                    mma_commit(su32(&bars.k_empty[st]));
-                    mma_commit(su32(&bars.s_full[st]));
-                }
-                if (j >= 1) {
-                    const int jj = j - 1, st = jj & 1;
-                    ok = mbar_wait(su32(&bars.p_full), (uint32_t)jj & 1u) &&
-                         mbar_wait(su32(&bars.v_full[st]), (uint32_t)(jj >> 1) & 1u);
-                    if (!ok) break;
-                    tc_fence_after();
+                for (int ks = 0; ks < 16; ks++)
+                    mma_f16_ts(tmem + TM_S + e * BN, tmem + TM_Q + ks * 8, kd + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4),
+                               idesc_qk, ks > 0);
+                mma_commit(su32(&bars.k_empty[st]));
+                mma_commit(su32(&bars.s_full[e]));
+            }
+        }
+    } else if (warp == 11) {
+        // ================= value MMAs =================
+        if (lane == 0) {
+            const uint32_t idesc_pv = (1u << 4) | (1u << 16) | (32u << 17) | (8u << 24);   // B MN-major, N 256, M 128
+            for (int j = 0; j < n_tiles && ok; j++) {
+                const int st = j % NS;
+                ok = mbar_wait(su32(&bars.p_full), (uint32_t)j & 1u) &&
+                     mbar_wait(su32(&bars.v_full[st]), (uint32_t)(j / NS) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t vd = smem_desc(base + SM_V + st * 32768, 8192, 1024);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ks++) {
-                        const uint64_t ad = smem_desc(base + SM_P + ks * 32, 16, 1024);
-                        const uint64_t bd = smem_desc(base + SM_V + st * 32768 + ks * 2048, 8192, 1024);
-                        mma_f16_ss(tmem + TM_O, ad, bd, idesc_pv, (jj > 0 || ks > 0) ? 1u : 0u);
-                    }
-                    mma_commit(su32(&bars.v_empty[st]));
-                    mma_commit(su32(&bars.p_empty));
-                    if (jj == n_tiles - 1) mma_commit(su32(&bars.o_done));
-                }
+                for (int ks = 0; ks < 4; ks++)
+                    mma_f16_ts(tmem + TM_O, tmem + TM_S + (j & 1) * BN + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
+                               (j > 0 || ks > 0) ? 1u : 0u);
+                mma_commit(su32(&bars.v_empty[st]));
+                mma_commit(su32(&bars.pv_done[j & 1]));
             }
         }
     } else {
-        // ================= softmax + epilogue: one thread per query row =================
-        const int row = warp * 32 + lane;
+        // ======== softmax + epilogue: two threads per query row (= TMEM lane), 32 columns each ========
+        const int wq = warp & 3, half = warp >> 2;             // TMEM lane quarter, column half
+        const int row = wq * 32 + lane;
         const bool live = row < rows_here;
         const int qpos = live ? len0 + q0 + row : 0x7fffffff;  // rows past the end mask nothing and are not stored
-        const float rscale = live ? a.rs[((size_t)b * a.nh + h) * a.T + q0 + row] : 0.0f;
-        const uint32_t lane_t = tmem + ((uint32_t)(warp * 32) << 16);
-        unsigned char *prow = smg + SM_P + row * 128;
+        const size_t qrow = ((size_t)b * a.nh + h) * a.T + q0 + row;
+        const float rscale = live ? a.rs[qrow] : 0.0f;
+        const uint32_t lane_t = tmem + ((uint32_t)(wq * 32) << 16);
+        {   // query row -> tensor memory: 128 of its 256 halves per thread, two halves per 32-bit column
+            const uint4 *src = reinterpret_cast<const uint4 *>(a.Qh + qrow * HD + 128 * half);
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                float q[32];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint4 v = live ? src[8 * c + i] : make_uint4(0u, 0u, 0u, 0u);
+                    q[4 * i] = __uint_as_float(v.x); q[4 * i + 1] = __uint_as_float(v.y);
+                    q[4 * i + 2] = __uint_as_float(v.z); q[4 * i + 3] = __uint_as_float(v.w);
+                }
+                tmem_st32(lane_t + TM_Q + 64 * half + 32 * c, q);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(su32(&bars.q_full));
+        }
         float m_ref = -INFINITY, l = 0.0f;
         for (int j = 0; j < n_tiles; j++) {
-            const int st = j & 1, key0 = j * BN;
-            ok = ok && mbar_wait(su32(&bars.s_full[st]), (uint32_t)(j >> 1) & 1u);
+            const int sb = j & 1, key0 = j * BN + 32 * half;
+            ok = ok && mbar_wait(su32(&bars.s_full[sb]), (uint32_t)(j >> 1) & 1u);
             tc_fence_after();
-            float s0[32], s1[32];
-            tmem_ld32(lane_t + TM_S + st * BN, s0);
-            tmem_ld32(lane_t + TM_S + st * BN + 32, s1);
+            float s[32];
+            tmem_ld32(lane_t + TM_S + sb * BN + 32 * half, s);
             tmem_wait_ld();
-            float mx = -INFINITY;
-            if (key0 + BN - 1 > qpos) {                        // the tile reaches past this row's diagonal
+            if (key0 + 31 > qpos) {                            // the tile reaches past this row's diagonal
 #pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    if (key0 + c > qpos) s0[c] = -INFINITY;
-                    if (key0 + 32 + c > qpos) s1[c] = -INFINITY;
-                }
+                for (int c = 0; c < 32; c++)
+                    if (key0 + c > qpos) s[c] = -INFINITY;
             }
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 32; c++) mx = fmaxf(mx, fmaxf(s0[c], s1[c]));
+            for (int c = 0; c < 32; c += 4) {
+                m4[0] = fmaxf(m4[0], s[c]); m4[1] = fmaxf(m4[1], s[c + 1]);
+                m4[2] = fmaxf(m4[2], s[c + 2]); m4[3] = fmaxf(m4[3], s[c + 3]);
+            }
+            float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            xch[sb][half][row] = mx;
+            pair_sync(1 + wq);                                 // also: both halves hold their scores in registers now
+            mx = fmaxf(mx, xch[sb][half ^ 1][row]);
             mx = live ? mx * rscale : 0.0f;                    // rscale > 0 on live rows
             float corr = 1.0f;
             const bool grow = mx > m_ref + GROW || m_ref == -INFINITY;
             if (grow && mx > -INFINITY) {
-                corr = exp2f(m_ref - mx);                      // 0 on the first tile
+                corr = ex2_approx(m_ref - mx);                 // 0 on the first tile
                 m_ref = mx;
                 l *= corr;
             }
             const float msafe = (m_ref == -INFINITY) ? 0.0f : m_ref;
-            uint32_t pk[32];
-            float ps = 0.0f;
+            float pk[16];
+            float p4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int c = 0; c < 16; c++) {
-                const float p0 = exp2f(s0[2 * c] * rscale - msafe), p1 = exp2f(s0[2 * c + 1] * rscale - msafe);
-                const float p2 = exp2f(s1[2 * c] * rscale - msafe), p3 = exp2f(s1[2 * c + 1] * rscale - msafe);
-                ps += (p0 + p1) + (p2 + p3);
-                pk[c] = pack_h2(p0, p1);
-                pk[16 + c] = pack_h2(p2, p3);
+            for (int c = 0; c < 8; c++) {
+                const float e0 = ex2_approx(fmaf(s[4 * c], rscale, -msafe)), e1 = ex2_approx(fmaf(s[4 * c + 1], rscale, -msafe));
+                const float e2 = ex2_approx(fmaf(s[4 * c + 2], rscale, -msafe)), e3 = ex2_approx(fmaf(s[4 * c + 3], rscale, -msafe));
+                p4[0] += e0; p4[1] += e1; p4[2] += e2; p4[3] += e3;
+                pk[2 * c] = __uint_as_float(pack_h2(e0, e1));
+                pk[2 * c + 1] = __uint_as_float(pack_h2(e2, e3));
             }
-            l += ps;
-            // the value product of the previous tile must be done before P is overwritten or O rescaled
-            if (j > 0) ok = ok && mbar_wait(su32(&bars.p_empty), (uint32_t)(j - 1) & 1u);
+            l += (p4[0] + p4[1]) + (p4[2] + p4[3]);
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // O may only be touched between two value products: the last one is done, the next waits for us
+                ok = ok && mbar_wait(su32(&bars.pv_done[(j - 1) & 1]), (uint32_t)((j - 1) >> 1) & 1u);
                 tc_fence_after();
 #pragma unroll 1
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = 0; c < HD / 2; c += 32) {         // this thread's half of the output row
                     float o[32];
-                    tmem_ld32(lane_t + TM_O + c, o);
+                    tmem_ld32(lane_t + TM_O + 128 * half + c, o);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] *= corr;
-                    tmem_st32(lane_t + TM_O + c, o);
+                    tmem_st32(lane_t + TM_O + 128 * half + c, o);
                 }
-                tmem_wait_st();
             }
-            // P row: 8 chunks of 8 halves, chunk c at ((c ^ (row & 7)) * 16) inside the row's 128 bytes
-#pragma unroll
-            for (int c = 0; c < 8; c++)
-                *reinterpret_cast<uint4 *>(prow + ((c ^ (row & 7)) * 16)) =
-                    make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // probabilities over the scores: key k of the tile in the low / high half of column k / 2
+            tmem_st16(lane_t + TM_S + sb * BN + 16 * half, pk);
+            tmem_wait_st();
             tc_fence_before();
             mbar_arrive(su32(&bars.p_full));
         }
-        ok = ok && mbar_wait(su32(&bars.o_done), 0);
+        // row sum = the two halves' sums (both were rescaled by the same factors)
+        lx[half][row] = l;
+        pair_sync(1 + wq);
+        l += lx[half ^ 1][row];
+        ok = ok && mbar_wait(su32(&bars.pv_done[(n_tiles - 1) & 1]), (uint32_t)((n_tiles - 1) >> 1) & 1u);
         tc_fence_after();
-        if (!ok) failed_s = 1;
         const float inv = ok ? 1.0f / l : NAN;
         const size_t tok = (size_t)b * a.T + q0 + row;
         const ACT *gate = (a.gated && live) ? (const ACT *)a.qproj + tok * a.nh * HD * 2 + (size_t)h * HD * 2 + HD : nullptr;
         ACT *out = (ACT *)a.out + (tok * a.nh + h) * HD;
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
+        for (int c = 128 * half; c < 128 * half + 128; c += 32) {
             float o[32];
             tmem_ld32(lane_t + TM_O + c, o);
             tmem_wait_ld();
@@ -345,10 +401,9 @@ __global__ void __launch_bounds__(192, 1) k_gqa_prefill_tc(const __grid_constant
             }
         }
     }
-    if (!ok) failed_s = 1;
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 11) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TM_COLS) : "memory");
     }
 }
@@ -398,12 +453,11 @@ ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, con
     const size_t qrows = (size_t)n_seq * nh * T;
     k_q_rows_to_f16<<<(unsigned)((qrows + 3) / 4), 128, 0, st>>>(q_prep, Qh, rs, n_seq, T, nh, scale);
     ORN_TRY(orn_check_launch("k_q_rows_to_f16"));
-    CUtensorMap mq, mk, mv;
-    ORN_TRY(f16_rows_map(&mq, Qh, qrows, BM));
+    CUtensorMap mk, mv;
     ORN_TRY(f16_rows_map(&mk, Kh, (uint64_t)n_seq * kv.nkv * Lp, BN));
     ORN_TRY(f16_rows_map(&mv, Vh, (uint64_t)n_seq * kv.nkv * Lp, BN));
     TcArgs a;
-    a.seq_off = kv.seq_off; a.kv_len = kv_len; a.rs = rs; a.qproj = qproj; a.out = out;
+    a.seq_off = kv.seq_off; a.kv_len = kv_len; a.Qh = Qh; a.rs = rs; a.qproj = qproj; a.out = out;
     a.nh = nh; a.nkv = kv.nkv; a.T = T; a.Lmax = Lmax; a.Lp = Lp; a.gated = gated;
     static bool configured = false;
     if (!configured) {
@@ -414,7 +468,7 @@ ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, con
         configured = true;
     }
     dim3 grid((T + BM - 1) / BM, nh, n_seq);
-    if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16><<<grid, 192, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
-    else          k_gqa_prefill_tc<float><<<grid, 192, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16><<<grid, 384, SM_BYTES + 1024, st>>>(mk, mv, a);
+    else          k_gqa_prefill_tc<float><<<grid, 384, SM_BYTES + 1024, st>>>(mk, mv, a);
     return orn_check_launch("k_gqa_prefill_tc");
 }
