@@ -101,6 +101,102 @@ __global__ void __launch_bounds__(128) k_full_prep(PrepArgs a) {
     }
 }
 
+// The same work with one warp per row and four rows per CTA, for prefill, where the
+// rows number in the millions and a CTA with block barriers per row is launch-bound.
+// Same products, sums (f64 sum of squares) and rounding as k_full_prep.
+template <typename ACT>
+__global__ void __launch_bounds__(128) k_full_prep_warp(PrepArgs a, long long n_rows, int rows_per_tok) {
+    extern __shared__ float rowbuf[];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int hd = a.kv.hd, nkv = a.kv.nkv, nh = a.nh;
+    const long long R = (long long)blockIdx.x * 4 + wid;
+    if (R >= n_rows) return;
+    const int tt = (int)(R / rows_per_tok), j = (int)(R % rows_per_tok) + a.row0, b = tt / a.T, t = tt % a.T;
+    const int64_t base = a.kv.seq_off[b];
+    const int cap = (int)(a.kv.seq_off[b + 1] - base);
+    const int slot = a.kv_len[b] + t;
+    if (slot >= cap) return;                              // full cache: silent no-op
+    const int pos = (a.rope_pos ? a.rope_pos[b] : a.kv_len[b]) + t;
+    float *row = rowbuf + wid * hd;
+
+    int kind, h;
+    const ACT *src;
+    const float *w;
+    if (j < nh) {
+        kind = 0; h = j; w = a.q_norm_w;
+        size_t per_tok = (size_t)nh * hd * (a.gated ? 2 : 1);
+        src = (const ACT *)a.qproj + (size_t)tt * per_tok + (size_t)h * hd * (a.gated ? 2 : 1);
+    } else if (j < nh + nkv) {
+        kind = 1; h = j - nh; w = a.k_norm_w;
+        src = (const ACT *)a.k + ((size_t)tt * nkv + h) * hd;
+    } else {
+        kind = 2; h = j - nh - nkv; w = nullptr;
+        src = (const ACT *)a.v + ((size_t)tt * nkv + h) * hd;
+    }
+    for (int i = lane; i < hd; i += 32) row[i] = act_ld(src, i);
+    __syncwarp();
+    if (w) {
+        double ss = 0.0;
+        for (int i = lane; i < hd; i += 32) ss += (double)row[i] * (double)row[i];
+        ss = warp_sum(ss);
+        const float inv = (float)(1.0 / sqrt(ss / (double)hd + (double)a.eps));
+        for (int i = lane; i < hd; i += 32) row[i] = __fmul_rn(__fmul_rn(row[i], inv), w[i]);
+        __syncwarp();
+    }
+    if (kind != 2 && a.rope_dim > 0) {
+        const int half = a.rope_dim / 2;
+        for (int i = lane; i < half; i += 32) {
+            float ang = __fmul_rn((float)pos, a.inv_freq[i]);
+            float c = cosf(ang), s = sinf(ang);
+            float lo = row[i], hi = row[i + half];
+            row[i]        = __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s));
+            row[i + half] = __fadd_rn(__fmul_rn(lo, s), __fmul_rn(hi, c));
+        }
+        __syncwarp();
+    }
+    if (kind == 0) {
+        float *dst = a.q_prep + ((size_t)tt * nh + h) * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = row[i];
+        return;
+    }
+    const size_t r = (size_t)(base + slot) * nkv + h;
+    uint8_t *pool = (kind == 1) ? a.kv.K : a.kv.V;
+    if (a.kv.mode == ORNITH_KV_F32) {
+        float *dst = reinterpret_cast<float *>(pool) + r * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = row[i];
+    } else if (a.kv.mode == ORNITH_KV_Q8_0) {
+        uint8_t *dst = pool + r * kv_row_bytes(ORNITH_KV_Q8_0, hd);
+        for (int blk = 0; blk < hd / 32; blk++) {         // as encode_row_q8_0, all blocks by this warp
+            const float x = row[blk * 32 + lane];
+            const float amax = warp_max(fabsf(x));
+            const float d = __fdiv_rn(amax, 127.0f);
+            const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+            int q = (int)roundf(__fmul_rn(x, id));
+            q = max(-127, min(127, q));
+            uint8_t *o = dst + (size_t)blk * 34;
+            if (lane == 0) *reinterpret_cast<unsigned short *>(o) = __half_as_ushort(__float2half_rn(d));
+            o[2 + lane] = (uint8_t)(int8_t)q;
+        }
+    } else {                                              // as encode_row_int8
+        int8_t *codes = reinterpret_cast<int8_t *>(pool) + r * hd;
+        float *sc = ((kind == 1) ? a.kv.Ks : a.kv.Vs) + r;
+        float m = 0.0f;
+        for (int i = lane; i < hd; i += 32) m = fmaxf(m, fabsf(row[i]));
+        const float amax = warp_max(m);
+        if (amax == 0.0f) {
+            for (int i = lane; i < hd; i += 32) codes[i] = 0;
+            if (lane == 0) *sc = 0.0f;
+            return;
+        }
+        const float inv = __fdiv_rn(127.0f, amax);
+        for (int i = lane; i < hd; i += 32) {
+            const int q = __float2int_rn(__fmul_rn(row[i], inv));
+            codes[i] = (int8_t)max(-127, min(127, q));
+        }
+        if (lane == 0) *sc = __fdiv_rn(amax, 127.0f);
+    }
+}
+
 // =============================================================================
 // split-K decode, generic in head_dim and group size
 // =============================================================================
@@ -403,7 +499,14 @@ static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_c
     a.q_norm_w = l->q_norm_w; a.k_norm_w = l->k_norm_w; a.inv_freq = l->rope_inv_freq;
     a.nh = l->n_heads; a.rope_dim = l->rope_dim; a.gated = l->gated; a.T = T; a.eps = l->eps;
     a.row0 = kv_only ? l->n_heads : 0;
-    dim3 grid(n_tok, (kv_only ? 0 : l->n_heads) + 2 * l->n_kv_heads);
+    const int rows_per_tok = (kv_only ? 0 : l->n_heads) + 2 * l->n_kv_heads;
+    if (n_tok >= 256) {                                   // prefill-sized: one warp per row
+        const long long n_rows = (long long)n_tok * rows_per_tok;
+        k_full_prep_warp<ACT><<<(unsigned)((n_rows + 3) / 4), 128, 4 * l->head_dim * sizeof(float), st>>>(a, n_rows,
+                                                                                                      rows_per_tok);
+        return orn_check_launch("k_full_prep_warp");
+    }
+    dim3 grid(n_tok, rows_per_tok);
     k_full_prep<ACT><<<grid, 128, l->head_dim * sizeof(float), st>>>(a);
     return orn_check_launch("k_full_prep");
 }
