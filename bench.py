@@ -50,6 +50,80 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of a cuBLAS GEMM on this pool: (burst, sustained, source)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+def run_prefill(dev, rank, world, T=32768, reps=3):
+    """BASELINE.json configs[3]: one 397B-shaped delta-net layer and one GQA layer over a 32768-token
+    prompt, batch 1, bf16 activations, head-sharded over the ranks (64/G value heads; 32/G query heads
+    with the KV heads they read), head outputs all-gathered.  Returns per-layer times (max over ranks)
+    and the figures derived from them; the stack has 45 delta-net and 15 GQA layers."""
+    import torch
+    import torch.distributed as dist
+    from ornithology_b200 import device as D
+    from ornithology_b200 import stack as S
+
+    g = torch.Generator(device="cpu").manual_seed(2)
+    nv, nk = 64 // world, min(16, 64 // world)
+    nh, nkv = 32 // world, max(1, 2 // world)
+    a = S.ARCHS["397b"]
+    w = S.linear_weights(dict(a, nk=nk, nv=nv), 0, 0)
+    lin = D.LinearLayer(nk, nv, 128, 128, w["conv_w"], w["a_coef"], w["dt_bias"], w["norm_w"], device=dev)
+    lst = D.LinearState(lin, 1)
+    pos = torch.zeros(1, dtype=torch.int32, device=dev)
+    lin_in = [torch.randn(1, T, n, generator=g).to(torch.bfloat16).to(dev) for n in (lin.cc, nv, nv, lin.vd)]
+    fw = S.full_weights(a, 0, 3)
+    full = D.FullLayer(nh, nkv, 256, fw["q_norm_w"], fw["k_norm_w"], device=dev)
+    kv = D.KvBatch(D.KV_Q8_0, nkv, 256, [T], device=dev)
+    full_in = [torch.randn(1, T, n, generator=g).to(torch.bfloat16).to(dev) for n in (nh * 512, nkv * 256, nkv * 256)]
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def gather(o):
+        if world == 1:
+            return o
+        full_o = torch.empty((world,) + tuple(o.shape), dtype=o.dtype, device=dev)
+        dist.all_gather_into_tensor(full_o, o)
+        return full_o
+
+    ms_lin = timed(lambda: gather(D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64)))
+    ms_full = timed(lambda: gather(D.full_attn_prefill(full, kv, pos, *full_in, T)))
+    ms_lin_k = timed(lambda: D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64))
+    ms_full_k = timed(lambda: D.full_attn_prefill(full, kv, pos, *full_in, T))
+    # algorithmic work of the whole layer (all ranks): causal QK^T + PV; chunked scan at C = 32
+    fl_full = 4.0 * 256 * 32 * T * (T + 1) / 2
+    fl_lin = 64.0 * (T / 32) * (6 * 32 * 128 * 128 + 2 * 32 * 32 * 256)
+    burst, sustained, src = measured_tensor_peak()
+    stack_ms = 45 * ms_lin + 15 * ms_full
+    return {"workload": "configs[3]: 32768-token prompt, 397B-shaped layers, batch 1, bf16, head-sharded x%d" % world,
+            "tokens": T, "delta_net_ms_per_layer": ms_lin, "gqa_ms_per_layer": ms_full,
+            "delta_net_ms_no_gather": ms_lin_k, "gqa_ms_no_gather": ms_full_k,
+            "stack_layers": "45 delta-net + 15 GQA", "stack_ms": stack_ms, "stack_tok_per_s": T / (stack_ms * 1e-3),
+            "gqa_tflops": fl_full / (ms_full_k * 1e-3) / 1e12 , "delta_net_tflops": fl_lin / (ms_lin_k * 1e-3) / 1e12,
+            "tensor_peak_tflops": burst * world, "tensor_peak_sustained_tflops": sustained * world,
+            "gqa_frac_of_tensor_peak": fl_full / (ms_full_k * 1e-3) / 1e12 / (burst * world), "peak_source": f"of {src}"}
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons sampled every 50 ms while active."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -302,6 +376,10 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, ms_e2e = float(times[0]), float(times[1])
 
+    prefill = None
+    if not args.no_prefill:
+        prefill = run_prefill(dev, rank, world)
+
     if rank == 0:
         tokens = args.seqs * world * args.steps
         value = tokens / (ms_total * 1e-3)
@@ -332,7 +410,7 @@ def run_ours(args, rank, world, local_rank):
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": ms_e2e / args.steps},
                 "gpu_launches": stack.launches_per_step() * args.steps,
-                "roofline": roof, "cpu_baseline": cpu, "clocks": clocks}
+                "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "prefill": prefill}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -349,6 +427,7 @@ def main():
     ap.add_argument("--max-ctx", type=int, default=32768)
     ap.add_argument("--seed", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the configs[3] prefill leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
