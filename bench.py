@@ -59,20 +59,22 @@ def measured_tensor_peak():
     return 1590.0, 1400.0, "fallback"
 
 
-def run_prefill(dev, rank, world, T=32768, reps=3):
+def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b"):
     """BASELINE.json configs[3]: one 397B-shaped delta-net layer and one GQA layer over a 32768-token
     prompt, batch 1, bf16 activations, head-sharded over the ranks (64/G value heads; 32/G query heads
     with the KV heads they read), head outputs all-gathered.  Returns per-layer times (max over ranks)
-    and the figures derived from them; the stack has 45 delta-net and 15 GQA layers."""
+    and the figures derived from them; the stack has 45 delta-net and 15 GQA layers.  shape="35b"
+    (32 value heads, 16 query heads) and a smaller T give the small cases the profiles are taken on."""
     import torch
     import torch.distributed as dist
     from ornithology_b200 import device as D
     from ornithology_b200 import stack as S
 
     g = torch.Generator(device="cpu").manual_seed(2)
-    nv, nk = 64 // world, min(16, 64 // world)
-    nh, nkv = 32 // world, max(1, 2 // world)
-    a = S.ARCHS["397b"]
+    NV, NH = (64, 32) if shape == "397b" else (32, 16)
+    nv, nk = NV // world, min(16, NV // world)
+    nh, nkv = NH // world, max(1, 2 // world)
+    a = S.ARCHS[shape]
     w = S.linear_weights(dict(a, nk=nk, nv=nv), 0, 0)
     lin = D.LinearLayer(nk, nv, 128, 128, w["conv_w"], w["a_coef"], w["dt_bias"], w["norm_w"], device=dev)
     lst = D.LinearState(lin, 1)
@@ -111,11 +113,11 @@ def run_prefill(dev, rank, world, T=32768, reps=3):
     ms_lin_k = timed(lambda: D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64))
     ms_full_k = timed(lambda: D.full_attn_prefill(full, kv, pos, *full_in, T))
     # algorithmic work of the whole layer (all ranks): causal QK^T + PV; chunked scan at C = 32
-    fl_full = 4.0 * 256 * 32 * T * (T + 1) / 2
-    fl_lin = 64.0 * (T / 32) * (6 * 32 * 128 * 128 + 2 * 32 * 32 * 256)
+    fl_full = 4.0 * 256 * NH * T * (T + 1) / 2
+    fl_lin = float(NV) * (T / 32) * (6 * 32 * 128 * 128 + 2 * 32 * 32 * 256)
     burst, sustained, src = measured_tensor_peak()
     stack_ms = 45 * ms_lin + 15 * ms_full
-    return {"workload": "configs[3]: 32768-token prompt, 397B-shaped layers, batch 1, bf16, head-sharded x%d" % world,
+    return {"workload": "configs[3]: %d-token prompt, %s-shaped layers, batch 1, bf16, head-sharded x%d" % (T, shape.upper(), world),
             "tokens": T, "delta_net_ms_per_layer": ms_lin, "gqa_ms_per_layer": ms_full,
             "delta_net_ms_no_gather": ms_lin_k, "gqa_ms_no_gather": ms_full_k,
             "stack_layers": "45 delta-net + 15 GQA", "stack_ms": stack_ms, "stack_tok_per_s": T / (stack_ms * 1e-3),
@@ -428,6 +430,9 @@ def main():
     ap.add_argument("--seed", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the configs[3] prefill leg")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the prefill leg (1 GPU) and print its figures")
+    ap.add_argument("--prefill-tokens", type=int, default=32768)
+    ap.add_argument("--prefill-shape", default="397b", choices=["397b", "35b"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -435,6 +440,12 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.prefill_only:
+        import torch
+        torch.cuda.set_device(local_rank)
+        print(json.dumps(run_prefill(torch.device("cuda", local_rank), 0, 1, T=args.prefill_tokens, reps=1,
+                                     shape=args.prefill_shape)), flush=True)
         return
     if world == 1 and args.gpus > 1:
         # launched without torchrun: re-launch one rank per GPU
