@@ -208,7 +208,9 @@ size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *layer
  * over the decoded rows, current token included, like T decode steps do.
  * Replaces the body of full_attn_prefill() (reference: src/ornith_rforward.c:529-551).
  *   qproj [n_seq][T][...], k,v [n_seq][T][...], out [n_seq][T][n_heads*head_dim]
- *   max_len: host upper bound on kv_len[b] + T (sizes the decoded-row image in the scratch) */
+ *   max_len: host upper bound on kv_len[b] + T (sizes the decoded-row image in the scratch)
+ * head_dim 256 runs on the tcgen05 tensor cores (f16 operands, f32 accumulation);
+ * ORNITH_CUDA_PREFILL_VARIANT=mma in the environment selects the mma.sync kernel instead. */
 ornith_status ornith_cuda_full_attn_prefill(const ornith_cuda_full_layer *layer, const ornith_cuda_kv *kv,
                                             const int32_t *kv_len, const int32_t *rope_pos,
                                             const void *qproj, const void *k, const void *v, void *out,
@@ -297,7 +299,10 @@ size_t ornith_cuda_linear_attn_prefill_scratch(const ornith_cuda_linear_layer *l
 /* T tokens per sequence through the chunked scan; state and conv history end
  * exactly where T decode steps would leave them.
  * Replaces linear_attn_prefill() minus its matvecs (reference: src/ornith_rforward.c:571-616).
- *   qkv [n_seq][T][Cc], a,b [n_seq][T][nv], z,out [n_seq][T][nv*dv]; chunk in {16,32,64} */
+ *   qkv [n_seq][T][Cc], a,b [n_seq][T][nv], z,out [n_seq][T][nv*dv]
+ *   scratch: 256-byte aligned.  With dk = dv = 128 the scan runs in 32-token chunks with tf32
+ *   tensor-core products whatever `chunk` says; with ORNITH_CUDA_PREFILL_FP32=1 in the
+ *   environment every product stays in fp32 and chunk >= 32 / < 32 selects 32 / 16 tokens. */
 ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *layer,
                                               const ornith_cuda_linear_state *st, const int32_t *pos,
                                               const void *qkv, const void *a, const void *b,
