@@ -43,32 +43,6 @@ __device__ __forceinline__ float conv_channel(const LinArgs &a, const float *rin
 // (4 x float4 each), so the two dot products per row reduce over 3 shuffles.
 // Three block barriers in all.
 
-__device__ __forceinline__ float4 lds128(const float *p) {        // not hoisted: keeps k/q out of registers
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
-    return v;
-}
-
-// conv of one channel from its four ring slots (slot of token t' is t' & 3); taps are the
-// tokens t-3, t-2, t-1 = slots sb, sb+1, sb+2 with sb = (t + 1) & 3.  Same operation order
-// and rounding as the engine (reference: src/ornith_attn.c:373-381), then SiLU.
-__device__ __forceinline__ float conv4_silu(const float (&h)[4], float xin, float4 w, float bias, int sb) {
-    float t0, t1, t2;
-    switch (sb) {                                                  // uniform over the CTA
-    case 0:  t0 = h[0]; t1 = h[1]; t2 = h[2]; break;
-    case 1:  t0 = h[1]; t1 = h[2]; t2 = h[3]; break;
-    case 2:  t0 = h[2]; t1 = h[3]; t2 = h[0]; break;
-    default: t0 = h[3]; t1 = h[0]; t2 = h[1]; break;
-    }
-    float acc = bias;
-    acc = __fadd_rn(acc, __fmul_rn(w.x, t0));
-    acc = __fadd_rn(acc, __fmul_rn(w.y, t1));
-    acc = __fadd_rn(acc, __fmul_rn(w.z, t2));
-    acc = __fadd_rn(acc, __fmul_rn(w.w, xin));
-    return silu_f(acc);
-}
-
 template <typename ACT>
 __global__ void __launch_bounds__(256, 2) k_linear_decode_128(LinArgs a) {
     __shared__ __align__(16) float q_s[128], k_s[128], v_s[128];
@@ -748,6 +722,12 @@ ornith_status ornith_cuda_linear_attn_step(const ornith_cuda_linear_layer *l, co
     const bool bf = act_dtype == ORNITH_ACT_BF16;
     if (l->dk == 128 && l->dv == 128 && l->conv_k == 4 && (st->S_seq_stride % 4) == 0 &&
         ((uintptr_t)st->S % 16) == 0 && ((uintptr_t)l->conv_w % 16) == 0) {
+        // Once there are more (sequence, head) units than the 2 x 148 CTAs the SMs hold, the persistent
+        // kernel that streams the state through a bulk-copy ring is faster (59 vs 66 us at 2048 units).
+        // ORNITH_CUDA_LINEAR_DECODE=ring | cta forces one of the two.
+        const char *variant = getenv("ORNITH_CUDA_LINEAR_DECODE");
+        const bool ring = variant ? variant[0] == 'r' : (long long)n_seq * l->nv > 296;
+        if (ring) return launch_linear_decode_ring(x, n_seq, act_dtype, s);
         if (bf) k_linear_decode_128<__nv_bfloat16><<<grid, 256, 0, s>>>(x);
         else    k_linear_decode_128<float><<<grid, 256, 0, s>>>(x);
         return orn_check_launch("k_linear_decode_128");

@@ -30,3 +30,33 @@ size_t linear_prefill_tc_blocks_bytes(int nv, int n_seq, int T);
 ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtype, float *Y, const float *rq,
                                        const float *rk, const float *la, const float *be, float *blocks,
                                        cudaStream_t s);
+
+__device__ __forceinline__ float4 lds128(const float *p) {        // not hoisted: keeps k/q out of registers
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+    return v;
+}
+
+// conv of one channel from its four ring slots (slot of token t' is t' & 3); taps are the
+// tokens t-3, t-2, t-1 = slots sb, sb+1, sb+2 with sb = (t + 1) & 3.  Same operation order
+// and rounding as the engine (reference: src/ornith_attn.c:373-381), then SiLU.
+__device__ __forceinline__ float conv4_silu(const float (&h)[4], float xin, float4 w, float bias, int sb) {
+    float t0, t1, t2;
+    switch (sb) {                                                  // uniform over the CTA
+    case 0:  t0 = h[0]; t1 = h[1]; t2 = h[2]; break;
+    case 1:  t0 = h[1]; t1 = h[2]; t2 = h[3]; break;
+    case 2:  t0 = h[2]; t1 = h[3]; t2 = h[0]; break;
+    default: t0 = h[3]; t1 = h[0]; t2 = h[1]; break;
+    }
+    float acc = bias;
+    acc = __fadd_rn(acc, __fmul_rn(w.x, t0));
+    acc = __fadd_rn(acc, __fmul_rn(w.y, t1));
+    acc = __fadd_rn(acc, __fmul_rn(w.z, t2));
+    acc = __fadd_rn(acc, __fmul_rn(w.w, xin));
+    return silu_f(acc);
+}
+
+// Persistent variant of the dk = dv = 128 decode step (linear_decode_ring.cu): the state is
+// streamed through a ring of bulk copies in shared memory.
+ornith_status launch_linear_decode_ring(const LinArgs &x, int n_seq, int act_dtype, cudaStream_t s);

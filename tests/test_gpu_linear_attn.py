@@ -74,6 +74,43 @@ def test_35b_shape_decode_steps(oracle, bf16, head_map, bias, scaled):
         assert (st.conv_image(b, T).cpu().numpy().ravel().view(np.uint32) == buf[b].view(np.uint32)).all()
 
 
+@pytest.mark.parametrize("variant", ["ring", "cta"])
+def test_decode_kernel_variants_against_oracle(oracle, monkeypatch, variant):
+    """Both forms of the dk = dv = 128 decode step (one CTA per unit; persistent CTAs fed by a
+    bulk-copy ring, several units per CTA) on a batch of 80 sequences x 8 heads = 640 units,
+    more than the 296 resident CTAs, so ring CTAs walk two or three units each: a sample of
+    the sequences against the oracle after 5 steps, and the two variants bit for bit."""
+    import torch
+    from ornithology_b200 import device as D
+    layer, kw = linear_case(12, nk=4, nv=8)
+    dl = device_linear(layer, kw)
+    B, T = 80, 5
+    g = np.random.default_rng(77)
+    ins = [g.standard_normal((T, B, n)).astype(np.float32) for n in (layer.cc, layer.nv, layer.nv, layer.vd)]
+
+    def run(which):
+        monkeypatch.setenv("ORNITH_CUDA_LINEAR_DECODE", which)
+        st = D.LinearState(dl, B)
+        pos = torch.zeros(B, dtype=torch.int32, device="cuda")
+        outs = []
+        for t in range(T):
+            outs.append(D.linear_attn_step(dl, st, pos, *[_t(x[t]) for x in ins]).cpu().numpy())
+            D.advance(pos)
+        return np.stack(outs), st.S.cpu().numpy(), st.conv.cpu().numpy()
+
+    out, S_dev, conv_dev = run(variant)
+    for b in (0, 37, 79):
+        S = np.zeros((layer.nv, 128, 128), np.float32); buf = np.zeros(3 * layer.cc, np.float32)
+        for t in range(T):
+            ref = oracle.linear_attn_step(layer, S, buf, *[x[t, b] for x in ins])
+            assert rel_err(out[t, b], ref) < TOL, (t, b)
+        assert rel_err(S_dev[b], S) < TOL
+    other = run("cta" if variant == "ring" else "ring")
+    assert (out.view(np.uint32) == other[0].view(np.uint32)).all()
+    assert (S_dev.view(np.uint32) == other[1].view(np.uint32)).all()
+    assert (conv_dev.view(np.uint32) == other[2].view(np.uint32)).all()
+
+
 def test_512_decode_steps_stay_within_tolerance(oracle):
     """The stated parity bar: outputs and recurrent state within 2e-3 over 512 decode steps."""
     import torch
