@@ -7,25 +7,27 @@
 // rows of the cache (k_kv_rows_to_f16), so quantised caches are attended over in their decoded
 // form, the current token included, exactly as the reference does.
 //
-// One CTA = 128 query tokens of one head, 12 warps:
-//   warp 8      producer  one lane issues the TMA loads (128B-swizzled boxes of 64 dims) of the
-//                         64-key K and V tiles, three stages each
-//   warps 9,10  scores    one lane each issues S_j = Q K_j^T (16 x tcgen05.mma M128 N64 K16) for
-//                         the even / the odd tiles into its own score buffer
-//   warp 11     values    one lane issues O += P_j V_j (4 x M128 N256 K16)
-//                         Three issuing threads because one thread issues at most one MMA per
-//                         64-96 cycles, several times what an N = 64 product occupies the pipe.
-//                         Both A operands are in tensor memory, so shared memory only feeds K
-//                         and V (its bandwidth bounded a version that also kept Q and P there).
+// One CTA = 128 query tokens of one head, 13 warps:
+//   warp 8      producer  one lane issues the TMA loads (128B-swizzled boxes of 64 dims): dims
+//                         128..255 of the query tile once, then the 64-key K tiles (3 stages)
+//                         and V tiles (2 stages)
+//   warps 9-11  scores    one lane each issues S_j = Q K_j^T (16 x tcgen05.mma M128 N64 K16) for
+//                         the tiles j = 0, 1, 2 (mod 3) into its own score buffer
+//   warp 12     values    one lane issues O += P_j V_j (4 x M128 N256 K16)
+//                         Several issuing threads because one thread issues at most one MMA per
+//                         64-96 cycles, several times what an N = 64 product occupies the pipe;
+//                         three score buffers so that the chain issue -> softmax -> value product
+//                         -> next issue of a buffer spans three tiles.
 //   warps 0-7   softmax   two threads per query row (= TMEM lane), 32 of the 64 scores each:
-//                         they first put the query tile into tensor memory (tcgen05.st), then
-//                         per tile tcgen05.ld the scores, online softmax in the log2 domain
-//                         against a reference maximum that is only moved (and O rescaled through
-//                         tcgen05.ld/st) when a row maximum exceeds it by 2^8, and store the f16
-//                         probabilities over the scores they came from; finally the epilogue
-//                         (1/l, sigmoid output gate, store).
-// Tensor memory columns: 0-255 the output tile, 256-319 and 320-383 the two score /
-// probability buffers, 384-511 the query tile (two f16 per column).
+//                         they first put dims 0..127 of the query tile into tensor memory
+//                         (tcgen05.st), then per tile tcgen05.ld the scores, online softmax in
+//                         the log2 domain against a reference maximum that is only moved (and O
+//                         rescaled through tcgen05.ld/st) when a row maximum exceeds it by 2^8,
+//                         and store the f16 probabilities over the scores they came from;
+//                         finally the epilogue (1/l, sigmoid output gate, store).
+// Tensor memory columns: 0-255 the output tile, 256-447 three score / probability buffers,
+// 448-511 dims 0..127 of the query tile (two f16 per column).  The A operands that live there
+// (half of Q, all of P) keep shared-memory bandwidth for K, V and the other half of Q.
 // Every wait on an mbarrier is bounded; a wait that gives up poisons the CTA's outputs.
 #include <cuda.h>
 
@@ -34,8 +36,8 @@
 namespace {
 
 constexpr int HD = 256, BM = 128, BN = 64;
-constexpr int SM_K = 0, SM_V = 98304, SM_BYTES = 196608;      // 3 + 3 stages of 32 KiB, + 1 KiB alignment slack
-constexpr int TM_O = 0, TM_S = 256, TM_Q = 384, TM_COLS = 512;   // tensor-memory columns
+constexpr int SM_K = 0, SM_V = 98304, SM_Q = 163840, SM_BYTES = 196608;   // 3 K + 2 V stages of 32 KiB, half the query tile; + 1 KiB slack
+constexpr int TM_O = 0, TM_S = 256, TM_Q = 448, TM_COLS = 512;   // tensor-memory columns
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float GROW = 8.0f;               // move the reference maximum when exceeded by 2^8
 
@@ -166,10 +168,11 @@ __global__ void __launch_bounds__(128) k_q_rows_to_f16(const float *q_prep, __ha
     if (lane == 0) rs[orow] = scale * exp2f((float)e) * LOG2E;
 }
 
-constexpr int NS = 3;                      // K and V stages
+constexpr int NSK = 3, NSV = 2;            // K and V stages
+constexpr int NB = 3;                      // score / probability buffers in tensor memory
 
 struct TcBars {
-    unsigned long long q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS], s_full[2], pv_done[2], p_full;
+    unsigned long long q_full, k_full[NSK], k_empty[NSK], v_full[NSV], v_empty[NSV], s_full[NB], pv_done[NB], p_full;
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -181,11 +184,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
 template <typename ACT>
-__global__ void __launch_bounds__(384, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mk,
+__global__ void __launch_bounds__(416, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mq,
+                                                           const __grid_constant__ CUtensorMap mk,
                                                            const __grid_constant__ CUtensorMap mv, TcArgs a) {
     extern __shared__ unsigned char smraw[];
     __shared__ TcBars bars;
-    __shared__ float xch[2][2][BM];                            // [tile parity][column half][row]: partial row maxima
+    __shared__ float xch[NB][2][BM];                           // [score buffer][column half][row]: partial row maxima
     __shared__ float lx[2][BM];                                // [column half][row]: partial row sums
     __shared__ uint32_t tmem_base_s;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -202,17 +206,14 @@ __global__ void __launch_bounds__(384, 1) k_gqa_prefill_tc(const __grid_constant
     const uint32_t base = (su32(smraw) + 1023u) & ~1023u;      // 128B-swizzle atoms are 1 KiB aligned
 
     if (tid == 0) {
-        mbar_init(su32(&bars.q_full), 256);
-        for (int s = 0; s < NS; s++) {
-            mbar_init(su32(&bars.k_full[s]), 1); mbar_init(su32(&bars.k_empty[s]), 1);
-            mbar_init(su32(&bars.v_full[s]), 1); mbar_init(su32(&bars.v_empty[s]), 1);
-        }
-        mbar_init(su32(&bars.s_full[0]), 1); mbar_init(su32(&bars.s_full[1]), 1);
-        mbar_init(su32(&bars.pv_done[0]), 1); mbar_init(su32(&bars.pv_done[1]), 1);
+        mbar_init(su32(&bars.q_full), 257);                    // 256 rows stored to tensor memory + the TMA half
+        for (int s = 0; s < NSK; s++) { mbar_init(su32(&bars.k_full[s]), 1); mbar_init(su32(&bars.k_empty[s]), 1); }
+        for (int s = 0; s < NSV; s++) { mbar_init(su32(&bars.v_full[s]), 1); mbar_init(su32(&bars.v_empty[s]), 1); }
+        for (int s = 0; s < NB; s++) { mbar_init(su32(&bars.s_full[s]), 1); mbar_init(su32(&bars.pv_done[s]), 1); }
         mbar_init(su32(&bars.p_full), 256);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 11) {
+    if (warp == 12) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(su32(&tmem_base_s)), "r"((uint32_t)TM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -226,65 +227,74 @@ __global__ void __launch_bounds__(384, 1) k_gqa_prefill_tc(const __grid_constant
     if (warp == 8) {
         // ================= producer =================
         if (lane == 0) {
+            // dims 128..255 of the query tile stay in shared memory (two 64-dim slabs)
+            mbar_expect_tx(su32(&bars.q_full), 32768u);
+            const int qrow = (b * a.nh + h) * a.T + q0;
+            for (int s = 0; s < 2; s++) tma_load_2d(base + SM_Q + s * 16384, &mq, 128 + s * 64, qrow, su32(&bars.q_full));
             const int krow = (b * a.nkv + kvh) * a.Lp;
             for (int j = 0; j < n_tiles; j++) {
-                const int st = j % NS;
-                const uint32_t par = (uint32_t)(j / NS - 1) & 1u;
-                if (j >= NS) ok = mbar_wait(su32(&bars.k_empty[st]), par);
+                const int sk = j % NSK, sv = j % NSV;
+                if (j >= NSK) ok = mbar_wait(su32(&bars.k_empty[sk]), (uint32_t)(j / NSK - 1) & 1u);
                 if (!ok) break;
-                mbar_expect_tx(su32(&bars.k_full[st]), 32768u);
+                mbar_expect_tx(su32(&bars.k_full[sk]), 32768u);
                 for (int s = 0; s < 4; s++)
-                    tma_load_2d(base + SM_K + st * 32768 + s * 8192, &mk, s * 64, krow + j * BN, su32(&bars.k_full[st]));
-                if (j >= NS) ok = mbar_wait(su32(&bars.v_empty[st]), par);
+                    tma_load_2d(base + SM_K + sk * 32768 + s * 8192, &mk, s * 64, krow + j * BN, su32(&bars.k_full[sk]));
+                if (j >= NSV) ok = mbar_wait(su32(&bars.v_empty[sv]), (uint32_t)(j / NSV - 1) & 1u);
                 if (!ok) break;
-                mbar_expect_tx(su32(&bars.v_full[st]), 32768u);
+                mbar_expect_tx(su32(&bars.v_full[sv]), 32768u);
                 for (int s = 0; s < 4; s++)
-                    tma_load_2d(base + SM_V + st * 32768 + s * 8192, &mv, s * 64, krow + j * BN, su32(&bars.v_full[st]));
+                    tma_load_2d(base + SM_V + sv * 32768 + s * 8192, &mv, s * 64, krow + j * BN, su32(&bars.v_full[sv]));
             }
         }
-    } else if (warp == 9 || warp == 10) {
-        // ================= score MMAs: warp 9 the even tiles, warp 10 the odd ones =================
-        // One thread cannot issue tcgen05.mma faster than one per ~64-96 cycles, which is two to
-        // three times the 32 cycles an M128 N64 K16 product occupies the pipe; several issuing
-        // threads do overlap.  Both A operands come from tensor memory (the query tile, and the
-        // probabilities written over the scores they came from): shared memory only feeds K and V.
+    } else if (warp >= 9 && warp <= 11) {
+        // ================= score MMAs: warp 9 + e issues the tiles j = e (mod 3) =================
+        // One thread cannot issue tcgen05.mma faster than one per ~64-96 cycles, two to three times
+        // the 32 cycles an M128 N64 K16 product occupies the pipe; several issuing threads overlap.
+        // With three score buffers the chain issue -> softmax -> value product -> next issue of a
+        // buffer spans three tiles.  Dims 0..127 of Q are a tensor-memory operand, dims 128..255 a
+        // shared-memory one (512 columns: output 256, scores 3 x 64, query 64).
         if (lane == 0) {
             const int e = warp - 9;
             const uint32_t idesc_qk = (1u << 4) | (8u << 17) | (8u << 24);                 // f16 x f16 -> f32, N 64, M 128
             ok = mbar_wait(su32(&bars.q_full), 0);
-            for (int j = e; j < n_tiles && ok; j += 2) {
-                const int st = j % NS;
-                ok = mbar_wait(su32(&bars.k_full[st]), (uint32_t)(j / NS) & 1u);
-                // this buffer still holds the probabilities of tile j-2 until their value product is done
-                if (ok && j >= 2) ok = mbar_wait(su32(&bars.pv_done[e]), (uint32_t)((j >> 1) - 1) & 1u);
+            const uint64_t qd = smem_desc(base + SM_Q, 16, 1024);
+            for (int j = e; j < n_tiles && ok; j += NB) {
+                const int st = j % NSK;
+                ok = mbar_wait(su32(&bars.k_full[st]), (uint32_t)(j / NSK) & 1u);
+                // this buffer still holds the probabilities of tile j-3 until their value product is done
+                if (ok && j >= NB) ok = mbar_wait(su32(&bars.pv_done[e]), (uint32_t)(j / NB - 1) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t kd = smem_desc(base + SM_K + st * 32768, 16, 1024);
 #pragma unroll
-                for (int ks = 0; ks < 16; ks++)
+                for (int ks = 0; ks < 8; ks++)
                     mma_f16_ts(tmem + TM_S + e * BN, tmem + TM_Q + ks * 8, kd + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4),
                                idesc_qk, ks > 0);
+#pragma unroll
+                for (int ks = 8; ks < 16; ks++)
+                    mma_f16_ss(tmem + TM_S + e * BN, qd + (uint64_t)((((ks - 8) >> 2) * 16384 + (ks & 3) * 32) >> 4),
+                               kd + (uint64_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4), idesc_qk, 1u);
                 mma_commit(su32(&bars.k_empty[st]));
                 mma_commit(su32(&bars.s_full[e]));
             }
         }
-    } else if (warp == 11) {
+    } else if (warp == 12) {
         // ================= value MMAs =================
         if (lane == 0) {
             const uint32_t idesc_pv = (1u << 4) | (1u << 16) | (32u << 17) | (8u << 24);   // B MN-major, N 256, M 128
             for (int j = 0; j < n_tiles && ok; j++) {
-                const int st = j % NS;
+                const int st = j % NSV, sb = j % NB;
                 ok = mbar_wait(su32(&bars.p_full), (uint32_t)j & 1u) &&
-                     mbar_wait(su32(&bars.v_full[st]), (uint32_t)(j / NS) & 1u);
+                     mbar_wait(su32(&bars.v_full[st]), (uint32_t)(j / NSV) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t vd = smem_desc(base + SM_V + st * 32768, 8192, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)
-                    mma_f16_ts(tmem + TM_O, tmem + TM_S + (j & 1) * BN + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
+                    mma_f16_ts(tmem + TM_O, tmem + TM_S + sb * BN + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
                                (j > 0 || ks > 0) ? 1u : 0u);
                 mma_commit(su32(&bars.v_empty[st]));
-                mma_commit(su32(&bars.pv_done[j & 1]));
+                mma_commit(su32(&bars.pv_done[sb]));
             }
         }
     } else {
@@ -296,27 +306,24 @@ __global__ void __launch_bounds__(384, 1) k_gqa_prefill_tc(const __grid_constant
         const size_t qrow = ((size_t)b * a.nh + h) * a.T + q0 + row;
         const float rscale = live ? a.rs[qrow] : 0.0f;
         const uint32_t lane_t = tmem + ((uint32_t)(wq * 32) << 16);
-        {   // query row -> tensor memory: 128 of its 256 halves per thread, two halves per 32-bit column
-            const uint4 *src = reinterpret_cast<const uint4 *>(a.Qh + qrow * HD + 128 * half);
+        {   // dims 0..127 of the query row -> tensor memory: 64 halves per thread, two per 32-bit column
+            const uint4 *src = reinterpret_cast<const uint4 *>(a.Qh + qrow * HD + 64 * half);
+            float q[32];
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                float q[32];
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const uint4 v = live ? src[8 * c + i] : make_uint4(0u, 0u, 0u, 0u);
-                    q[4 * i] = __uint_as_float(v.x); q[4 * i + 1] = __uint_as_float(v.y);
-                    q[4 * i + 2] = __uint_as_float(v.z); q[4 * i + 3] = __uint_as_float(v.w);
-                }
-                tmem_st32(lane_t + TM_Q + 64 * half + 32 * c, q);
+            for (int i = 0; i < 8; i++) {
+                const uint4 v = live ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+                q[4 * i] = __uint_as_float(v.x); q[4 * i + 1] = __uint_as_float(v.y);
+                q[4 * i + 2] = __uint_as_float(v.z); q[4 * i + 3] = __uint_as_float(v.w);
             }
+            tmem_st32(lane_t + TM_Q + 32 * half, q);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(su32(&bars.q_full));
         }
         float m_ref = -INFINITY, l = 0.0f;
         for (int j = 0; j < n_tiles; j++) {
-            const int sb = j & 1, key0 = j * BN + 32 * half;
-            ok = ok && mbar_wait(su32(&bars.s_full[sb]), (uint32_t)(j >> 1) & 1u);
+            const int sb = j % NB, key0 = j * BN + 32 * half;
+            ok = ok && mbar_wait(su32(&bars.s_full[sb]), (uint32_t)(j / NB) & 1u);
             tc_fence_after();
             float s[32];
             tmem_ld32(lane_t + TM_S + sb * BN + 32 * half, s);
@@ -358,7 +365,7 @@ __global__ void __launch_bounds__(384, 1) k_gqa_prefill_tc(const __grid_constant
             l += (p4[0] + p4[1]) + (p4[2] + p4[3]);
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 // O may only be touched between two value products: the last one is done, the next waits for us
-                ok = ok && mbar_wait(su32(&bars.pv_done[(j - 1) & 1]), (uint32_t)((j - 1) >> 1) & 1u);
+                ok = ok && mbar_wait(su32(&bars.pv_done[(j - 1) % NB]), (uint32_t)((j - 1) / NB) & 1u);
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < HD / 2; c += 32) {         // this thread's half of the output row
@@ -380,7 +387,7 @@ __global__ void __launch_bounds__(384, 1) k_gqa_prefill_tc(const __grid_constant
         lx[half][row] = l;
         pair_sync(1 + wq);
         l += lx[half ^ 1][row];
-        ok = ok && mbar_wait(su32(&bars.pv_done[(n_tiles - 1) & 1]), (uint32_t)((n_tiles - 1) >> 1) & 1u);
+        ok = ok && mbar_wait(su32(&bars.pv_done[(n_tiles - 1) % NB]), (uint32_t)((n_tiles - 1) / NB) & 1u);
         tc_fence_after();
         const float inv = ok ? 1.0f / l : NAN;
         const size_t tok = (size_t)b * a.T + q0 + row;
@@ -403,7 +410,7 @@ __global__ void __launch_bounds__(384, 1) k_gqa_prefill_tc(const __grid_constant
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 11) {
+    if (warp == 12) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TM_COLS) : "memory");
     }
 }
@@ -453,7 +460,8 @@ ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, con
     const size_t qrows = (size_t)n_seq * nh * T;
     k_q_rows_to_f16<<<(unsigned)((qrows + 3) / 4), 128, 0, st>>>(q_prep, Qh, rs, n_seq, T, nh, scale);
     ORN_TRY(orn_check_launch("k_q_rows_to_f16"));
-    CUtensorMap mk, mv;
+    CUtensorMap mq, mk, mv;
+    ORN_TRY(f16_rows_map(&mq, Qh, qrows, BM));
     ORN_TRY(f16_rows_map(&mk, Kh, (uint64_t)n_seq * kv.nkv * Lp, BN));
     ORN_TRY(f16_rows_map(&mv, Vh, (uint64_t)n_seq * kv.nkv * Lp, BN));
     TcArgs a;
@@ -468,7 +476,7 @@ ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, con
         configured = true;
     }
     dim3 grid((T + BM - 1) / BM, nh, n_seq);
-    if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16><<<grid, 384, SM_BYTES + 1024, st>>>(mk, mv, a);
-    else          k_gqa_prefill_tc<float><<<grid, 384, SM_BYTES + 1024, st>>>(mk, mv, a);
+    if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16><<<grid, 416, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    else          k_gqa_prefill_tc<float><<<grid, 416, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
     return orn_check_launch("k_gqa_prefill_tc");
 }
