@@ -7,10 +7,10 @@
 // rows of the cache (k_kv_rows_to_f16), so quantised caches are attended over in their decoded
 // form, the current token included, exactly as the reference does.
 //
-// One CTA = 128 query tokens of one head, 13 warps:
-//   warp 8      producer  one lane issues the TMA loads (128B-swizzled boxes of 64 dims): dims
-//                         128..255 of the query tile once, then the 64-key K tiles (3 stages)
-//                         and V tiles (2 stages)
+// One CTA = 128 query tokens of one head, 14 warps:
+//   warps 8,13  producers one lane each issues TMA loads (128B-swizzled boxes of 64 dims): warp 8
+//                         dims 128..255 of the query tile once, then the 64-key K tiles (3
+//                         stages); warp 13 the V tiles (2 stages)
 //   warps 9-11  scores    one lane each issues S_j = Q K_j^T (16 x tcgen05.mma M128 N64 K16) for
 //                         the tiles j = 0, 1, 2 (mod 3) into its own score buffer
 //   warp 12     values    one lane issues O += P_j V_j (4 x M128 N256 K16)
@@ -184,7 +184,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
 template <typename ACT>
-__global__ void __launch_bounds__(416, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mq,
+__global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mq,
                                                            const __grid_constant__ CUtensorMap mk,
                                                            const __grid_constant__ CUtensorMap mv, TcArgs a) {
     extern __shared__ unsigned char smraw[];
@@ -233,12 +233,22 @@ __global__ void __launch_bounds__(416, 1) k_gqa_prefill_tc(const __grid_constant
             for (int s = 0; s < 2; s++) tma_load_2d(base + SM_Q + s * 16384, &mq, 128 + s * 64, qrow, su32(&bars.q_full));
             const int krow = (b * a.nkv + kvh) * a.Lp;
             for (int j = 0; j < n_tiles; j++) {
-                const int sk = j % NSK, sv = j % NSV;
+                const int sk = j % NSK;
                 if (j >= NSK) ok = mbar_wait(su32(&bars.k_empty[sk]), (uint32_t)(j / NSK - 1) & 1u);
                 if (!ok) break;
                 mbar_expect_tx(su32(&bars.k_full[sk]), 32768u);
                 for (int s = 0; s < 4; s++)
                     tma_load_2d(base + SM_K + sk * 32768 + s * 8192, &mk, s * 64, krow + j * BN, su32(&bars.k_full[sk]));
+            }
+        }
+    } else if (warp == 13) {
+        // ================= producer of the V tiles =================
+        // its own lane: a V stage is released late (after the value product of its tile), and
+        // waiting for that must not hold back the K tiles, which the score MMAs need much earlier
+        if (lane == 0) {
+            const int krow = (b * a.nkv + kvh) * a.Lp;
+            for (int j = 0; j < n_tiles; j++) {
+                const int sv = j % NSV;
                 if (j >= NSV) ok = mbar_wait(su32(&bars.v_empty[sv]), (uint32_t)(j / NSV - 1) & 1u);
                 if (!ok) break;
                 mbar_expect_tx(su32(&bars.v_full[sv]), 32768u);
@@ -476,7 +486,7 @@ ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, con
         configured = true;
     }
     dim3 grid((T + BM - 1) / BM, nh, n_seq);
-    if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16><<<grid, 416, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
-    else          k_gqa_prefill_tc<float><<<grid, 416, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16><<<grid, 448, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    else          k_gqa_prefill_tc<float><<<grid, 448, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
     return orn_check_launch("k_gqa_prefill_tc");
 }
