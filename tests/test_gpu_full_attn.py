@@ -165,3 +165,82 @@ def test_long_context_split_k(oracle, L):
     out = D.full_attn_step(dl, kv, kv_len, torch.from_numpy(QP).cuda(), torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
     ref = oracle.full_attn_step(layer, okv, L, QP[0], K[0], V[0])
     assert rel_err(out.cpu().numpy()[0], ref) < TOL
+
+
+def _prefill(D, dl, kv, kv_len, QP, K, V, T, max_len=None, bf16=False):
+    import torch
+    dt = torch.bfloat16 if bf16 else torch.float32
+    to = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda().to(dt)
+    return D.full_attn_prefill(dl, kv, kv_len, to(QP), to(K), to(V), T, max_len=max_len).float().cpu().numpy()
+
+
+def test_tensor_core_prefill_long_prompt(oracle, monkeypatch):
+    """1500-token prompt at the 35B head shape (12 tiles of 128 query rows, up to 24 key tiles each):
+    the tcgen05 kernel against the oracle, then the same prompt in two calls (the second one
+    attends over a non-empty cache), and the mma.sync variant; cache bytes identical throughout."""
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(21)
+    dl = device_full(layer)
+    T = 1500
+    QP, K, V = full_inputs(210, layer, T)
+    okv = oracle.kv(T, layer.nkv, layer.hd, 2)
+    ref = oracle.full_attn_prefill(layer, okv, 0, QP, K, V)
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    monkeypatch.setenv("ORNITH_CUDA_PREFILL_VARIANT", "tc")
+    kv_a = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [T])
+    out_a = _prefill(D, dl, kv_a, z, QP[None], K[None], V[None], T)[0]
+    assert rel_err(out_a, ref) < TOL
+
+    kv_b = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [T])
+    T1 = 811                                               # not a multiple of any tile size
+    out_b1 = _prefill(D, dl, kv_b, z, QP[None, :T1], K[None, :T1], V[None, :T1], T1)[0]
+    n1 = torch.full((1,), T1, dtype=torch.int32, device="cuda")
+    out_b2 = _prefill(D, dl, kv_b, n1, QP[None, T1:], K[None, T1:], V[None, T1:], T - T1, max_len=T)[0]
+    assert rel_err(np.vstack([out_b1, out_b2]), ref) < TOL
+    assert rel_err(np.vstack([out_b1, out_b2]), out_a) < 5e-4
+
+    monkeypatch.setenv("ORNITH_CUDA_PREFILL_VARIANT", "mma")
+    kv_c = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [T])
+    out_c = _prefill(D, dl, kv_c, z, QP[None], K[None], V[None], T)[0]
+    assert rel_err(out_c, ref) < TOL
+    for other in (kv_b, kv_c):
+        assert (kv_a.K.cpu().numpy() == other.K.cpu().numpy()).all() and (kv_a.V.cpu().numpy() == other.V.cpu().numpy()).all()
+
+
+def test_tensor_core_prefill_ragged_batch_bf16():
+    """Two sequences in one call, one of them continuing a 700-token cache, bf16 activations:
+    each must equal the same sequence run alone."""
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(22)
+    dl = device_full(layer)
+    T, L0 = 600, 700
+    seqs = [full_inputs(220 + b, layer, L0 + T, bf16=True) for b in range(2)]
+    z1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    alone = []
+    for b, (QP, K, V) in enumerate(seqs):
+        kv = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [L0 + T])
+        if b == 1:
+            _prefill(D, dl, kv, z1, QP[None, :L0], K[None, :L0], V[None, :L0], L0, bf16=True)
+            start = torch.full((1,), L0, dtype=torch.int32, device="cuda")
+            alone.append(_prefill(D, dl, kv, start, QP[None, L0:], K[None, L0:], V[None, L0:], T, max_len=L0 + T, bf16=True)[0])
+        else:
+            alone.append(_prefill(D, dl, kv, z1, QP[None, :T], K[None, :T], V[None, :T], T, bf16=True)[0])
+    kv = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [T, L0 + T])
+    # sequence 1 gets its first L0 tokens through a single-sequence view of the shared pools
+    import ctypes as C
+    from ornithology_b200._lib import CudaKv
+    one = D.KvBatch.__new__(D.KvBatch)
+    one.__dict__.update(kv.__dict__)
+    off = kv.seq_off[1:3].clone()
+    one.n_seq = 1
+    one.c = CudaKv(D.KV_Q8_0, layer.nkv, layer.hd, 1, kv.c.K, kv.c.V, kv.c.Ks, kv.c.Vs, C.c_void_p(off.data_ptr()))
+    QP1, K1, V1 = seqs[1]
+    _prefill(D, dl, one, z1, QP1[None, :L0], K1[None, :L0], V1[None, :L0], L0, bf16=True)
+    lens = torch.tensor([0, L0], dtype=torch.int32, device="cuda")
+    QPb = np.stack([seqs[0][0][:T], QP1[L0:]]); Kb = np.stack([seqs[0][1][:T], K1[L0:]]); Vb = np.stack([seqs[0][2][:T], V1[L0:]])
+    both = _prefill(D, dl, kv, lens, QPb, Kb, Vb, T, max_len=L0 + T, bf16=True)
+    for b in range(2):
+        assert rel_err(both[b], alone[b]) < 1e-5, b

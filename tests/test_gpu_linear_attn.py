@@ -186,3 +186,32 @@ def test_prefill_equals_decode_on_gpu_bf16_batch(monkeypatch, B, T, fp32_scan, g
     assert rel_err(pre, dec) < TOL_BF16_IO
     assert rel_err(sa.S.cpu().numpy(), sb.S.cpu().numpy()) < (2e-4 if fp32_scan else TOL)
     assert (sa.conv.cpu().numpy() == sb.conv.cpu().numpy()).all()
+
+
+def test_tensor_core_scan_long_prompt_against_fp32_scan(monkeypatch):
+    """2000 tokens at the 35B head shape (63 chunks, the last one ragged): the tf32 tensor-core scan
+    in one call, in three calls with the state carried, and the all-fp32 scan."""
+    import torch
+    from ornithology_b200 import device as D
+    layer, kw = linear_case(31)                            # 16 key / 32 value heads
+    dl = device_linear(layer, kw)
+    T = 2000
+    ins = [_t(x)[None] for x in linear_inputs(310, layer, T)]
+
+    def run(parts, fp32):
+        monkeypatch.setenv("ORNITH_CUDA_PREFILL_FP32", "1" if fp32 else "0")
+        st = D.LinearState(dl, 1)
+        pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+        outs, t0 = [], 0
+        for n in parts:
+            outs.append(D.linear_attn_prefill(dl, st, pos, *[x[:, t0:t0 + n].contiguous() for x in ins], n, chunk=32))
+            D.advance(pos, n)
+            t0 += n
+        return torch.cat(outs, dim=1).cpu().numpy()[0], st.S.cpu().numpy()[0], st.conv.cpu().numpy()
+
+    o_ref, S_ref, c_ref = run([T], True)
+    o_tc, S_tc, c_tc = run([T], False)
+    o_3, S_3, c_3 = run([700, 1, 1299], False)
+    assert rel_err(o_tc, o_ref) < TOL and rel_err(S_tc, S_ref) < TOL
+    assert rel_err(o_3, o_ref) < TOL and rel_err(S_3, S_ref) < TOL
+    assert (c_tc == c_ref).all() and (c_3 == c_ref).all()
