@@ -36,6 +36,8 @@ constexpr int LDG = 33;
 constexpr int BLK_P = TC * LDP, BLK_AUX = 2 * TC * LDP;
 constexpr int BLK_FLOATS = BLK_AUX + 4 * TC;              // A, P, then p | beta | w_end | beta*p
 constexpr uint32_t BLK_BYTES = BLK_FLOATS * 4;
+constexpr int TILE_FLOATS = TC * LDK;                     // one chunk of normalised k (or q) rows, padded as in shared memory
+constexpr uint32_t TILE_BYTES = TILE_FLOATS * 4;
 
 __device__ __forceinline__ float tf32r(float x) {
     uint32_t u;
@@ -64,8 +66,9 @@ __device__ __forceinline__ void frag_a(float (&a)[4], const float *base, int ld,
 // =============================================================================
 // state-independent part: one CTA per (chunk, key head, sequence)
 // =============================================================================
-// Normalises the chunk's q / k rows in place in Y (tf32-rounded), then for every
-// value head that reads this key head writes one block of BLK_FLOATS floats:
+// Writes the chunk's normalised, tf32-rounded q / k rows as two packed tiles [32][132] (the
+// layout the scan keeps in shared memory, so that one bulk copy fetches a tile), then for
+// every value head that reads this key head one block of BLK_FLOATS floats:
 // A [32][36], P [32][36] (both tf32), p, beta, w_end, beta*p [32 each].
 struct PrepSmem {
     float Ks[TC * LDK];
@@ -76,9 +79,9 @@ struct PrepSmem {
     float Gw[4][TC], Bw[4][TC];
 };
 
-__global__ void __launch_bounds__(128) k_delta_chunk_prep(LinArgs a, float *Y, const float *rq, const float *rk,
+__global__ void __launch_bounds__(128) k_delta_chunk_prep(LinArgs a, const float *Y, const float *rq, const float *rk,
                                                           const float *la, const float *be, float *blocks,
-                                                          int n_chunks) {
+                                                          float *Kp, float *Qp, int n_chunks) {
     extern __shared__ __align__(16) unsigned char smraw[];
     PrepSmem &sm = *reinterpret_cast<PrepSmem *>(smraw);
     const int chunk = blockIdx.x, kh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -91,19 +94,28 @@ __global__ void __launch_bounds__(128) k_delta_chunk_prep(LinArgs a, float *Y, c
         const int i = e >> 5, c = (e & 31) * 4;
         float4 q = make_float4(0.f, 0.f, 0.f, 0.f), k = q;
         if (i < n) {
-            float *y = Y + (tok0 + i) * Cc + kh * 128 + c;
+            const float *y = Y + (tok0 + i) * Cc + kh * 128 + c;
             const float sq = rq[(tok0 + i) * a.nk + kh], sk = rk[(tok0 + i) * a.nk + kh];
             q = *reinterpret_cast<const float4 *>(y);
             k = *reinterpret_cast<const float4 *>(y + qd);
             q.x = tf32r(q.x * sq); q.y = tf32r(q.y * sq); q.z = tf32r(q.z * sq); q.w = tf32r(q.w * sq);
             k.x = tf32r(k.x * sk); k.y = tf32r(k.y * sk); k.z = tf32r(k.z * sk); k.w = tf32r(k.w * sk);
-            *reinterpret_cast<float4 *>(y) = q;
-            *reinterpret_cast<float4 *>(y + qd) = k;
         }
         *reinterpret_cast<float4 *>(&sm.Qs[i * LDK + c]) = q;
         *reinterpret_cast<float4 *>(&sm.Ks[i * LDK + c]) = k;
     }
+    if (tid < TC) {                                       // the four pad columns travel with the tile
+        *reinterpret_cast<float4 *>(&sm.Qs[tid * LDK + 128]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4 *>(&sm.Ks[tid * LDK + 128]) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     __syncthreads();
+    {
+        const size_t tile = (((size_t)b * a.nk + kh) * n_chunks + chunk) * TILE_FLOATS;
+        for (int e = tid; e < TILE_FLOATS / 4; e += 128) {
+            reinterpret_cast<float4 *>(Kp + tile)[e] = reinterpret_cast<const float4 *>(sm.Ks)[e];
+            reinterpret_cast<float4 *>(Qp + tile)[e] = reinterpret_cast<const float4 *>(sm.Qs)[e];
+        }
+    }
     {   // Gram tiles on or below the diagonal: warps 0-1 K K^T, warps 2-3 Q K^T; mt = w & 1
         const int which = w >> 1, mt = w & 1, ntn = 2 * mt + 2;
         float acc[4][4];
@@ -216,10 +228,19 @@ __device__ __forceinline__ void st_async_f32(uint32_t addr, float v, uint32_t ba
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];\n"
                  ::"r"(addr), "r"(__float_as_uint(v)), "r"(bar) : "memory");
 }
-__device__ __forceinline__ float2 ld2(const float *p, size_t i) { return *reinterpret_cast<const float2 *>(p + i); }
-__device__ __forceinline__ float2 ld2(const __nv_bfloat16 *p, size_t i) {
-    const uint32_t u = *reinterpret_cast<const uint32_t *>(p + i);
-    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+// Two adjacent activations, loaded raw: converting at the load would make the thread wait for
+// the data there and then; the values are only needed at the end of the chunk.
+struct Raw2 { uint32_t lo, hi; };
+__device__ __forceinline__ Raw2 ld2_raw(const float *p, size_t i) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p + i);
+    return Raw2{u.x, u.y};
+}
+__device__ __forceinline__ Raw2 ld2_raw(const __nv_bfloat16 *p, size_t i) {
+    return Raw2{*reinterpret_cast<const uint32_t *>(p + i), 0u};
+}
+__device__ __forceinline__ float2 cvt2(const float *, Raw2 r) { return make_float2(__uint_as_float(r.lo), __uint_as_float(r.hi)); }
+__device__ __forceinline__ float2 cvt2(const __nv_bfloat16 *, Raw2 r) {
+    return make_float2(__uint_as_float(r.lo << 16), __uint_as_float(r.lo & 0xffff0000u));
 }
 __device__ __forceinline__ void st2(float *p, size_t i, float x, float y) {
     *reinterpret_cast<float2 *>(p + i) = make_float2(x, y);
@@ -228,33 +249,44 @@ __device__ __forceinline__ void st2(__nv_bfloat16 *p, size_t i, float x, float y
     *reinterpret_cast<__nv_bfloat162 *>(p + i) = __floats2bfloat162_rn(x, y);
 }
 
-// Request one chunk: warp w copies rows 4w .. 4w+3 of K, Q and V (one lane per row and
-// matrix), thread 0 arms the barrier and copies the A / P / gate block.  Rows past the
-// end of the sequence are not copied; they keep finite leftovers, which beta = 0 cancels.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+// the mbarrier counts this thread's earlier cp.async copies as one arrival when they land
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+// Request one chunk.  The copy engine takes tens of cycles per bulk request whatever its size
+// (97 row-sized requests per chunk cost 2.6k of a 6.9k-cycle chunk), so a chunk is three bulk
+// copies — the packed k tile, the packed q tile, the A / P / gate block — issued by thread 0,
+// and its V columns arrive through per-thread 16-byte cp.async copies (one or two per thread)
+// that arrive on the same mbarrier: 1 + 256 arrivals per phase.  V rows past the end of the
+// sequence are not copied; they keep finite leftovers, which beta = 0 cancels.  No proxy fence:
+// the stage was only read since its last fill, and those reads are ordered before this call by
+// the CTA barrier at the top of the chunk loop.
 template <int NR>
 __device__ __forceinline__ void issue_chunk(typename ScanSmem<NR>::Stage &st, uint32_t bar, const float *Y,
-                                            size_t tok0, int nvalid, int Cc, int koff, int qoff, int voff,
-                                            const float *blk, int w, int lane) {
-    constexpr int LDN = ScanSmem<NR>::LDN;
-    if (lane < 12) {                                      // row = 4w + lane / 3, matrix = lane % 3
-        bc_fence_proxy_async();
-        if (w == 0 && lane == 0) {
-            bc_mbar_expect_tx(bar, (uint32_t)nvalid * (512u + 512u + NR * 4u) + BLK_BYTES);
-            bc_copy(bc_smem_u32(st.blk), blk, BLK_BYTES, bar);
-        }
-        const int row = 4 * w + lane / 3, which = lane % 3;
-        if (row < nvalid) {
-            const float *y = Y + (tok0 + row) * Cc;
-            if (which == 0) bc_copy(bc_smem_u32(&st.Ks[row * LDK]), y + koff, 512u, bar);
-            else if (which == 1) bc_copy(bc_smem_u32(&st.Qs[row * LDK]), y + qoff, 512u, bar);
-            else bc_copy(bc_smem_u32(&st.Vs[row * LDN]), y + voff, NR * 4u, bar);
-        }
+                                            size_t tok0, int nvalid, int Cc, int voff, const float *ktile,
+                                            const float *qtile, const float *blk, int tid) {
+    constexpr int LDN = ScanSmem<NR>::LDN, CPR = NR / 4;  // 16-byte pieces per V row
+    if (tid == 0) {
+        bc_mbar_expect_tx(bar, 2u * TILE_BYTES + BLK_BYTES);
+        bc_copy(bc_smem_u32(st.Ks), ktile, TILE_BYTES, bar);
+        bc_copy(bc_smem_u32(st.Qs), qtile, TILE_BYTES, bar);
+        bc_copy(bc_smem_u32(st.blk), blk, BLK_BYTES, bar);
     }
+#pragma unroll
+    for (int e = tid; e < TC * CPR; e += 256) {
+        const int row = e / CPR, c = e % CPR;
+        if (row < nvalid) cp_async16(bc_smem_u32(&st.Vs[row * LDN + 4 * c]), Y + (tok0 + row) * Cc + voff + 4 * c);
+    }
+    cp_async_arrive(bar);
 }
 
 template <int NR, typename ACT>
 __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const float *Y, const float *blocks,
-                                                             int n_chunks) {
+                                                             const float *Kp, const float *Qp, int n_chunks) {
     using SM = ScanSmem<NR>;
     constexpr int LDN = SM::LDN, CS = 128 / NR, NT = NR / 8, NTW = NR / 32;
     extern __shared__ __align__(128) unsigned char smraw[];
@@ -263,7 +295,8 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
     const int rank = (int)bc_cluster_rank(), hv = blockIdx.x / CS, b = blockIdx.y;
     const int kh = key_head_of(a, hv), qd = a.nk * 128, vd = a.nv * 128, Cc = 2 * qd + vd;
     const int col0 = rank * NR;
-    const int qoff = kh * 128, koff = qd + kh * 128, voff = 2 * qd + hv * 128 + col0;
+    const int voff = 2 * qd + hv * 128 + col0;
+    const float *kt0 = Kp + ((size_t)b * a.nk + kh) * n_chunks * TILE_FLOATS, *qt0 = Qp + ((size_t)b * a.nk + kh) * n_chunks * TILE_FLOATS;
     float *S = a.S + (size_t)b * a.S_stride + (size_t)hv * 128 * 128 + (size_t)col0 * 128;
     const float *blk0 = blocks + ((size_t)b * a.nv + hv) * n_chunks * BLK_FLOATS;
     const int mt = w & 1, wp = w >> 1, ntb = wp * NTW;   // [token][r] tiles: rows 16 mt.., n-tiles ntb..
@@ -278,18 +311,14 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
     const uint32_t uw_all = bc_smem_u32(sm.Uw) + 4u * (uint32_t)(brow * LDP + bcol);
 
     if (tid == 0) {
-        bc_mbar_init(bc_smem_u32(&sm.bar[0]), 1);
-        bc_mbar_init(bc_smem_u32(&sm.bar[1]), 1);
+        bc_mbar_init(bc_smem_u32(&sm.bar[0]), 257);      // thread 0's expect_tx + one cp.async arrival per thread
+        bc_mbar_init(bc_smem_u32(&sm.bar[1]), 257);
         bc_mbar_init(bc_smem_u32(&sm.rbar[0]), 1);
         bc_mbar_init(bc_smem_u32(&sm.rbar[1]), 1);
         bc_mbar_init_fence();
         sm.failed = 0;
     }
-    // rows of a stage that a short last chunk does not fill must hold finite values
-    for (int e = tid; e < TC * LDK; e += 256) {
-        sm.stage[0].Ks[e] = 0.0f; sm.stage[1].Ks[e] = 0.0f;
-        sm.stage[0].Qs[e] = 0.0f; sm.stage[1].Qs[e] = 0.0f;
-    }
+    // V rows of a stage that a short last chunk does not fill must hold finite values
     for (int e = tid; e < TC * LDN; e += 256) { sm.stage[0].Vs[e] = 0.0f; sm.stage[1].Vs[e] = 0.0f; }
     // state: st[nt][x] = S[8 nt + 2j + (x & 1)][m0 + g + 8 (x >> 1)] (rows local to this CTA)
     float st[NT][4];
@@ -304,11 +333,11 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
         nw[t][0] = a.norm_w[col0 + 8 * (ntb + t) + 2 * j];
         nw[t][1] = a.norm_w[col0 + 8 * (ntb + t) + 2 * j + 1];
     }
+    bc_fence_proxy_async();                               // the zeros above, before any bulk copy into the stages
     __syncthreads();
     bc_cluster_arrive();                                  // every CTA of the cluster is resident
     bc_cluster_wait();
-    issue_chunk<NR>(sm.stage[0], bc_smem_u32(&sm.bar[0]), Y, (size_t)b * a.T, min(TC, a.T), Cc, koff, qoff, voff, blk0,
-                    w, lane);
+    issue_chunk<NR>(sm.stage[0], bc_smem_u32(&sm.bar[0]), Y, (size_t)b * a.T, min(TC, a.T), Cc, voff, kt0, qt0, blk0, tid);
     bool ok = true;
     // where this thread's sums of squares go: slot [token][4 rank + wp] in every CTA of the cluster
     uint32_t red_peer[CS], rbar_peer[CS];
@@ -324,19 +353,20 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
         typename SM::Stage &sg = sm.stage[buf];
         __syncthreads();                                  // chunk n-1 is finished with the other stage, Tt, Ut, Sn
         if (n + 1 < n_chunks)
-            issue_chunk<NR>(sm.stage[buf ^ 1], bc_smem_u32(&sm.bar[buf ^ 1]), Y, tok0 + TC, min(TC, a.T - t0 - TC), Cc,
-                            koff, qoff, voff, blk0 + (size_t)(n + 1) * BLK_FLOATS, w, lane);
+            issue_chunk<NR>(sm.stage[buf ^ 1], bc_smem_u32(&sm.bar[buf ^ 1]), Y, tok0 + TC, min(TC, a.T - t0 - TC), Cc, voff,
+                            kt0 + (size_t)(n + 1) * TILE_FLOATS, qt0 + (size_t)(n + 1) * TILE_FLOATS,
+                            blk0 + (size_t)(n + 1) * BLK_FLOATS, tid);
         if (tid == 32) bc_mbar_expect_tx(bc_smem_u32(&sm.rbar[buf]), (uint32_t)(TC * 4 * CS * 4));
         // z of this thread's outputs, requested now and used at the end of the chunk
-        float2 zv[2][NTW];
+        Raw2 zv[2][NTW];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int i = 16 * mt + g + 8 * h;
 #pragma unroll
             for (int t = 0; t < NTW; t++) {
-                zv[h][t] = make_float2(0.0f, 0.0f);
+                zv[h][t] = Raw2{0u, 0u};
                 if (i < nvalid)
-                    zv[h][t] = ld2((const ACT *)a.z, (tok0 + i) * vd + (size_t)hv * 128 + col0 + 8 * (ntb + t) + 2 * j);
+                    zv[h][t] = ld2_raw((const ACT *)a.z, (tok0 + i) * vd + (size_t)hv * 128 + col0 + 8 * (ntb + t) + 2 * j);
             }
         }
         ok = ok && bc_mbar_wait(bc_smem_u32(&sm.bar[buf]), (uint32_t)(n >> 1) & 1u);   // one timeout at most
@@ -510,8 +540,11 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
             const size_t off = (tok0 + i) * vd + (size_t)hv * 128 + col0;
 #pragma unroll
             for (int t = 0; t < NTW; t++)
-                st2((ACT *)a.out, off + 8 * (ntb + t) + 2 * j, o[t][2 * h] * inv * nw[t][0] * silu_fast(zv[h][t].x),
-                    o[t][2 * h + 1] * inv * nw[t][1] * silu_fast(zv[h][t].y));
+            {
+                const float2 zz = cvt2((const ACT *)nullptr, zv[h][t]);
+                st2((ACT *)a.out, off + 8 * (ntb + t) + 2 * j, o[t][2 * h] * inv * nw[t][0] * silu_fast(zz.x),
+                    o[t][2 * h + 1] * inv * nw[t][1] * silu_fast(zz.y));
+            }
         }
         if (!ok) sm.failed = 1;
     }
@@ -527,8 +560,8 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
 }
 
 template <int NR, typename ACT>
-ornith_status launch_scan(const LinArgs &x, int n_seq, const float *Y, const float *blocks, int n_chunks,
-                          cudaStream_t s) {
+ornith_status launch_scan(const LinArgs &x, int n_seq, const float *Y, const float *blocks, const float *Kp,
+                          const float *Qp, int n_chunks, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_chunk_scan<NR, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -548,15 +581,19 @@ ornith_status launch_scan(const LinArgs &x, int n_seq, const float *Y, const flo
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    ORN_TRY(orn_check(cudaLaunchKernelEx(&cfg, k_delta_chunk_scan<NR, ACT>, x, Y, blocks, n_chunks),
+    ORN_TRY(orn_check(cudaLaunchKernelEx(&cfg, k_delta_chunk_scan<NR, ACT>, x, Y, blocks, Kp, Qp, n_chunks),
                       "k_delta_chunk_scan launch"));
     return orn_check_launch("k_delta_chunk_scan");
 }
 
 }  // namespace
 
-size_t linear_prefill_tc_blocks_bytes(int nv, int n_seq, int T) {
-    return (size_t)n_seq * nv * ((T + TC - 1) / TC) * BLK_BYTES;
+static size_t blocks_part(int nv, int n_seq, int n_chunks) { return align_up((size_t)n_seq * nv * n_chunks * BLK_BYTES, 256); }
+static size_t tiles_part(int nk, int n_seq, int n_chunks) { return align_up((size_t)n_seq * nk * n_chunks * TILE_BYTES, 256); }
+
+size_t linear_prefill_tc_blocks_bytes(int nk, int nv, int n_seq, int T) {
+    const int n_chunks = (T + TC - 1) / TC;
+    return blocks_part(nv, n_seq, n_chunks) + 2 * tiles_part(nk, n_seq, n_chunks);
 }
 
 ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtype, float *Y, const float *rq,
@@ -570,14 +607,16 @@ ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtyp
                           "delta chunk prep smem opt-in"));
         configured = true;
     }
+    float *Kp = (float *)((char *)blocks + blocks_part(x.nv, n_seq, n_chunks));
+    float *Qp = (float *)((char *)Kp + tiles_part(x.nk, n_seq, n_chunks));
     k_delta_chunk_prep<<<dim3((unsigned)n_chunks, (unsigned)x.nk, (unsigned)n_seq), 128, sizeof(PrepSmem), s>>>(
-        x, Y, rq, rk, la, be, blocks, n_chunks);
+        x, Y, rq, rk, la, be, blocks, Kp, Qp, n_chunks);
     ORN_TRY(orn_check_launch("k_delta_chunk_prep"));
     const bool bf = act_dtype == ORNITH_ACT_BF16;
     // 32-column CTAs (clusters of 4) while they all fit on the SMs at once, else 64-column (clusters of 2)
     if ((long long)x.nv * n_seq * 4 <= 148)
-        return bf ? launch_scan<32, __nv_bfloat16>(x, n_seq, Y, blocks, n_chunks, s)
-                  : launch_scan<32, float>(x, n_seq, Y, blocks, n_chunks, s);
-    return bf ? launch_scan<64, __nv_bfloat16>(x, n_seq, Y, blocks, n_chunks, s)
-              : launch_scan<64, float>(x, n_seq, Y, blocks, n_chunks, s);
+        return bf ? launch_scan<32, __nv_bfloat16>(x, n_seq, Y, blocks, Kp, Qp, n_chunks, s)
+                  : launch_scan<32, float>(x, n_seq, Y, blocks, Kp, Qp, n_chunks, s);
+    return bf ? launch_scan<64, __nv_bfloat16>(x, n_seq, Y, blocks, Kp, Qp, n_chunks, s)
+              : launch_scan<64, float>(x, n_seq, Y, blocks, Kp, Qp, n_chunks, s);
 }

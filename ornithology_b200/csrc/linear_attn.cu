@@ -742,7 +742,7 @@ size_t ornith_cuda_linear_attn_prefill_scratch(const ornith_cuda_linear_layer *l
     if (!l || n_seq <= 0 || T <= 0) return 0;
     const size_t n_tok = (size_t)n_seq * T, Cc = 2 * (size_t)l->nk * l->dk + (size_t)l->nv * l->dv;
     size_t bytes = align_up(n_tok * Cc * 4, 256) + 2 * align_up(n_tok * l->nk * 4, 256) + 2 * align_up(n_tok * l->nv * 4, 256);
-    if (l->dk == 128 && l->dv == 128) bytes += align_up(linear_prefill_tc_blocks_bytes(l->nv, n_seq, T), 256);
+    if (l->dk == 128 && l->dv == 128) bytes += align_up(linear_prefill_tc_blocks_bytes(l->nk, l->nv, n_seq, T), 256);
     return bytes;
 }
 

@@ -23,10 +23,10 @@ __device__ __forceinline__ bool owns_key_head(const LinArgs &a, int hv) {
 }
 
 // Tensor-core chunked scan for dk = dv = 128 (delta_prefill_tc.cu).  Y holds the
-// conv + SiLU image of qkv (its q / k parts are normalised in place), rq / rk the
+// conv + SiLU image of qkv, rq / rk the
 // per-(token, key head) inverse norms, la / be the per-(token, value head) log-decay
 // and write gate, blocks a work area of linear_prefill_tc_blocks_bytes() bytes.
-size_t linear_prefill_tc_blocks_bytes(int nv, int n_seq, int T);
+size_t linear_prefill_tc_blocks_bytes(int nk, int nv, int n_seq, int T);
 ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtype, float *Y, const float *rq,
                                        const float *rk, const float *la, const float *be, float *blocks,
                                        cudaStream_t s);

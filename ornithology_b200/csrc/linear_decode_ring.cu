@@ -20,14 +20,21 @@ constexpr int STAGES = 3;
 constexpr int STAGE_FLOATS = 64 * 128;                // half a head: 64 rows of the state, 32 KiB
 constexpr uint32_t STAGE_BYTES = STAGE_FLOATS * 4;
 
-struct UnitOperands {                                 // everything a unit needs apart from its state
-    float h0[4], h1[4], x0, x1, bias0, bias1, ain, bin, acoef, dtb, zin[2][2], nw[2][2];
+// Everything a unit needs apart from its state.  Activations stay in their storage type until
+// they are used: a conversion at the load would make the thread wait for the data there, and
+// these loads are issued a whole unit ahead precisely so that nobody waits for them.
+template <typename ACT>
+struct UnitOperands {
+    float h0[4], h1[4], bias0, bias1, acoef, dtb, nw[2][2];
+    ACT x0, x1, ain, bin, zin[2][2];
     float4 w0, w1;
     int t;
 };
+__device__ __forceinline__ float act_f(float v) { return v; }
+__device__ __forceinline__ float act_f(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 template <typename ACT>
-__device__ __forceinline__ void load_operands(UnitOperands &o, const LinArgs &a, int b, int hv, int tid, int w, int sr,
+__device__ __forceinline__ void load_operands(UnitOperands<ACT> &o, const LinArgs &a, int b, int hv, int tid, int w, int sr,
                                               int cc) {
     const int kh = key_head_of(a, hv), qd = a.nk * 128, vd = a.nv * 128, Cc = 2 * qd + vd;
     const float *ring = a.conv + (size_t)b * a.conv_stride;
@@ -37,20 +44,20 @@ __device__ __forceinline__ void load_operands(UnitOperands &o, const LinArgs &a,
     const int c1 = qd + kh * 128 + (tid & 127);
 #pragma unroll
     for (int sl = 0; sl < 4; sl++) { o.h0[sl] = ring[(size_t)sl * Cc + c0]; o.h1[sl] = 0.0f; }
-    o.x0 = act_ld(x, c0);
+    o.x0 = x[c0];
     o.w0 = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)c0 * 4);
     o.bias0 = a.conv_b ? a.conv_b[c0] : 0.0f;
-    o.x1 = 0.0f; o.bias1 = 0.0f; o.w1 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    o.x1 = x[c0]; o.bias1 = 0.0f; o.w1 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);      // x1 only matters on q/k threads
     if (qk_thread) {
 #pragma unroll
         for (int sl = 0; sl < 4; sl++) o.h1[sl] = ring[(size_t)sl * Cc + c1];
-        o.x1 = act_ld(x, c1);
+        o.x1 = x[c1];
         o.w1 = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)c1 * 4);
         o.bias1 = a.conv_b ? a.conv_b[c1] : 0.0f;
     }
     o.t = a.pos[b];
-    o.ain = act_ld((const ACT *)a.a, (size_t)b * a.nv + hv);
-    o.bin = act_ld((const ACT *)a.b, (size_t)b * a.nv + hv);
+    o.ain = ((const ACT *)a.a)[(size_t)b * a.nv + hv];
+    o.bin = ((const ACT *)a.b)[(size_t)b * a.nv + hv];
     o.acoef = a.a_coef[hv]; o.dtb = a.dt_bias[hv];
     const size_t out_base = (size_t)b * vd + (size_t)hv * 128;
 #pragma unroll
@@ -58,7 +65,7 @@ __device__ __forceinline__ void load_operands(UnitOperands &o, const LinArgs &a,
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             const int r = 64 * h + 8 * w + 4 * i + sr;
-            o.zin[h][i] = (cc == 0) ? act_ld((const ACT *)a.z, out_base + r) : 0.0f;
+            o.zin[h][i] = ((const ACT *)a.z)[out_base + (cc == 0 ? r : 0)];
             o.nw[h][i] = (cc == 0) ? a.norm_w[r] : 0.0f;
         }
 }
@@ -92,7 +99,7 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_
         }
     }
     bool ok = true;
-    UnitOperands nxt;
+    UnitOperands<ACT> nxt;
     load_operands<ACT>(nxt, a, (int)blockIdx.x / a.nv, (int)blockIdx.x % a.nv, tid, w, sr, cc);
 
     for (int k = 0; k < n_mine; k++) {
@@ -100,7 +107,7 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_
         const int kh = key_head_of(a, hv);
         float *S = a.S + (size_t)b * a.S_stride + (size_t)hv * 128 * 128;
         float *ring = a.conv + (size_t)b * a.conv_stride;
-        const UnitOperands cur = nxt;
+        const UnitOperands<ACT> cur = nxt;
         if (k + 1 < n_mine) {
             const int un = u + (int)gridDim.x;
             load_operands<ACT>(nxt, a, un / a.nv, un % a.nv, tid, w, sr, cc);
@@ -113,13 +120,14 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_
         // ---- conv + SiLU, q/k L2-norm (reference: src/ornith_tensor.c:155-160), gates ------------
         const int sb = (t + 1) & 3;
         const bool own = owns_key_head(a, hv);
-        const float y0 = conv4_silu(cur.h0, cur.x0, cur.w0, cur.bias0, sb);
+        const float x0 = act_f(cur.x0), x1 = act_f(cur.x1);
+        const float y0 = conv4_silu(cur.h0, x0, cur.w0, cur.bias0, sb);
         float y1 = 0.0f;
         if (qk_thread) {
-            y1 = conv4_silu(cur.h1, cur.x1, cur.w1, cur.bias1, sb);
-            if (own) { ring[(size_t)(t & 3) * Cc + c0] = cur.x0; ring[(size_t)(t & 3) * Cc + c1] = cur.x1; }
+            y1 = conv4_silu(cur.h1, x1, cur.w1, cur.bias1, sb);
+            if (own) { ring[(size_t)(t & 3) * Cc + c0] = x0; ring[(size_t)(t & 3) * Cc + c1] = x1; }
         } else {
-            ring[(size_t)(t & 3) * Cc + c0] = cur.x0;
+            ring[(size_t)(t & 3) * Cc + c0] = x0;
             v_s[tid - 128] = y0;
         }
         {
@@ -134,8 +142,8 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_
             k_s[tid] = y1 * (float)(1.0 / sqrt(ssk + (double)1e-6f));
         }
         if (tid == 0) {   // decay and write gates (reference: src/ornith_rforward.c:282-284, :493-496)
-            gates[0] = expf(cur.acoef * softplus_f(cur.ain + cur.dtb));
-            gates[1] = sigmoid_f(cur.bin);
+            gates[0] = expf(cur.acoef * softplus_f(act_f(cur.ain) + cur.dtb));
+            gates[1] = sigmoid_f(act_f(cur.bin));
         }
         __syncthreads();
 
@@ -210,7 +218,7 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_
                 for (int i = 0; i < 2; i++) {
                     const int r = 64 * h + 8 * w + 4 * i + sr;
                     float y = orow[h][i] * inv * cur.nw[h][i];
-                    y *= silu_f(cur.zin[h][i]);
+                    y *= silu_f(act_f(cur.zin[h][i]));
                     act_st((ACT *)a.out, out_base + r, y);
                 }
         }
