@@ -215,7 +215,7 @@ struct ScanSmem {
 __device__ __forceinline__ void ldsm4(float (&r)[4], uint32_t addr) {
     uint32_t x0, x1, x2, x3;
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
+                 : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr));
     r[0] = __uint_as_float(x0); r[1] = __uint_as_float(x1); r[2] = __uint_as_float(x2); r[3] = __uint_as_float(x3);
 }
 // Round to tf32 for an MMA operand in one integer add (finite inputs): the tensor core
@@ -523,6 +523,15 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
                 for (int x = 0; x < 4; x++)
                     sm.Sn[(8 * nt + 2 * j + (x & 1)) * LDK + m0 + g + 8 * (x >> 1)] = tf32q(st[nt][x]);
         }
+        // everything of the epilogue that does not need the row sums: o * norm weight * SiLU(z)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int t = 0; t < NTW; t++) {
+                const float2 zz = cvt2((const ACT *)nullptr, zv[h][t]);
+                o[t][2 * h] *= nw[t][0] * silu_fast(zz.x);
+                o[t][2 * h + 1] *= nw[t][1] * silu_fast(zz.y);
+            }
         ok = ok && bc_mbar_wait(bc_smem_u32(&sm.rbar[buf]), (uint32_t)(n >> 1) & 1u);
         // ---- RMSNorm over the head row, SiLU(z) gate, store
         const bool bad = !ok || *(volatile int *)&sm.failed;
@@ -540,11 +549,7 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
             const size_t off = (tok0 + i) * vd + (size_t)hv * 128 + col0;
 #pragma unroll
             for (int t = 0; t < NTW; t++)
-            {
-                const float2 zz = cvt2((const ACT *)nullptr, zv[h][t]);
-                st2((ACT *)a.out, off + 8 * (ntb + t) + 2 * j, o[t][2 * h] * inv * nw[t][0] * silu_fast(zz.x),
-                    o[t][2 * h + 1] * inv * nw[t][1] * silu_fast(zz.y));
-            }
+                st2((ACT *)a.out, off + 8 * (ntb + t) + 2 * j, o[t][2 * h] * inv, o[t][2 * h + 1] * inv);
         }
         if (!ok) sm.failed = 1;
     }
