@@ -21,6 +21,9 @@ struct PrepArgs {
     const int32_t *kv_len, *rope_pos;
     const void *qproj, *k, *v;
     float *q_prep;                       // [n_tok][nh][hd] f32
+    __half *Qh;                          // if set: query rows as f16 [n_seq*nh*T][hd], each scaled by 2^-e, instead of q_prep
+    float *rs;                           //         and scale * 2^e * log2(e) per row
+    float scale;
     const float *q_norm_w, *k_norm_w, *inv_freq;
     int nh, rope_dim, gated, T;
     int row0;                            // first row handled (nh skips the query heads)
@@ -155,6 +158,23 @@ __global__ void __launch_bounds__(128) k_full_prep_warp(PrepArgs a, long long n_
         __syncwarp();
     }
     if (kind == 0) {
+        if (a.Qh) {                                       // f16 image for the tensor-core kernel (hd = 256)
+            float mx = 0.0f;
+            for (int i = lane; i < hd; i += 32) mx = fmaxf(mx, fabsf(row[i]));
+            mx = warp_max(mx);
+            int e = 0;
+            if (mx > 0.0f && mx < INFINITY) (void)frexpf(mx, &e);
+            const float down = exp2f((float)-e);
+            const size_t orow = ((size_t)b * nh + h) * a.T + t;
+            const float *src8 = row + lane * 8;           // hd = 256: eight values per lane
+            __half2 p0 = __floats2half2_rn(src8[0] * down, src8[1] * down), p1 = __floats2half2_rn(src8[2] * down, src8[3] * down);
+            __half2 p2 = __floats2half2_rn(src8[4] * down, src8[5] * down), p3 = __floats2half2_rn(src8[6] * down, src8[7] * down);
+            *reinterpret_cast<uint4 *>(a.Qh + orow * hd + lane * 8) =
+                make_uint4(*reinterpret_cast<uint32_t *>(&p0), *reinterpret_cast<uint32_t *>(&p1),
+                           *reinterpret_cast<uint32_t *>(&p2), *reinterpret_cast<uint32_t *>(&p3));
+            if (lane == 0) a.rs[orow] = a.scale * exp2f((float)e) * 1.4426950408889634f;
+            return;
+        }
         float *dst = a.q_prep + ((size_t)tt * nh + h) * hd;
         for (int i = lane; i < hd; i += 32) dst[i] = row[i];
         return;
@@ -492,8 +512,9 @@ template <typename ACT>
 static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
                                  const int32_t *kv_len, const int32_t *rope_pos, const void *qproj,
                                  const void *k, const void *v, float *q_prep, int n_tok, int T,
-                                 cudaStream_t st, bool kv_only = false) {
+                                 cudaStream_t st, bool kv_only = false, __half *Qh = nullptr, float *rs = nullptr) {
     PrepArgs a;
+    a.Qh = Qh; a.rs = rs; a.scale = attn_scale(l);
     a.kv = make_view(kv); a.kv_len = kv_len; a.rope_pos = rope_pos;
     a.qproj = qproj; a.k = k; a.v = v; a.q_prep = q_prep;
     a.q_norm_w = l->q_norm_w; a.k_norm_w = l->k_norm_w; a.inv_freq = l->rope_inv_freq;
@@ -629,12 +650,19 @@ ornith_status ornith_cuda_full_attn_prefill(const ornith_cuda_full_layer *l, con
     const int hd = l->head_dim, nh = l->n_heads, G = nh / l->n_kv_heads;
     float *q_prep = (float *)scratch;
     const bool bf = act_dtype == ORNITH_ACT_BF16;
-    if (bf) ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st));
-    else    ORN_TRY(launch_prep<float>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st));
+    const bool tensor_path = gqa_prefill_mma_supported(make_view(kv)) && !force_generic_decode();
+    void *kvh = (char *)scratch + align_up((size_t)B * T * nh * hd * sizeof(float), 256);
+    __half *Qh = nullptr;
+    float *rs = nullptr;
+    // the warp-per-row front end (B * T >= 256) writes the f16 query image of the tcgen05 kernel itself
+    const bool q_image = tensor_path && (long long)B * T >= 256 &&
+                         gqa_prefill_q_image(kvh, B, l->n_kv_heads, nh, T, max_len, &Qh, &rs);
+    if (!q_image) { Qh = nullptr; rs = nullptr; }
+    if (bf) ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st, false, Qh, rs));
+    else    ORN_TRY(launch_prep<float>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st, false, Qh, rs));
 
-    if (gqa_prefill_mma_supported(make_view(kv)) && !force_generic_decode()) {
-        void *kvh = (char *)scratch + align_up((size_t)B * T * nh * hd * sizeof(float), 256);
-        return launch_gqa_prefill_mma(make_view(kv), kv_len, q_prep, kvh, qproj, out, nh, T, max_len, l->gated,
+    if (tensor_path) {
+        return launch_gqa_prefill_mma(make_view(kv), kv_len, q_image ? nullptr : q_prep, kvh, qproj, out, nh, T, max_len, l->gated,
                                       attn_scale(l), B, bf, st);
     }
     PrefillArgs a;

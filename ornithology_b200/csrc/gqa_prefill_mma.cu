@@ -303,6 +303,14 @@ static bool prefer_mma_sync() {
     return v && v[0] == 'm';
 }
 
+bool gqa_prefill_q_image(void *kvh_scratch, int n_seq, int nkv, int nh, int T, int Lmax, __half **Qh, float **rs) {
+    if (prefer_mma_sync() || ((uintptr_t)kvh_scratch % 16) != 0) return false;
+    char *q = (char *)kvh_scratch + 2 * image_bytes(n_seq, nkv, Lmax);
+    *Qh = (__half *)q;
+    *rs = (float *)(q + align_up((size_t)n_seq * nh * T * HD * sizeof(__half), 256));
+    return true;
+}
+
 ornith_status launch_gqa_prefill_mma(const KvView &kv, const int32_t *kv_len, const float *q_prep, void *kvh_scratch,
                                      const void *qproj, void *out, int nh, int T, int Lmax, int gated, float scale,
                                      int n_seq, bool bf16_act, cudaStream_t st) {

@@ -468,8 +468,10 @@ ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, con
     __half *Qh = (__half *)q_scratch;
     float *rs = (float *)((char *)q_scratch + align_up((size_t)n_seq * nh * T * HD * sizeof(__half), 256));
     const size_t qrows = (size_t)n_seq * nh * T;
-    k_q_rows_to_f16<<<(unsigned)((qrows + 3) / 4), 128, 0, st>>>(q_prep, Qh, rs, n_seq, T, nh, scale);
-    ORN_TRY(orn_check_launch("k_q_rows_to_f16"));
+    if (q_prep) {                                          // otherwise the front end has written the image itself
+        k_q_rows_to_f16<<<(unsigned)((qrows + 3) / 4), 128, 0, st>>>(q_prep, Qh, rs, n_seq, T, nh, scale);
+        ORN_TRY(orn_check_launch("k_q_rows_to_f16"));
+    }
     CUtensorMap mq, mk, mv;
     ORN_TRY(f16_rows_map(&mq, Qh, qrows, BM));
     ORN_TRY(f16_rows_map(&mk, Kh, (uint64_t)n_seq * kv.nkv * Lp, BN));
