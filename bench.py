@@ -110,8 +110,9 @@ def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b"):
 
     ms_lin = timed(lambda: gather(D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64)))
     ms_full = timed(lambda: gather(D.full_attn_prefill(full, kv, pos, *full_in, T)))
-    ms_lin_k = timed(lambda: D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64))
-    ms_full_k = timed(lambda: D.full_attn_prefill(full, kv, pos, *full_in, T))
+    # without the all-gather (the same call when there is one rank)
+    ms_lin_k = ms_lin if world == 1 else timed(lambda: D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64))
+    ms_full_k = ms_full if world == 1 else timed(lambda: D.full_attn_prefill(full, kv, pos, *full_in, T))
     # algorithmic work of the whole layer (all ranks): causal QK^T + PV; chunked scan at C = 32
     fl_full = 4.0 * 256 * NH * T * (T + 1) / 2
     fl_lin = float(NV) * (T / 32) * (6 * 32 * 128 * 128 + 2 * 32 * 32 * 256)

@@ -582,6 +582,10 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
         }
         d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
         ORN_TRY(launch_gqa_decode_q8_mma(d, B, st));
+    } else if (gqa_decode_f32_tc_supported(d.kv, nh) && !force_generic_decode()) {
+        const int tps_tc = split_tokens_mma(max_len);
+        d.tokens_per_split = tps_tc; d.nsplit = nsplit_used = (max_len + tps_tc - 1) / tps_tc;
+        ORN_TRY(launch_gqa_decode_f32_tc(d, B, st));
     } else {
         d.tokens_per_split = tps; d.nsplit = nsplit_used = nsplit;
         dim3 grid(nsplit, nh, B);

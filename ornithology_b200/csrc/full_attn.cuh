@@ -21,6 +21,11 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
 // from the staged raw rows (gqa_decode_q8_raw.cu).
 ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st);
 
+// Tensor-core (tf32) split-K decode over f32 rows, head_dim 256, up to 8 query heads per KV head
+// (gqa_decode_f32.cu).  Same partials.
+bool gqa_decode_f32_tc_supported(const KvView &kv, int nh);
+ornith_status launch_gqa_decode_f32_tc(const DecodeArgs &a, int n_seq, cudaStream_t st);
+
 // Tensor-core causal prefill for head_dim 256 (gqa_prefill_mma.cu): decodes the visible cache
 // rows into an f16 image in `kvh_scratch` (gqa_prefill_mma_scratch bytes), then attends with
 // the tcgen05 kernel (gqa_prefill_tc.cu) or, on request, the mma.sync one.
