@@ -586,6 +586,10 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
         const int tps_tc = split_tokens_mma(max_len);
         d.tokens_per_split = tps_tc; d.nsplit = nsplit_used = (max_len + tps_tc - 1) / tps_tc;
         ORN_TRY(launch_gqa_decode_f32_tc(d, B, st));
+    } else if (gqa_decode_i8_raw_supported(d.kv, nh) && !force_generic_decode()) {
+        const int tps_tc = split_tokens_mma(max_len);
+        d.tokens_per_split = tps_tc; d.nsplit = nsplit_used = (max_len + tps_tc - 1) / tps_tc;
+        ORN_TRY(launch_gqa_decode_i8_raw(d, B, st));
     } else {
         d.tokens_per_split = tps; d.nsplit = nsplit_used = nsplit;
         dim3 grid(nsplit, nh, B);

@@ -21,6 +21,10 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
 // from the staged raw rows (gqa_decode_q8_raw.cu).
 ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st);
 
+// The same for int8-per-head rows (gqa_decode_i8_raw.cu), up to 8 query heads per KV head.
+bool gqa_decode_i8_raw_supported(const KvView &kv, int nh);
+ornith_status launch_gqa_decode_i8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st);
+
 // Tensor-core (tf32) split-K decode over f32 rows, head_dim 256, up to 8 query heads per KV head
 // (gqa_decode_f32.cu).  Same partials.
 bool gqa_decode_f32_tc_supported(const KvView &kv, int nh);

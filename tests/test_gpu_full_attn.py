@@ -244,3 +244,57 @@ def test_tensor_core_prefill_ragged_batch_bf16():
     both = _prefill(D, dl, kv, lens, QPb, Kb, Vb, T, max_len=L0 + T, bf16=True)
     for b in range(2):
         assert rel_err(both[b], alone[b]) < 1e-5, b
+
+
+@pytest.mark.parametrize("L", [1500, 9001])
+def test_long_context_split_k_f32_rows(oracle, L):
+    """The tf32 tensor-core decode over f32 rows: several splits, a ragged last split and tile."""
+    import ctypes as C
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(6)
+    dl = device_full(layer)
+    rng = np.random.default_rng(18)
+    kv = D.KvBatch(D.KV_F32, layer.nkv, layer.hd, [L + 1])
+    okv = oracle.kv(L + 1, layer.nkv, layer.hd, 0)
+    Kraw = rng.standard_normal((L, layer.nkv * layer.hd)).astype(np.float32)
+    Vraw = rng.standard_normal((L, layer.nkv * layer.hd)).astype(np.float32)
+    kv.K.view(torch.float32)[:Kraw.size] = torch.from_numpy(Kraw.ravel()).cuda()
+    kv.V.view(torch.float32)[:Vraw.size] = torch.from_numpy(Vraw.ravel()).cuda()
+    C.memmove(okv.c.K, Kraw.ctypes.data, Kraw.nbytes); C.memmove(okv.c.V, Vraw.ctypes.data, Vraw.nbytes)
+    okv.c.len = L
+    QP, K, V = full_inputs(19, layer, 1)
+    kv_len = torch.tensor([L], dtype=torch.int32, device="cuda")
+    out = D.full_attn_step(dl, kv, kv_len, torch.from_numpy(QP).cuda(), torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
+    ref = oracle.full_attn_step(layer, okv, L, QP[0], K[0], V[0])
+    assert rel_err(out.cpu().numpy()[0], ref) < TOL
+
+
+@pytest.mark.parametrize("L", [1500, 9001])
+def test_long_context_split_k_int8_rows(oracle, L):
+    """The raw-fragment decode over int8-per-head rows (the engine's own quantised cache)."""
+    import ctypes as C
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(7)
+    dl = device_full(layer)
+    rng = np.random.default_rng(28)
+    n = L * layer.nkv
+    kv = D.KvBatch(D.KV_INT8_HEAD, layer.nkv, layer.hd, [L + 1])
+    okv = oracle.kv(L + 1, layer.nkv, layer.hd, 1)
+    Kq = rng.integers(-127, 128, (n, layer.hd)).astype(np.int8)
+    Vq = rng.integers(-127, 128, (n, layer.hd)).astype(np.int8)
+    Ks = rng.uniform(0.005, 0.04, n).astype(np.float32)
+    Vs = rng.uniform(0.005, 0.04, n).astype(np.float32)
+    kv.K[:Kq.size] = torch.from_numpy(Kq.view(np.uint8).ravel()).cuda()
+    kv.V[:Vq.size] = torch.from_numpy(Vq.view(np.uint8).ravel()).cuda()
+    kv.Ks[:n] = torch.from_numpy(Ks).cuda()
+    kv.Vs[:n] = torch.from_numpy(Vs).cuda()
+    C.memmove(okv.c.Kq, Kq.ctypes.data, Kq.nbytes); C.memmove(okv.c.Vq, Vq.ctypes.data, Vq.nbytes)
+    C.memmove(okv.c.Ks, Ks.ctypes.data, Ks.nbytes); C.memmove(okv.c.Vs, Vs.ctypes.data, Vs.nbytes)
+    okv.c.len = L
+    QP, K, V = full_inputs(29, layer, 1)
+    kv_len = torch.tensor([L], dtype=torch.int32, device="cuda")
+    out = D.full_attn_step(dl, kv, kv_len, torch.from_numpy(QP).cuda(), torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
+    ref = oracle.full_attn_step(layer, okv, L, QP[0], K[0], V[0])
+    assert rel_err(out.cpu().numpy()[0], ref) < TOL
