@@ -1,5 +1,5 @@
 // gqa_decode_f32.cu — split-K GQA decode over f32 KV rows on the tensor cores (tf32),
-// head_dim 256, groups of up to 8 query heads per KV head.
+// head_dim 256, groups of up to 16 query heads per KV head (two CTAs of 8 heads beyond 8).
 //
 // Replaces the attend half of ornith_gqa_step for the f32 cache (reference:
 // src/ornith_attn.c:111-148).  An f32 row is 1 KiB; at 8 query heads per KV head the
@@ -67,15 +67,18 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_f32_tc(DecodeArgs a) {
     float *Kt = reinterpret_cast<float *>(smem + QS_BYTES + warp * WARP_BYTES), *Vt = Kt + TILE * LDKT;
     if (tid == 0) pipe_failed = 0;
 
-    const int kvh = blockIdx.x, split = blockIdx.y, b = blockIdx.z, nkv = a.kv.nkv;
-    const int G = a.nh / nkv;
+    // a group of more than 8 query heads is walked by two CTAs of 8 heads each; they sit side by side on
+    // the fastest grid axis, so the second one finds the rows the first one fetched in L2
+    const int nkv = a.kv.nkv, Gall = a.nh / nkv, sub = (Gall + 7) / 8;
+    const int kvh = (int)blockIdx.x / sub, hs = (int)blockIdx.x % sub, split = blockIdx.y, b = blockIdx.z;
+    const int G = min(8, Gall - 8 * hs), head0 = kvh * Gall + 8 * hs;
     const int64_t base = a.kv.seq_off[b];
     const int cap = (int)(a.kv.seq_off[b + 1] - base);
     const int len0 = a.kv_len[b];
     if (len0 >= cap) return;
     const int L = len0 + 1;
     const int t0 = split * a.tokens_per_split, t1 = min(L, t0 + a.tokens_per_split);
-    float *part0 = a.part + (((size_t)b * a.nh + (size_t)kvh * G) * a.nsplit + split) * (HD + 2);
+    float *part0 = a.part + (((size_t)b * a.nh + (size_t)head0) * a.nsplit + split) * (HD + 2);
     const size_t part_stride = (size_t)a.nsplit * (HD + 2);
     if (t0 >= L) {
         if (tid < G) { part0[tid * part_stride] = -INFINITY; part0[tid * part_stride + 1] = 0.0f; }
@@ -84,7 +87,7 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_f32_tc(DecodeArgs a) {
     // ---- query group -> shared memory, tf32; rows of heads the group does not have are zero
     for (int e = tid; e < 8 * HD; e += 128) {
         const int h = e >> 8, d = e & 255;
-        Q_s[h * LDQ + d] = (h < G) ? tf32r(a.q_prep[((size_t)b * a.nh + (size_t)kvh * G + h) * HD + d]) : 0.0f;
+        Q_s[h * LDQ + d] = (h < G) ? tf32r(a.q_prep[((size_t)b * a.nh + (size_t)head0 + h) * HD + d]) : 0.0f;
     }
     // staging slots: zero once (skipped tail rows must stay finite), one mbarrier per slot
     for (int i = lane; i < WARP_BYTES / 16; i += 32) reinterpret_cast<uint4 *>(Kt)[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(128, 3) k_gqa_decode_f32_tc(DecodeArgs a) {
 }  // namespace
 
 bool gqa_decode_f32_tc_supported(const KvView &kv, int nh) {
-    return kv.mode == ORNITH_KV_F32 && kv.hd == HD && nh % kv.nkv == 0 && nh / kv.nkv <= 8 &&
+    return kv.mode == ORNITH_KV_F32 && kv.hd == HD && nh % kv.nkv == 0 && nh / kv.nkv <= 16 &&
            ((uintptr_t)kv.K % 16) == 0 && ((uintptr_t)kv.V % 16) == 0;
 }
 
@@ -216,7 +219,7 @@ ornith_status launch_gqa_decode_f32_tc(const DecodeArgs &a, int n_seq, cudaStrea
                           "f32 gqa decode smem opt-in"));
         configured = true;
     }
-    dim3 grid(a.kv.nkv, a.nsplit, n_seq);
+    dim3 grid(a.kv.nkv * ((a.nh / a.kv.nkv + 7) / 8), a.nsplit, n_seq);
     k_gqa_decode_f32_tc<<<grid, 128, SMEM_BYTES, st>>>(a);
     return orn_check_launch("k_gqa_decode_f32_tc");
 }

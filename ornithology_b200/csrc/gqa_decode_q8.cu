@@ -563,7 +563,7 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
         configured3 = true;
     }
     dim3 grid(a.nsplit, a.kv.nkv, n_seq);
-    if (a.nh / a.kv.nkv <= 8) {
+    if (a.nh / a.kv.nkv <= 8) {                          // larger groups: k_gqa_decode_q8_mma below (the raw kernel would convert every row twice)
         // ORNITH_CUDA_DECODE_VARIANT=tile selects the variant that decodes V into an f16 tile
         static int use_tile = -1;
         if (use_tile < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); use_tile = (e && e[0] == 't') ? 1 : 0; }

@@ -188,15 +188,18 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
 
     // KV head on the fastest grid axis: the CTAs that read the two interleaved halves of the
     // same token rows are launched side by side and share DRAM pages while they are open
-    const int kvh = blockIdx.x, split = blockIdx.y, b = blockIdx.z, nkv = a.kv.nkv;
-    const int G = a.nh / nkv;
+    // a group of more than 8 query heads is walked by two CTAs of 8 heads each; they sit side by side on
+    // the fastest grid axis, so the second one finds the rows the first one fetched in L2
+    const int nkv = a.kv.nkv, Gall = a.nh / nkv, sub = (Gall + 7) / 8;
+    const int kvh = (int)blockIdx.x / sub, hs = (int)blockIdx.x % sub, split = blockIdx.y, b = blockIdx.z;
+    const int G = min(8, Gall - 8 * hs), head0 = kvh * Gall + 8 * hs;
     const int64_t base = a.kv.seq_off[b];
     const int cap = (int)(a.kv.seq_off[b + 1] - base);
     const int len0 = a.kv_len[b];
     if (len0 >= cap) return;
     const int L = len0 + 1;
     const int t0 = split * a.tokens_per_split, t1 = min(L, t0 + a.tokens_per_split);
-    float *part0 = a.part + (((size_t)b * a.nh + (size_t)kvh * G) * a.nsplit + split) * (HD + 2);
+    float *part0 = a.part + (((size_t)b * a.nh + (size_t)head0) * a.nsplit + split) * (HD + 2);
     const size_t part_stride = (size_t)a.nsplit * (HD + 2);
     if (t0 >= L) {
         if (tid < G) { part0[tid * part_stride] = -INFINITY; part0[tid * part_stride + 1] = 0.0f; }
@@ -208,7 +211,7 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
     //      holds q at the dims of elements 8c+2j and 8c+2j+1 (zeros where the stream has a scale)
     float rs_mine;
     {
-        const float *q = a.q_prep + ((size_t)b * a.nh + (size_t)kvh * G + (r < G ? r : 0)) * HD;
+        const float *q = a.q_prep + ((size_t)b * a.nh + (size_t)head0 + (r < G ? r : 0)) * HD;
         float mx = 0.0f;
         {   // 16 independent 128-bit loads: the prologue is per CTA, keep it off the latency path
             const float4 *q4 = reinterpret_cast<const float4 *>(q + j * 64);
@@ -423,7 +426,7 @@ ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStrea
                                                SMEM_BYTES), "gqa decode smem opt-in"));
         configured = true;
     }
-    dim3 grid(a.kv.nkv, a.nsplit, n_seq);
+    dim3 grid(a.kv.nkv * ((a.nh / a.kv.nkv + 7) / 8), a.nsplit, n_seq);
     k_gqa_decode_q8_raw<<<grid, 128, SMEM_BYTES, st>>>(a);
     return orn_check_launch("k_gqa_decode_q8_raw");
 }

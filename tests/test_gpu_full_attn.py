@@ -298,3 +298,61 @@ def test_long_context_split_k_int8_rows(oracle, L):
     out = D.full_attn_step(dl, kv, kv_len, torch.from_numpy(QP).cuda(), torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
     ref = oracle.full_attn_step(layer, okv, L, QP[0], K[0], V[0])
     assert rel_err(out.cpu().numpy()[0], ref) < TOL
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_groups_of_16_query_heads(oracle, mode):
+    """397B head shape on one GPU: 32 query heads over 2 KV heads.  Each group of 16 is walked by two
+    CTAs of 8 heads; decode steps over a ragged batch against the oracle."""
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(9, nh=32, nkv=2)
+    dl = device_full(layer)
+    dm, om = _modes(mode)
+    ctx, steps = [75, 210], 3
+    caps = [c + steps for c in ctx]
+    kv = D.KvBatch(dm, layer.nkv, layer.hd, caps)
+    okvs, data = [], []
+    for b, c in enumerate(ctx):
+        QP, K, V = full_inputs(300 + b, layer, c + steps)
+        data.append((QP, K, V))
+        okv = oracle.kv(caps[b], layer.nkv, layer.hd, om)
+        oracle.full_attn_prefill(layer, okv, 0, QP[:c], K[:c], V[:c])
+        okvs.append(okv)
+    # fill the device cache token by token through the decode path itself (exercises every context length)
+    kv_len = torch.zeros(len(ctx), dtype=torch.int32, device="cuda")
+    for t in range(max(ctx)):
+        qp = np.stack([data[b][0][min(t, ctx[b] - 1)] for b in range(len(ctx))])
+        k = np.stack([data[b][1][min(t, ctx[b] - 1)] for b in range(len(ctx))])
+        v = np.stack([data[b][2][min(t, ctx[b] - 1)] for b in range(len(ctx))])
+        live = torch.tensor([t < c for c in ctx], device="cuda")
+        # sequences that already hold their whole prompt re-append nothing: run them on a scratch copy of the lengths
+        if not bool(live.all()):
+            break
+        D.full_attn_step(dl, kv, kv_len, torch.from_numpy(qp).cuda(), torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda(),
+                         max_len=max(caps))
+        D.advance(kv_len)
+    # the shorter prompt is in; finish the longer one alone through a single-sequence view
+    import ctypes as C
+    from ornithology_b200._lib import CudaKv
+    one = D.KvBatch.__new__(D.KvBatch)
+    one.__dict__.update(kv.__dict__)
+    off = kv.seq_off[1:3].clone()
+    one.n_seq = 1
+    one.c = CudaKv(dm, layer.nkv, layer.hd, 1, kv.c.K, kv.c.V, kv.c.Ks, kv.c.Vs, C.c_void_p(off.data_ptr()))
+    l1 = kv_len[1:2].clone()
+    for t in range(ctx[0], ctx[1]):
+        D.full_attn_step(dl, one, l1, torch.from_numpy(data[1][0][t:t + 1]).cuda(), torch.from_numpy(data[1][1][t:t + 1]).cuda(),
+                         torch.from_numpy(data[1][2][t:t + 1]).cuda(), max_len=max(caps))
+        D.advance(l1)
+    kv_len = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    for s in range(steps):
+        qp = np.stack([data[b][0][ctx[b] + s] for b in range(len(ctx))])
+        k = np.stack([data[b][1][ctx[b] + s] for b in range(len(ctx))])
+        v = np.stack([data[b][2][ctx[b] + s] for b in range(len(ctx))])
+        out = D.full_attn_step(dl, kv, kv_len, torch.from_numpy(qp).cuda(), torch.from_numpy(k).cuda(),
+                               torch.from_numpy(v).cuda(), max_len=max(caps)).cpu().numpy()
+        for b in range(len(ctx)):
+            ref = oracle.full_attn_step(layer, okvs[b], ctx[b] + s, qp[b], k[b], v[b])
+            assert rel_err(out[b], ref) < TOL, (s, b)
+        D.advance(kv_len)
