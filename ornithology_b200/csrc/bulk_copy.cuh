@@ -47,6 +47,3 @@ __device__ __forceinline__ uint32_t bc_map_rank(const void *p, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(a) : "r"(bc_smem_u32(p)), "r"(rank));
     return a;
 }
-__device__ __forceinline__ void bc_st_cluster_f64(uint32_t addr, double v) {
-    asm volatile("st.shared::cluster.f64 [%0], %1;\n" ::"r"(addr), "d"(v) : "memory");
-}

@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
                                                              const float *Kp, const float *Qp, int n_chunks) {
     using SM = ScanSmem<NR>;
     constexpr int LDN = SM::LDN, CS = 128 / NR, NT = NR / 8, NTW = NR / 32;
-    extern __shared__ __align__(128) unsigned char smraw[];
+    extern __shared__ __align__(16) unsigned char smraw[];
     SM &sm = *reinterpret_cast<SM *>(smraw);
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, j = lane & 3;
     const int rank = (int)bc_cluster_rank(), hv = blockIdx.x / CS, b = blockIdx.y;

@@ -42,11 +42,6 @@ constexpr int SMEM_BYTES = QS_BYTES + NWARP * WARP_BYTES;     // 39168: four CTA
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -82,9 +77,8 @@ __device__ __forceinline__ uint32_t h2_mul_sub(uint32_t biased, uint32_t scale) 
 }
 
 // stream element e of a row: block e / 17; index 0 of a block is its scale, index i > 0
-// is the code pair of dims 2(i-1), 2(i-1)+1.  Returns the first dim, or -1 for a scale.
+// is the code pair of dims 2(i-1), 2(i-1)+1.
 __host__ __device__ constexpr int elem_block(int e) { return e / 17; }
-__host__ __device__ constexpr int elem_dim(int e) { return (e % 17 == 0) ? -1 : 32 * (e / 17) + 2 * (e % 17 - 1); }
 
 // ---- one k-step of S^T = K Q^T from chunk C of the staged K rows -------------------------
 // raw0 / raw1: the lane's ldmatrix registers for token rows r and r + 8 (elements
