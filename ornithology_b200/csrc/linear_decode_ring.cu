@@ -1,16 +1,29 @@
 // linear_decode_ring.cu — persistent form of the fused delta-net decode step (dk = dv = 128,
-// conv_k = 4): the recurrent state is streamed through a ring of bulk copies.
+// conv_k = 4): a small front-end kernel, then the recurrent state streamed through a ring of
+// bulk copies.
 //
 // Same arithmetic, operation order and results as k_linear_decode_128 (linear_attn.cu; reference:
 // src/ornith_rforward.c:457-503, :300-319, src/ornith_attn.c:203-212, :373-381).  What differs is
-// how the 64 KiB state of a head reaches the registers.  Two CTAs per SM stay resident and walk
-// the (sequence, value head) units in a fixed stride; each keeps three 32 KiB stages (half a
-// head) in shared memory, filled by cp.async.bulk with completion on an mbarrier, and requests
-// half-head m+3 as soon as half-head m has been lifted into registers.  The copy engine thus has
-// work queued for the whole life of the CTA, instead of each short-lived CTA starting with an
-// empty pipe; the small per-unit operands (conv ring, activations, gates, z) of the next unit are
-// requested one unit ahead.  Every mbarrier wait is bounded; a wait that gives up poisons the
-// outputs of the CTA.
+// how the work is cut.
+//
+// k_linear_decode_front does everything that does not touch the state, once per (sequence, head):
+// conv + SiLU of the q, k and v channels, the new conv history slot, the L2 norms of q and k, the
+// decay and write gates.  It leaves, per sequence, one 1 KiB block per key head (q then k,
+// normalised) and one 528-byte block per value head (v, then the two gates).  In the one-CTA-per-
+// head kernel these steps sit, with their double-precision reductions and two CTA barriers, in
+// front of every head's state traffic, and each key head is recomputed by all its value heads.
+//
+// k_linear_decode_ring then only moves state.  Two CTAs per SM stay resident and walk the
+// (sequence, value head) units in a fixed stride; each keeps three 32 KiB stages (half a head) in
+// shared memory, filled by cp.async.bulk with completion on an mbarrier, and requests half-head
+// m+3 as soon as half-head m has been lifted into registers.  The unit's two front-end blocks
+// arrive with its first half on the same mbarrier.  The copy engine thus has work queued for the
+// whole life of the CTA.  The RMSNorm + SiLU(z) epilogue of a unit is finished after the first
+// barrier of the next unit, so a unit costs two CTA barriers.  Every mbarrier wait is bounded; a
+// wait that gives up poisons the outputs of the CTA.
+#include <map>
+#include <mutex>
+#include <utility>
 #include "bulk_copy.cuh"
 #include "linear_attn.cuh"
 
@@ -19,148 +32,185 @@ namespace {
 constexpr int STAGES = 3;
 constexpr int STAGE_FLOATS = 64 * 128;                // half a head: 64 rows of the state, 32 KiB
 constexpr uint32_t STAGE_BYTES = STAGE_FLOATS * 4;
+constexpr int QK_FLOATS = 256;                        // front-end block of a key head: q[128], k[128]
+constexpr int VB_FLOATS = 132;                        // of a value head: v[128], alpha, beta, 0, 0
+constexpr uint32_t QK_BYTES = QK_FLOATS * 4, VB_BYTES = VB_FLOATS * 4;
+constexpr int OPND_FLOATS = QK_FLOATS + VB_FLOATS;
+constexpr int RING_SMEM = STAGES * (STAGE_FLOATS + OPND_FLOATS) * 4;
 
-// Everything a unit needs apart from its state.  Activations stay in their storage type until
-// they are used: a conversion at the load would make the thread wait for the data there, and
-// these loads are issued a whole unit ahead precisely so that nobody waits for them.
-template <typename ACT>
-struct UnitOperands {
-    float h0[4], h1[4], bias0, bias1, acoef, dtb, nw[2][2];
-    ACT x0, x1, ain, bin, zin[2][2];
-    float4 w0, w1;
-    int t;
-};
 __device__ __forceinline__ float act_f(float v) { return v; }
 __device__ __forceinline__ float act_f(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+__host__ __device__ inline size_t front_stride(int nk, int nv) { return (size_t)nk * QK_FLOATS + (size_t)nv * VB_FLOATS; }
+
+// grid (nk + ceil(nv / 2), n_seq), 128 threads: blocks 0..nk-1 take a key head, the rest two value heads each
 template <typename ACT>
-__device__ __forceinline__ void load_operands(UnitOperands<ACT> &o, const LinArgs &a, int b, int hv, int tid, int w, int sr,
-                                              int cc) {
-    const int kh = key_head_of(a, hv), qd = a.nk * 128, vd = a.nv * 128, Cc = 2 * qd + vd;
-    const float *ring = a.conv + (size_t)b * a.conv_stride;
+__global__ void __launch_bounds__(128) k_linear_decode_front(LinArgs a, float *front) {
+    __shared__ double redd[8];
+    // the state kernel may start its prologue (it waits for this grid before it reads the blocks)
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, b = blockIdx.y, j = blockIdx.x;
+    const int qd = a.nk * 128, vd = a.nv * 128, Cc = 2 * qd + vd;
+    float *ring = a.conv + (size_t)b * a.conv_stride;
     const ACT *x = (const ACT *)a.qkv + (size_t)b * Cc;
-    const bool qk_thread = tid < 128;
-    const int c0 = qk_thread ? kh * 128 + tid : 2 * qd + hv * 128 + (tid - 128);
-    const int c1 = qd + kh * 128 + (tid & 127);
+    float *fb = front + (size_t)b * front_stride(a.nk, a.nv);
+    const int t = a.pos[b], sb = (t + 1) & 3;
+
+    auto channel = [&](int c) -> float {               // conv + SiLU of channel c; stores the new history slot
+        float h[4];
 #pragma unroll
-    for (int sl = 0; sl < 4; sl++) { o.h0[sl] = ring[(size_t)sl * Cc + c0]; o.h1[sl] = 0.0f; }
-    o.x0 = x[c0];
-    o.w0 = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)c0 * 4);
-    o.bias0 = a.conv_b ? a.conv_b[c0] : 0.0f;
-    o.x1 = x[c0]; o.bias1 = 0.0f; o.w1 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);      // x1 only matters on q/k threads
-    if (qk_thread) {
+        for (int sl = 0; sl < 4; sl++) h[sl] = ring[(size_t)sl * Cc + c];
+        const float xin = act_f(x[c]);
+        const float4 wt = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)c * 4);
+        const float y = conv4_silu(h, xin, wt, a.conv_b ? a.conv_b[c] : 0.0f, sb);
+        ring[(size_t)(t & 3) * Cc + c] = xin;
+        return y;
+    };
+
+    if (j < a.nk) {                                    // q/k L2-norm (reference: src/ornith_tensor.c:155-160)
+        const float y0 = channel(j * 128 + tid), y1 = channel(qd + j * 128 + tid);
+        double sq = (double)y0 * (double)y0, sk = (double)y1 * (double)y1;
+        sq = warp_sum(sq); sk = warp_sum(sk);
+        if (lane == 0) { redd[w] = sq; redd[4 + w] = sk; }
+        __syncthreads();
+        const double ssq = redd[0] + redd[1] + redd[2] + redd[3], ssk = redd[4] + redd[5] + redd[6] + redd[7];
+        fb[(size_t)j * QK_FLOATS + tid] = y0 * (float)(1.0 / sqrt(ssq + (double)1e-6f));
+        fb[(size_t)j * QK_FLOATS + 128 + tid] = y1 * (float)(1.0 / sqrt(ssk + (double)1e-6f));
+    } else {                                           // two value heads per block, one channel of each per thread
+        const int hv0 = 2 * (j - a.nk);
+        float y[2];
 #pragma unroll
-        for (int sl = 0; sl < 4; sl++) o.h1[sl] = ring[(size_t)sl * Cc + c1];
-        o.x1 = x[c1];
-        o.w1 = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)c1 * 4);
-        o.bias1 = a.conv_b ? a.conv_b[c1] : 0.0f;
-    }
-    o.t = a.pos[b];
-    o.ain = ((const ACT *)a.a)[(size_t)b * a.nv + hv];
-    o.bin = ((const ACT *)a.b)[(size_t)b * a.nv + hv];
-    o.acoef = a.a_coef[hv]; o.dtb = a.dt_bias[hv];
-    const size_t out_base = (size_t)b * vd + (size_t)hv * 128;
+        for (int e = 0; e < 2; e++) y[e] = hv0 + e < a.nv ? channel(2 * qd + (hv0 + e) * 128 + tid) : 0.0f;
 #pragma unroll
-    for (int h = 0; h < 2; h++)
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const int r = 64 * h + 8 * w + 4 * i + sr;
-            o.zin[h][i] = ((const ACT *)a.z)[out_base + (cc == 0 ? r : 0)];
-            o.nw[h][i] = (cc == 0) ? a.norm_w[r] : 0.0f;
+        for (int e = 0; e < 2; e++) {
+            const int hv = hv0 + e;
+            if (hv >= a.nv) break;
+            float *vb = fb + (size_t)a.nk * QK_FLOATS + (size_t)hv * VB_FLOATS;
+            vb[tid] = y[e];
+            if (tid == 32 * e) {   // decay and write gates (reference: src/ornith_rforward.c:282-284, :493-496)
+                const float ain = act_f(((const ACT *)a.a)[(size_t)b * a.nv + hv]);
+                const float bin = act_f(((const ACT *)a.b)[(size_t)b * a.nv + hv]);
+                vb[128] = expf(a.a_coef[hv] * softplus_f(ain + a.dt_bias[hv]));
+                vb[129] = sigmoid_f(bin);
+                vb[130] = 0.0f; vb[131] = 0.0f;
+            }
         }
+    }
 }
 
 template <typename ACT>
-__global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_units) {
+__global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, const float *front, int n_units) {
     extern __shared__ __align__(128) unsigned char smraw[];
     float *stage = reinterpret_cast<float *>(smraw);
-    __shared__ __align__(16) float q_s[128], k_s[128], v_s[128];
-    __shared__ double redd[32];
-    __shared__ float gates[2];
+    float *opnd = stage + STAGES * STAGE_FLOATS;       // per stage: the front-end blocks of the unit whose first half it holds
+    __shared__ double redd[2][8];
     __shared__ unsigned long long full[STAGES];
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, sr = lane >> 3, cc = lane & 7;
-    const int qd = a.nk * 128, vd = a.nv * 128, Cc = 2 * qd + vd;
+    const int vd = a.nv * 128;
     const int n_mine = (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int M = 2 * n_mine;                            // half-heads this CTA walks
+    const int M = 2 * n_mine;                          // half-heads this CTA walks
+    const size_t fstride = front_stride(a.nk, a.nv);
 
-    auto half_src = [&](int m) -> const float * {        // state rows 64 (m&1) .. of this CTA's unit m/2
-        const int u = (int)blockIdx.x + (m >> 1) * (int)gridDim.x;
-        return a.S + (size_t)(u / a.nv) * a.S_stride + (size_t)(u % a.nv) * 128 * 128 + (size_t)(m & 1) * STAGE_FLOATS;
+    // one thread: request half-head m (parts & 1) and, with a first half, its unit's front-end blocks (parts & 2)
+    auto issue = [&](int m, int parts) {
+        const int slot = m % STAGES, u = (int)blockIdx.x + (m >> 1) * (int)gridDim.x, b = u / a.nv, hv = u % a.nv;
+        const uint32_t bar = bc_smem_u32(&full[slot]);
+        if (parts & 1) {
+            const float *src = a.S + (size_t)b * a.S_stride + (size_t)hv * 128 * 128 + (size_t)(m & 1) * STAGE_FLOATS;
+            bc_mbar_expect_tx(bar, (m & 1) ? STAGE_BYTES : STAGE_BYTES + QK_BYTES + VB_BYTES);
+            bc_copy(bc_smem_u32(stage + slot * STAGE_FLOATS), src, STAGE_BYTES, bar);
+        }
+        if ((parts & 2) && !(m & 1)) {
+            const float *fb = front + (size_t)b * fstride;
+            bc_copy(bc_smem_u32(opnd + slot * OPND_FLOATS), fb + (size_t)key_head_of(a, hv) * QK_FLOATS, QK_BYTES, bar);
+            bc_copy(bc_smem_u32(opnd + slot * OPND_FLOATS + QK_FLOATS), fb + (size_t)a.nk * QK_FLOATS + (size_t)hv * VB_FLOATS,
+                    VB_BYTES, bar);
+        }
     };
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) bc_mbar_init(bc_smem_u32(&full[s]), 1);
         bc_mbar_init_fence();
     }
     __syncthreads();
-    if (tid == 0) {
-        for (int m = 0; m < STAGES && m < M; m++) {
-            bc_mbar_expect_tx(bc_smem_u32(&full[m]), STAGE_BYTES);
-            bc_copy(bc_smem_u32(stage + m * STAGE_FLOATS), half_src(m), STAGE_BYTES, bc_smem_u32(&full[m]));
-        }
-    }
+    // The state does not depend on the front-end kernel of this call: its first copies start while
+    // that kernel is still running (programmatic dependent launch); the blocks follow once it is done.
+    if (tid == 0)
+        for (int m = 0; m < STAGES && m < M; m++) issue(m, 1);
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (tid == 0)
+        for (int m = 0; m < STAGES && m < M; m++) issue(m, 2);
+
+    float nw[2][2];                                    // RMSNorm weights of this thread's rows (lanes with cc == 0 store)
+    ACT zn[2][2];                                      // z of the next unit, requested a unit ahead
+    auto load_z = [&](int u) {
+        const size_t base = (size_t)(u / a.nv) * vd + (size_t)(u % a.nv) * 128;
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int i = 0; i < 2; i++) zn[h][i] = ((const ACT *)a.z)[base + (cc == 0 ? 64 * h + 8 * w + 4 * i + sr : 0)];
+    };
+#pragma unroll
+    for (int h = 0; h < 2; h++)
+#pragma unroll
+        for (int i = 0; i < 2; i++) nw[h][i] = (cc == 0) ? a.norm_w[64 * h + 8 * w + 4 * i + sr] : 0.0f;
+    load_z((int)blockIdx.x);
+
     bool ok = true;
-    UnitOperands<ACT> nxt;
-    load_operands<ACT>(nxt, a, (int)blockIdx.x / a.nv, (int)blockIdx.x % a.nv, tid, w, sr, cc);
+    float po[2][2] = {};                               // the previous unit, waiting for its epilogue
+    ACT pz[2][2] = {};
+    size_t pbase = 0;
+
+    // per-head RMSNorm and SiLU(z) gate of the previous unit (reference: src/ornith_rforward.c:305-314);
+    // its partial sums in redd[p] are complete once a CTA barrier has passed
+    auto finish = [&](int p) {
+        if (cc == 0) {
+            double tot = 0.0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) tot += redd[p][i];
+            const float inv = ok ? (float)(1.0 / sqrt(tot / 128.0 + (double)a.eps)) : NAN;
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    float y = po[h][i] * inv * nw[h][i];
+                    y *= silu_f(act_f(pz[h][i]));
+                    act_st((ACT *)a.out, pbase + 64 * h + 8 * w + 4 * i + sr, y);
+                }
+        }
+    };
 
     for (int k = 0; k < n_mine; k++) {
         const int u = (int)blockIdx.x + k * (int)gridDim.x, b = u / a.nv, hv = u % a.nv;
-        const int kh = key_head_of(a, hv);
         float *S = a.S + (size_t)b * a.S_stride + (size_t)hv * 128 * 128;
-        float *ring = a.conv + (size_t)b * a.conv_stride;
-        const UnitOperands<ACT> cur = nxt;
-        if (k + 1 < n_mine) {
-            const int un = u + (int)gridDim.x;
-            load_operands<ACT>(nxt, a, un / a.nv, un % a.nv, tid, w, sr, cc);
-        }
-        const bool qk_thread = tid < 128;
-        const int c0 = qk_thread ? kh * 128 + tid : 2 * qd + hv * 128 + (tid - 128);
-        const int c1 = qd + kh * 128 + (tid & 127);
-        const int t = cur.t;
-
-        // ---- conv + SiLU, q/k L2-norm (reference: src/ornith_tensor.c:155-160), gates ------------
-        const int sb = (t + 1) & 3;
-        const bool own = owns_key_head(a, hv);
-        const float x0 = act_f(cur.x0), x1 = act_f(cur.x1);
-        const float y0 = conv4_silu(cur.h0, x0, cur.w0, cur.bias0, sb);
-        float y1 = 0.0f;
-        if (qk_thread) {
-            y1 = conv4_silu(cur.h1, x1, cur.w1, cur.bias1, sb);
-            if (own) { ring[(size_t)(t & 3) * Cc + c0] = x0; ring[(size_t)(t & 3) * Cc + c1] = x1; }
-        } else {
-            ring[(size_t)(t & 3) * Cc + c0] = x0;
-            v_s[tid - 128] = y0;
-        }
-        {
-            double sq = qk_thread ? (double)y0 * (double)y0 : 0.0, sk = (double)y1 * (double)y1;
-            sq = warp_sum(sq); sk = warp_sum(sk);
-            if (lane == 0) { redd[w] = sq; redd[8 + w] = sk; }
-        }
-        __syncthreads();
-        if (qk_thread) {
-            const double ssq = redd[0] + redd[1] + redd[2] + redd[3], ssk = redd[8] + redd[9] + redd[10] + redd[11];
-            q_s[tid] = y0 * (float)(1.0 / sqrt(ssq + (double)1e-6f));
-            k_s[tid] = y1 * (float)(1.0 / sqrt(ssk + (double)1e-6f));
-        }
-        if (tid == 0) {   // decay and write gates (reference: src/ornith_rforward.c:282-284, :493-496)
-            gates[0] = expf(cur.acoef * softplus_f(act_f(cur.ain) + cur.dtb));
-            gates[1] = sigmoid_f(act_f(cur.bin));
-        }
-        __syncthreads();
+        ACT zc[2][2];
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int i = 0; i < 2; i++) zc[h][i] = zn[h][i];
+        if (k + 1 < n_mine) load_z(u + (int)gridDim.x);
 
         // ---- S <- alpha S; u = beta (v - S k); S += u k^T; o = S q  (reference: src/ornith_attn.c:203-212)
-        const float alpha = gates[0], beta = gates[1];
-        float4 kr[4], qr[4];                              // this lane's 16 columns of k and q, for all its rows
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            kr[j] = *reinterpret_cast<const float4 *>(k_s + (cc + j * 8) * 4);
-            qr[j] = *reinterpret_cast<const float4 *>(q_s + (cc + j * 8) * 4);
-        }
+        float4 kr[4], qr[4];                               // this lane's 16 columns of k and q, for all its rows
+        float vv[2][2], alpha = 0.0f, beta = 0.0f;
         float orow[2][2];
         double ss = 0.0;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const int m = 2 * k + h, slot = m % STAGES;
             ok = ok && bc_mbar_wait(bc_smem_u32(&full[slot]), (uint32_t)(m / STAGES) & 1u);
+            if (h == 0) {
+                const float *op = opnd + slot * OPND_FLOATS;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    qr[j] = *reinterpret_cast<const float4 *>(op + (cc + j * 8) * 4);
+                    kr[j] = *reinterpret_cast<const float4 *>(op + 128 + (cc + j * 8) * 4);
+                }
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++)
+#pragma unroll
+                    for (int i = 0; i < 2; i++) vv[hh][i] = op[QK_FLOATS + 64 * hh + 8 * w + 4 * i + sr];
+                alpha = op[QK_FLOATS + 128]; beta = op[QK_FLOATS + 129];
+            }
             float4 s[2][4];
 #pragma unroll
             for (int i = 0; i < 2; i++)
@@ -170,9 +220,9 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_
             __syncthreads();                              // the half-head is in registers everywhere: refill the slot
             if (tid == 0 && m + STAGES < M) {
                 bc_fence_proxy_async();
-                bc_mbar_expect_tx(bc_smem_u32(&full[slot]), STAGE_BYTES);
-                bc_copy(bc_smem_u32(stage + slot * STAGE_FLOATS), half_src(m + STAGES), STAGE_BYTES, bc_smem_u32(&full[slot]));
+                issue(m + STAGES, 3);
             }
+            if (h == 0 && k > 0) finish((k - 1) & 1);
 #pragma unroll
             for (int i = 0; i < 2; i++) {
                 const int r = 64 * h + 8 * w + 4 * i + sr;
@@ -185,7 +235,7 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_
                 recall += __shfl_xor_sync(0xffffffffu, recall, 1);
                 recall += __shfl_xor_sync(0xffffffffu, recall, 2);
                 recall += __shfl_xor_sync(0xffffffffu, recall, 4);
-                const float uu = beta * (v_s[r] - recall);
+                const float uu = beta * (vv[h][i] - recall);
                 float read = 0.0f;
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
@@ -201,48 +251,70 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, int n_
                 if (cc == 0) ss += (double)orow[h][i] * (double)orow[h][i];
             }
         }
-
-        // ---- per-head RMSNorm and SiLU(z) gate (reference: src/ornith_rforward.c:305-314) ---------
         ss = warp_sum(ss);
-        if (lane == 0) redd[16 + w] = ss;
-        __syncthreads();
-        if (cc == 0) {
-            double tot = 0.0;
+        if (lane == 0) redd[k & 1][w] = ss;
 #pragma unroll
-            for (int i = 0; i < 8; i++) tot += redd[16 + i];
-            const float inv = ok ? (float)(1.0 / sqrt(tot / 128.0 + (double)a.eps)) : NAN;
-            const size_t out_base = (size_t)b * vd + (size_t)hv * 128;
+        for (int h = 0; h < 2; h++)
 #pragma unroll
-            for (int h = 0; h < 2; h++)
-#pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    const int r = 64 * h + 8 * w + 4 * i + sr;
-                    float y = orow[h][i] * inv * cur.nw[h][i];
-                    y *= silu_f(act_f(cur.zin[h][i]));
-                    act_st((ACT *)a.out, out_base + r, y);
-                }
-        }
+            for (int i = 0; i < 2; i++) { po[h][i] = orow[h][i]; pz[h][i] = zc[h][i]; }
+        pbase = (size_t)b * vd + (size_t)hv * 128;
     }
+    __syncthreads();
+    if (n_mine > 0) finish((n_mine - 1) & 1);
+}
+
+// The front-end blocks of a call live in a buffer kept per (device, stream): calls on one stream
+// run in order and may share it, calls on different streams must not.  It only ever grows, so a
+// host that has made one call at its largest batch allocates nothing on the token path afterwards
+// (growing frees the old buffer with cudaFree, which waits for the work that still reads it).
+struct FrontBuf { float *p = nullptr; size_t bytes = 0; };
+ornith_status front_blocks(cudaStream_t s, size_t bytes, float **out) {
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, FrontBuf> bufs;
+    int dev = 0;
+    ORN_TRY(orn_check(cudaGetDevice(&dev), "cudaGetDevice"));
+    std::lock_guard<std::mutex> lock(mu);
+    FrontBuf &fb = bufs[{dev, s}];
+    if (fb.bytes < bytes) {
+        if (fb.p) ORN_TRY(orn_check(cudaFree(fb.p), "decode front-end blocks (free)"));
+        fb.p = nullptr; fb.bytes = 0;
+        ORN_TRY(orn_check(cudaMalloc((void **)&fb.p, bytes), "decode front-end blocks"));
+        fb.bytes = bytes;
+    }
+    *out = fb.p;
+    return ORNITH_OK;
 }
 
 template <typename ACT>
-ornith_status launch_ring(const LinArgs &x, int n_units, cudaStream_t s) {
+ornith_status launch_ring(const LinArgs &x, int n_seq, cudaStream_t s) {
     static int n_sm = 0;
     if (!n_sm) {
         int dev = 0;
         ORN_TRY(orn_check(cudaGetDevice(&dev), "cudaGetDevice"));
         ORN_TRY(orn_check(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev), "SM count"));
-        ORN_TRY(orn_check(cudaFuncSetAttribute(k_linear_decode_ring<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)(STAGES * STAGE_BYTES)), "decode ring smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_linear_decode_ring<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_SMEM),
+                          "decode ring smem opt-in"));
     }
-    const int grid = n_units < 2 * n_sm ? n_units : 2 * n_sm;
-    k_linear_decode_ring<ACT><<<grid, 256, STAGES * STAGE_BYTES, s>>>(x, n_units);
-    return orn_check_launch("k_linear_decode_ring");
+    float *front = nullptr;
+    ORN_TRY(front_blocks(s, (size_t)n_seq * front_stride(x.nk, x.nv) * sizeof(float), &front));
+    const int n_units = n_seq * x.nv;
+    k_linear_decode_front<ACT><<<dim3(x.nk + (x.nv + 1) / 2, n_seq), 128, 0, s>>>(x, front);
+    ornith_status st = orn_check_launch("k_linear_decode_front");
+    if (st == ORNITH_OK) {
+        const int grid = n_units < 2 * n_sm ? n_units : 2 * n_sm;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = RING_SMEM; cfg.stream = s;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        st = orn_check(cudaLaunchKernelEx(&cfg, k_linear_decode_ring<ACT>, x, (const float *)front, n_units), "k_linear_decode_ring");
+    }
+    return st;
 }
 
 }  // namespace
 
 ornith_status launch_linear_decode_ring(const LinArgs &x, int n_seq, int act_dtype, cudaStream_t s) {
-    const int n_units = n_seq * x.nv;
-    return act_dtype == ORNITH_ACT_BF16 ? launch_ring<__nv_bfloat16>(x, n_units, s) : launch_ring<float>(x, n_units, s);
+    return act_dtype == ORNITH_ACT_BF16 ? launch_ring<__nv_bfloat16>(x, n_seq, s) : launch_ring<float>(x, n_seq, s);
 }
