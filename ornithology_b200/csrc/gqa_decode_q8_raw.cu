@@ -20,12 +20,20 @@
 //     f16 pair and broadcasts it with one shuffle.
 //
 // Nothing is decoded into a second shared-memory buffer: per 16-token tile the
-// shared-memory pipe moves the staged bytes once in (cp.async) and once out
-// (ldmatrix), plus 16 two-byte scale loads for K.
+// shared-memory pipe moves the staged bytes once in and once out (ldmatrix), plus 16
+// two-byte scale loads for K.
+//
+// Staging: the rows of one KV head are 272 bytes long and nkv * 272 bytes apart.  A full
+// 16-token tile is fetched by ONE tensor copy (cp.async.bulk.tensor, 3-d view
+// [token][kv head][68 words], box 16 x 1 x 68) that lands the rows back to back; a
+// per-row bulk copy costs a dozen issue slots per row (the copy instruction takes uniform
+// registers, so per-lane addresses are walked one lane at a time), which was a third of all
+// instructions of this kernel.  Only the ragged last tile of a split still uses row copies.
 //
 // Precision: as the other tensor-core decode kernel — q scaled per head by a
 // power of two and rounded to f16, decoded K/V elements carry one f16 rounding,
 // probabilities scaled by 2^8 before the f16 rounding, f32 accumulation.
+#include <cuda.h>
 #include "full_attn.cuh"
 
 namespace {
@@ -146,14 +154,27 @@ __device__ __forceinline__ void bulk_copy_row(uint32_t dst, const void *src, uin
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                  ::"r"(dst), "l"(src), "r"(ROWB), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tensor_copy_tile(uint32_t dst, const CUtensorMap *map, int head, int token, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(head), "r"(token) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-// Stage the 16 rows of one tile of K (or V): lanes 0-15 copy one row each.  Rows past the
-// end of the split are not copied: the slot keeps earlier (finite) contents and the token
-// is masked in the softmax.
+// Stage the 16 rows of one tile of K (or V).  A full tile is one tensor copy (map != nullptr;
+// tok_abs = the tile's first token counted from the start of the pool); otherwise lanes 0-15
+// copy one row each, and rows past the end of the split are not copied: the slot keeps
+// earlier (finite) contents and the token is masked in the softmax.
 __device__ __forceinline__ void issue_rows16(unsigned char *slot, uint32_t bar, const unsigned char *src_base,
-                                             size_t row_stride, int tok0, int t1, int lane) {
+                                             size_t row_stride, int tok0, int t1, int lane, const CUtensorMap *map,
+                                             int head, int tok_abs) {
     const int valid = min(TILE, t1 - tok0);
+    if (map != nullptr && valid == TILE) {
+        if (lane == 0) {
+            mbar_expect_tx(bar, (uint32_t)RAW_TILE);
+            tensor_copy_tile(smem_u32(slot), map, head, tok_abs, bar);
+        }
+        return;
+    }
     if (lane == 0) mbar_expect_tx(bar, (uint32_t)(valid * ROWB));
     __syncwarp();
     if (lane < valid) bulk_copy_row(smem_u32(slot + lane * ROWB), src_base + (size_t)(tok0 + lane) * row_stride, bar);
@@ -170,8 +191,9 @@ __device__ __forceinline__ void store_chunk(float *Ow, const float (&acc)[4], in
     Ow[(2 * j + 1) * HD + dim + 1] = acc[3];
 }
 
-__global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
-    extern __shared__ __align__(16) unsigned char smem[];
+__global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, const __grid_constant__ CUtensorMap map_k,
+                                                              const __grid_constant__ CUtensorMap map_v, int tensor_copies) {
+    extern __shared__ __align__(128) unsigned char smem[];
     __shared__ float m_s[NWARP][8], l_s[NWARP][8];
     __shared__ __align__(8) unsigned long long bars[NWARP][2];
     __shared__ int pipe_failed;
@@ -244,6 +266,8 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
     const size_t row_stride = (size_t)nkv * ROWB;
     const unsigned char *Kbase = a.kv.K + ((size_t)base * nkv + kvh) * ROWB;
     const unsigned char *Vbase = a.kv.V + ((size_t)base * nkv + kvh) * ROWB;
+    const CUtensorMap *mk = tensor_copies ? &map_k : nullptr, *mv = tensor_copies ? &map_v : nullptr;
+    const int tok_pool = (int)base + t0;                        // first token of the split, counted from the start of the pool
 
     float o[NCHUNK][4];
 #pragma unroll
@@ -274,8 +298,8 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
 
     int it = warp;
     if (it < ntiles) {
-        issue_rows16(rawK, barK, Kbase, row_stride, t0 + it * TILE, t1, lane);
-        issue_rows16(rawV, barV, Vbase, row_stride, t0 + it * TILE, t1, lane);
+        issue_rows16(rawK, barK, Kbase, row_stride, t0 + it * TILE, t1, lane, mk, kvh, tok_pool + it * TILE);
+        issue_rows16(rawV, barV, Vbase, row_stride, t0 + it * TILE, t1, lane, mv, kvh, tok_pool + it * TILE);
     }
     for (uint32_t n = 0; it < ntiles; it += NWARP, n++) {
         const int tok0 = t0 + it * TILE;
@@ -311,7 +335,7 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
         __syncwarp();                                             // every lane is done with the K slot
         if (more) {
             fence_proxy_async();
-            issue_rows16(rawK, barK, Kbase, row_stride, tok0 + NWARP * TILE, t1, lane);
+            issue_rows16(rawK, barK, Kbase, row_stride, tok0 + NWARP * TILE, t1, lane, mk, kvh, tok_pool + (it + NWARP) * TILE);
         }
 
         // ---- online softmax over tokens (rows r, r+8); columns = heads 2j, 2j+1 -------------
@@ -363,7 +387,7 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
         __syncwarp();                                             // every lane is done with the V slot
         if (more) {
             fence_proxy_async();
-            issue_rows16(rawV, barV, Vbase, row_stride, tok0 + NWARP * TILE, t1, lane);
+            issue_rows16(rawV, barV, Vbase, row_stride, tok0 + NWARP * TILE, t1, lane, mv, kvh, tok_pool + (it + NWARP) * TILE);
         }
     }
     if (!pipe_ok && lane == 0) pipe_failed = 1;
@@ -411,6 +435,37 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a) {
     }
 }
 
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn tensor_map_encoder() {
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        cudaDriverEntryPointQueryResult q;
+        void *p = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeFn)p;
+    }
+    return fn;
+}
+
+// View of a pool of Q8_0 rows as [token][kv head][68 32-bit words]; one box = the 16 rows of one
+// head for 16 consecutive tokens.  Only full tiles of valid tokens are ever requested, so the
+// token extent is left open-ended rather than tied to the size of the pool.
+bool q8_rows_map(CUtensorMap *m, const void *pool, int nkv) {
+    EncodeFn enc = tensor_map_encoder();
+    if (!enc || ((uintptr_t)pool & 15) != 0) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)(ROWB / 4), (cuuint64_t)nkv, (cuuint64_t)1 << 31};
+    cuuint64_t strides[2] = {(cuuint64_t)ROWB, (cuuint64_t)nkv * ROWB};
+    cuuint32_t box[3] = {(cuuint32_t)(ROWB / 4), 1, (cuuint32_t)TILE};
+    cuuint32_t es[3] = {1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void *>(pool), dims, strides, box, es,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st) {
@@ -420,7 +475,13 @@ ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStrea
                                                SMEM_BYTES), "gqa decode smem opt-in"));
         configured = true;
     }
+    // without the tensor maps (driver entry point missing, pool not 16-byte aligned) every tile falls back to row copies
+    CUtensorMap mk, mv;
+    memset(&mk, 0, sizeof mk);
+    memset(&mv, 0, sizeof mv);
+    const char *env = getenv("ORNITH_CUDA_DECODE_ROW_COPIES");
+    const int tensor_copies = !(env && env[0] == '1') && q8_rows_map(&mk, a.kv.K, a.kv.nkv) && q8_rows_map(&mv, a.kv.V, a.kv.nkv);
     dim3 grid(a.kv.nkv * ((a.nh / a.kv.nkv + 7) / 8), a.nsplit, n_seq);
-    k_gqa_decode_q8_raw<<<grid, 128, SMEM_BYTES, st>>>(a);
+    k_gqa_decode_q8_raw<<<grid, 128, SMEM_BYTES, st>>>(a, mk, mv, tensor_copies);
     return orn_check_launch("k_gqa_decode_q8_raw");
 }
