@@ -28,6 +28,8 @@ struct PrepArgs {
     int nh, rope_dim, gated, T;
     int row0;                            // first row handled (nh skips the query heads)
     float eps;
+    int *group_ctr;                      // if set: n_ctr arrival counters of the decode kernel's fused merge, zeroed here
+    int n_ctr;
 };
 
 // Row j of token tt: j < nh is a query head (normalise, rotate, write f32 to the
@@ -41,6 +43,9 @@ __global__ void __launch_bounds__(128) k_full_prep(PrepArgs a) {
     __shared__ double redd[32];
     __shared__ float redf[32];
     const int hd = a.kv.hd, nkv = a.kv.nkv, nh = a.nh;
+    if (a.group_ctr)
+        for (int i = (blockIdx.y * gridDim.x + blockIdx.x) * 128 + threadIdx.x; i < a.n_ctr; i += gridDim.x * gridDim.y * 128)
+            a.group_ctr[i] = 0;
     const int j = blockIdx.y + a.row0, tt = blockIdx.x, b = tt / a.T, t = tt % a.T;
     const int64_t base = a.kv.seq_off[b];
     const int cap = (int)(a.kv.seq_off[b + 1] - base);
@@ -112,6 +117,9 @@ __global__ void __launch_bounds__(128) k_full_prep_warp(PrepArgs a, long long n_
     extern __shared__ float rowbuf[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int hd = a.kv.hd, nkv = a.kv.nkv, nh = a.nh;
+    if (a.group_ctr)
+        for (long long i = (long long)blockIdx.x * 128 + threadIdx.x; i < a.n_ctr; i += (long long)gridDim.x * 128)
+            a.group_ctr[i] = 0;
     const long long R = (long long)blockIdx.x * 4 + wid;
     if (R >= n_rows) return;
     const int tt = (int)(R / rows_per_tok), j = (int)(R % rows_per_tok) + a.row0, b = tt / a.T, t = tt % a.T;
@@ -512,8 +520,10 @@ template <typename ACT>
 static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
                                  const int32_t *kv_len, const int32_t *rope_pos, const void *qproj,
                                  const void *k, const void *v, float *q_prep, int n_tok, int T,
-                                 cudaStream_t st, bool kv_only = false, __half *Qh = nullptr, float *rs = nullptr) {
+                                 cudaStream_t st, bool kv_only = false, __half *Qh = nullptr, float *rs = nullptr,
+                                 int *group_ctr = nullptr, int n_ctr = 0) {
     PrepArgs a;
+    a.group_ctr = group_ctr; a.n_ctr = n_ctr;
     a.Qh = Qh; a.rs = rs; a.scale = attn_scale(l);
     a.kv = make_view(kv); a.kv_len = kv_len; a.rope_pos = rope_pos;
     a.qproj = qproj; a.k = k; a.v = v; a.q_prep = q_prep;
@@ -540,7 +550,7 @@ size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *l, int n
     const int nsplit = max_splits(max_len);
     size_t qp = align_up((size_t)n_seq * l->n_heads * l->head_dim * sizeof(float), 256);
     size_t part = (size_t)n_seq * l->n_heads * nsplit * (l->head_dim + 2) * sizeof(float);
-    return qp + align_up(part, 256);
+    return qp + align_up(part, 256) + align_up((size_t)n_seq * l->n_heads * sizeof(int), 256);   // + merge counters
 }
 
 ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
@@ -562,15 +572,21 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     const int tps = split_tokens(max_len), nsplit = (max_len + tps - 1) / tps;
     float *q_prep = (float *)scratch;
     float *part = (float *)((char *)scratch + align_up((size_t)B * nh * hd * sizeof(float), 256));
+    // the arrival counters sit behind the partials of the largest split count the scratch is sized for
+    int *group_ctr = (int *)((char *)part + align_up((size_t)B * nh * max_splits(max_len) * (hd + 2) * sizeof(float), 256));
 
     if (act_dtype == ORNITH_ACT_BF16)
-        ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B, 1, st));
+        ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B, 1, st, false, nullptr, nullptr,
+                                           group_ctr, B * nh));
     else
-        ORN_TRY(launch_prep<float>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B, 1, st));
+        ORN_TRY(launch_prep<float>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B, 1, st, false, nullptr, nullptr,
+                                   group_ctr, B * nh));
 
     DecodeArgs d;
     d.kv = make_view(kv); d.kv_len = kv_len; d.q_prep = q_prep; d.part = part;
     d.nh = nh; d.scale = attn_scale(l);
+    d.group_ctr = group_ctr; d.qproj = qproj; d.out = out; d.gated = l->gated; d.act_dtype = act_dtype;
+    bool merged = false;
     int nsplit_used;
     if (gqa_decode_q8_mma_supported(d.kv, nh) && !force_generic_decode()) {
         // tensor-core path: larger splits (fewer partials); never more splits than the scratch was sized for
@@ -581,7 +597,7 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
             if (forced >= 512 && max_len > 1024) tps_mma = forced / 16 * 16;
         }
         d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
-        ORN_TRY(launch_gqa_decode_q8_mma(d, B, st));
+        ORN_TRY(launch_gqa_decode_q8_mma(d, B, st, &merged));
     } else if (gqa_decode_f32_tc_supported(d.kv, nh) && !force_generic_decode()) {
         const int tps_tc = split_tokens_mma(max_len);
         d.tokens_per_split = tps_tc; d.nsplit = nsplit_used = (max_len + tps_tc - 1) / tps_tc;
@@ -602,6 +618,7 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
         ORN_TRY(orn_check_launch("k_gqa_decode_generic"));
     }
 
+    if (merged) return ORNITH_OK;
     CombineArgs c;
     c.kv = d.kv; c.kv_len = kv_len; c.part = part; c.qproj = qproj; c.out = out;
     c.nh = nh; c.nsplit = nsplit_used; c.gated = l->gated; c.tokens_per_split = d.tokens_per_split;

@@ -10,16 +10,23 @@ struct DecodeArgs {
     float *part;                         // [n_seq][nh][nsplit][hd + 2]: m, l, o[hd]
     int nh, nsplit, tokens_per_split;
     float scale;
+    // Fused merge (kernels that support it; group_ctr == nullptr leaves the merge to k_gqa_combine): the last CTA
+    // of a (sequence, head group) to finish merges the group's partials, applies the output gate and stores.
+    int *group_ctr;                      // [n_seq][grid.x] arrival counters, zero when the kernel starts
+    const void *qproj;                   // gate = second half of each head's projection row (gated != 0)
+    void *out;
+    int gated, act_dtype;
 };
 
 // Tensor-core split-K decode over Q8_0 rows, head_dim 256, up to 16 query heads
 // per KV head.  Writes the same partials as the generic kernel.
 bool gqa_decode_q8_mma_supported(const KvView &kv, int nh);
-ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st);
+// *merged is set when the launched kernel did the merge itself (a.group_ctr given and supported).
+ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged);
 
 // Variant for groups of up to 8 query heads that builds its MMA fragments straight
 // from the staged raw rows (gqa_decode_q8_raw.cu).
-ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st);
+ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged);
 
 // The same for int8-per-head rows (gqa_decode_i8_raw.cu), up to 8 query heads per KV head.
 bool gqa_decode_i8_raw_supported(const KvView &kv, int nh);

@@ -549,7 +549,8 @@ bool gqa_decode_q8_mma_supported(const KvView &kv, int nh) {
            ((uintptr_t)kv.K % 16) == 0 && ((uintptr_t)kv.V % 16) == 0;
 }
 
-ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st) {
+ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged) {
+    *merged = false;
     static bool configured = false;
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -567,7 +568,7 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
         // ORNITH_CUDA_DECODE_VARIANT=tile selects the variant that decodes V into an f16 tile
         static int use_tile = -1;
         if (use_tile < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); use_tile = (e && e[0] == 't') ? 1 : 0; }
-        if (!use_tile) return launch_gqa_decode_q8_raw(a, n_seq, st);
+        if (!use_tile) return launch_gqa_decode_q8_raw(a, n_seq, st, merged);
         k_gqa_decode_q8_tok<<<grid, 128, SMEM3_BYTES, st>>>(a);
         return orn_check_launch("k_gqa_decode_q8_tok");
     }

@@ -433,6 +433,77 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, cons
             part[2 + d] = acc * (1.0f / 256.0f) + poison;
         }
     }
+    if (a.group_ctr == nullptr) return;
+
+    // ---- fused merge: the last CTA of this (sequence, head group) to get here combines the partials of the
+    //      group's live splits (reference: src/ornith_attn.c:131-148 normalisation, src/ornith_rforward.c:450 gate).
+    //      Nobody waits: every CTA publishes its partials, counts itself, and only the one that counts last goes on.
+    __shared__ int last_one;
+    __threadfence();
+    __syncthreads();
+    const int nlive = min(a.nsplit, (len0 + a.tokens_per_split) / a.tokens_per_split);   // splits with t0 < L
+    if (tid == 0) {
+        int *ctr = a.group_ctr + (size_t)b * gridDim.x + blockIdx.x;
+        last_one = (atomicAdd(ctr, 1) == nlive - 1);
+    }
+    __syncthreads();
+    if (!last_one) return;
+    __threadfence();
+    for (int h = warp; h < G; h += NWARP) {               // a warp per head; partials of other SMs: read past L1
+        const float *ph = part0 - (size_t)split * (HD + 2) + h * part_stride;   // split 0 of head h
+        float lsum = 0.0f, acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+        // (m, l) of up to 32 splits per lane-round; the group maximum first
+        float M = -INFINITY;
+        for (int s0 = 0; s0 < nlive; s0 += 32) {
+            const int s = s0 + lane;
+            const float2 ml = s < nlive ? __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2))) : make_float2(0.0f, 0.0f);
+            if (ml.y > 0.0f) M = fmaxf(M, ml.x);
+        }
+        M = warp_max(M);
+        for (int s0 = 0; s0 < nlive; s0 += 32) {
+            const int s = s0 + lane;
+            const float2 ml = s < nlive ? __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2))) : make_float2(0.0f, 0.0f);
+            const float w = (ml.y > 0.0f) ? expf(ml.x - M) : 0.0f;
+            lsum += ml.y * w;
+            const int n = min(32, nlive - s0);
+            for (int i0 = 0; i0 < n; i0 += 4) {           // four splits' rows in flight at a time
+                float2 v[4][4];
+                float wi[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    wi[u] = __shfl_sync(0xffffffffu, w, (i0 + u) & 31);
+                    if (i0 + u >= n) wi[u] = 0.0f;
+                    const float2 *o2 = reinterpret_cast<const float2 *>(ph + (size_t)(s0 + min(i0 + u, n - 1)) * (HD + 2) + 2);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) v[u][k] = __ldcg(o2 + lane + 32 * k);   // dims 2 lane + 64 k, +1
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if (wi[u] != 0.0f) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++) { acc[2 * k] += v[u][k].x * wi[u]; acc[2 * k + 1] += v[u][k].y * wi[u]; }
+                    }
+            }
+        }
+        const float inv = 1.0f / warp_sum(lsum);
+        const size_t head = (size_t)b * a.nh + (size_t)head0 + h;
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int d = 2 * lane + 64 * k + e;
+                float o = acc[2 * k + e] * inv;
+                if (a.act_dtype == ORNITH_ACT_BF16) {
+                    if (a.gated) o *= sigmoid_f(act_ld((const __nv_bfloat16 *)a.qproj, head * HD * 2 + HD + d));
+                    act_st((__nv_bfloat16 *)a.out, head * HD + d, o);
+                } else {
+                    if (a.gated) o *= sigmoid_f(act_ld((const float *)a.qproj, head * HD * 2 + HD + d));
+                    act_st((float *)a.out, head * HD + d, o);
+                }
+            }
+    }
 }
 
 typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -468,7 +539,8 @@ bool q8_rows_map(CUtensorMap *m, const void *pool, int nkv) {
 
 }  // namespace
 
-ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st) {
+ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged) {
+    *merged = a.group_ctr != nullptr;
     static bool configured = false;
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_raw, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -131,6 +131,7 @@ class AttnStack:
                  shard: HeadShard | None = None, n_layers: int | None = None):
         self.arch = arch = ARCHS[arch_name] if isinstance(arch_name, str) else arch_name
         self.n_seq = len(capacities)
+        self.kv_mode = kv_mode
         self.device = torch.device(device)
         self.shard = shard
         self.layers = []                # (kind, layer, state)
@@ -225,8 +226,15 @@ class AttnStack:
         return out
 
     def launches_per_step(self):
+        """Kernel launches of one decode step, mirroring the library's dispatch: a full-attention layer is
+        append + split-K decode (+ a merge kernel unless the decode kernel merges itself: Q8_0 rows, head_dim 256,
+        groups of at most 8 query heads); a delta-net layer is one kernel, or front-end + state kernel above 296
+        (sequence, value head) units; one launch advances the positions."""
         n_full = sum(1 for k, _, _ in self.layers if k == "full")
-        return 3 * n_full + (len(self.layers) - n_full) + 1
+        n_lin = len(self.layers) - n_full
+        fused_merge = self.kv_mode == D.KV_Q8_0 and self.arch["hd"] == 256 and self.nh // max(self.nkv, 1) <= 8
+        two_kernels = self.arch["dk"] == 128 and self.arch["dv"] == 128 and self.n_seq * self.nv > 296
+        return (2 if fused_merge else 3) * n_full + (2 if two_kernels else 1) * n_lin + 1
 
     # ---- synthetic prefill of the state (bench set-up) -------------------------------
     def fill(self, contexts, seed=0, linear_tokens=64, block=2048):
