@@ -564,10 +564,12 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
         configured3 = true;
     }
     dim3 grid(a.nsplit, a.kv.nkv, n_seq);
-    if (a.nh / a.kv.nkv <= 8) {                          // larger groups: k_gqa_decode_q8_mma below (the raw kernel would convert every row twice)
-        // ORNITH_CUDA_DECODE_VARIANT=tile selects the variant that decodes V into an f16 tile
-        static int use_tile = -1;
-        if (use_tile < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); use_tile = (e && e[0] == 't') ? 1 : 0; }
+    // ORNITH_CUDA_DECODE_VARIANT=tile selects the variant that decodes V into an f16 tile, =raw the raw-fragment
+    // kernel for groups of 9-16 heads too (two CTAs of 8 heads per KV head)
+    static int variant = -1;
+    if (variant < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); variant = !e ? 0 : (e[0] == 't' ? 1 : (e[0] == 'r' ? 2 : 0)); }
+    const int use_tile = variant == 1;
+    if (a.nh / a.kv.nkv <= 8 || variant == 2) {          // larger groups: k_gqa_decode_q8_mma below (the raw kernel would convert every row twice)
         if (!use_tile) return launch_gqa_decode_q8_raw(a, n_seq, st, merged);
         k_gqa_decode_q8_tok<<<grid, 128, SMEM3_BYTES, st>>>(a);
         return orn_check_launch("k_gqa_decode_q8_tok");

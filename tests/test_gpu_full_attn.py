@@ -167,6 +167,47 @@ def test_long_context_split_k(oracle, L):
     assert rel_err(out.cpu().numpy()[0], ref) < TOL
 
 
+def test_long_context_ragged_batch_q8(oracle):
+    """Sequences whose contexts reach different numbers of splits, in one pool (non-zero row
+    offsets for the tile copies), stepped twice: the in-kernel merge of the split partials
+    must see only the live splits of each sequence, and its arrival counters must be re-armed."""
+    import ctypes as C
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(6)
+    dl = device_full(layer)
+    rng = np.random.default_rng(21)
+    ctx = [9001, 700, 3000, 15]
+    caps = [c + 2 for c in ctx]
+    kv = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, caps)
+    okvs = []
+    rb = layer.nkv * 272
+    for b, L in enumerate(ctx):
+        Kraw = rng.standard_normal((L * layer.nkv, layer.hd)).astype(np.float32)
+        Vraw = rng.standard_normal((L * layer.nkv, layer.hd)).astype(np.float32)
+        Kb = np.stack([oracle.q8_0_encode(r) for r in Kraw])
+        Vb = np.stack([oracle.q8_0_encode(r) for r in Vraw])
+        o = int(kv.seq_off_host[b]) * rb
+        kv.K[o:o + Kb.size] = torch.from_numpy(Kb.ravel()).cuda()
+        kv.V[o:o + Vb.size] = torch.from_numpy(Vb.ravel()).cuda()
+        okv = oracle.kv(caps[b], layer.nkv, layer.hd, 2)
+        C.memmove(okv.c.Kb, Kb.ctypes.data, Kb.size); C.memmove(okv.c.Vb, Vb.ctypes.data, Vb.size)
+        Kd = np.stack([oracle.q8_0_decode(r) for r in Kb]).astype(np.float32)
+        Vd = np.stack([oracle.q8_0_decode(r) for r in Vb]).astype(np.float32)
+        C.memmove(okv.c.K, Kd.ctypes.data, Kd.nbytes); C.memmove(okv.c.V, Vd.ctypes.data, Vd.nbytes)
+        okv.c.len = L
+        okvs.append(okv)
+    kv_len = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    for s in range(2):
+        QP, K, V = full_inputs(30 + s, layer, len(ctx))
+        out = D.full_attn_step(dl, kv, kv_len, torch.from_numpy(QP).cuda(), torch.from_numpy(K).cuda(),
+                               torch.from_numpy(V).cuda(), max_len=max(caps)).cpu().numpy()
+        for b, L in enumerate(ctx):
+            ref = oracle.full_attn_step(layer, okvs[b], L + s, QP[b], K[b], V[b])
+            assert rel_err(out[b], ref) < TOL, (s, b)
+        D.advance(kv_len)
+
+
 def _prefill(D, dl, kv, kv_len, QP, K, V, T, max_len=None, bf16=False):
     import torch
     dt = torch.bfloat16 if bf16 else torch.float32
