@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(128) k_full_prep(PrepArgs a) {
     __shared__ double redd[32];
     __shared__ float redf[32];
     const int hd = a.kv.hd, nkv = a.kv.nkv, nh = a.nh;
+    // a decode kernel launched behind this one may begin its prologue now; it waits for this grid before it reads its output
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     if (a.group_ctr)
         for (int i = (blockIdx.y * gridDim.x + blockIdx.x) * 128 + threadIdx.x; i < a.n_ctr; i += gridDim.x * gridDim.y * 128)
             a.group_ctr[i] = 0;

@@ -223,6 +223,42 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, cons
     }
     const int r = lane >> 2, j = lane & 3;
 
+    const int ntiles = (t1 - t0 + TILE - 1) / TILE;
+    const size_t row_stride = (size_t)nkv * ROWB;
+    const unsigned char *Kbase = a.kv.K + ((size_t)base * nkv + kvh) * ROWB;
+    const unsigned char *Vbase = a.kv.V + ((size_t)base * nkv + kvh) * ROWB;
+    const CUtensorMap *mk = tensor_copies ? &map_k : nullptr, *mv = tensor_copies ? &map_v : nullptr;
+    const int tok_pool = (int)base + t0;                        // first token of the split, counted from the start of the pool
+
+
+    // ---- per-warp staging slots (K rows, V rows): zero them once (skipped tail rows must stay
+    //      finite), one mbarrier each.  K of the next tile is requested as soon as the score
+    //      loop is done with the slot, V right after the value loop.  The first tile is requested
+    //      before anything else so that its latency hides behind the query prologue; under
+    //      programmatic dependent launch that happens while the append kernel of this call may
+    //      still be running, so only for tiles that end before the row it appends (token len0).
+    unsigned char *rawK = wbase, *rawV = wbase + RAW_TILE;
+    {
+        uint4 *z = reinterpret_cast<uint4 *>(wbase);
+        for (int i = lane; i < WARP_BYTES / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (lane == 0) {
+            mbar_init(smem_u32(&bars[warp][0]), 1);
+            mbar_init(smem_u32(&bars[warp][1]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        }
+        fence_proxy_async();                                      // generic-proxy zeros before async-proxy copies
+        __syncwarp();
+    }
+    const uint32_t barK = smem_u32(&bars[warp][0]), barV = smem_u32(&bars[warp][1]);
+    int it = warp;
+    const bool first_issued = it < ntiles && t0 + (it + 1) * TILE <= len0;
+    if (first_issued) {
+        issue_rows16(rawK, barK, Kbase, row_stride, t0 + it * TILE, t1, lane, mk, kvh, tok_pool + it * TILE);
+        issue_rows16(rawV, barV, Vbase, row_stride, t0 + it * TILE, t1, lane, mv, kvh, tok_pool + it * TILE);
+    }
+    // everything below reads what the append kernel of this call wrote (query rows, the new K/V row, zeroed counters)
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
     // ---- query group -> B fragments in stream order: lane (head r, quarter j), k-step c
     //      holds q at the dims of elements 8c+2j and 8c+2j+1 (zeros where the stream has a scale)
     float rs_mine;
@@ -262,13 +298,6 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, cons
     const float rsA = __shfl_sync(0xffffffffu, rs_mine, (2 * j) * 4);
     const float rsB = __shfl_sync(0xffffffffu, rs_mine, (2 * j + 1) * 4);
 
-    const int ntiles = (t1 - t0 + TILE - 1) / TILE;
-    const size_t row_stride = (size_t)nkv * ROWB;
-    const unsigned char *Kbase = a.kv.K + ((size_t)base * nkv + kvh) * ROWB;
-    const unsigned char *Vbase = a.kv.V + ((size_t)base * nkv + kvh) * ROWB;
-    const CUtensorMap *mk = tensor_copies ? &map_k : nullptr, *mv = tensor_copies ? &map_v : nullptr;
-    const int tok_pool = (int)base + t0;                        // first token of the split, counted from the start of the pool
-
     float o[NCHUNK][4];
 #pragma unroll
     for (int i = 0; i < NCHUNK; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
@@ -277,27 +306,10 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, cons
     // matrices 2,3 = chunk c + 1
     const uint32_t lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
 
-    // ---- per-warp staging slots (K rows, V rows): zero them once (skipped tail rows must stay
-    //      finite), one mbarrier each.  K of the next tile is requested as soon as the score
-    //      loop is done with the slot, V right after the value loop.
-    unsigned char *rawK = wbase, *rawV = wbase + RAW_TILE;
-    {
-        uint4 *z = reinterpret_cast<uint4 *>(wbase);
-        for (int i = lane; i < WARP_BYTES / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (lane == 0) {
-            mbar_init(smem_u32(&bars[warp][0]), 1);
-            mbar_init(smem_u32(&bars[warp][1]), 1);
-            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        }
-        fence_proxy_async();                                      // generic-proxy zeros before async-proxy copies
-    }
-    __syncthreads();                                              // also publishes Q_s
-    const uint32_t barK = smem_u32(&bars[warp][0]), barV = smem_u32(&bars[warp][1]);
+    __syncthreads();                                              // publishes Q_s
     const uint2 *q_frag = Q_s + lane;
     bool pipe_ok = true;
-
-    int it = warp;
-    if (it < ntiles) {
+    if (it < ntiles && !first_issued) {
         issue_rows16(rawK, barK, Kbase, row_stride, t0 + it * TILE, t1, lane, mk, kvh, tok_pool + it * TILE);
         issue_rows16(rawV, barV, Vbase, row_stride, t0 + it * TILE, t1, lane, mv, kvh, tok_pool + it * TILE);
     }
@@ -415,7 +427,9 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, cons
         l_s[warp][2 * j] = lA; l_s[warp][2 * j + 1] = lB;
     }
     __syncthreads();
-    for (int h = 0; h < G; h++) {
+#pragma unroll                                                    // unrolled: the heads' loads and stores overlap
+    for (int h = 0; h < 8; h++) {
+        if (h >= G) break;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NWARP; w++) if (l_s[w][h] > 0.0f) M = fmaxf(M, m_s[w][h]);
@@ -558,6 +572,12 @@ ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStrea
     const char *env = getenv("ORNITH_CUDA_DECODE_ROW_COPIES");
     const int tensor_copies = !(env && env[0] == '1') && q8_rows_map(&mk, a.kv.K, a.kv.nkv) && q8_rows_map(&mv, a.kv.V, a.kv.nkv);
     dim3 grid(a.kv.nkv * ((a.nh / a.kv.nkv + 7) / 8), a.nsplit, n_seq);
-    k_gqa_decode_q8_raw<<<grid, 128, SMEM_BYTES, st>>>(a, mk, mv, tensor_copies);
-    return orn_check_launch("k_gqa_decode_q8_raw");
+    // may start while the append kernel in front of it still runs: it waits (griddepcontrol.wait) before it reads that kernel's output
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return orn_check(cudaLaunchKernelEx(&cfg, k_gqa_decode_q8_raw, a, mk, mv, tensor_copies), "k_gqa_decode_q8_raw");
 }
