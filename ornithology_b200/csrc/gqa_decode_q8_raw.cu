@@ -467,52 +467,58 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, cons
     __syncthreads();
     if (!last_one) return;
     __threadfence();
-    for (int h = warp; h < G; h += NWARP) {               // a warp per head; partials of other SMs: read past L1
+    // 16 threads per head, all heads at once: thread (h, q) owns the float2 columns q + 16 k of head h.
+    // Partials of other SMs are read past L1.  Four splits' rows are in flight per thread at a time.
+    const int h = tid >> 4, q = tid & 15;
+    if (h < G) {
+        const unsigned hm = 0xffffu << (lane & 16);           // this half-warp (the other half may belong to no head)
         const float *ph = part0 - (size_t)split * (HD + 2) + h * part_stride;   // split 0 of head h
-        float lsum = 0.0f, acc[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) acc[i] = 0.0f;
-        // (m, l) of up to 32 splits per lane-round; the group maximum first
         float M = -INFINITY;
-        for (int s0 = 0; s0 < nlive; s0 += 32) {
-            const int s = s0 + lane;
-            const float2 ml = s < nlive ? __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2))) : make_float2(0.0f, 0.0f);
+        for (int s = q; s < nlive; s += 16) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2)));
             if (ml.y > 0.0f) M = fmaxf(M, ml.x);
         }
-        M = warp_max(M);
-        for (int s0 = 0; s0 < nlive; s0 += 32) {
-            const int s = s0 + lane;
+#pragma unroll
+        for (int sft = 8; sft >= 1; sft >>= 1) M = fmaxf(M, __shfl_xor_sync(hm, M, sft, 16));
+        float lsum = 0.0f;
+        float2 acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc[k] = make_float2(0.0f, 0.0f);
+        for (int s0 = 0; s0 < nlive; s0 += 16) {
+            const int s = s0 + q;
             const float2 ml = s < nlive ? __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2))) : make_float2(0.0f, 0.0f);
             const float w = (ml.y > 0.0f) ? expf(ml.x - M) : 0.0f;
             lsum += ml.y * w;
-            const int n = min(32, nlive - s0);
-            for (int i0 = 0; i0 < n; i0 += 4) {           // four splits' rows in flight at a time
-                float2 v[4][4];
+            const int n = min(16, nlive - s0);
+            for (int i0 = 0; i0 < n; i0 += 4) {
+                float2 v[4][8];
                 float wi[4];
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    wi[u] = __shfl_sync(0xffffffffu, w, (i0 + u) & 31);
+                    wi[u] = __shfl_sync(hm, w, (i0 + u) & 15, 16);
                     if (i0 + u >= n) wi[u] = 0.0f;
                     const float2 *o2 = reinterpret_cast<const float2 *>(ph + (size_t)(s0 + min(i0 + u, n - 1)) * (HD + 2) + 2);
 #pragma unroll
-                    for (int k = 0; k < 4; k++) v[u][k] = __ldcg(o2 + lane + 32 * k);   // dims 2 lane + 64 k, +1
+                    for (int k = 0; k < 8; k++) v[u][k] = __ldcg(o2 + q + 16 * k);       // dims 2 (q + 16 k), +1
                 }
 #pragma unroll
                 for (int u = 0; u < 4; u++)
                     if (wi[u] != 0.0f) {
 #pragma unroll
-                        for (int k = 0; k < 4; k++) { acc[2 * k] += v[u][k].x * wi[u]; acc[2 * k + 1] += v[u][k].y * wi[u]; }
+                        for (int k = 0; k < 8; k++) { acc[k].x += v[u][k].x * wi[u]; acc[k].y += v[u][k].y * wi[u]; }
                     }
             }
         }
-        const float inv = 1.0f / warp_sum(lsum);
+#pragma unroll
+        for (int sft = 8; sft >= 1; sft >>= 1) lsum += __shfl_xor_sync(hm, lsum, sft, 16);
+        const float inv = 1.0f / lsum;
         const size_t head = (size_t)b * a.nh + (size_t)head0 + h;
 #pragma unroll
-        for (int k = 0; k < 4; k++)
+        for (int k = 0; k < 8; k++)
 #pragma unroll
             for (int e = 0; e < 2; e++) {
-                const int d = 2 * lane + 64 * k + e;
-                float o = acc[2 * k + e] * inv;
+                const int d = 2 * (q + 16 * k) + e;
+                float o = (e ? acc[k].y : acc[k].x) * inv;
                 if (a.act_dtype == ORNITH_ACT_BF16) {
                     if (a.gated) o *= sigmoid_f(act_ld((const __nv_bfloat16 *)a.qproj, head * HD * 2 + HD + d));
                     act_st((__nv_bfloat16 *)a.out, head * HD + d, o);
