@@ -29,8 +29,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # DRAM bytes (read + write) per launch over algorithmic bytes, from the ncu captures summarised in
-# profiles/gqa_decode_q8_raw_24seq_8k-16k.txt (308.4 MB moved for 303.8 MB) and
-# profiles/linear_decode_128_64seq.txt (the state a launch writes is partly still dirty in L2 when
+# profiles/gqa_decode_q8_raw_24seq_8k-16k.txt (308.5 MB moved for 303.8 MB) and
+# profiles/linear_decode_ring_64seq.txt, profiles/linear_decode_128_64seq.txt (the state a launch writes is partly still dirty in L2 when
 # it ends, so DRAM writes are undercounted there; 1.0 = the algorithmic bytes are what moves).
 DRAM_OVER_ALGORITHMIC = {"full_attn_step": 1.015, "linear_attn_step": 1.0}
 
