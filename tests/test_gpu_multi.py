@@ -71,3 +71,41 @@ def test_head_sharded_decode_matches_unsharded():
         assert p.exitcode == 0
     worst = q.get(timeout=10)
     assert worst < 1e-5, worst          # same kernels on the same heads: only the gather differs
+
+
+@pytest.mark.parametrize("arch,world", [("35b", 8), ("397b", 8), ("397b", 4)])
+def test_head_shards_one_after_the_other_on_one_gpu(arch, world):
+    """The sub-layers every rank of an 8-way (4-way) head sharding would run, executed in turn on one
+    GPU and concatenated in rank order, must reproduce the unsharded stack: covers the per-rank
+    shapes (1 KV head with 2 or 4 query heads, 4 or 8 value heads) without needing the GPUs."""
+    import torch
+    from ornithology_b200 import device as D
+    from ornithology_b200 import stack as S
+    dev = torch.device("cuda", 0)
+    ctx, steps, n_layers, T = [300, 40, 700], 2, 4, 16
+    caps = [c + steps + 1 for c in ctx]
+    stacks = [S.AttnStack(arch, caps, kv_mode=D.KV_Q8_0, seed=1, device=dev, n_layers=n_layers)]
+    stacks += [S.AttnStack(arch, caps, kv_mode=D.KV_Q8_0, seed=1, device=dev, n_layers=n_layers,
+                           shard=S.head_shard(S.ARCHS[arch], r, world)) for r in range(world)]
+    full = stacks[0]
+    g = torch.Generator(device="cpu").manual_seed(7)
+    z = torch.zeros(len(ctx), dtype=torch.int32, device=dev)
+    pre = [[torch.randn(len(ctx), T, w, generator=g).to(dev) for w in full.input_widths(kind)] for kind, _, _ in full.layers]
+    for st in stacks:
+        for (kind, layer, state), x in zip(st.layers, st.shard_inputs(pre)):
+            if kind == "full":
+                D.full_attn_prefill(layer, state, z, *x, T)
+            else:
+                D.linear_attn_prefill(layer, state, z, *x, T)
+        st.pos = torch.full((len(ctx),), T, dtype=torch.int32, device=dev)
+    worst = 0.0
+    for s in range(steps):
+        ins = [[torch.randn(len(ctx), w, generator=g).to(dev) for w in full.input_widths(kind)] for kind, _, _ in full.layers]
+        ref = full.decode_step(ins)
+        parts = [st.decode_step(st.shard_inputs(ins)) for st in stacks[1:]]
+        for i, b in enumerate(ref):
+            a = torch.cat([p[i] for p in parts], dim=-1)
+            worst = max(worst, float((a - b).abs().max() / b.abs().max()))
+    # same arithmetic per head; the delta-net prefill that built the state spreads a head over 2 or 4 CTAs
+    # depending on how many heads there are, which changes the order of a few f32 sums
+    assert worst < 1e-4, worst
