@@ -109,3 +109,36 @@ def test_head_shards_one_after_the_other_on_one_gpu(arch, world):
     # same arithmetic per head; the delta-net prefill that built the state spreads a head over 2 or 4 CTAs
     # depending on how many heads there are, which changes the order of a few f32 sums
     assert worst < 1e-4, worst
+
+
+def test_prefill_head_shards_one_after_the_other_on_one_gpu():
+    """A 1024-token prompt through one delta-net and one full-attention layer at the 397B shape,
+    unsharded and as the 8 per-rank head shards run in turn: the concatenated shard outputs must
+    match (the tensor-core prefill kernels at 8 value heads / 4 query heads over 1 KV head)."""
+    import torch
+    from ornithology_b200 import device as D
+    from ornithology_b200 import stack as S
+    dev = torch.device("cuda", 0)
+    arch, world, T = "397b", 8, 1024
+    caps = [T + 8]
+    stacks = [S.AttnStack(arch, caps, kv_mode=D.KV_Q8_0, seed=2, device=dev, n_layers=4)]
+    stacks += [S.AttnStack(arch, caps, kv_mode=D.KV_Q8_0, seed=2, device=dev, n_layers=4,
+                           shard=S.head_shard(S.ARCHS[arch], r, world)) for r in range(world)]
+    full = stacks[0]
+    g = torch.Generator(device="cpu").manual_seed(11)
+    z = torch.zeros(1, dtype=torch.int32, device=dev)
+    pre = [[torch.randn(1, T, w, generator=g).to(dev) for w in full.input_widths(kind)] for kind, _, _ in full.layers]
+    outs = []
+    for st in stacks:
+        o = []
+        for (kind, layer, state), x in zip(st.layers, st.shard_inputs(pre)):
+            if kind == "full":
+                o.append(D.full_attn_prefill(layer, state, z, *x, T))
+            else:
+                o.append(D.linear_attn_prefill(layer, state, z, *x, T))
+        outs.append(o)
+    for i, (kind, _, _) in enumerate(full.layers[2:], start=2):     # one delta-net layer and the full-attention layer
+        a = torch.cat([outs[1 + r][i] for r in range(world)], dim=-1).float()
+        b = outs[0][i].float()
+        err = float((a - b).abs().max() / b.abs().max())
+        assert err < 2e-4, (kind, err)
