@@ -181,8 +181,11 @@ typedef struct {
     const float *rope_inv_freq;    /* device [rope_dim/2], NULL with rope_dim == 0 */
 } ornith_cuda_full_layer;
 
-/* scratch bytes ornith_cuda_full_attn_step needs for n_seq sequences whose
- * longest context (after the append) is max_len */
+/* scratch bytes ornith_cuda_full_attn_step asks for with n_seq sequences whose
+ * longest context (after the append) is max_len: room for the split length that fills
+ * the GPU at this batch (short splits for few sequences).  The step adapts to what it
+ * is given: with less it uses longer splits, down to the need of the coarsest split
+ * (2048 tokens above a 16k context); below that it fails with ORNITH_ERR_FORMAT. */
 size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *layer, int n_seq, int max_len);
 
 /* One decode step of a full-attention layer for n_seq sequences, between the
@@ -237,9 +240,10 @@ ornith_status ornith_cuda_kv_append(const ornith_cuda_full_layer *layer, const o
  * rows + split-K partials) comes from a fixed array inside the library image, which
  * every GPU that loads the library keeps resident until the process exits.
  *
- *  - Limit: ornith_cuda_full_attn_step_scratch(layer, n_seq, max_len) must not exceed
+ *  - Limit: the scratch of the step at its coarsest split length must not exceed
  *    ORNITH_CUDA_STATIC_SCRATCH_BYTES (8 MiB; e.g. 8 sequences x 16 heads x 256 at an
- *    8k context).  Larger requests return ORNITH_ERR_UNSUPPORTED with a message.
+ *    8k context); within the array the step uses the shortest splits that fit.
+ *    Larger requests return ORNITH_ERR_UNSUPPORTED with a message.
  *  - The first call on each device looks up the array's device address (with that
  *    device current); make that call before starting any stream capture.
  *  - Calls never call cudaMalloc/cudaFree or any allocating library routine.

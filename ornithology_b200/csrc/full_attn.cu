@@ -508,14 +508,36 @@ static int split_tokens(int max_len) {
     // tokens per split: long contexts use 512-token splits; short ones fewer CTAs
     return max_len <= 512 ? 128 : 512;
 }
-// split length of the tensor-core decode kernels (larger splits, fewer partials)
-static int split_tokens_mma(int max_len) {
+// Split length of the tensor-core decode kernels.
+// coarse: by context alone, the fewest partials (what the smallest accepted scratch holds).
+static int split_tokens_coarse(int max_len) {
     return max_len > 16384 ? 2048 : (max_len > 8192 ? 1024 : (max_len > 1024 ? 512 : 256));
 }
-// the largest split count either decode path may use: what the scratch is sized for
-static int max_splits(int max_len) {
-    const int a = split_tokens(max_len), b = split_tokens_mma(max_len), t = a < b ? a : b;
-    return (max_len + t - 1) / t;
+// fine: for batches too small to fill the GPU with coarse splits.  A CTA walks one split of one head group and
+// 4 CTAs are resident per SM; if even at max_len the coarse splits give less than one wave (592 CTAs on 148
+// SMs), the splits are shortened towards one wave, but never to more than about 32 per sequence: the last CTA
+// of a group merges the group's partials alone, and past that its work outweighs the gain.  Batches that
+// fill the GPU keep the coarse length (their CTA count depends on the actual contexts, which the host does
+// not know).
+static int split_tokens_fine(int max_len, long long n_groups) {
+    const int coarse = split_tokens_coarse(max_len);
+    if (n_groups * ((max_len + coarse - 1) / coarse) >= 592) return coarse;
+    long long t = (n_groups * (long long)max_len / 592 + 63) / 64 * 64;
+    const long long floor_t = ((max_len / 32 > 256 ? max_len / 32 : 256) + 63) / 64 * 64;
+    if (t < floor_t) t = floor_t;
+    return (int)(t < coarse ? t : coarse);
+}
+static long long head_groups(const ornith_cuda_full_layer *l, int n_seq) {
+    const int g = l->n_heads / l->n_kv_heads;
+    return (long long)n_seq * l->n_kv_heads * ((g + 7) / 8);
+}
+// Scratch of one decode step whose tensor-core kernels use splits of tps_mma tokens: query rows, one arrival
+// counter per (sequence, head), then the partials (the CUDA-core kernel's split count is covered too).
+static size_t step_need(const ornith_cuda_full_layer *l, int n_seq, int max_len, int tps_mma) {
+    const int ta = split_tokens(max_len), t = ta < tps_mma ? ta : tps_mma, nsplit = (max_len + t - 1) / t;
+    return align_up((size_t)n_seq * l->n_heads * l->head_dim * sizeof(float), 256) +
+           align_up((size_t)n_seq * l->n_heads * sizeof(int), 256) +
+           align_up((size_t)n_seq * l->n_heads * nsplit * (l->head_dim + 2) * sizeof(float), 256);
 }
 
 template <typename ACT>
@@ -547,12 +569,9 @@ static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_c
 extern "C" {
 
 size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *l, int n_seq, int max_len) {
-    if (!l || n_seq <= 0) return 0;
+    if (!l || n_seq <= 0 || l->n_kv_heads <= 0) return 0;
     if (max_len < 1) max_len = 1;
-    const int nsplit = max_splits(max_len);
-    size_t qp = align_up((size_t)n_seq * l->n_heads * l->head_dim * sizeof(float), 256);
-    size_t part = (size_t)n_seq * l->n_heads * nsplit * (l->head_dim + 2) * sizeof(float);
-    return qp + align_up(part, 256) + align_up((size_t)n_seq * l->n_heads * sizeof(int), 256);   // + merge counters
+    return step_need(l, n_seq, max_len, split_tokens_fine(max_len, head_groups(l, n_seq)));
 }
 
 ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
@@ -565,7 +584,19 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     const int B = kv->n_seq;
     if (B <= 0) return ORNITH_OK;
     if (max_len < 1) max_len = 1;
-    if (scratch_bytes < ornith_cuda_full_attn_step_scratch(l, B, max_len) || !scratch) {
+    // Split length of the tensor-core kernels: the fine one if the scratch holds its partials, else doubled until
+    // it fits, down to the coarse one (ornith_cuda_full_attn_step_scratch asks for the fine one; a caller with a
+    // fixed budget may pass less).  ORNITH_CUDA_DECODE_SPLIT=<tokens> overrides it when that fits too.
+    int tps_mma = split_tokens_fine(max_len, head_groups(l, B));
+    {
+        const int coarse = split_tokens_coarse(max_len), tps_max = tps_mma > coarse ? tps_mma : coarse;
+        while (step_need(l, B, max_len, tps_mma) > scratch_bytes && tps_mma < tps_max)
+            tps_mma = (2 * tps_mma < tps_max) ? 2 * tps_mma : tps_max;
+        static int forced = -1;
+        if (forced < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_SPLIT"); forced = e ? atoi(e) : 0; }
+        if (forced >= 64 && step_need(l, B, max_len, forced / 64 * 64) <= scratch_bytes) tps_mma = forced / 64 * 64;
+    }
+    if (!scratch || step_need(l, B, max_len, tps_mma) > scratch_bytes) {
         orn_record_error("full_attn_step: scratch too small (%zu bytes given)", scratch_bytes);
         return ORNITH_ERR_FORMAT;
     }
@@ -573,9 +604,8 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     const int hd = l->head_dim, nh = l->n_heads;
     const int tps = split_tokens(max_len), nsplit = (max_len + tps - 1) / tps;
     float *q_prep = (float *)scratch;
-    float *part = (float *)((char *)scratch + align_up((size_t)B * nh * hd * sizeof(float), 256));
-    // the arrival counters sit behind the partials of the largest split count the scratch is sized for
-    int *group_ctr = (int *)((char *)part + align_up((size_t)B * nh * max_splits(max_len) * (hd + 2) * sizeof(float), 256));
+    int *group_ctr = (int *)((char *)scratch + align_up((size_t)B * nh * hd * sizeof(float), 256));
+    float *part = (float *)((char *)group_ctr + align_up((size_t)B * nh * sizeof(int), 256));
 
     if (act_dtype == ORNITH_ACT_BF16)
         ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B, 1, st, false, nullptr, nullptr,
@@ -591,22 +621,13 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     bool merged = false;
     int nsplit_used;
     if (gqa_decode_q8_mma_supported(d.kv, nh) && !force_generic_decode()) {
-        // tensor-core path: larger splits (fewer partials); never more splits than the scratch was sized for
-        int tps_mma = split_tokens_mma(max_len);
-        {   // ORNITH_CUDA_DECODE_SPLIT=<tokens> overrides the split length for long contexts (tuning knob)
-            static int forced = -1;
-            if (forced < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_SPLIT"); forced = e ? atoi(e) : 0; }
-            if (forced >= 512 && max_len > 1024) tps_mma = forced / 16 * 16;
-        }
         d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
         ORN_TRY(launch_gqa_decode_q8_mma(d, B, st, &merged));
     } else if (gqa_decode_f32_tc_supported(d.kv, nh) && !force_generic_decode()) {
-        const int tps_tc = split_tokens_mma(max_len);
-        d.tokens_per_split = tps_tc; d.nsplit = nsplit_used = (max_len + tps_tc - 1) / tps_tc;
+        d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
         ORN_TRY(launch_gqa_decode_f32_tc(d, B, st));
     } else if (gqa_decode_i8_raw_supported(d.kv, nh) && !force_generic_decode()) {
-        const int tps_tc = split_tokens_mma(max_len);
-        d.tokens_per_split = tps_tc; d.nsplit = nsplit_used = (max_len + tps_tc - 1) / tps_tc;
+        d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
         ORN_TRY(launch_gqa_decode_i8_raw(d, B, st));
     } else {
         d.tokens_per_split = tps; d.nsplit = nsplit_used = nsplit;
@@ -747,7 +768,9 @@ ornith_status ornith_cuda_full_attn_step_static(const ornith_cuda_full_layer *l,
     ORN_TRY(orn_require_device());
     ORN_TRY(check_full(l, kv));
     if (kv->n_seq <= 0) return ORNITH_OK;
-    const size_t need = ornith_cuda_full_attn_step_scratch(l, kv->n_seq, max_len);
+    // the step adapts its split length to the scratch it is given: what must fit is the coarse split's need
+    const int mlen = max_len < 1 ? 1 : max_len, fine = split_tokens_fine(mlen, head_groups(l, kv->n_seq)), coarse = split_tokens_coarse(mlen);
+    const size_t need = step_need(l, kv->n_seq, mlen, fine > coarse ? fine : coarse);
     if (need > (size_t)ORNITH_CUDA_STATIC_SCRATCH_BYTES) {
         orn_record_error("full_attn_step_static: %d sequences x context %d need %zu bytes of scratch, the built-in "
                          "array holds %u; use ornith_cuda_full_attn_step with caller scratch",
