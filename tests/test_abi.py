@@ -64,6 +64,27 @@ def test_no_cpu_fallback_without_a_gpu(lib):
     attn.kv_free(c)
 
 
+def test_decode_scratch_follows_the_batch(lib):
+    """Host-side sizing only (no GPU work): the decode scratch asks for finer splits, hence more
+    partials per head, when the batch is too small to fill the GPU, and for the coarse 2048-token
+    splits when it is not."""
+    from ornithology_b200._lib import CudaFullLayer
+    layer = CudaFullLayer(16, 2, 256, 64, 1, 1e-6, 0.0, None, None, None)
+
+    def splits(n_seq, max_len):
+        total = lib.ornith_cuda_full_attn_step_scratch(C.byref(layer), n_seq, max_len)
+        fixed = (n_seq * 16 * 256 * 4 + 255) // 256 * 256 + (n_seq * 16 * 4 + 255) // 256 * 256
+        return (total - fixed) / (n_seq * 16 * 258 * 4)
+
+    big = splits(64, 32832)            # 64 sequences of up to 32k tokens: 512-token splits of the CUDA-core path bound it
+    assert abs(big - 65) < 0.01
+    four = splits(4, 8256)             # 4 sequences x 8k: 320-token splits -> 26 partials per head (coarse: 9, CUDA-core path: 17)
+    assert abs(four - 26) < 0.5
+    eight = splits(8, 16448)           # 8 sequences x 16k: 576-token splits -> 29, below the CUDA-core path's 33
+    assert abs(eight - 33) < 0.5
+    assert lib.ornith_cuda_full_attn_step_scratch(C.byref(layer), 0, 100) == 0
+
+
 def test_product_does_not_touch_the_oracle():
     """Nothing under the package or include/ may reference oracle/."""
     pkg = os.path.join(ROOT, "ornithology_b200")
