@@ -144,7 +144,26 @@ ornith_status ornith_cuda_free(void *dev_ptr);
 ornith_status ornith_cuda_memset(void *dev_ptr, int value, size_t bytes);
 ornith_status ornith_cuda_h2d(void *dev_dst, const void *host_src, size_t bytes);
 ornith_status ornith_cuda_d2h(void *host_dst, const void *dev_src, size_t bytes);
+/* Waits for `stream`; returns ORNITH_ERR_BACKEND (with a message) when a kernel of this library
+ * gave up a bounded wait since the last check — its outputs are then NaN-poisoned, not valid. */
 ornith_status ornith_cuda_sync(void *stream);
+/* The same check without waiting: reads and clears the current device's status word. */
+ornith_status ornith_cuda_poll_status(void);
+/* Every wait inside the kernels (on an mbarrier, for a copy or a tensor-core result) is bounded.
+ * This runs a one-thread kernel that waits `polls` polls on a barrier nobody arrives on, and checks
+ * that the wait comes back and is reported: the expected return value is ORNITH_ERR_BACKEND with
+ * the status word set; ORNITH_ERR_FORMAT means the give-up path did not work.  Nothing faults. */
+ornith_status ornith_cuda_selftest_wait_timeout(int polls);
+/* Allocation hook (host-side failure injection; reference: the OOM checks of the init functions,
+ * src/ornith_attn.c:32-46): when set, every device allocation the library makes — ornith_cuda_malloc,
+ * the tier-1 mirrors, the delta-net decode work buffer — first calls hook(bytes, user); a non-zero
+ * return makes that allocation fail with ORNITH_ERR_OOM without touching the device.  NULL clears it. */
+typedef int (*ornith_cuda_alloc_hook)(size_t bytes, void *user);
+void ornith_cuda_set_alloc_hook(ornith_cuda_alloc_hook hook, void *user);
+/* Frees the work buffer the delta-net decode step keeps for `stream` on the current device (for every
+ * stream of the device when all_streams != 0), after waiting for the work queued there.  Call it
+ * before destroying a stream that ran ornith_cuda_linear_attn_step. */
+ornith_status ornith_cuda_stream_release(void *stream, int all_streams);
 /* inverse RoPE frequencies theta^(-2i/rotary_dim), i < rotary_dim/2, computed on
  * the host with the engine's own expression (reference: src/ornith_tensor.c:171);
  * upload them once and pass the device copy as `rope_inv_freq`. */

@@ -91,6 +91,10 @@ SYMBOLS = {
     "ornith_cuda_h2d": (_I, [vp, vp, _SZ]),
     "ornith_cuda_d2h": (_I, [vp, vp, _SZ]),
     "ornith_cuda_sync": (_I, [vp]),
+    "ornith_cuda_poll_status": (_I, []),
+    "ornith_cuda_selftest_wait_timeout": (_I, [_I]),
+    "ornith_cuda_set_alloc_hook": (None, [vp, vp]),
+    "ornith_cuda_stream_release": (_I, [vp, _I]),
     "ornith_cuda_rope_inv_freq": (None, [_F, _I, f32p]),
     "ornith_cuda_q8_0_encode": (_I, [vp, vp, _SZ, vp]),
     "ornith_cuda_q8_0_decode": (_I, [vp, vp, _SZ, vp]),

@@ -50,6 +50,7 @@ def _stale() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
+    extra = os.environ.get("ORNITH_NVCC_EXTRA", "").split()       # e.g. -DORNITH_SCAN_TRACE for kernel bring-up
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
     cu, c = sources()
@@ -57,7 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_cu(f):
         o = os.path.join(OBJ, f + ".o")
-        r = subprocess.run([nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, f), "-o", o],
+        r = subprocess.run([nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, f), "-o", o],
                            capture_output=True, text=True)
         logs[f] = r.stderr
         if r.returncode:

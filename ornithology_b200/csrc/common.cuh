@@ -14,6 +14,23 @@ ornith_status orn_check(cudaError_t e, const char *what);
 ornith_status orn_check_launch(const char *what);     // cudaGetLastError after a launch
 ornith_status orn_require_device();                    // ORNITH_ERR_BACKEND when no usable GPU
 
+// Per-device bookkeeping.  Attributes such as the dynamic shared-memory opt-in of a kernel and
+// the SM count belong to a device, not to the process: one process may drive several GPUs
+// (ornith_cuda_set_device), so "done once" flags are arrays indexed by the current device.
+#define ORN_MAX_DEVICES 64
+int orn_device_index();                                // current device, clamped to [0, ORN_MAX_DEVICES)
+// cudaMalloc through the allocation hook (ornith_cuda_set_alloc_hook): every device allocation the
+// library makes on its own goes through here, so a host can make the N-th one fail.
+ornith_status orn_device_alloc(void **p, size_t bytes, const char *what);
+// Status word of the current device: host memory the kernels can write.  A bounded wait that gives
+// up ORs a code into it; ornith_cuda_sync / ornith_cuda_poll_status turn it into ORNITH_ERR_BACKEND.
+// nullptr when the word could not be set up (the kernels then only poison their outputs).
+unsigned int *orn_status_word();
+#define ORN_WAIT_GQA_PREFILL 0x1u
+#define ORN_WAIT_DELTA_SCAN  0x2u
+#define ORN_WAIT_SELFTEST    0x4u
+#define ORN_WAIT_DECODE      0x8u
+
 #define ORN_TRY(expr)                                   \
     do {                                                \
         ornith_status _s = (expr);                      \

@@ -567,7 +567,8 @@ __global__ void __launch_bounds__(256, 1) k_delta_chunk_scan(LinArgs a, const fl
 template <int NR, typename ACT>
 ornith_status launch_scan(const LinArgs &x, int n_seq, const float *Y, const float *blocks, const float *Kp,
                           const float *Qp, int n_chunks, cudaStream_t s) {
-    static bool configured = false;
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_chunk_scan<NR, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)sizeof(ScanSmem<NR>)),
@@ -605,7 +606,8 @@ ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtyp
                                        const float *rk, const float *la, const float *be, float *blocks,
                                        cudaStream_t s) {
     const int n_chunks = (x.T + TC - 1) / TC;
-    static bool configured = false;
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_chunk_prep, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)sizeof(PrepSmem)),

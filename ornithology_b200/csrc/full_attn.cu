@@ -666,7 +666,8 @@ size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *l, in
 
 template <int MODE, typename ACT>
 static ornith_status launch_prefill(const PrefillArgs &a, dim3 grid, size_t smem, cudaStream_t st) {
-    static bool configured = false;                      // per instantiation
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];                      // per instantiation
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill<MODE, ACT>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024),

@@ -213,7 +213,8 @@ bool gqa_decode_f32_tc_supported(const KvView &kv, int nh) {
 }
 
 ornith_status launch_gqa_decode_f32_tc(const DecodeArgs &a, int n_seq, cudaStream_t st) {
-    static bool configured = false;
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_f32_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES),
                           "f32 gqa decode smem opt-in"));

@@ -369,7 +369,8 @@ bool gqa_decode_i8_raw_supported(const KvView &kv, int nh) {
 }
 
 ornith_status launch_gqa_decode_i8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st) {
-    static bool configured = false;
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_i8_raw, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SMEM_BYTES), "int8 gqa decode smem opt-in"));

@@ -551,13 +551,15 @@ bool gqa_decode_q8_mma_supported(const KvView &kv, int nh) {
 
 ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged) {
     *merged = false;
-    static bool configured = false;
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_mma, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SMEM_BYTES), "gqa decode smem opt-in"));
         configured = true;
     }
-    static bool configured3 = false;
+    static bool configured3_dev[ORN_MAX_DEVICES] = {};
+    bool &configured3 = configured3_dev[orn_device_index()];
     if (!configured3) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_tok, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SMEM3_BYTES), "gqa decode smem opt-in"));

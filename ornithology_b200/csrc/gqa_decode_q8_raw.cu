@@ -565,7 +565,8 @@ bool q8_rows_map(CUtensorMap *m, const void *pool, int nkv) {
 
 ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged) {
     *merged = a.group_ctr != nullptr;
-    static bool configured = false;
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_raw, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SMEM_BYTES), "gqa decode smem opt-in"));

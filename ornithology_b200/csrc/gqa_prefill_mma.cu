@@ -331,7 +331,8 @@ ornith_status launch_gqa_prefill_mma(const KvView &kv, const int32_t *kv_len, co
     if (!prefer_mma_sync() && ((uintptr_t)kvh_scratch % 16) == 0)
         return launch_gqa_prefill_tc(kv, kv_len, q_prep, a.Kh, a.Vh, (char *)kvh_scratch + 2 * half_bytes, qproj, out, nh,
                                      T, Lmax, a.Lp, gated, scale, n_seq, bf16_act, st);
-    static bool configured = false;
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_mma<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SMEM_BYTES), "prefill smem opt-in"));

@@ -32,6 +32,7 @@
 #include <cuda.h>
 
 #include "full_attn.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -49,95 +50,11 @@ struct TcArgs {
     const void *qproj;
     void *out;
     int nh, nkv, T, Lmax, Lp, gated;
+    unsigned int *status;                  // status word of the device: a wait that gives up reports here
 };
 
-__device__ __forceinline__ uint32_t su32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// No suspend-time hint: every hand-off in this kernel is on the critical path of the tensor pipe.
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded: gives up after about a second of polling
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < (1 << 24); i++)
-        if (mbar_try(bar, parity)) return true;
-    return false;
-}
-// x (innermost coordinate, elements) must be a multiple of 8 for f16
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-// shared-memory matrix descriptor, 128-byte swizzle; offsets in bytes
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-// A operand in tensor memory: row m in lane m, elements 2c and 2c+1 of the row in column c
-__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
-    uint32_t u[32];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]),
-                   "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]),
-                   "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
-                   "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
-                 : "r"(taddr) : "memory");
-#pragma unroll
-    for (int i = 0; i < 32; i++) r[i] = __uint_as_float(u[i]);
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-                 ::"r"(taddr),
-                   "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])), "r"(__float_as_uint(r[3])),
-                   "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])), "r"(__float_as_uint(r[6])), "r"(__float_as_uint(r[7])),
-                   "r"(__float_as_uint(r[8])), "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])), "r"(__float_as_uint(r[11])),
-                   "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])), "r"(__float_as_uint(r[15])),
-                   "r"(__float_as_uint(r[16])), "r"(__float_as_uint(r[17])), "r"(__float_as_uint(r[18])), "r"(__float_as_uint(r[19])),
-                   "r"(__float_as_uint(r[20])), "r"(__float_as_uint(r[21])), "r"(__float_as_uint(r[22])), "r"(__float_as_uint(r[23])),
-                   "r"(__float_as_uint(r[24])), "r"(__float_as_uint(r[25])), "r"(__float_as_uint(r[26])), "r"(__float_as_uint(r[27])),
-                   "r"(__float_as_uint(r[28])), "r"(__float_as_uint(r[29])), "r"(__float_as_uint(r[30])), "r"(__float_as_uint(r[31]))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&r)[16]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                 ::"r"(taddr),
-                   "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])), "r"(__float_as_uint(r[3])),
-                   "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])), "r"(__float_as_uint(r[6])), "r"(__float_as_uint(r[7])),
-                   "r"(__float_as_uint(r[8])), "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])), "r"(__float_as_uint(r[11])),
-                   "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])), "r"(__float_as_uint(r[15]))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+using namespace tc5;
+
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&h);
@@ -218,9 +135,9 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
                      ::"r"(su32(&tmem_base_s)), "r"((uint32_t)TM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    tc_fence_before();
+    fence_before();
     __syncthreads();
-    tc_fence_after();
+    fence_after();
     const uint32_t tmem = tmem_base_s;
     bool ok = true;
 
@@ -274,7 +191,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
                 // this buffer still holds the probabilities of tile j-3 until their value product is done
                 if (ok && j >= NB) ok = mbar_wait(su32(&bars.pv_done[e]), (uint32_t)(j / NB - 1) & 1u);
                 if (!ok) break;
-                tc_fence_after();
+                fence_after();
                 const uint64_t kd = smem_desc(base + SM_K + st * 32768, 16, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)
@@ -297,7 +214,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
                 ok = mbar_wait(su32(&bars.p_full), (uint32_t)j & 1u) &&
                      mbar_wait(su32(&bars.v_full[st]), (uint32_t)(j / NSV) & 1u);
                 if (!ok) break;
-                tc_fence_after();
+                fence_after();
                 const uint64_t vd = smem_desc(base + SM_V + st * 32768, 8192, 1024);
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)
@@ -327,14 +244,14 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
             }
             tmem_st32(lane_t + TM_Q + 32 * half, q);
             tmem_wait_st();
-            tc_fence_before();
+            fence_before();
             mbar_arrive(su32(&bars.q_full));
         }
         float m_ref = -INFINITY, l = 0.0f;
         for (int j = 0; j < n_tiles; j++) {
             const int sb = j % NB, key0 = j * BN + 32 * half;
             ok = ok && mbar_wait(su32(&bars.s_full[sb]), (uint32_t)(j / NB) & 1u);
-            tc_fence_after();
+            fence_after();
             float s[32];
             tmem_ld32(lane_t + TM_S + sb * BN + 32 * half, s);
             tmem_wait_ld();
@@ -376,7 +293,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 // O may only be touched between two value products: the last one is done, the next waits for us
                 ok = ok && mbar_wait(su32(&bars.pv_done[(j - 1) % NB]), (uint32_t)((j - 1) / NB) & 1u);
-                tc_fence_after();
+                fence_after();
 #pragma unroll 1
                 for (int c = 0; c < HD / 2; c += 32) {         // this thread's half of the output row
                     float o[32];
@@ -390,7 +307,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
             // probabilities over the scores: key k of the tile in the low / high half of column k / 2
             tmem_st16(lane_t + TM_S + sb * BN + 16 * half, pk);
             tmem_wait_st();
-            tc_fence_before();
+            fence_before();
             mbar_arrive(su32(&bars.p_full));
         }
         // row sum = the two halves' sums (both were rescaled by the same factors)
@@ -398,7 +315,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
         pair_sync(1 + wq);
         l += lx[half ^ 1][row];
         ok = ok && mbar_wait(su32(&bars.pv_done[(n_tiles - 1) % NB]), (uint32_t)((n_tiles - 1) / NB) & 1u);
-        tc_fence_after();
+        fence_after();
         const float inv = ok ? 1.0f / l : NAN;
         const size_t tok = (size_t)b * a.T + q0 + row;
         const ACT *gate = (a.gated && live) ? (const ACT *)a.qproj + tok * a.nh * HD * 2 + (size_t)h * HD * 2 + HD : nullptr;
@@ -418,32 +335,17 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
             }
         }
     }
-    tc_fence_before();
+    if (!ok) report_timeout(a.status, ORN_WAIT_GQA_PREFILL);
+    fence_before();
     __syncthreads();
     if (warp == 12) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TM_COLS) : "memory");
     }
 }
 
-typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn tensor_map_encoder() {
-    static EncodeFn fn = nullptr;
-    if (!fn) {
-        cudaDriverEntryPointQueryResult q;
-        void *p = nullptr;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeFn)p;
-    }
-    return fn;
-}
-
 // [rows][256] f16, boxes of 64 dims x box_rows rows, 128-byte swizzle
 ornith_status f16_rows_map(CUtensorMap *m, const void *basep, uint64_t rows, uint32_t box_rows) {
-    EncodeFn enc = tensor_map_encoder();
+    OrnTensorMapEncodeFn enc = orn_tensor_map_encoder();
     if (!enc) { orn_record_error("prefill: cuTensorMapEncodeTiled is not available"); return (ornith_status)ORNITH_ERR_BACKEND; }
     cuuint64_t dims[2] = {(cuuint64_t)HD, rows};
     cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
@@ -479,7 +381,9 @@ ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, con
     TcArgs a;
     a.seq_off = kv.seq_off; a.kv_len = kv_len; a.Qh = Qh; a.rs = rs; a.qproj = qproj; a.out = out;
     a.nh = nh; a.nkv = kv.nkv; a.T = T; a.Lmax = Lmax; a.Lp = Lp; a.gated = gated;
-    static bool configured = false;
+    a.status = orn_status_word();
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SM_BYTES + 1024), "tcgen05 prefill smem opt-in"));

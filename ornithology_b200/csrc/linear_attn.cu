@@ -380,6 +380,8 @@ __device__ __forceinline__ float silu_sel(float x) { return FAST ? silu_fast(x) 
 // rounding as k_conv_silu_prefill.  grid (ceil(Cc/512), ceil(T/CONV4_TOK), n_seq).
 constexpr int CONV4_TOK = 16;
 
+// nearest tf32 value (ties away from zero, finite inputs), in integer arithmetic
+__device__ __forceinline__ float tf32_rna(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 template <typename ACT, bool FAST>
 __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y) {
     const int qd = a.nk * a.dk, Cc = 2 * qd + a.nv * a.dv;
@@ -412,6 +414,9 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y)
                                          __fmul_rn(WC.w, x[i + 3].F)))
         ORN_CONV4(x, w[0], bias.x); ORN_CONV4(y, w[1], bias.y); ORN_CONV4(z, w[2], bias.z); ORN_CONV4(w, w[3], bias.w);
 #undef ORN_CONV4
+        if (FAST && ch < 2 * qd) {                        // q and k feed tf32 tensor-core products: round once, here
+            y.x = tf32_rna(y.x); y.y = tf32_rna(y.y); y.z = tf32_rna(y.z); y.w = tf32_rna(y.w);
+        }
         *reinterpret_cast<float4 *>(Y + ((size_t)b * a.T + t0 + i) * Cc + ch) = y;
     }
 }
@@ -685,6 +690,13 @@ __global__ void __launch_bounds__(256, 1) k_linear_prefill_chunk128(LinArgs a, c
 // host entry points
 // =============================================================================
 
+// Kernel bring-up aid, not part of the public interface: when set, the tcgen05 scan copies the first
+// chunk's intermediate tiles (KS, U, QS, PU; [128][64] floats each per (sequence, head)) there.
+static float *g_delta_scan_dump = nullptr;
+extern "C" void ornith_cuda_debug_delta_scan_dump(float *dev) { g_delta_scan_dump = dev; }
+long long *g_delta_scan_trace = nullptr;
+extern "C" void ornith_cuda_debug_delta_scan_trace(long long *dev) { g_delta_scan_trace = dev; }
+
 static ornith_status check_linear(const ornith_cuda_linear_layer *l, const ornith_cuda_linear_state *st) {
     if (!l || !st || l->nk <= 0 || l->nv <= 0 || l->dk <= 0 || l->dv <= 0 || l->nv % l->nk ||
         l->conv_k < 1 || l->conv_k > 9 || !l->conv_w || !l->a_coef || !l->dt_bias || !l->norm_w ||
@@ -742,7 +754,10 @@ size_t ornith_cuda_linear_attn_prefill_scratch(const ornith_cuda_linear_layer *l
     if (!l || n_seq <= 0 || T <= 0) return 0;
     const size_t n_tok = (size_t)n_seq * T, Cc = 2 * (size_t)l->nk * l->dk + (size_t)l->nv * l->dv;
     size_t bytes = align_up(n_tok * Cc * 4, 256) + 2 * align_up(n_tok * l->nk * 4, 256) + 2 * align_up(n_tok * l->nv * 4, 256);
-    if (l->dk == 128 && l->dv == 128) bytes += align_up(linear_prefill_tc_blocks_bytes(l->nk, l->nv, n_seq, T), 256);
+    if (l->dk == 128 && l->dv == 128) {                   // work area of whichever tensor-core scan is selected at run time
+        const size_t w_mma = linear_prefill_tc_blocks_bytes(l->nk, l->nv, n_seq, T), w_tc5 = linear_prefill_tc5_work_bytes(l->nk, l->nv, n_seq, T);
+        bytes += align_up(w_mma > w_tc5 ? w_mma : w_tc5, 256);
+    }
     return bytes;
 }
 
@@ -751,7 +766,8 @@ size_t ornith_cuda_linear_attn_prefill_scratch(const ornith_cuda_linear_layer *l
 template <int C, typename ACT>
 static ornith_status launch_chunk(const LinArgs &x, dim3 grid, const float *Y, const float *rq, const float *rk,
                                   const float *la, const float *be, cudaStream_t s) {
-    static bool configured = false;
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_linear_prefill_chunk128<C, ACT>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -817,7 +833,14 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     dim3 grid(l->nv, n_seq);
     if (l->dk == 128 && l->dv == 128) {
         // default: tf32 tensor-core scan; ORNITH_CUDA_PREFILL_FP32=1 keeps every product in fp32
-        if (tc) return launch_linear_prefill_tc(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, s);
+        if (tc) {
+            // tcgen05 scan unless ORNITH_CUDA_DELTA_SCAN=mma asks for the mma.sync one (or the state is not 16-byte aligned)
+            const char *variant = getenv("ORNITH_CUDA_DELTA_SCAN");
+            const bool aligned = ((uintptr_t)st->S % 16) == 0 && (st->S_seq_stride % 4) == 0;
+            if (aligned && !(variant && variant[0] == 'm'))
+                return launch_linear_prefill_tc5(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, g_delta_scan_dump, s);
+            return launch_linear_prefill_tc(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, s);
+        }
         if (chunk >= 32) return bf ? launch_chunk<32, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)
                                    : launch_chunk<32, float>(x, grid, Y, rq, rk, la, be, s);
         return bf ? launch_chunk<16, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)

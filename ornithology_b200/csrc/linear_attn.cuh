@@ -31,6 +31,14 @@ ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtyp
                                        const float *rk, const float *la, const float *be, float *blocks,
                                        cudaStream_t s);
 
+// The same scan on the 5th-generation tensor cores (delta_scan_tc5.cu): tcgen05.mma in tf32 with the
+// state in tensor memory, operands staged by TMA, 64-token chunks.  Y must hold the q and k channels
+// rounded to tf32 (k_conv4_silu_prefill does that); work = linear_prefill_tc5_work_bytes() bytes.
+size_t linear_prefill_tc5_work_bytes(int nk, int nv, int n_seq, int T);
+ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dtype, const float *Y, const float *rq,
+                                        const float *rk, const float *la, const float *be, float *work, float *dbg,
+                                        cudaStream_t s);
+
 __device__ __forceinline__ float4 lds128(const float *p) {        // not hoisted: keeps k/q out of registers
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"

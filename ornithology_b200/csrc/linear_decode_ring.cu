@@ -268,17 +268,18 @@ __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, const 
 // host that has made one call at its largest batch allocates nothing on the token path afterwards
 // (growing frees the old buffer with cudaFree, which waits for the work that still reads it).
 struct FrontBuf { float *p = nullptr; size_t bytes = 0; };
+std::mutex g_front_mu;
+std::map<std::pair<int, cudaStream_t>, FrontBuf> g_front_bufs;
+
 ornith_status front_blocks(cudaStream_t s, size_t bytes, float **out) {
-    static std::mutex mu;
-    static std::map<std::pair<int, cudaStream_t>, FrontBuf> bufs;
     int dev = 0;
     ORN_TRY(orn_check(cudaGetDevice(&dev), "cudaGetDevice"));
-    std::lock_guard<std::mutex> lock(mu);
-    FrontBuf &fb = bufs[{dev, s}];
+    std::lock_guard<std::mutex> lock(g_front_mu);
+    FrontBuf &fb = g_front_bufs[{dev, s}];
     if (fb.bytes < bytes) {
         if (fb.p) ORN_TRY(orn_check(cudaFree(fb.p), "decode front-end blocks (free)"));
         fb.p = nullptr; fb.bytes = 0;
-        ORN_TRY(orn_check(cudaMalloc((void **)&fb.p, bytes), "decode front-end blocks"));
+        ORN_TRY(orn_device_alloc((void **)&fb.p, bytes, "decode front-end blocks"));
         fb.bytes = bytes;
     }
     *out = fb.p;
@@ -287,13 +288,15 @@ ornith_status front_blocks(cudaStream_t s, size_t bytes, float **out) {
 
 template <typename ACT>
 ornith_status launch_ring(const LinArgs &x, int n_seq, cudaStream_t s) {
-    static int n_sm = 0;
+    static int n_sm_dev[ORN_MAX_DEVICES] = {};             // SM count and smem opt-in are per device
+    int &n_sm = n_sm_dev[orn_device_index()];
     if (!n_sm) {
-        int dev = 0;
+        int dev = 0, n = 0;
         ORN_TRY(orn_check(cudaGetDevice(&dev), "cudaGetDevice"));
-        ORN_TRY(orn_check(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev), "SM count"));
+        ORN_TRY(orn_check(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev), "SM count"));
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_linear_decode_ring<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_SMEM),
                           "decode ring smem opt-in"));
+        n_sm = n;
     }
     float *front = nullptr;
     ORN_TRY(front_blocks(s, (size_t)n_seq * front_stride(x.nk, x.nv) * sizeof(float), &front));
@@ -314,6 +317,24 @@ ornith_status launch_ring(const LinArgs &x, int n_seq, cudaStream_t s) {
 }
 
 }  // namespace
+
+// Frees the front-end buffer kept for `s` on the current device (all streams of the device when
+// all is set), after the work queued on it has finished.
+ornith_status release_linear_decode_buffers(cudaStream_t s, bool all) {
+    int dev = 0;
+    ORN_TRY(orn_check(cudaGetDevice(&dev), "cudaGetDevice"));
+    std::lock_guard<std::mutex> lock(g_front_mu);
+    ornith_status rc = ORNITH_OK;
+    for (auto it = g_front_bufs.begin(); it != g_front_bufs.end();) {
+        if (it->first.first == dev && (all || it->first.second == s)) {
+            if (it->second.p && cudaFree(it->second.p) != cudaSuccess) { (void)cudaGetLastError(); rc = (ornith_status)ORNITH_ERR_BACKEND; }
+            it = g_front_bufs.erase(it);
+        } else {
+            ++it;
+        }
+    }
+    return rc;
+}
 
 ornith_status launch_linear_decode_ring(const LinArgs &x, int n_seq, int act_dtype, cudaStream_t s) {
     return act_dtype == ORNITH_ACT_BF16 ? launch_ring<__nv_bfloat16>(x, n_seq, s) : launch_ring<float>(x, n_seq, s);

@@ -5,7 +5,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 static thread_local char g_cuda_err[512];
 
@@ -51,9 +54,140 @@ ornith_status orn_require_device() {
     return (ornith_status)ORNITH_ERR_BACKEND;
 }
 
+int orn_device_index() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return d < 0 ? 0 : (d >= ORN_MAX_DEVICES ? ORN_MAX_DEVICES - 1 : d);
+}
+
+// ---- allocation hook ---------------------------------------------------------------
+static std::mutex g_hook_mu;
+static ornith_cuda_alloc_hook g_alloc_hook = nullptr;
+static void *g_alloc_hook_user = nullptr;
+
+ornith_status orn_device_alloc(void **p, size_t bytes, const char *what) {
+    *p = nullptr;
+    ornith_cuda_alloc_hook hook;
+    void *user;
+    {
+        std::lock_guard<std::mutex> lock(g_hook_mu);
+        hook = g_alloc_hook; user = g_alloc_hook_user;
+    }
+    if (hook && hook(bytes, user) != 0) {
+        orn_record_error("%s: allocation of %zu bytes refused by the allocation hook", what, bytes);
+        return ORNITH_ERR_OOM;
+    }
+    return orn_check(cudaMalloc(p, bytes), what);
+}
+
+// ---- status word ---------------------------------------------------------------------
+static unsigned int *g_status_host[ORN_MAX_DEVICES] = {};
+static unsigned int *g_status_dev[ORN_MAX_DEVICES] = {};
+static bool g_status_tried[ORN_MAX_DEVICES] = {};
+
+unsigned int *orn_status_word() {
+    const int d = orn_device_index();
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!g_status_tried[d]) {
+        g_status_tried[d] = true;
+        void *h = nullptr, *dv = nullptr;
+        if (cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess &&
+            cudaHostGetDevicePointer(&dv, h, 0) == cudaSuccess) {
+            memset(h, 0, 64);
+            g_status_host[d] = (unsigned int *)h;
+            g_status_dev[d] = (unsigned int *)dv;
+        } else {
+            (void)cudaGetLastError();
+        }
+    }
+    return g_status_dev[d];
+}
+
+// non-zero status word of the current device -> error text + ORNITH_ERR_BACKEND, word cleared
+static ornith_status take_status_word() {
+    const int d = orn_device_index();
+    volatile unsigned int *w = g_status_host[d];
+    if (!w || !*w) return ORNITH_OK;
+    const unsigned int code = *w;
+    *w = 0;
+    orn_record_error("a kernel gave up a bounded wait (status 0x%x:%s%s%s%s): its outputs are not valid", code,
+                     (code & ORN_WAIT_GQA_PREFILL) ? " full-attention prefill" : "",
+                     (code & ORN_WAIT_DELTA_SCAN) ? " delta-net prefill scan" : "",
+                     (code & ORN_WAIT_DECODE) ? " decode" : "", (code & ORN_WAIT_SELFTEST) ? " self-test" : "");
+    return (ornith_status)ORNITH_ERR_BACKEND;
+}
+
+OrnTensorMapEncodeFn orn_tensor_map_encoder() {
+    static OrnTensorMapEncodeFn fn = nullptr;
+    if (!fn) {
+        cudaDriverEntryPointQueryResult q;
+        void *p = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (OrnTensorMapEncodeFn)p;
+        else
+            (void)cudaGetLastError();
+    }
+    return fn;
+}
+
+// A kernel whose only job is to wait, a few polls long, on an mbarrier nobody arrives on: the wait
+// helper of the tensor-core kernels must come back, report through the status word, and leave the
+// context usable.  Nothing is in flight when it gives up.
+__global__ void k_wait_selftest(unsigned int *status, int polls, int *gave_up) {
+    __shared__ unsigned long long bar;
+    if (threadIdx.x == 0) {
+        tc5::mbar_init(tc5::su32(&bar), 1);
+        tc5::mbar_init_fence();
+        const bool ok = tc5::mbar_wait(tc5::su32(&bar), 0, polls);
+        if (!ok) tc5::report_timeout(status, ORN_WAIT_SELFTEST);
+        *gave_up = ok ? 0 : 1;
+    }
+}
+
+ornith_status release_linear_decode_buffers(cudaStream_t s, bool all);   // linear_decode_ring.cu
+
 extern "C" {
 
 int ornith_backend_cuda_available(void) { return probe_device(); }
+
+void ornith_cuda_set_alloc_hook(ornith_cuda_alloc_hook hook, void *user) {
+    std::lock_guard<std::mutex> lock(g_hook_mu);
+    g_alloc_hook = hook;
+    g_alloc_hook_user = user;
+}
+
+ornith_status ornith_cuda_poll_status(void) {
+    ORN_TRY(orn_require_device());
+    return take_status_word();
+}
+
+ornith_status ornith_cuda_stream_release(void *stream, int all_streams) {
+    ORN_TRY(orn_require_device());
+    if (all_streams) ORN_TRY(orn_check(cudaDeviceSynchronize(), "device sync"));
+    else ORN_TRY(orn_check(cudaStreamSynchronize(as_stream(stream)), "stream sync"));
+    return release_linear_decode_buffers(as_stream(stream), all_streams != 0);
+}
+
+ornith_status ornith_cuda_selftest_wait_timeout(int polls) {
+    ORN_TRY(orn_require_device());
+    if (polls < 1) polls = 1;
+    if (polls > (1 << 16)) polls = 1 << 16;
+    unsigned int *status = orn_status_word();
+    int *flag = nullptr;
+    ORN_TRY(orn_check(cudaMalloc((void **)&flag, sizeof(int)), "selftest flag"));
+    int gave_up = -1;
+    k_wait_selftest<<<1, 32>>>(status, polls, flag);
+    ornith_status st = orn_check_launch("k_wait_selftest");
+    if (st == ORNITH_OK) st = orn_check(cudaMemcpy(&gave_up, flag, sizeof(int), cudaMemcpyDeviceToHost), "selftest read-back");
+    (void)cudaFree(flag);
+    if (st != ORNITH_OK) return st;
+    if (gave_up != 1) { orn_record_error("wait self-test: the wait did not give up (%d)", gave_up); return ORNITH_ERR_FORMAT; }
+    st = take_status_word();                       // must report the give-up
+    if (st == ORNITH_OK && status) { orn_record_error("wait self-test: the status word stayed clear"); return ORNITH_ERR_FORMAT; }
+    return st == ORNITH_OK ? (ornith_status)ORNITH_ERR_BACKEND : st;   // the expected outcome is ORNITH_ERR_BACKEND
+}
 
 const char *ornith_cuda_last_error(void) { return g_cuda_err[0] ? g_cuda_err : "(no detail)"; }
 
@@ -66,7 +200,7 @@ ornith_status ornith_cuda_malloc(void **dev_ptr, size_t bytes) {
     ORN_TRY(orn_require_device());
     *dev_ptr = nullptr;
     if (bytes == 0) bytes = 16;
-    ORN_TRY(orn_check(cudaMalloc(dev_ptr, bytes), "cudaMalloc"));
+    ORN_TRY(orn_device_alloc(dev_ptr, bytes, "cudaMalloc"));
     return orn_check(cudaMemset(*dev_ptr, 0, bytes), "cudaMemset");
 }
 
@@ -94,7 +228,8 @@ ornith_status ornith_cuda_d2h(void *host_dst, const void *dev_src, size_t bytes)
 
 ornith_status ornith_cuda_sync(void *stream) {
     ORN_TRY(orn_require_device());
-    return orn_check(cudaStreamSynchronize(as_stream(stream)), "stream sync");
+    ORN_TRY(orn_check(cudaStreamSynchronize(as_stream(stream)), "stream sync"));
+    return take_status_word();
 }
 
 // theta^(-2i/rot) with the host libm, the same expression the engine evaluates
