@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(256, 2) k_delta_prep64(LinArgs a, const float 
 // =============================================================================
 // sequential part: one CTA per (value head, sequence), 18 warps
 // =============================================================================
-constexpr int W_TMA = 16, W_MMA = 17, W_PU = 18, NTHREADS = 19 * 32;
+constexpr int W_TMA = 24, W_MMA = 25, W_PU = 26, NTHREADS = 27 * 32;
 constexpr int TM_S = 0, TM_KQ = 128, TM_TU = 384, TM_U = 448, TM_COLS = 512;   // tensor-memory columns
 // Shared memory.  The K | Q tile is needed first in a chunk and is double-buffered; the operands of the
 // later products (second K copy for the state update, A, P) have one buffer each, refilled as soon as
@@ -271,7 +271,7 @@ constexpr int SCAN_SMEM = SM_AUX2 + (int)AUX_BYTES + 1024;   // + alignment slac
 constexpr uint32_t TX_KQ = 65536 + AUX_BYTES, TX_KM = 32768, TX_A = 12288, TX_P = 12288 + AUX_BYTES, TX_V = 32768;
 
 struct ScanBars {
-    unsigned long long full_kq[2], empty_kq[2], kq_done[2], pu_done[2], o_read[2], red[2][2];
+    unsigned long long full_kq[2], empty_kq[2], kq_done[2], pu_done[2], o_read[2], red[2][4];
     unsigned long long full_km, empty_km, full_a, empty_a, full_p, empty_p, full_v, empty_v, t_ready, u_done, u_ready, s_final;
 };
 
@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
                                                                const __grid_constant__ CUtensorMap map_v, ScanArgs a) {
     extern __shared__ unsigned char smraw[];
     __shared__ ScanBars bars;
-    __shared__ float red[2][2][4][32];                    // [chunk parity][token half][lane quarter][token]
+    __shared__ float red[2][4][4][16];                    // [chunk parity][group of 16 tokens][lane quarter][token]
     __shared__ uint32_t tmem_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hv = blockIdx.x, b = blockIdx.y, N = a.n_chunks;
@@ -343,12 +343,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
         for (int s = 0; s < 2; s++) {
             mbar_init(su32(&bars.full_kq[s]), 1); mbar_init(su32(&bars.empty_kq[s]), 9);
             mbar_init(su32(&bars.kq_done[s]), 1); mbar_init(su32(&bars.pu_done[s]), 1);
-            mbar_init(su32(&bars.o_read[s]), 256);
-            mbar_init(su32(&bars.red[s][0]), 128); mbar_init(su32(&bars.red[s][1]), 128);
+            mbar_init(su32(&bars.o_read[s]), 512);
+            for (int g = 0; g < 4; g++) mbar_init(su32(&bars.red[s][g]), 128);
         }
         mbar_init(su32(&bars.full_km), 1); mbar_init(su32(&bars.empty_km), 1);
         mbar_init(su32(&bars.full_a), 1); mbar_init(su32(&bars.empty_a), 1);
-        mbar_init(su32(&bars.full_p), 1); mbar_init(su32(&bars.empty_p), 9);
+        mbar_init(su32(&bars.full_p), 1); mbar_init(su32(&bars.empty_p), 17);
         mbar_init(su32(&bars.full_v), 1); mbar_init(su32(&bars.empty_v), 8);
         mbar_init(su32(&bars.t_ready), 256); mbar_init(su32(&bars.u_done), 1);
         mbar_init(su32(&bars.u_ready), 256); mbar_init(su32(&bars.s_final), 1);
@@ -522,13 +522,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
                 for (int i = 0; i < 32; i++) dbg[row * 64 + 32 * half + i] = x[i];
             }
 #pragma unroll
-            for (int i = 0; i < 8; i++) {                                // T = beta v - (beta p rk) KS
-                const float4 be4 = *reinterpret_cast<const float4 *>(aux + 32 * half + 4 * i);
-                const float4 bp4 = *reinterpret_cast<const float4 *>(aux + C + 32 * half + 4 * i);
-                x[4 * i] = tf32q(fmaf(-bp4.x, x[4 * i], be4.x * Vs[(4 * i) * 128]));
-                x[4 * i + 1] = tf32q(fmaf(-bp4.y, x[4 * i + 1], be4.y * Vs[(4 * i + 1) * 128]));
-                x[4 * i + 2] = tf32q(fmaf(-bp4.z, x[4 * i + 2], be4.z * Vs[(4 * i + 2) * 128]));
-                x[4 * i + 3] = tf32q(fmaf(-bp4.w, x[4 * i + 3], be4.w * Vs[(4 * i + 3) * 128]));
+            for (int hh = 0; hh < 4; hh++) {                             // T = beta v - (beta p rk) KS, 8 tokens at a time
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = Vs[(8 * hh + i) * 128];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const float4 be4 = *reinterpret_cast<const float4 *>(aux + 32 * half + 8 * hh + 4 * i);
+                    const float4 bp4 = *reinterpret_cast<const float4 *>(aux + C + 32 * half + 8 * hh + 4 * i);
+                    const int k = 8 * hh + 4 * i;
+                    x[k] = tf32q(fmaf(-bp4.x, x[k], be4.x * v[4 * i]));
+                    x[k + 1] = tf32q(fmaf(-bp4.y, x[k + 1], be4.y * v[4 * i + 1]));
+                    x[k + 2] = tf32q(fmaf(-bp4.z, x[k + 2], be4.z * v[4 * i + 2]));
+                    x[k + 3] = tf32q(fmaf(-bp4.w, x[k + 3], be4.w * v[4 * i + 3]));
+                }
             }
             if (tid == 0) TR(4, n, 1);
             tmem_st32(lane_t + TM_TU + 32 * half, x);                    // T^T
@@ -564,15 +571,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
                 for (int i = 0; i < 32; i++) dbg[128 * 64 + row * 64 + 32 * half + i] = x[i];
             }
 #pragma unroll
-            for (int hh = 0; hh < 2; hh++) {                             // (w rk U)^T over T^T, 16 tokens at a time
-                float f[16];
+            for (int hh = 0; hh < 4; hh++) {                             // (w rk U)^T over T^T, 8 tokens at a time
+                float f[8];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float4 w4 = *reinterpret_cast<const float4 *>(aux + 2 * C + 32 * half + 16 * hh + 4 * i);   // w rk
-                    f[4 * i] = tf32q(w4.x * x[16 * hh + 4 * i]); f[4 * i + 1] = tf32q(w4.y * x[16 * hh + 4 * i + 1]);
-                    f[4 * i + 2] = tf32q(w4.z * x[16 * hh + 4 * i + 2]); f[4 * i + 3] = tf32q(w4.w * x[16 * hh + 4 * i + 3]);
+                for (int i = 0; i < 2; i++) {
+                    const float4 w4 = *reinterpret_cast<const float4 *>(aux + 2 * C + 32 * half + 8 * hh + 4 * i);   // w rk
+                    f[4 * i] = tf32q(w4.x * x[8 * hh + 4 * i]); f[4 * i + 1] = tf32q(w4.y * x[8 * hh + 4 * i + 1]);
+                    f[4 * i + 2] = tf32q(w4.z * x[8 * hh + 4 * i + 2]); f[4 * i + 3] = tf32q(w4.w * x[8 * hh + 4 * i + 3]);
                 }
-                tmem_st16(lane_t + TM_TU + 32 * half + 16 * hh, f);
+                tmem_st8(lane_t + TM_TU + 32 * half + 8 * hh, f);
             }
 #pragma unroll
             for (int i = 0; i < 32; i++) x[i] = tf32q(x[i]);
@@ -598,44 +605,52 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             for (int i = 0; i < 8; i++)
                 dst[i] = ok ? make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]) : make_float4(NAN, NAN, NAN, NAN);
         }
-    } else if (warp < 16) {
+    } else if (warp < 24) {
         // ================= output epilogue =================
+        // 16 warps: lane quarter qtr, group grp of 16 tokens
+        const int grp = (warp - 8) >> 2;
         const float nwr = a.norm_w[row];
         const size_t zoff = (size_t)b * a.T * vd + (size_t)hv * 128 + row;
         const ACT *zp = (const ACT *)a.z;
         ACT *op = (ACT *)a.out;
-        const float *aux = reinterpret_cast<const float *>(gbase + SM_AUX2);
-        // z of this thread's 32 outputs of a chunk is requested one chunk ahead and stays in these registers until
-        // it is used: the loads (DRAM latency, 2 bytes per lane) would otherwise be exposed twice per chunk.  To make
-        // room, the output tiles are read from tensor memory twice (once for the sum of squares, once for the store)
-        // instead of being kept.
-        uint32_t zr[32];
+        const float *aux = reinterpret_cast<const float *>(gbase + SM_AUX2) + 3 * C + 16 * grp;       // p rq of this group's tokens
+        const uint32_t t_qs = lane_t + TM_KQ + 64 + 16 * grp, t_pu = lane_t + TM_KQ + 16 * grp;
+        // z of this thread's 16 outputs of a chunk is requested one chunk ahead and stays in these registers until it
+        // is used: the loads (DRAM latency, 2 bytes per lane) would otherwise be exposed in every chunk.  The output
+        // tiles are read from tensor memory twice (for the sum of squares, then for the store) instead of being kept.
+        uint32_t zr[16];
 #pragma unroll
-        for (int i = 0; i < 32; i++) zr[i] = (32 * half + i < a.T) ? ld_raw(zp, zoff + (size_t)(32 * half + i) * vd) : 0u;
+        for (int i = 0; i < 16; i++) zr[i] = (16 * grp + i < a.T) ? ld_raw(zp, zoff + (size_t)(16 * grp + i) * vd) : 0u;
         int n = 0;
         for (; n < N; n++) {
-            const int s = n & 1, tok = n * C + 32 * half;
+            const int s = n & 1, tok = n * C + 16 * grp;
             if (tid == 256) TR(2, n, 0);
+            // the gate factors of this chunk, while the tensor core still works on it: norm weight x SiLU(z), in place
+#pragma unroll
+            for (int h8 = 0; h8 < 2; h8++) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) zr[8 * h8 + i] = __float_as_uint(nwr * silu_fast(cvt_raw(zp, zr[8 * h8 + i])));
+                asm volatile("" ::: "memory");                           // keeps the two batches apart (registers)
+            }
             ok = mbar_wait(su32(&bars.full_p), (uint32_t)n & 1u) && mbar_wait(su32(&bars.pu_done[s]), (uint32_t)(n >> 1) & 1u);
             if (!ok) break;
             if (tid == 256) TR(2, n, 1);
             fence_after();
-#pragma unroll
-            for (int ps = 0; ps < 2; ps++) {                             // 16 tokens at a time
+            {
                 float q[16], x[16];
-                tmem_ld16(lane_t + TM_KQ + 128 * s + 64 + 32 * half + 16 * ps, q);     // QS^T
-                tmem_ld16(lane_t + TM_KQ + 128 * s + 32 * half + 16 * ps, x);          // (P U)^T
+                tmem_ld16(t_qs + 128 * s, q);                            // QS^T
+                tmem_ld16(t_pu + 128 * s, x);                            // (P U)^T
                 tmem_wait_ld();
                 if (dbg && n == 0) {
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
-                        dbg[2 * 128 * 64 + row * 64 + 32 * half + 16 * ps + i] = q[i];
-                        dbg[3 * 128 * 64 + row * 64 + 32 * half + 16 * ps + i] = x[i];
+                        dbg[2 * 128 * 64 + row * 64 + 16 * grp + i] = q[i];
+                        dbg[3 * 128 * 64 + row * 64 + 16 * grp + i] = x[i];
                     }
                 }
 #pragma unroll
                 for (int i = 0; i < 4; i++) {                            // O = p rq QS + P U (the output scale comes later)
-                    const float4 p4 = *reinterpret_cast<const float4 *>(aux + 3 * C + 32 * half + 16 * ps + 4 * i);
+                    const float4 p4 = *reinterpret_cast<const float4 *>(aux + 4 * i);
                     x[4 * i] = fmaf(p4.x, q[4 * i], x[4 * i]); x[4 * i + 1] = fmaf(p4.y, q[4 * i + 1], x[4 * i + 1]);
                     x[4 * i + 2] = fmaf(p4.z, q[4 * i + 2], x[4 * i + 2]); x[4 * i + 3] = fmaf(p4.w, q[4 * i + 3], x[4 * i + 3]);
                 }
@@ -654,30 +669,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
                         x[k] = keep + __shfl_xor_sync(0xffffffffu, send, off);
                     }
                 }
-                if (lane < 16) red[s][half][qtr][16 * ps + lane] = x[0];
+                if (lane < 16) red[s][grp][qtr][lane] = x[0];
             }
             if (tid == 256) TR(2, n, 2);
-            mbar_arrive(su32(&bars.red[s][half]));
+            mbar_arrive(su32(&bars.red[s][grp]));
             if (tid == 256) TR(2, n, 3);
-            ok = mbar_wait(su32(&bars.red[s][half]), (uint32_t)(n >> 1) & 1u);
+            ok = mbar_wait(su32(&bars.red[s][grp]), (uint32_t)(n >> 1) & 1u);
             if (!ok) break;
             if (tid == 256) TR(2, n, 4);
+            const int tl = lane & 15;
             const float ss = a.out_scale * a.out_scale *
-                             ((red[s][half][0][lane] + red[s][half][1][lane]) + (red[s][half][2][lane] + red[s][half][3][lane]));
-            const float inv = rsqrtf(ss * (1.0f / 128.0f) + a.eps) * a.out_scale;
+                             ((red[s][grp][0][tl] + red[s][grp][1][tl]) + (red[s][grp][2][tl] + red[s][grp][3][tl]));
+            const float inv = rsqrtf(ss * (1.0f / 128.0f) + a.eps) * a.out_scale;   // of token tl
 #pragma unroll
-            for (int ps = 0; ps < 4; ps++) {                             // 8 tokens at a time: 96 registers per thread must do
+            for (int ps = 0; ps < 2; ps++) {                             // 8 tokens at a time
                 float q[8], x[8];
-                tmem_ld8(lane_t + TM_KQ + 128 * s + 64 + 32 * half + 8 * ps, q);
-                tmem_ld8(lane_t + TM_KQ + 128 * s + 32 * half + 8 * ps, x);
+                tmem_ld8(t_qs + 128 * s + 8 * ps, q);
+                tmem_ld8(t_pu + 128 * s + 8 * ps, x);
                 tmem_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
-                    const float4 p4 = *reinterpret_cast<const float4 *>(aux + 3 * C + 32 * half + 8 * ps + 4 * i);
+                    const float4 p4 = *reinterpret_cast<const float4 *>(aux + 8 * ps + 4 * i);
                     x[4 * i] = fmaf(p4.x, q[4 * i], x[4 * i]); x[4 * i + 1] = fmaf(p4.y, q[4 * i + 1], x[4 * i + 1]);
                     x[4 * i + 2] = fmaf(p4.z, q[4 * i + 2], x[4 * i + 2]); x[4 * i + 3] = fmaf(p4.w, q[4 * i + 3], x[4 * i + 3]);
                 }
-                if (ps == 3) {                                           // both tiles and the factors have been read for the last time
+                if (ps == 1) {                                           // both tiles and the factors have been read for the last time
                     fence_before();
                     mbar_arrive(su32(&bars.o_read[s]));
                     __syncwarp();
@@ -687,18 +703,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
                 // would end a basic block per token and keep the independent chains (shuffle, exp, reciprocal) from
                 // overlapping.
                 const size_t o0 = zoff + (size_t)(tok + 8 * ps) * vd;
-                if (tok + 8 * ps + 8 <= a.T) {
 #pragma unroll
-                    for (int i = 0; i < 8; i++)
-                        x[i] = x[i] * __shfl_sync(0xffffffffu, inv, 8 * ps + i) * nwr * silu_fast(cvt_raw(zp, zr[8 * ps + i]));
+                for (int i = 0; i < 8; i++) x[i] *= __shfl_sync(0xffffffffu, inv, 8 * ps + i) * __uint_as_float(zr[8 * ps + i]);
+                if (tok + 8 * ps + 8 <= a.T) {
 #pragma unroll
                     for (int i = 0; i < 8; i++) act_st(op, o0 + (size_t)i * vd, x[i]);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float iv = __shfl_sync(0xffffffffu, inv, 8 * ps + i);
-                        if (tok + 8 * ps + i < a.T) act_st(op, o0 + (size_t)i * vd, x[i] * iv * nwr * silu_fast(cvt_raw(zp, zr[8 * ps + i])));
-                    }
+                    for (int i = 0; i < 8; i++)
+                        if (tok + 8 * ps + i < a.T) act_st(op, o0 + (size_t)i * vd, x[i]);
                 }
                 if (tok + C + 8 * ps + 8 <= a.T) {                       // the same tokens of the next chunk
 #pragma unroll
@@ -712,8 +725,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             if (tid == 256) TR(2, n, 5);
         }
         for (; n < N; n++) {                                             // a wait gave up: poison what was not written
-            const int tok = n * C + 32 * half;
-            for (int i = 0; i < 32; i++)
+            const int tok = n * C + 16 * grp;
+            for (int i = 0; i < 16; i++)
                 if (tok + i < a.T) act_st(op, zoff + (size_t)(tok + i) * vd, NAN);
         }
     }
