@@ -1,11 +1,20 @@
 #!/usr/bin/env python
-"""Attention-stack decode benchmark (BASELINE.json configs[2]).
+"""Attention-stack decode benchmark.
 
-One step = one token for each of 64 concurrent sequences through the 40-layer
-35B-shaped attention stack (30 gated delta-net + 10 GQA layers, 3:1), Q8_0 KV
-cache, fp32 recurrent state, bf16 activations, contexts uniform in [1k, 32k].
-Multi-GPU runs shard by sequence: every rank owns 64 sequences of its own
-(weak scaling, nothing is exchanged inside the stack).
+Headline workload: batched decode through a 40-layer 35B-shaped attention stack (30 gated
+delta-net + 10 GQA layers, 3:1).  One step = one token for each of 64 concurrent sequences per
+GPU, Q8_0 KV cache, fp32 recurrent state, bf16 activations, contexts uniform in [1k, 32k].
+Multi-GPU runs shard by sequence: N x 64 sequences are drawn once and dealt to the ranks so that
+the summed contexts balance (weak scaling, nothing is exchanged inside the stack).
+
+Further legs on the same JSON line (each an object of its own):
+  prefill     long prefill at the 397B shape: one delta-net and one GQA layer over a 32768-token prompt,
+              head-sharded over the ranks, head outputs all-gathered slab by slab while the next slab computes
+  strong      the 64 sequences of the headline workload split over the N GPUs (N > 1)
+  decode_397b 8-GPU-style head-sharded decode at the 397B shape: 256 sequences at an 8192-token context,
+              per-layer times with and without the all-gather (N > 1)
+  single_layer  one delta-net layer (prefill 512 + 128 decode steps) and one GQA layer (prefill 4096 + 256
+              decode steps, f32 and Q8_0 caches), f32 activations, batch 1, with the CPU reference beside them (N = 1)
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     torchrun ... bench.py --gpus N ...
@@ -59,14 +68,72 @@ def measured_tensor_peak():
     return 1590.0, 1400.0, "fallback"
 
 
-def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b"):
-    """BASELINE.json configs[3]: one 397B-shaped delta-net layer and one GQA layer over a 32768-token
-    prompt, batch 1, bf16 activations, head-sharded over the ranks (64/G value heads; 32/G query heads
-    with the KV heads they read), head outputs all-gathered.  Returns per-layer times (max over ranks)
-    and the figures derived from them; the stack has 45 delta-net and 15 GQA layers.  shape="35b"
-    (32 value heads, 16 query heads) and a smaller T give the small cases the profiles are taken on."""
+def _timed(fn, dev, world, reps):
+    """Average device time of fn() in ms over `reps` calls after one warm-up call, max over ranks."""
     import torch
     import torch.distributed as dist
+    fn()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+class SlabGather:
+    """All-gather of head outputs that overlaps the layer: the prompt is processed in slabs of tokens, and the
+    gather of slab k (NCCL, on its own stream) runs while slab k+1 is computed.  Only the last slab's gather is
+    exposed.  Nothing but plain NCCL touches another GPU's memory."""
+
+    def __init__(self, dev, world):
+        import torch
+        self.dev, self.world = dev, world
+        self.comm = torch.cuda.Stream(dev) if world > 1 else None
+        self.bufs = {}
+
+    def run(self, layer_fn, T, slab, width, dtype):
+        """layer_fn(t0, n) -> [1, n, width] output of tokens t0..t0+n; returns the gathered [world][1][T][width]."""
+        import torch
+        import torch.distributed as dist
+        if self.world == 1:
+            for t0 in range(0, T, slab):
+                layer_fn(t0, min(slab, T - t0))
+            return None
+        key = (T, width, dtype)
+        if key not in self.bufs:
+            self.bufs[key] = torch.empty((self.world, 1, T, width), dtype=dtype, device=self.dev)
+        out = self.bufs[key]
+        main = torch.cuda.current_stream(self.dev)
+        for t0 in range(0, T, slab):
+            n = min(slab, T - t0)
+            o = layer_fn(t0, n)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(self.comm):
+                self.comm.wait_event(ev)
+                piece = torch.empty((self.world, 1, n, width), dtype=dtype, device=self.dev)
+                dist.all_gather_into_tensor(piece, o.contiguous())
+                out[:, :, t0:t0 + n].copy_(piece)
+                o.record_stream(self.comm)
+        main.wait_stream(self.comm)
+        return out
+
+
+def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b", slab=8192):
+    """Long prefill: one 397B-shaped delta-net layer and one GQA layer over a T-token prompt, batch 1, bf16
+    activations, head-sharded over the ranks (64/G value heads; 32/G query heads with the KV heads they read),
+    head outputs all-gathered.  Returns per-layer times (max over ranks) and the figures derived from them;
+    the stack has 45 delta-net and 15 GQA layers.  shape="35b" (32 value heads, 16 query heads) and a smaller T
+    give the small cases the profiles are taken on."""
+    import torch
     from ornithology_b200 import device as D
     from ornithology_b200 import stack as S
 
@@ -84,47 +151,257 @@ def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b"):
     full = D.FullLayer(nh, nkv, 256, fw["q_norm_w"], fw["k_norm_w"], device=dev)
     kv = D.KvBatch(D.KV_Q8_0, nkv, 256, [T], device=dev)
     full_in = [torch.randn(1, T, n, generator=g).to(torch.bfloat16).to(dev) for n in (nh * 512, nkv * 256, nkv * 256)]
+    gather = SlabGather(dev, world)
 
-    def timed(fn):
-        fn()
-        torch.cuda.synchronize(dev)
-        if world > 1:
-            dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize(dev)
-        t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
+    def lin_whole():
+        pos.zero_()
+        return D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64)
 
-    def gather(o):
-        if world == 1:
-            return o
-        full_o = torch.empty((world,) + tuple(o.shape), dtype=o.dtype, device=dev)
-        dist.all_gather_into_tensor(full_o, o)
-        return full_o
+    def full_whole():
+        pos.zero_()
+        return D.full_attn_prefill(full, kv, pos, *full_in, T)
 
-    ms_lin = timed(lambda: gather(D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64)))
-    ms_full = timed(lambda: gather(D.full_attn_prefill(full, kv, pos, *full_in, T)))
-    # without the all-gather (the same call when there is one rank)
-    ms_lin_k = ms_lin if world == 1 else timed(lambda: D.linear_attn_prefill(lin, lst, pos, *lin_in, T, chunk=64))
-    ms_full_k = ms_full if world == 1 else timed(lambda: D.full_attn_prefill(full, kv, pos, *full_in, T))
-    # algorithmic work of the whole layer (all ranks): causal QK^T + PV; chunked scan at C = 32
+    def lin_slab(t0, n):
+        pos.fill_(t0)                                   # conv ring phase = index of the first token of the slab
+        return D.linear_attn_prefill(lin, lst, pos, *[x[:, t0:t0 + n] for x in lin_in], n, chunk=64)
+
+    def full_slab(t0, n):
+        pos.fill_(t0)                                   # rows already in the cache
+        return D.full_attn_prefill(full, kv, pos, *[x[:, t0:t0 + n] for x in full_in], n, max_len=T)
+
+    # one rank: the layer in one call; several ranks: slabs of tokens, gather of slab k under the compute of slab k+1
+    if world == 1:
+        ms_lin = ms_lin_k = _timed(lin_whole, dev, world, reps)
+        ms_full = ms_full_k = _timed(full_whole, dev, world, reps)
+    else:
+        ms_lin = _timed(lambda: gather.run(lin_slab, T, slab, lin.vd, torch.bfloat16), dev, world, reps)
+        ms_full = _timed(lambda: gather.run(full_slab, T, slab, nh * 256, torch.bfloat16), dev, world, reps)
+        ms_lin_k = _timed(lin_whole, dev, world, reps)
+        ms_full_k = _timed(full_whole, dev, world, reps)
+    # algorithmic work of the whole layer (all ranks): causal QK^T + PV; chunked scan of 64-token chunks
     fl_full = 4.0 * 256 * NH * T * (T + 1) / 2
-    fl_lin = float(NV) * (T / 32) * (6 * 32 * 128 * 128 + 2 * 32 * 32 * 256)
+    fl_lin = float(NV) * (T / 64) * (6 * 64 * 128 * 128 + 2 * 64 * 64 * 256)
     burst, sustained, src = measured_tensor_peak()
     stack_ms = 45 * ms_lin + 15 * ms_full
-    return {"workload": "configs[3]: %d-token prompt, %s-shaped layers, batch 1, bf16, head-sharded x%d" % (T, shape.upper(), world),
+    tf_full = fl_full / (ms_full_k * 1e-3) / 1e12
+    tf_lin = fl_lin / (ms_lin_k * 1e-3) / 1e12
+    return {"workload": "%d-token prompt, %s-shaped layers, batch 1, bf16, head-sharded x%d" % (T, shape.upper(), world),
             "tokens": T, "delta_net_ms_per_layer": ms_lin, "gqa_ms_per_layer": ms_full,
             "delta_net_ms_no_gather": ms_lin_k, "gqa_ms_no_gather": ms_full_k,
+            "gather": "none" if world == 1 else f"NCCL all-gather per {slab}-token slab on a second stream, under the next slab's compute",
             "stack_layers": "45 delta-net + 15 GQA", "stack_ms": stack_ms, "stack_tok_per_s": T / (stack_ms * 1e-3),
-            "gqa_tflops": fl_full / (ms_full_k * 1e-3) / 1e12 , "delta_net_tflops": fl_lin / (ms_lin_k * 1e-3) / 1e12,
+            "gqa_tflops": tf_full, "delta_net_tflops": tf_lin,
+            "roofline": {"bound": "tensor", "kernel": "k_gqa_prefill_tc", "achieved": tf_full, "peak": burst * world,
+                         "unit": "TFLOP/s", "frac": tf_full / (burst * world), "peak_source": f"of {src} (bf16 burst)",
+                         "flop_per_layer": fl_full, "ms": ms_full_k},
+            "roofline_delta_net": {"bound": "tensor", "kernel": "k_delta_scan_tc5 (+ conv and chunk preparation)",
+                                   "achieved": tf_lin, "peak": burst * world, "unit": "TFLOP/s",
+                                   "frac": tf_lin / (burst * world), "flop_per_layer": fl_lin, "ms": ms_lin_k,
+                                   "note": "tf32 products run at half the bf16 rate; a sequential scan: chunks x chain latency bound it, not the pipe"},
             "tensor_peak_tflops": burst * world, "tensor_peak_sustained_tflops": sustained * world,
-            "gqa_frac_of_tensor_peak": fl_full / (ms_full_k * 1e-3) / 1e12 / (burst * world), "peak_source": f"of {src}"}
+            "gqa_frac_of_tensor_peak": tf_full / (burst * world), "peak_source": f"of {src}"}
+
+
+def run_decode_397b(dev, rank, world, n_seq=256, ctx=8192, steps=10, warmup=3):
+    """Head-sharded batched decode at the 397B shape: n_seq sequences at a ctx-token context, Q8_0 KV, fp32 state,
+    bf16 activations; a rank owns 64/G value heads of the delta-net layers (with the key heads they pair with) and
+    32/G query heads of the full layers with the KV head they read (replicated beyond 2 ranks); every layer's head
+    outputs are all-gathered.  One delta-net layer and one GQA layer are timed (all sequences, `steps` consecutive
+    steps each); the stack has 45 + 15 of them."""
+    import torch
+    import torch.distributed as dist
+    from ornithology_b200 import device as D
+    from ornithology_b200 import stack as S
+    a = S.ARCHS["397b"]
+    sh = S.head_shard(a, rank, world)
+    nv, nk, nh, nkv = len(sh.v_heads), len(sh.k_heads), len(sh.q_heads), len(sh.kv_heads)
+    w, _ = S.shard_linear_weights(a, S.linear_weights(a, 4, 0), sh)
+    lin = D.LinearLayer(nk, nv, 128, 128, w["conv_w"], w["a_coef"], w["dt_bias"], w["norm_w"], device=dev)
+    fw = S.full_weights(a, 4, 3)
+    full = D.FullLayer(nh, nkv, 256, fw["q_norm_w"], fw["k_norm_w"], device=dev)
+    total = warmup + steps + 2
+    kv = D.KvBatch(D.KV_Q8_0, nkv, 256, [ctx + 2 * total] * n_seq, device=dev)     # room for one pass of steps and the warm-up
+    st = D.LinearState(lin, n_seq, device=dev)
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    bf = torch.bfloat16
+    # state: a short seeded prompt through the prefill; cache: seeded N(0,1) rows through the append kernel
+    z0 = torch.zeros(n_seq, dtype=torch.int32, device=dev)
+    pre = [torch.randn(n_seq, 64, n, generator=g, device=dev).to(bf) for n in (lin.cc, nv, nv, lin.vd)]
+    D.linear_attn_prefill(lin, st, z0, *pre, 64, chunk=64)
+    del pre
+    done = torch.zeros(n_seq, dtype=torch.int32, device=dev)
+    for t0 in range(0, ctx, 1024):
+        n = min(1024, ctx - t0)
+        k = torch.randn(n_seq, n, nkv * 256, generator=g, device=dev).to(bf)
+        v = torch.randn(n_seq, n, nkv * 256, generator=g, device=dev).to(bf)
+        D.kv_append(full, kv, done, k, v, T=n)
+        done += n
+    pos = torch.full((n_seq,), ctx, dtype=torch.int32, device=dev)
+    lin_in = [torch.randn(n_seq, n, generator=g, device=dev).to(bf) for n in (lin.cc, nv, nv, lin.vd)]
+    full_in = [torch.randn(n_seq, n, generator=g, device=dev).to(bf) for n in (nh * 512, nkv * 256, nkv * 256)]
+    lin_out = torch.empty(n_seq, lin.vd, dtype=bf, device=dev)
+    full_out = torch.empty(n_seq, nh * 256, dtype=bf, device=dev)
+    g_lin = torch.empty(world, n_seq, lin.vd, dtype=bf, device=dev)
+    g_full = torch.empty(world, n_seq, nh * 256, dtype=bf, device=dev)
+    max_len = ctx + 2 * total
+
+    def lin_step(gather):
+        D.linear_attn_step(lin, st, pos, *lin_in, out=lin_out)
+        if gather and world > 1:
+            dist.all_gather_into_tensor(g_lin, lin_out)
+
+    def full_step(gather):
+        D.full_attn_step(full, kv, pos, *full_in, out=full_out, max_len=max_len)
+        D.advance(pos)
+        if gather and world > 1:
+            dist.all_gather_into_tensor(g_full, full_out)
+
+    def loop(fn, gather):
+        def run():
+            pos.fill_(ctx)                              # every pass runs the same `steps` positions (appended rows are overwritten)
+            for _ in range(steps):
+                fn(gather)
+        return _timed(run, dev, world, 1) / steps
+
+    for _ in range(warmup):
+        lin_step(True); full_step(True)
+    pos.fill_(ctx)
+    ms_lin, ms_full = loop(lin_step, True), loop(full_step, True)
+    ms_lin_k, ms_full_k = loop(lin_step, False), loop(full_step, False)
+    cc = lin.cc
+    b_lin = n_seq * (2 * nv * 128 * 128 * 4 + 4 * cc * 4 + cc * 2 + 2 * nv * 2 + 2 * lin.vd * 2)
+    b_full = n_seq * (2 * nkv * 272 * (ctx + total) + 2 * nkv * 272 + nh * 256 * 3 * 2 + 2 * nkv * 256 * 2)
+    peak, src = measured_peaks()
+    stack_ms = 45 * ms_lin + 15 * ms_full
+    return {"workload": "397B-shaped head-sharded decode x%d: %d sequences at a %d-token context, Q8_0 KV, fp32 state, bf16" % (world, n_seq, ctx),
+            "per_rank_heads": {"value": nv, "key": nk, "query": nh, "kv": nkv},
+            "steps_timed": steps, "delta_net_ms_per_layer": ms_lin, "gqa_ms_per_layer": ms_full,
+            "delta_net_ms_no_gather": ms_lin_k, "gqa_ms_no_gather": ms_full_k,
+            "gather_bytes_per_layer": {"delta_net": n_seq * lin.vd * 2 * world, "gqa": n_seq * nh * 256 * 2 * world},
+            "stack_layers": "45 delta-net + 15 GQA", "stack_ms_per_step": stack_ms, "stack_tok_per_s": n_seq / (stack_ms * 1e-3),
+            "delta_net": {"bytes_per_rank": b_lin, "gbs": b_lin / (ms_lin_k * 1e-3) / 1e9, "frac": b_lin / (ms_lin_k * 1e-3) / 1e9 / peak},
+            "gqa": {"bytes_per_rank": b_full, "gbs": b_full / (ms_full_k * 1e-3) / 1e9, "frac": b_full / (ms_full_k * 1e-3) / 1e9 / peak},
+            "peak_gbs": peak, "peak_source": f"of {src}",
+            "note": "KV heads are replicated beyond 2 ranks, so the GQA bytes per rank stop shrinking at 2 ranks"}
+
+
+def run_single_layer(dev, cpu=True):
+    """The two single-layer workloads, batch 1, f32 activations: a 35B-shaped delta-net layer (prefill 512 tokens,
+    then 128 decode steps, seed 0) and a 35B-shaped GQA layer (prefill 4096 tokens, then 256 decode steps, with an f32
+    and with a Q8_0 cache, seed 1).  Batch-1 decode is launch-bound on a GPU: one or two kernels of a few
+    microseconds per step.  The CPU reference is timed beside them on bounded samples (see `cpu`)."""
+    import torch
+    from ornithology_b200 import device as D
+    from ornithology_b200 import stack as S
+    a = S.ARCHS["35b"]
+    res = {}
+    f32 = torch.float32
+    # ---- delta-net layer
+    w = S.linear_weights(a, 0, 0)
+    lin = D.LinearLayer(a["nk"], a["nv"], 128, 128, w["conv_w"], w["a_coef"], w["dt_bias"], w["norm_w"], device=dev)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    T, steps = 512, 128
+    ins = [torch.randn(1, T + steps, n, generator=g).to(dev) for n in (lin.cc, a["nv"], a["nv"], lin.vd)]
+    st = D.LinearState(lin, 1)
+    pos = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def lin_prefill():
+        pos.zero_()
+        return D.linear_attn_prefill(lin, st, pos, *[x[:, :T] for x in ins], T, chunk=64)
+
+    def lin_decode():
+        pos.fill_(T)
+        for t in range(T, T + steps):
+            D.linear_attn_step(lin, st, pos, *[x[:, t] for x in ins])
+            D.advance(pos)
+
+    res["delta_net"] = {"prefill_tokens": T, "decode_steps": steps, "prefill_ms": _timed(lin_prefill, dev, 1, 3),
+                        "decode_ms_per_step": _timed(lin_decode, dev, 1, 2) / steps}
+    res["delta_net"]["prefill_tok_per_s"] = T / (res["delta_net"]["prefill_ms"] * 1e-3)
+    res["delta_net"]["decode_tok_per_s"] = 1e3 / res["delta_net"]["decode_ms_per_step"]
+    # ---- GQA layer, both caches
+    fw = S.full_weights(a, 1, 3)
+    full = D.FullLayer(a["nh"], a["nkv"], 256, fw["q_norm_w"], fw["k_norm_w"], device=dev)
+    g = torch.Generator(device="cpu").manual_seed(1)
+    T, steps = 4096, 256
+    fin = [torch.randn(1, T + steps, n, generator=g).to(dev) for n in (a["nh"] * 512, a["nkv"] * 256, a["nkv"] * 256)]
+    for name, mode in (("gqa_f32_kv", D.KV_F32), ("gqa_q8_0_kv", D.KV_Q8_0)):
+        kv = D.KvBatch(mode, a["nkv"], 256, [T + steps], device=dev)
+        kv_len = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        def full_prefill():
+            kv_len.zero_()
+            return D.full_attn_prefill(full, kv, kv_len, *[x[:, :T] for x in fin], T)
+
+        def full_decode():
+            kv_len.fill_(T)
+            for t in range(T, T + steps):
+                D.full_attn_step(full, kv, kv_len, *[x[:, t] for x in fin], max_len=T + steps)
+                D.advance(kv_len)
+
+        r = {"prefill_tokens": T, "decode_steps": steps, "prefill_ms": _timed(full_prefill, dev, 1, 3),
+             "decode_ms_per_step": _timed(full_decode, dev, 1, 2) / steps}
+        r["prefill_tok_per_s"] = T / (r["prefill_ms"] * 1e-3)
+        r["decode_tok_per_s"] = 1e3 / r["decode_ms_per_step"]
+        r["prefill_tflops"] = 4.0 * 256 * a["nh"] * T * (T + 1) / 2 / (r["prefill_ms"] * 1e-3) / 1e12
+        res[name] = r
+    res["note"] = "batch 1: decode is launch-bound (one or two kernels of a few microseconds per step), not a bandwidth case"
+    if cpu:
+        res["cpu"] = cpu_single_layer()
+    return res
+
+
+def cpu_single_layer():
+    """The CPU reference on the two single-layer workloads (one thread: the attention core is single-threaded in the
+    engine).  The delta-net layer runs in full; of the GQA layer the decode steps run in full (64 of them, at the
+    4096-token context) and the O(T^2) prefill is timed on its first 1024 tokens and scaled by the number of
+    (query, key) pairs."""
+    from oracle import oracle as O
+    from ornithology_b200.stack import ARCHS, full_weights, linear_weights
+    a = ARCHS["35b"]
+    orc = O.Oracle()
+    ref = O.Ref() if O.Ref.available() else None
+    g = np.random.default_rng(0)
+    w = linear_weights(a, 0, 0)
+    lin = O.LinearLayer(a["nk"], a["nv"], a["dk"], a["dv"], w["conv_w"], w["a_coef"], w["dt_bias"], w["norm_w"])
+    T, steps = 512, 128
+    ins = [g.standard_normal((T + steps, n)).astype(np.float32) for n in (lin.cc, a["nv"], a["nv"], lin.vd)]
+    S = np.zeros((a["nv"], 128, 128), np.float32); buf = np.zeros(3 * lin.cc + 1, np.float32)
+    t0 = time.perf_counter()
+    orc.linear_attn_prefill(lin, S, buf[:3 * lin.cc], *[x[:T] for x in ins], chunk=64)
+    t1 = time.perf_counter()
+    for t in range(T, T + steps):
+        if ref is not None:
+            O.ref_linear_step(ref, lin, S, buf, *[x[t] for x in ins])
+        else:
+            orc.linear_attn_step(lin, S, buf[:3 * lin.cc], *[x[t] for x in ins])
+    t2 = time.perf_counter()
+    out = {"kind": "reference" if ref is not None else "port", "cores": 1,
+           "delta_net": {"prefill_ms": (t1 - t0) * 1e3, "prefill_tok_per_s": T / (t1 - t0),
+                         "decode_ms_per_step": (t2 - t1) * 1e3 / steps, "decode_tok_per_s": steps / (t2 - t1),
+                         "sample": "in full (prefill through the restated chunked scan, decode steps through the engine's own objects)"}}
+    fw = full_weights(a, 1, 3)
+    full = O.FullLayer(a["nh"], a["nkv"], a["hd"], fw["q_norm_w"], fw["k_norm_w"], rope_dim=a["rope_dim"], theta=a["theta"])
+    T, Ts, dsteps = 4096, 1024, 64
+    fin = [g.standard_normal((T + dsteps, n)).astype(np.float32) for n in (a["nh"] * 512, a["nkv"] * 256, a["nkv"] * 256)]
+    okv = orc.kv(T + dsteps, a["nkv"], a["hd"], O.KV_F32)
+    t0 = time.perf_counter()
+    orc.full_attn_prefill(full, okv, 0, *[x[:Ts] for x in fin])
+    t1 = time.perf_counter()
+    import ctypes as C
+    rows = g.standard_normal((T, a["nkv"] * a["hd"])).astype(np.float32)      # stand-in rows up to the 4096-token context
+    C.memmove(okv.c.K, rows.ctypes.data, rows.nbytes); C.memmove(okv.c.V, rows.ctypes.data, rows.nbytes)
+    okv.c.len = T
+    t2 = time.perf_counter()
+    for t in range(T, T + dsteps):
+        orc.full_attn_step(full, okv, t, *[x[t] for x in fin])
+    t3 = time.perf_counter()
+    scale = (T * (T + 1) / 2) / (Ts * (Ts + 1) / 2)
+    out["gqa_f32_kv"] = {"prefill_ms": (t1 - t0) * 1e3 * scale, "prefill_tok_per_s": T / ((t1 - t0) * scale),
+                         "decode_ms_per_step": (t3 - t2) * 1e3 / dsteps, "decode_tok_per_s": dsteps / (t3 - t2),
+                         "sample": f"prefill: first {Ts} tokens timed ({(t1 - t0):.1f} s), scaled x{scale:.1f} by (query, key) pairs; "
+                                   f"decode: {dsteps} steps at the {T}-token context"}
+    return out
 
 
 class ClockSampler:
@@ -247,7 +524,9 @@ def run_reference(args, rank, world):
             break
     value = float(np.mean(vals)) if vals else v
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * args.seqs / value,
+            "steps": args.steps, "warmup": args.warmup, "steps_timed": len(vals),
+            "step": "each timed step is a bounded sample of one decode step (see cpu_baseline.sample), scaled to the full stack",
+            "ms_per_step": 1e3 * args.seqs / value,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args, contexts, 1),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
@@ -257,10 +536,10 @@ def run_reference(args, rank, world):
 
 
 def workload_config(args, contexts, world):
-    return {"workload": "configs[2]: batched decode, 40-layer 35B-shaped attention stack (30 delta-net + 10 GQA)",
+    return {"workload": "batched decode, 40-layer 35B-shaped attention stack (30 delta-net + 10 GQA)",
             "sequences_per_gpu": args.seqs, "context": f"uniform[{args.min_ctx},{args.max_ctx}] seed {args.seed}",
             "sum_context_rank0": int(np.sum(contexts[:args.seqs])), "kv_cache": "Q8_0", "state": "fp32",
-            "activations": "bf16", "parallelism": f"sequence-sharded x{world}",
+            "activations": "bf16", "parallelism": f"sequence-sharded x{world}, sequences dealt by summed context",
             "l2": "inputs larger than L2 (every step streams all KV rows and all recurrent state)"}
 
 
@@ -274,9 +553,11 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    from ornithology_b200.stack import sequence_shard
     all_ctx = draw_contexts(args.seqs * world, args.min_ctx, args.max_ctx, args.seed)
-    contexts = all_ctx[rank * args.seqs:(rank + 1) * args.seqs]
-    total_steps = 2 * (args.warmup + args.steps) + 4
+    # one draw for the whole job, dealt so that every rank gets the same count and the summed contexts balance
+    contexts = all_ctx[sequence_shard(all_ctx, rank, world)]
+    total_steps = 2 * (args.warmup + args.steps) + 12
     caps = [int(c) + total_steps + 8 for c in contexts]
     stack = AttnStack("35b", caps, kv_mode=D.KV_Q8_0, seed=args.seed, device=dev)
     stack.fill(contexts, seed=args.seed + 17)
@@ -297,12 +578,19 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(args.warmup):
         stack.decode_step(ins, outs, max_len=max_len)
     n_layers = len(stack.layers)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n_layers + 1)] for _ in range(args.steps)]
     barrier()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     for s in range(args.steps):
-        # same work as decode_step, with an event between layers (per-kernel-family timing)
+        stack.decode_step(ins, outs, max_len=max_len)
+    t_end.record()
+    barrier()
+    ms_total = t_start.elapsed_time(t_end)
+    # per-family times: a separate pass with an event between the layers (events between the launches cost the
+    # overlap of a kernel's prologue with its predecessor's tail, so they stay out of the timed region above)
+    fam_steps = max(3, min(args.steps, 5))
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n_layers + 1)] for _ in range(fam_steps)]
+    for s in range(fam_steps):
         for i, (kind, layer, state) in enumerate(stack.layers):
             ev[s][i].record()
             if kind == "full":
@@ -311,12 +599,10 @@ def run_ours(args, rank, world, local_rank):
                 D.linear_attn_step(layer, state, stack.pos, *ins[i], out=outs[i])
         ev[s][n_layers].record()
         D.advance(stack.pos)
-    t_end.record()
-    barrier()
-    ms_total = t_start.elapsed_time(t_end)
-    ms_lin = np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)
+    torch.cuda.synchronize(dev)
+    ms_lin = np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(fam_steps)
                       for i, (k, _, _) in enumerate(stack.layers) if k == "linear"])
-    ms_full = np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)
+    ms_full = np.mean([ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(fam_steps)
                        for i, (k, _, _) in enumerate(stack.layers) if k == "full"])
 
     # ---- e2e: host buffers, copies inside the timed region -------------------------------
@@ -374,33 +660,77 @@ def run_ours(args, rank, world, local_rank):
     ms_e2e = e_start.elapsed_time(e_end)
     clocks = sampler.stop() if rank == 0 else None
 
+    ctx_now = [int(c) + args.warmup + args.steps // 2 for c in contexts]      # contexts mid-way through the timed steps
+    b_lin, b_full = stack.decode_bytes(ctx_now)
+    # every rank's own figures: step time, per-family times, algorithmic bytes, summed context
+    mine = torch.tensor([ms_total / args.steps, float(ms_lin), float(ms_full), float(b_lin), float(b_full),
+                         float(np.sum(contexts))], dtype=torch.float64, device=dev)
+    per_rank = [torch.zeros_like(mine) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(per_rank, mine)
+    else:
+        per_rank = [mine]
+    per_rank = [[float(x) for x in t.cpu()] for t in per_rank]
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, ms_e2e = float(times[0]), float(times[1])
+    launches = stack.launches_per_step()
+    n_lin = sum(1 for k, _, _ in stack.layers if k == "linear")
+    n_full = n_layers - n_lin
+
+    # ---- strong scaling: the 64 sequences of the workload split over the ranks ------------
+    strong = None
+    if world > 1 and not args.no_extras:
+        ctx64 = draw_contexts(args.seqs, args.min_ctx, args.max_ctx, args.seed)
+        mine64 = ctx64[sequence_shard(ctx64, rank, world)]
+        del stack, ins, outs, h_ins, h_outs
+        torch.cuda.empty_cache()
+        small = AttnStack("35b", [int(c) + 3 * args.steps + 16 for c in mine64], kv_mode=D.KV_Q8_0, seed=args.seed, device=dev)
+        small.fill(mine64, seed=args.seed + 17)
+        s_ins = small.random_inputs(args.seed + 5, dtype=torch.bfloat16, device=dev)
+        s_max = int(max(mine64)) + 3 * args.steps + 16
+
+        def s_loop():
+            for _ in range(args.steps):
+                small.decode_step(s_ins, max_len=s_max)
+        ms = _timed(s_loop, dev, world, 1) / args.steps
+        strong = {"workload": "the %d sequences of the headline workload split over %d GPUs (%d per GPU), balanced by summed context"
+                              % (args.seqs, world, len(mine64)),
+                  "ms_per_step": ms, "tok_per_s": args.seqs / (ms * 1e-3), "scaling": "strong",
+                  "note": "few sequences per GPU: the delta-net layers run one CTA per (sequence, head) and the step is latency-bound"}
+        del small, s_ins
+        torch.cuda.empty_cache()
 
     prefill = None
     if not args.no_prefill:
         prefill = run_prefill(dev, rank, world)
+    decode_397b = None
+    if world > 1 and not args.no_extras:
+        decode_397b = run_decode_397b(dev, rank, world)
+    single = None
+    if world == 1 and not args.no_extras:
+        single = run_single_layer(dev, cpu=not args.no_cpu)
 
     if rank == 0:
         tokens = args.seqs * world * args.steps
         value = tokens / (ms_total * 1e-3)
         e2e = tokens / (ms_e2e * 1e-3)
-        ctx_now = [int(c) + args.warmup + args.steps // 2 for c in contexts]      # contexts mid-way through the timed steps
-        b_lin, b_full = stack.decode_bytes(ctx_now)
-        n_lin = sum(1 for k, _, _ in stack.layers if k == "linear")
-        n_full = n_layers - n_lin
         peak, src = measured_peaks()
-        fam = {"linear_attn_step": {"ms_per_launch": float(ms_lin), "bytes_per_launch": b_lin / n_lin,
-                                    "gbs": b_lin / n_lin / (ms_lin * 1e-3) / 1e9, "launches_per_step": n_lin},
-               "full_attn_step": {"ms_per_launch": float(ms_full), "bytes_per_launch": b_full / n_full,
-                                  "gbs": b_full / n_full / (ms_full * 1e-3) / 1e9, "launches_per_step": n_full}}
+        slow = max(range(world), key=lambda r: per_rank[r][0])                    # the rank the step waits for
+        _, r_lin, r_full, rb_lin, rb_full, _ = per_rank[slow]
+        fam = {"linear_attn_step": {"ms_per_launch": r_lin, "bytes_per_launch": rb_lin / n_lin,
+                                    "gbs": rb_lin / n_lin / (r_lin * 1e-3) / 1e9, "launches_per_step": n_lin},
+               "full_attn_step": {"ms_per_launch": r_full, "bytes_per_launch": rb_full / n_full,
+                                  "gbs": rb_full / n_full / (r_full * 1e-3) / 1e9, "launches_per_step": n_full}}
         dom = max(fam, key=lambda k: fam[k]["ms_per_launch"] * fam[k]["launches_per_step"])
         roof = {"bound": "hbm", "kernel": dom, "achieved": fam[dom]["gbs"], "peak": peak, "unit": "GB/s",
                 "frac": fam[dom]["gbs"] / peak, "peak_source": f"of {src}",
                 "traffic": fam[dom]["bytes_per_launch"] * DRAM_OVER_ALGORITHMIC[dom], "families": fam,
-                "whole_step_gbs": (b_lin + b_full) / (ms_total / args.steps * 1e-3) / 1e9}
+                "rank": slow, "timing": "per-family times from a separate pass with an event between the layers",
+                "whole_step_gbs": (rb_lin + rb_full) / (per_rank[slow][0] * 1e-3) / 1e9}
+        ranks = [{"rank": r, "sum_context": int(per_rank[r][5]), "ms_per_step": per_rank[r][0],
+                  "step_gbs": (per_rank[r][3] + per_rank[r][4]) / (per_rank[r][0] * 1e-3) / 1e9} for r in range(world)]
         cpu = None
         if world == 1 and not args.no_cpu:
             threads = min(os.cpu_count() or 1, 32)
@@ -412,8 +742,9 @@ def run_ours(args, rank, world, local_rank):
                 "config": workload_config(args, contexts, world),
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": ms_e2e / args.steps},
-                "gpu_launches": stack.launches_per_step() * args.steps,
-                "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "prefill": prefill}
+                "gpu_launches": launches * args.steps,
+                "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "ranks": ranks, "prefill": prefill,
+                "strong": strong, "decode_397b": decode_397b, "single_layer": single}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -430,7 +761,8 @@ def main():
     ap.add_argument("--max-ctx", type=int, default=32768)
     ap.add_argument("--seed", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the configs[3] prefill leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the long-prefill leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the strong-scaling, 397B-decode and single-layer legs")
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill leg (1 GPU) and print its figures")
     ap.add_argument("--prefill-tokens", type=int, default=32768)
     ap.add_argument("--prefill-shape", default="397b", choices=["397b", "35b"])

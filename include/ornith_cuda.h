@@ -341,6 +341,30 @@ ornith_status ornith_cuda_conv_export(const float *dev_ring, int conv_k, int Cc,
 ornith_status ornith_cuda_conv_import(float *dev_ring, int conv_k, int Cc, int pos,
                                       const float *dev_image, void *stream);
 
+/* ---- multi-GPU plan (one process per GPU, or one process driving several devices) ---------------------- */
+
+/* What rank `rank` of `world` owns under head sharding (reference: heads never interact — loop bodies
+ * src/ornith_rforward.c:488-498, :594-611; KV head of a query head src/ornith_attn.c:113-116):
+ * nv/world value heads of every delta-net layer with the key heads they pair with (tiled map kh = hv % nk),
+ * nh/world query heads of every full layer with the KV heads they read (replicated once world > n_kv_heads).
+ * A shard is just a smaller layer: slice the weights and the projection outputs to these heads and call the
+ * layer entry points above with the shard's head counts.  Pure host arithmetic. */
+typedef struct {
+    int32_t rank, world;
+    int32_t v_head0, n_v_heads;     /* value heads [v_head0, v_head0 + n_v_heads) */
+    int32_t k_head0, n_k_heads;     /* key heads */
+    int32_t q_head0, n_q_heads;     /* query heads */
+    int32_t kv_head0, n_kv_heads;   /* KV heads */
+} ornith_cuda_shard;
+ornith_status ornith_cuda_head_shard(int nk, int nv, int nh, int nkv, int rank, int world, ornith_cuda_shard *out);
+
+/* After an all-gather of per-rank head outputs (NCCL or any other transport; it delivers rank blocks one after
+ * the other, gathered [world][rows][width]), lay them out as the full-width rows the output projection consumes,
+ * full [rows][world * width] (reference call sites of that projection: src/ornith_rforward.c:452, :316).
+ * elem_bytes: 2 (bf16) or 4 (f32); width * elem_bytes must be a multiple of 16. */
+ornith_status ornith_cuda_gather_layout(const void *gathered, void *full, int world, size_t rows, int width,
+                                        int elem_bytes, void *stream);
+
 /* ---- per-head primitives on device pointers (what tier 1 is built from) ---- */
 
 /* reference: src/ornith_attn.c:198-213; n_heads independent states S [h][dv][dk],

@@ -41,8 +41,9 @@ def build(force: bool = False) -> None:
     if force or not os.path.exists(ORACLE_SO) or \
             os.path.getmtime(ORACLE_SO) < os.path.getmtime(os.path.join(_HERE, "ornith_oracle.c")):
         subprocess.check_call(["make", "-C", _HERE, "oracle"], stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference/src") and (force or not os.path.exists(REF_SO)):
-        subprocess.check_call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
+    ref = os.environ.get("ORNITH_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference"))
+    if os.path.isdir(os.path.join(ref, "src")) and (force or not os.path.exists(REF_SO)):
+        subprocess.check_call(["make", "-C", _HERE, "ref", f"REF={ref}"], stdout=subprocess.DEVNULL)
 
 
 class _KV(C.Structure):

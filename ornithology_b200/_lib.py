@@ -54,6 +54,11 @@ class CudaLinearLayer(C.Structure):         # ornith_cuda_linear_layer
                 ("conv_w", vp), ("conv_b", vp), ("a_coef", vp), ("dt_bias", vp), ("norm_w", vp)]
 
 
+class CudaShard(C.Structure):               # ornith_cuda_shard
+    _fields_ = [(n, C.c_int32) for n in ("rank", "world", "v_head0", "n_v_heads", "k_head0", "n_k_heads",
+                                          "q_head0", "n_q_heads", "kv_head0", "n_kv_heads")]
+
+
 class CudaLinearState(C.Structure):         # ornith_cuda_linear_state
     _fields_ = [("S", vp), ("conv", vp), ("S_seq_stride", C.c_int64), ("conv_seq_stride", C.c_int64)]
 
@@ -105,6 +110,8 @@ SYMBOLS = {
     "ornith_cuda_full_attn_prefill": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, _I, vp, _SZ, vp]),
     "ornith_cuda_kv_append": (_I, [vp, vp, vp, vp, vp, vp, _I, _I, vp]),
     "ornith_cuda_advance": (_I, [vp, _I, _I, vp]),
+    "ornith_cuda_head_shard": (_I, [_I, _I, _I, _I, _I, _I, vp]),
+    "ornith_cuda_gather_layout": (_I, [vp, vp, _I, _SZ, _I, _I, vp]),
     "ornith_cuda_linear_attn_step": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, vp]),
     "ornith_cuda_linear_attn_prefill_scratch": (_SZ, [vp, _I, _I]),
     "ornith_cuda_linear_attn_prefill": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, _I, _I, vp, _SZ, vp]),

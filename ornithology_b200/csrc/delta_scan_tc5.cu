@@ -52,7 +52,10 @@ using namespace tc5;
 constexpr int C = 64;                                   // tokens per chunk
 constexpr int AUX_FLOATS = 5 * C;                       // beta | beta p rk | w rk | p rq | p_63 (first word)
 constexpr uint32_t AUX_BYTES = AUX_FLOATS * 4;
-constexpr int AP_FLOATS = 2 * C * C;                    // A then P, row-major [64][64]
+// A and P are lower triangular.  Stored per block as four dense pieces of 32 columns: A columns 0..31 (64 rows),
+// A columns 32..63 of rows 32..63 (32 rows), then the same for P: 192 rows of 32 floats.
+constexpr int AP_ROWS = 192, AP_A1 = 64, AP_P0 = 96, AP_P1 = 160;
+constexpr int AP_FLOATS = AP_ROWS * 32;
 constexpr uint32_t AP_BYTES = AP_FLOATS * 4;
 
 // Round to tf32 (nearest, ties away from zero; finite inputs) with integer arithmetic: cvt.rna.tf32.f32 runs at
@@ -107,14 +110,14 @@ __device__ __forceinline__ void inv_unit_lower(const float *Mb, int lane, float 
         x[i] = acc;
     }
 }
-// y[i] = sum_l B[i][l] x[l], 32x32 block in shared memory, x in registers
-__device__ __forceinline__ void block_matvec(const float *B, const float (&x)[32], float (&y)[32]) {
+// y[i] = sum_l B[row0 + i][l] x[l] for 16 rows of a 32x32 block in shared memory, x in registers
+__device__ __forceinline__ void block_matvec16(const float *B, int row0, const float (&x)[32], float (&y)[16]) {
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
+    for (int i = 0; i < 16; i++) {
         float a0 = 0.0f, a1 = 0.0f;
 #pragma unroll
         for (int l4 = 0; l4 < 8; l4++) {
-            const float4 m = *reinterpret_cast<const float4 *>(B + i * LDB + 4 * l4);
+            const float4 m = *reinterpret_cast<const float4 *>(B + (row0 + i) * LDB + 4 * l4);
             a0 = fmaf(m.x, x[4 * l4], a0); a1 = fmaf(m.y, x[4 * l4 + 1], a1);
             a0 = fmaf(m.z, x[4 * l4 + 2], a0); a1 = fmaf(m.w, x[4 * l4 + 3], a1);
         }
@@ -122,6 +125,7 @@ __device__ __forceinline__ void block_matvec(const float *B, const float (&x)[32
     }
 }
 
+template <typename ACT>
 __global__ void __launch_bounds__(256, 2) k_delta_prep64(LinArgs a, const float *Y, const float *rqg, const float *rkg,
                                                       const float *la, const float *be, float *AP, float *aux,
                                                       int n_chunks) {
@@ -190,9 +194,15 @@ __global__ void __launch_bounds__(256, 2) k_delta_prep64(LinArgs a, const float 
     for (int m = pr; m < nvk; m += 4) {                   // one pair of warps per value head of this key head
         const int hv = a.head_map == ORNITH_HEADMAP_GROUPED ? kh * nvk + m : kh + m * a.nk;
         const size_t blk = ((size_t)b * a.nv + hv) * n_chunks + chunk;
-        float *Ag = AP + blk * AP_FLOATS, *Pg = Ag + C * C, *ax = aux + blk * AUX_FLOATS;
-        float gg = 0.0f, bb = 0.0f;                       // thread pt = token pt
-        if (pt < n) { gg = la[(tok0 + pt) * a.nv + hv]; bb = be[(tok0 + pt) * a.nv + hv]; }
+        float *Ag = AP + blk * AP_FLOATS, *ax = aux + blk * AUX_FLOATS;
+        float gg = 0.0f, bb = 0.0f;                       // thread pt = token pt: log-decay and write gate
+        if (pt < n) {
+            if (la) { gg = la[(tok0 + pt) * a.nv + hv]; bb = be[(tok0 + pt) * a.nv + hv]; }
+            else {                                        // reference: decay_alpha, src/ornith_rforward.c:282-284
+                gg = a.a_coef[hv] * softplus_f(act_ld((const ACT *)a.a, (tok0 + pt) * a.nv + hv) + a.dt_bias[hv]);
+                bb = sigmoid_f(act_ld((const ACT *)a.b, (tok0 + pt) * a.nv + hv));
+            }
+        }
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const float up = __shfl_up_sync(0xffffffffu, gg, o);
@@ -212,39 +222,42 @@ __global__ void __launch_bounds__(256, 2) k_delta_prep64(LinArgs a, const float 
         // thread pt = column l of M and P
 #pragma unroll 4
         for (int i = 0; i < C; i++) {
-            const float gam = (pt <= i) ? expf(ps.g[i] - gg) : 0.0f;
+            const float gam = (pt <= i) ? __expf(ps.g[i] - gg) : 0.0f;
             const float mv = (pt < i) ? ps.be[i] * gam * sm.GK[i * LDG + pt] : 0.0f;
             if (i < 32) { if (pt < 32) ps.M11[i * LDB + pt] = mv; }
             else if (pt < 32) ps.M21[(i - 32) * LDB + pt] = mv;
             else ps.M22[(i - 32) * LDB + pt - 32] = mv;
-            Pg[i * C + pt] = (pt <= i) ? tf32r(gam * sm.GQ[i * LDG + pt]) : 0.0f;
+            if (pt < 32) Ag[(AP_P0 + i) * 32 + pt] = (pt <= i) ? tf32r(gam * sm.GQ[i * LDG + pt]) : 0.0f;
+            else if (i >= 32) Ag[(AP_P1 + i - 32) * 32 + pt - 32] = (pt <= i) ? tf32r(gam * sm.GQ[i * LDG + pt]) : 0.0f;
         }
         pair_sync(1 + pr);
-        // A = (I + M)^-1 = [[A11, 0], [-A22 M21 A11, A22]]; lane = column
+        // A = (I + M)^-1 = [[A11, 0], [-A22 M21 A11, A22]]; lane = column.  The two diagonal blocks are inverted by one
+        // warp each; the two products of the off-diagonal block are split by rows between the warps.
         float x[32];
         if (wl == 0) {
             inv_unit_lower(ps.M11, lane, x);
 #pragma unroll
-            for (int i = 0; i < 32; i++) Ag[i * C + lane] = tf32r(x[i]);
-            float y[32];
-            block_matvec(ps.M21, x, y);                   // column `lane` of M21 A11
-#pragma unroll
-            for (int i = 0; i < 32; i++) x[i] = y[i];
+            for (int i = 0; i < 32; i++) { Ag[i * 32 + lane] = tf32r(x[i]); ps.M11[i * LDB + lane] = x[i]; }   // A11 over M11
         } else {
             inv_unit_lower(ps.M22, lane, x);
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                ps.A22[i * LDB + lane] = x[i];
-                Ag[(32 + i) * C + 32 + lane] = tf32r(x[i]);
-                Ag[i * C + 32 + lane] = 0.0f;
-            }
+            for (int i = 0; i < 32; i++) { Ag[(AP_A1 + i) * 32 + lane] = tf32r(x[i]); ps.A22[i * LDB + lane] = x[i]; }
         }
         pair_sync(1 + pr);
-        if (wl == 0) {
-            float y[32];
-            block_matvec(ps.A22, x, y);
+        {
+            float y[16];
 #pragma unroll
-            for (int i = 0; i < 32; i++) Ag[(32 + i) * C + lane] = tf32r(-y[i]);
+            for (int l = 0; l < 32; l++) x[l] = ps.M11[l * LDB + lane];          // column `lane` of A11
+            block_matvec16(ps.M21, 16 * wl, x, y);                               // rows 16 wl .. of M21 A11
+            pair_sync(1 + pr);                                                   // M22 has been read for the last time
+#pragma unroll
+            for (int i = 0; i < 16; i++) ps.M22[(16 * wl + i) * LDB + lane] = y[i];   // B = M21 A11 over M22
+            pair_sync(1 + pr);
+#pragma unroll
+            for (int l = 0; l < 32; l++) x[l] = ps.M22[l * LDB + lane];          // column `lane` of B
+            block_matvec16(ps.A22, 16 * wl, x, y);
+#pragma unroll
+            for (int i = 0; i < 16; i++) Ag[(32 + 16 * wl + i) * 32 + lane] = tf32r(-y[i]);
         }
         pair_sync(1 + pr);                                // the pair buffers are reused by the next head
     }
@@ -408,8 +421,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             auto load_a = [&](int n) {
                 if (n >= 1 && !mbar_wait(su32(&bars.empty_a), (uint32_t)(n - 1) & 1u)) return false;
                 mbar_expect_tx(su32(&bars.full_a), TX_A);
-                tma_load_2d(base + SM_A, &map_ap, 0, (int)((blk0 + n) * 128), su32(&bars.full_a));
-                tma_load_2d(base + SM_A + 8192, &map_ap32, 32, (int)((blk0 + n) * 128) + 32, su32(&bars.full_a));
+                tma_load_2d(base + SM_A, &map_ap, 0, (int)((blk0 + n) * AP_ROWS), su32(&bars.full_a));
+                tma_load_2d(base + SM_A + 8192, &map_ap32, 0, (int)((blk0 + n) * AP_ROWS) + AP_A1, su32(&bars.full_a));
                 return true;
             };
             auto load_v = [&](int n) {
@@ -428,8 +441,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             auto load_p = [&](int n) {
                 if (n >= 1 && !mbar_wait(su32(&bars.empty_p), (uint32_t)(n - 1) & 1u)) return false;
                 mbar_expect_tx(su32(&bars.full_p), TX_P);
-                tma_load_2d(base + SM_P, &map_ap, 0, (int)((blk0 + n) * 128) + C, su32(&bars.full_p));
-                tma_load_2d(base + SM_P + 8192, &map_ap32, 32, (int)((blk0 + n) * 128) + C + 32, su32(&bars.full_p));
+                tma_load_2d(base + SM_P, &map_ap, 0, (int)((blk0 + n) * AP_ROWS) + AP_P0, su32(&bars.full_p));
+                tma_load_2d(base + SM_P + 8192, &map_ap32, 0, (int)((blk0 + n) * AP_ROWS) + AP_P1, su32(&bars.full_p));
                 bulk_load(base + SM_AUX2, a.aux + (blk0 + n) * AUX_FLOATS, AUX_BYTES, su32(&bars.full_p));
                 return true;
             };
@@ -787,7 +800,7 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
     const int n_chunks = (x.T + C - 1) / C;
     const size_t n_blocks = (size_t)n_seq * x.nv * n_chunks;
     const int Cc = 2 * x.nk * 128 + x.nv * 128;
-    if ((size_t)n_seq * x.T >= (1u << 31) || n_blocks * 128 >= (1u << 31)) {
+    if ((size_t)n_seq * x.T >= (1u << 31) || n_blocks * AP_ROWS >= (1u << 31)) {
         orn_record_error("delta scan: %d sequences x %d tokens exceed the tensor-map coordinates", n_seq, x.T);
         return ORNITH_ERR_UNSUPPORTED;
     }
@@ -795,7 +808,9 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
     static bool configured_dev[ORN_MAX_DEVICES] = {};
     bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
-        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_prep64, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PrepSmem)),
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_prep64<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PrepSmem)),
+                          "delta prep smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_prep64<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PrepSmem)),
                           "delta prep smem opt-in"));
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_scan_tc5<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM),
                           "delta scan smem opt-in"));
@@ -803,15 +818,16 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
                           "delta scan smem opt-in"));
         configured = true;
     }
-    k_delta_prep64<<<dim3((unsigned)n_chunks, (unsigned)x.nk, (unsigned)n_seq), 256, sizeof(PrepSmem), s>>>(
-        x, Y, rq, rk, la, be, AP, aux, n_chunks);
+    const dim3 pgrid((unsigned)n_chunks, (unsigned)x.nk, (unsigned)n_seq);
+    if (act_dtype == ORNITH_ACT_BF16) k_delta_prep64<__nv_bfloat16><<<pgrid, 256, sizeof(PrepSmem), s>>>(x, Y, rq, rk, la, be, AP, aux, n_chunks);
+    else                              k_delta_prep64<float><<<pgrid, 256, sizeof(PrepSmem), s>>>(x, Y, rq, rk, la, be, AP, aux, n_chunks);
     ORN_TRY(orn_check_launch("k_delta_prep64"));
     CUtensorMap my, mym, map_ap, map_ap32, map_v;
     ORN_TRY(f32_rows_map(&my, Y, (uint64_t)Cc, (uint64_t)n_seq * x.T, C, 1));
     ORN_TRY(f32_rows_map(&mym, Y, (uint64_t)Cc, (uint64_t)n_seq * x.T, C, 2));
     ORN_TRY(f32_rows_map(&map_v, Y, (uint64_t)Cc, (uint64_t)n_seq * x.T, C, 0, 128));
-    ORN_TRY(f32_rows_map(&map_ap, AP, (uint64_t)C, n_blocks * 128, C, 1));
-    ORN_TRY(f32_rows_map(&map_ap32, AP, (uint64_t)C, n_blocks * 128, 32, 1));
+    ORN_TRY(f32_rows_map(&map_ap, AP, 32, n_blocks * AP_ROWS, C, 1));
+    ORN_TRY(f32_rows_map(&map_ap32, AP, 32, n_blocks * AP_ROWS, 32, 1));
     ScanArgs a;
     a.Y = Y; a.aux = aux; a.S = x.S; a.S_stride = x.S_stride; a.z = x.z; a.out = x.out; a.norm_w = x.norm_w;
     a.nk = x.nk; a.nv = x.nv; a.head_map = x.head_map; a.T = x.T; a.n_chunks = n_chunks;

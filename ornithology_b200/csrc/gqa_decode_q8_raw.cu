@@ -212,12 +212,16 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, cons
     const int64_t base = a.kv.seq_off[b];
     const int cap = (int)(a.kv.seq_off[b + 1] - base);
     const int len0 = a.kv_len[b];
-    if (len0 >= cap) return;
+    // A CTA that leaves early still has to wait for the grid in front (programmatic dependent launch):
+    // a grid whose CTAs all returned without waiting would retire, and let the next kernel in the
+    // stream start, before the append kernel has finished.
+    if (len0 >= cap) { asm volatile("griddepcontrol.wait;\n" ::: "memory"); return; }
     const int L = len0 + 1;
     const int t0 = split * a.tokens_per_split, t1 = min(L, t0 + a.tokens_per_split);
     float *part0 = a.part + (((size_t)b * a.nh + (size_t)head0) * a.nsplit + split) * (HD + 2);
     const size_t part_stride = (size_t)a.nsplit * (HD + 2);
     if (t0 >= L) {
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
         if (tid < G) { part0[tid * part_stride] = -INFINITY; part0[tid * part_stride + 1] = 0.0f; }
         return;
     }

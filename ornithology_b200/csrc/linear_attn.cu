@@ -382,8 +382,11 @@ constexpr int CONV4_TOK = 16;
 
 // nearest tf32 value (ties away from zero, finite inputs), in integer arithmetic
 __device__ __forceinline__ float tf32_rna(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
-template <typename ACT, bool FAST>
-__global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y) {
+// NORMS (needs dk = 128, so that the 32 threads of a warp own exactly one q or k head): the kernel also leaves the
+// inverse L2 norms 1/sqrt(sum x^2 + 1e-6) of the q and k rows it produces in rq / rk [token][key head], which saves
+// the pass of k_linear_prep over the image (reference: ot_l2norm_eps, src/ornith_tensor.c:155-160).
+template <typename ACT, bool FAST, bool NORMS>
+__global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y, float *rq, float *rk) {
     const int qd = a.nk * a.dk, Cc = 2 * qd + a.nv * a.dv;
     const int ch = (blockIdx.x * 128 + threadIdx.x) * 4, b = blockIdx.z, t0 = blockIdx.y * CONV4_TOK;
     if (ch >= Cc) return;
@@ -403,6 +406,9 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y)
     for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const float4 *>(a.conv_w + (size_t)(ch + c) * 4);
     float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
     if (a.conv_b) bias = *reinterpret_cast<const float4 *>(a.conv_b + ch);
+    float ss[CONV4_TOK];                                  // this thread's share of each token's sum of squares
+#pragma unroll
+    for (int i = 0; i < CONV4_TOK; i++) ss[i] = 0.0f;
 #pragma unroll
     for (int i = 0; i < CONV4_TOK; i++) {
         if (t0 + i >= a.T) break;
@@ -418,6 +424,27 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y)
             y.x = tf32_rna(y.x); y.y = tf32_rna(y.y); y.z = tf32_rna(y.z); y.w = tf32_rna(y.w);
         }
         *reinterpret_cast<float4 *>(Y + ((size_t)b * a.T + t0 + i) * Cc + ch) = y;
+        if (NORMS) ss[i] = (y.x * y.x + y.y * y.y) + (y.z * y.z + y.w * y.w);
+    }
+    if (NORMS && ch < 2 * qd) {                           // warp-uniform: a warp covers 128 channels = one head
+        const int lane = threadIdx.x & 31;
+        // sums over the 32 lanes for 16 tokens: token t ends up in lanes t and t + 16
+#pragma unroll
+        for (int i = 0; i < CONV4_TOK; i++) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], 16);
+#pragma unroll
+        for (int off = 8; off >= 1; off >>= 1) {
+            const bool up = (lane & off) != 0;
+#pragma unroll
+            for (int k = 0; k < off; k++) {
+                const float send = up ? ss[k] : ss[k + off], keep = up ? ss[k + off] : ss[k];
+                ss[k] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+        }
+        if (lane < CONV4_TOK && t0 + lane < a.T) {
+            const bool is_k = ch >= qd;
+            const int kh = (is_k ? ch - qd : ch) / 128;
+            (is_k ? rk : rq)[((size_t)b * a.T + t0 + lane) * a.nk + kh] = 1.0f / sqrtf(ss[0] + 1e-6f);
+        }
     }
 }
 
@@ -805,16 +832,25 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     if (((uintptr_t)scratch % 256) != 0) { orn_record_error("linear_attn_prefill: scratch must be 256-byte aligned"); return ORNITH_ERR_FORMAT; }
     LinArgs x = make_args(l, st, pos, qkv, a, b, z, out, T);
 
-    // dk = dv = 128 scans on the tensor cores in tf32 unless ORNITH_CUDA_PREFILL_FP32=1 asks for fp32 products
+    // dk = dv = 128 scans on the tensor cores in tf32 unless ORNITH_CUDA_PREFILL_FP32=1 asks for fp32 products;
+    // tcgen05 scan unless ORNITH_CUDA_DELTA_SCAN=mma asks for the mma.sync one (or the state is not 16-byte aligned)
     const char *exact = getenv("ORNITH_CUDA_PREFILL_FP32");
     const bool tc = l->dk == 128 && l->dv == 128 && !(exact && exact[0] == '1');
+    const char *variant = getenv("ORNITH_CUDA_DELTA_SCAN");
+    const bool tc5 = tc && ((uintptr_t)st->S % 16) == 0 && (st->S_seq_stride % 4) == 0 && !(variant && variant[0] == 'm');
+    bool fused_norms = false;                            // the conv kernel has written rq / rk
     if (l->conv_k == 4 && Cc % 4 == 0 && st->conv_seq_stride % 4 == 0 && ((uintptr_t)qkv % 16) == 0 &&
         ((uintptr_t)st->conv % 16) == 0 && ((uintptr_t)l->conv_w % 16) == 0 && ((uintptr_t)l->conv_b % 16) == 0) {
         dim3 cgrid((unsigned)((Cc + 511) / 512), (T + CONV4_TOK - 1) / CONV4_TOK, n_seq);
-        if (bf && tc)  k_conv4_silu_prefill<__nv_bfloat16, true><<<cgrid, 128, 0, s>>>(x, Y);
-        else if (bf)   k_conv4_silu_prefill<__nv_bfloat16, false><<<cgrid, 128, 0, s>>>(x, Y);
-        else if (tc)   k_conv4_silu_prefill<float, true><<<cgrid, 128, 0, s>>>(x, Y);
-        else           k_conv4_silu_prefill<float, false><<<cgrid, 128, 0, s>>>(x, Y);
+        if (tc5) {
+            if (bf) k_conv4_silu_prefill<__nv_bfloat16, true, true><<<cgrid, 128, 0, s>>>(x, Y, rq, rk);
+            else    k_conv4_silu_prefill<float, true, true><<<cgrid, 128, 0, s>>>(x, Y, rq, rk);
+            fused_norms = true;
+        }
+        else if (bf && tc)  k_conv4_silu_prefill<__nv_bfloat16, true, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr);
+        else if (bf)   k_conv4_silu_prefill<__nv_bfloat16, false, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr);
+        else if (tc)   k_conv4_silu_prefill<float, true, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr);
+        else           k_conv4_silu_prefill<float, false, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr);
         ORN_TRY(orn_check_launch("k_conv4_silu_prefill"));
     } else {
         dim3 cgrid((unsigned)((Cc + 127) / 128), (T + CONV_TOK - 1) / CONV_TOK, n_seq);
@@ -826,21 +862,19 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     if (bf) k_conv_ring_refresh<__nv_bfloat16><<<rgrid, 256, 0, s>>>(x);
     else    k_conv_ring_refresh<float><<<rgrid, 256, 0, s>>>(x);
     ORN_TRY(orn_check_launch("k_conv_ring_refresh"));
-    if (bf) k_linear_prep<__nv_bfloat16><<<(unsigned)n_tok, 128, 0, s>>>(x, Y, (int)n_tok, rq, rk, la, be);
-    else    k_linear_prep<float><<<(unsigned)n_tok, 128, 0, s>>>(x, Y, (int)n_tok, rq, rk, la, be);
-    ORN_TRY(orn_check_launch("k_linear_prep"));
+    // the tcgen05 path computes the gates in its own preparation kernel and takes the norms from the conv kernel
+    if (!(tc5 && fused_norms)) {
+        if (bf) k_linear_prep<__nv_bfloat16><<<(unsigned)n_tok, 128, 0, s>>>(x, Y, (int)n_tok, rq, rk, la, be);
+        else    k_linear_prep<float><<<(unsigned)n_tok, 128, 0, s>>>(x, Y, (int)n_tok, rq, rk, la, be);
+        ORN_TRY(orn_check_launch("k_linear_prep"));
+    }
 
     dim3 grid(l->nv, n_seq);
     if (l->dk == 128 && l->dv == 128) {
         // default: tf32 tensor-core scan; ORNITH_CUDA_PREFILL_FP32=1 keeps every product in fp32
-        if (tc) {
-            // tcgen05 scan unless ORNITH_CUDA_DELTA_SCAN=mma asks for the mma.sync one (or the state is not 16-byte aligned)
-            const char *variant = getenv("ORNITH_CUDA_DELTA_SCAN");
-            const bool aligned = ((uintptr_t)st->S % 16) == 0 && (st->S_seq_stride % 4) == 0;
-            if (aligned && !(variant && variant[0] == 'm'))
-                return launch_linear_prefill_tc5(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, g_delta_scan_dump, s);
-            return launch_linear_prefill_tc(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, s);
-        }
+        if (tc5) return launch_linear_prefill_tc5(x, n_seq, act_dtype, Y, rq, rk, fused_norms ? nullptr : la, fused_norms ? nullptr : be,
+                                                  blocks, g_delta_scan_dump, s);
+        if (tc) return launch_linear_prefill_tc(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, s);
         if (chunk >= 32) return bf ? launch_chunk<32, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)
                                    : launch_chunk<32, float>(x, grid, Y, rq, rk, la, be, s);
         return bf ? launch_chunk<16, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)

@@ -33,7 +33,8 @@ ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtyp
 
 // The same scan on the 5th-generation tensor cores (delta_scan_tc5.cu): tcgen05.mma in tf32 with the
 // state in tensor memory, operands staged by TMA, 64-token chunks.  Y must hold the q and k channels
-// rounded to tf32 (k_conv4_silu_prefill does that); work = linear_prefill_tc5_work_bytes() bytes.
+// rounded to tf32 (k_conv4_silu_prefill does that); work = linear_prefill_tc5_work_bytes() bytes;
+// la = be = nullptr: the gates are computed from the layer's a / b inputs.
 size_t linear_prefill_tc5_work_bytes(int nk, int nv, int n_seq, int T);
 ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dtype, const float *Y, const float *rq,
                                         const float *rk, const float *la, const float *be, float *work, float *dbg,

@@ -65,8 +65,8 @@ static std::mutex g_hook_mu;
 static ornith_cuda_alloc_hook g_alloc_hook = nullptr;
 static void *g_alloc_hook_user = nullptr;
 
-ornith_status orn_device_alloc(void **p, size_t bytes, const char *what) {
-    *p = nullptr;
+// 0 = go ahead, else the allocation is refused (host-side failure injection)
+static ornith_status alloc_hook_check(size_t bytes, const char *what) {
     ornith_cuda_alloc_hook hook;
     void *user;
     {
@@ -77,6 +77,12 @@ ornith_status orn_device_alloc(void **p, size_t bytes, const char *what) {
         orn_record_error("%s: allocation of %zu bytes refused by the allocation hook", what, bytes);
         return ORNITH_ERR_OOM;
     }
+    return ORNITH_OK;
+}
+
+ornith_status orn_device_alloc(void **p, size_t bytes, const char *what) {
+    *p = nullptr;
+    ORN_TRY(alloc_hook_check(bytes, what));
     return orn_check(cudaMalloc(p, bytes), what);
 }
 
@@ -197,10 +203,11 @@ ornith_status ornith_cuda_set_device(int device) {
 }
 
 ornith_status ornith_cuda_malloc(void **dev_ptr, size_t bytes) {
-    ORN_TRY(orn_require_device());
     *dev_ptr = nullptr;
     if (bytes == 0) bytes = 16;
-    ORN_TRY(orn_device_alloc(dev_ptr, bytes, "cudaMalloc"));
+    ORN_TRY(alloc_hook_check(bytes, "ornith_cuda_malloc"));      // before the device is touched: a host can test its OOM paths without a GPU
+    ORN_TRY(orn_require_device());
+    ORN_TRY(orn_check(cudaMalloc(dev_ptr, bytes), "cudaMalloc"));
     return orn_check(cudaMemset(*dev_ptr, 0, bytes), "cudaMemset");
 }
 
@@ -239,6 +246,62 @@ void ornith_cuda_rope_inv_freq(float theta, int rotary_dim, float *host_out) {
     int half = rotary_dim / 2;
     for (int i = 0; i < half; i++)
         host_out[i] = powf(theta, -2.0f * (float)i / (float)rotary_dim);
+}
+
+// ---- multi-GPU plan -------------------------------------------------------------
+ornith_status ornith_cuda_head_shard(int nk, int nv, int nh, int nkv, int rank, int world, ornith_cuda_shard *out) {
+    if (!out || nk <= 0 || nv <= 0 || nh <= 0 || nkv <= 0 || world <= 0 || rank < 0 || rank >= world) {
+        orn_record_error("head_shard: bad arguments");
+        return ORNITH_ERR_FORMAT;
+    }
+    if (nv % world || nh % world || nh % nkv) {
+        orn_record_error("head_shard: %d ranks do not divide %d value heads / %d query heads", world, nv, nh);
+        return ORNITH_ERR_UNSUPPORTED;
+    }
+    const int pv = nv / world, ph = nh / world, v0 = rank * pv;
+    int k0, n_k;
+    if (pv >= nk) {
+        if (pv % nk) { orn_record_error("head_shard: value heads per rank must be a multiple of the key heads"); return ORNITH_ERR_UNSUPPORTED; }
+        k0 = 0; n_k = nk;
+    } else {
+        if (nk % pv) { orn_record_error("head_shard: key heads must be a multiple of the value heads per rank"); return ORNITH_ERR_UNSUPPORTED; }
+        k0 = v0 % nk; n_k = pv;
+    }
+    const int group = nh / nkv, kv_lo = (rank * ph) / group, kv_hi = (rank * ph + ph - 1) / group;
+    out->rank = rank; out->world = world;
+    out->v_head0 = v0; out->n_v_heads = pv;
+    out->k_head0 = k0; out->n_k_heads = n_k;
+    out->q_head0 = rank * ph; out->n_q_heads = ph;
+    out->kv_head0 = kv_lo; out->n_kv_heads = kv_hi - kv_lo + 1;
+    return ORNITH_OK;
+}
+
+// gathered [world][rows][w16] -> full [rows][world][w16], 16-byte pieces
+__global__ void k_gather_layout(const uint4 *gathered, uint4 *full, int world, size_t rows, int w16) {
+    const size_t n = (size_t)world * rows * w16;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(e % w16);
+        const size_t t = e / w16;
+        const int r = (int)(t % world);
+        const size_t row = t / world;
+        full[e] = gathered[((size_t)r * rows + row) * w16 + c];
+    }
+}
+
+ornith_status ornith_cuda_gather_layout(const void *gathered, void *full, int world, size_t rows, int width,
+                                        int elem_bytes, void *stream) {
+    ORN_TRY(orn_require_device());
+    if (!gathered || !full || world <= 0 || width <= 0 || (elem_bytes != 2 && elem_bytes != 4) ||
+        ((size_t)width * elem_bytes) % 16 || ((uintptr_t)gathered % 16) || ((uintptr_t)full % 16)) {
+        orn_record_error("gather_layout: bad arguments (rows of a multiple of 16 bytes, 16-byte aligned buffers)");
+        return ORNITH_ERR_FORMAT;
+    }
+    if (rows == 0) return ORNITH_OK;
+    const int w16 = (int)((size_t)width * elem_bytes / 16);
+    const size_t n = (size_t)world * rows * w16;
+    const unsigned blocks = (unsigned)((n + 255) / 256 < 148u * 16u ? (n + 255) / 256 : 148u * 16u);
+    k_gather_layout<<<blocks, 256, 0, as_stream(stream)>>>((const uint4 *)gathered, (uint4 *)full, world, rows, w16);
+    return orn_check_launch("k_gather_layout");
 }
 
 // ---- counters ------------------------------------------------------------------

@@ -61,7 +61,8 @@ def test_delta_net_layer_prefill_512_then_128_steps(oracle):
 def test_gqa_layer_prefill_4096_then_256_steps(oracle, mode):
     """16 query / 2 KV heads x 256, f32 activations, seed 1: causal prefill of 4096 tokens, 256 decode steps.  The
     oracle runs the engine's path (one ornith_gqa_step per token).  Outputs within 2e-3; the cache rows — after
-    k RMSNorm, partial RoPE and, for Q8_0, the codec — are compared byte for byte."""
+    k RMSNorm, partial RoPE and, for Q8_0, the codec — are compared with the oracle's: V rows and the Q8_0 K rows
+    byte for byte, f32 K rows bit for bit outside the rotated dims and to the last place inside them."""
     import torch
     from ornithology_b200 import device as D
     layer = full_case(1)
@@ -88,9 +89,19 @@ def test_gqa_layer_prefill_4096_then_256_steps(oracle, mode):
     Kg, Vg = kv.rows(0, n)
     Ko, Vo = okv.rows_q8_0() if mode == "q8_0" else okv.rows_f32()
     Ko = np.asarray(Ko)[:n].reshape(Kg.shape); Vo = np.asarray(Vo)[:n].reshape(Vg.shape)
-    dk = int((Kg.view(np.uint8) != Ko.view(np.uint8)).sum()); dv = int((Vg.view(np.uint8) != Vo.view(np.uint8)).sum())
-    assert dv == 0, f"{dv} differing V bytes"
-    assert dk == 0, f"{dk} of {Kg.view(np.uint8).size} K bytes differ"
+    assert (Vg.view(np.uint8) == Vo.view(np.uint8)).all(), "V rows differ"
+    if mode == "q8_0":
+        dk = int((Kg != Ko).sum())
+        assert dk == 0, f"{dk} of {Kg.size} K bytes differ"
+    else:
+        # f32 rows: everything but the 64 rotated dims is bit-exact; the rotated dims go through the device's sincosf
+        # where the CPU uses libm's cosf / sinf, which differ in the last place for some angles
+        rot = layer.rope_dim
+        assert (Kg[..., rot:].view(np.uint32) == Ko[..., rot:].view(np.uint32)).all(), "non-rotated K dims differ"
+        a, b = Kg[..., :rot].astype(np.float64), Ko[..., :rot].astype(np.float64)
+        assert np.abs(a - b).max() <= 4e-7 * np.abs(b).max(), "rotated K dims differ by more than a few ulp"
+        frac = float((Kg[..., :rot].view(np.uint32) != Ko[..., :rot].view(np.uint32)).mean())
+        assert frac < 0.2, f"{frac:.3f} of the rotated values differ in the last place"
 
 
 def test_gqa_512_consecutive_decode_steps(oracle):

@@ -145,3 +145,28 @@ def test_two_gloo_ranks_all_gather_head_outputs():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert q.get(timeout=10) is True
+
+
+def test_c_head_shard_matches_the_python_plan():
+    """The C entry point a host engine would call (ornith_cuda_head_shard) and the Python harness agree on who owns
+    which heads, for both model shapes and every rank count that divides the heads; bad splits are refused."""
+    import ctypes as C
+    from ornithology_b200 import _lib, build
+    from ornithology_b200.stack import ARCHS, head_shard
+    build.build()
+    lib = _lib.load()
+    for name, a in ARCHS.items():
+        for world in (1, 2, 4, 8, 16):
+            if a["nv"] % world or a["nh"] % world:
+                continue
+            for rank in range(world):
+                sh = _lib.CudaShard()
+                assert lib.ornith_cuda_head_shard(a["nk"], a["nv"], a["nh"], a["nkv"], rank, world, C.byref(sh)) == 0
+                py = head_shard(a, rank, world)
+                assert (sh.v_head0, sh.n_v_heads) == (py.v_heads.start, len(py.v_heads)), (name, world, rank)
+                assert (sh.k_head0, sh.n_k_heads) == (py.k_heads.start, len(py.k_heads))
+                assert (sh.q_head0, sh.n_q_heads) == (py.q_heads.start, len(py.q_heads))
+                assert (sh.kv_head0, sh.n_kv_heads) == (py.kv_heads.start, len(py.kv_heads))
+    sh = _lib.CudaShard()
+    assert lib.ornith_cuda_head_shard(16, 32, 16, 2, 0, 3, C.byref(sh)) != 0          # 3 ranks do not divide the heads
+    assert lib.ornith_cuda_head_shard(16, 32, 16, 2, 5, 4, C.byref(sh)) != 0          # rank out of range
