@@ -52,6 +52,19 @@ template <> __device__ __forceinline__ void act_st<__nv_bfloat16>(__nv_bfloat16 
     p[i] = __float2bfloat16_rn(v);
 }
 
+// four adjacent activations (16-byte / 8-byte aligned)
+__device__ __forceinline__ float4 act_ld4(const float *p, size_t i) { return *reinterpret_cast<const float4 *>(p + i); }
+__device__ __forceinline__ float4 act_ld4(const __nv_bfloat16 *p, size_t i) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(p + i);
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                       __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
+__device__ __forceinline__ void act_st4(float *p, size_t i, float4 v) { *reinterpret_cast<float4 *>(p + i) = v; }
+__device__ __forceinline__ void act_st4(__nv_bfloat16 *p, size_t i, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(p + i) = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+}
+
 // ---- scalar math in the engine's form (reference: src/ornith_tensor.c:117-119)
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }

@@ -297,6 +297,17 @@ struct ScanArgs {
     const float *norm_w;
     int nk, nv, head_map, T, n_chunks;
     float out_scale, eps;
+    // Segment-parallel form (n_seg > 1; for few heads): the prompt is cut into n_seg runs of seg_chunks chunks that
+    // are scanned at the same time by different CTAs (grid.z = 2 n_seg - 1).  The state enters the recurrence
+    // linearly, S_t = S_{t-1} M_t + beta_t v_t k_t^T with M_t = alpha_t (I - beta_t k_t k_t^T) acting on the key
+    // index, so a run needs the incoming state only through two things that do not depend on it: the scan of
+    // the run from a ZERO state (outputs o0_t, final state S0) and the scan of the run from the IDENTITY with
+    // V = 0 (outputs qt_t = Phi_t q_t, final state Phi = prod M_t).  Then o_t = o0_t + S_in qt_t and
+    // S_out = S_in Phi + S0; k_delta_seg_carry walks the runs, k_delta_seg_finish adds the correction and
+    // applies the output norm and gate.  Run 0 starts from the real state and is final as it is.
+    int n_seg, seg_chunks;
+    float *seg_state;                    // [n_seq * nv][3 n_seg][128][128]: slot 3j: S0 (j = 0: end state of run 0), 3j+1: Phi, 3j+2: S_in
+    float *seg_raw;                      // [2][n_seq * nv][T][128] f32: o0, then qt
     unsigned int *status;
     long long *trace;                    // bring-up aid: clock64 stamps of CTA (0, 0), [role][chunk][8]
     float *dbg;                          // bring-up aid: first chunk's KS, U, QS, PU and the state after it (nullptr in production)
@@ -335,7 +346,7 @@ __device__ __forceinline__ void issue_tri(uint32_t d, uint32_t x, uint32_t l) {
     for (int ks = 0; ks < 4; ks++) mma_tf32_ts(d + 32, x + 32 + 8 * ks, smem_desc(l + 8192 + ks * 32, 16, 1024), ID_32, 1u);
 }
 
-template <typename ACT>
+template <typename ACT, bool SEG>
 __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_constant__ CUtensorMap map_y,
                                                                const __grid_constant__ CUtensorMap map_ym,
                                                                const __grid_constant__ CUtensorMap map_ap,
@@ -346,7 +357,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
     __shared__ float red[2][4][4][16];                    // [chunk parity][group of 16 tokens][lane quarter][token]
     __shared__ uint32_t tmem_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int hv = blockIdx.x, b = blockIdx.y, N = a.n_chunks;
+    const int hv = blockIdx.x, b = blockIdx.y;
+    // what this CTA scans: kind 0 = from the caller's state, final outputs; 1 = from zero, raw outputs;
+    // 2 = from the identity with V = 0, raw outputs
+    int kind = 0, seg = 0;
+    if (SEG && blockIdx.z > 0) { seg = 1 + ((int)blockIdx.z - 1) / 2; kind = 1 + ((int)blockIdx.z - 1) % 2; }
+    const int c0 = SEG ? seg * a.seg_chunks : 0;                               // first chunk
+    const int N = SEG ? min(a.seg_chunks, a.n_chunks - c0) : a.n_chunks;       // chunks of this CTA
     const int kh = a.head_map == ORNITH_HEADMAP_GROUPED ? hv / (a.nv / a.nk) : hv % a.nk;
     const int qd = a.nk * 128, vd = a.nv * 128;
     const uint32_t base = (su32(smraw) + 1023u) & ~1023u; // swizzle atoms are 1 KiB aligned
@@ -372,7 +389,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
     __syncthreads();
     fence_after();
     const uint32_t tmem = tmem_slot;
-    float *Sg = a.S + (size_t)b * a.S_stride + (size_t)hv * 128 * 128;
+    float *Sg = a.S + (size_t)b * a.S_stride + (size_t)hv * 128 * 128;     // incoming state (kind 0)
+    float *Sout = Sg;                                                       // where the final state goes
+    float *raw = nullptr;                                                   // raw output rows [T][128] (kinds 1, 2)
+    if (SEG) {
+        Sout = a.seg_state + (((size_t)b * a.nv + hv) * 3 * a.n_seg + 3 * seg + (kind == 2 ? 1 : 0)) * (128 * 128);
+        if (kind) raw = a.seg_raw + ((size_t)(kind - 1) * gridDim.y * a.nv + (size_t)b * a.nv + hv) * (size_t)a.T * 128;
+    }
     // lane quarter and token (column) half of an epilogue thread
     const int qtr = warp & 3, half = (warp >> 2) & 1, row = 32 * qtr + lane;
     const uint32_t lane_t = tmem + ((uint32_t)(32 * qtr) << 16);
@@ -392,7 +415,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
 #pragma unroll 1
         for (int cc = 0; cc < 2; cc++) {
             float s[32];
-            ld_row32(Sg + (size_t)row * 128 + 64 * half + 32 * cc, s);
+            if (kind == 0) ld_row32(Sg + (size_t)row * 128 + 64 * half + 32 * cc, s);
+            else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) s[i] = (SEG && kind == 2 && 64 * half + 32 * cc + i == row) ? 1.0f : 0.0f;
+            }
             tmem_st32(lane_t + TM_S + 64 * half + 32 * cc, s);
         }
         tmem_wait_st();
@@ -404,8 +431,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
     if (warp == W_TMA) {
         // ================= producer =================
         if (lane == 0) {
-            const int yrow0 = b * a.T;
-            const size_t blk0 = ((size_t)b * a.nv + hv) * N;
+            const int yrow0 = b * a.T + c0 * C;                       // first row of this CTA's first chunk
+            const size_t blk0 = ((size_t)b * a.nv + hv) * a.n_chunks + c0;
             auto load_kq = [&](int n) {
                 const int s = n & 1;
                 if (n >= 2 && !mbar_wait(su32(&bars.empty_kq[s]), (uint32_t)((n >> 1) - 1) & 1u)) return false;
@@ -538,7 +565,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             for (int hh = 0; hh < 4; hh++) {                             // T = beta v - (beta p rk) KS, 8 tokens at a time
                 float v[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) v[i] = Vs[(8 * hh + i) * 128];
+                for (int i = 0; i < 8; i++) v[i] = (SEG && kind == 2) ? 0.0f : Vs[(8 * hh + i) * 128];
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                     const float4 be4 = *reinterpret_cast<const float4 *>(aux + 32 * half + 8 * hh + 4 * i);
@@ -613,7 +640,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             float x[32];
             tmem_ld32(lane_t + TM_S + 64 * half + 32 * cc, x);
             tmem_wait_ld();
-            float4 *dst = reinterpret_cast<float4 *>(Sg + (size_t)row * 128 + 64 * half + 32 * cc);
+            float4 *dst = reinterpret_cast<float4 *>(Sout + (size_t)row * 128 + 64 * half + 32 * cc);
 #pragma unroll
             for (int i = 0; i < 8; i++)
                 dst[i] = ok ? make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]) : make_float4(NAN, NAN, NAN, NAN);
@@ -633,10 +660,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
         // tiles are read from tensor memory twice (for the sum of squares, then for the store) instead of being kept.
         uint32_t zr[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) zr[i] = (16 * grp + i < a.T) ? ld_raw(zp, zoff + (size_t)(16 * grp + i) * vd) : 0u;
+        for (int i = 0; i < 16; i++)
+            zr[i] = (!(SEG && kind) && c0 * C + 16 * grp + i < a.T) ? ld_raw(zp, zoff + (size_t)(c0 * C + 16 * grp + i) * vd) : 0u;
         int n = 0;
+        if (SEG && kind) {
+            // raw outputs p rq QS + P U of a run scanned from zero / from the identity: no norm, no gate
+            for (; n < N; n++) {
+                const int s = n & 1, tok = (c0 + n) * C + 16 * grp;
+                ok = mbar_wait(su32(&bars.full_p), (uint32_t)n & 1u) && mbar_wait(su32(&bars.pu_done[s]), (uint32_t)(n >> 1) & 1u);
+                if (!ok) break;
+                fence_after();
+                float q[16], x[16];
+                tmem_ld16(t_qs + 128 * s, q);
+                tmem_ld16(t_pu + 128 * s, x);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float4 p4 = *reinterpret_cast<const float4 *>(aux + 4 * i);
+                    x[4 * i] = fmaf(p4.x, q[4 * i], x[4 * i]); x[4 * i + 1] = fmaf(p4.y, q[4 * i + 1], x[4 * i + 1]);
+                    x[4 * i + 2] = fmaf(p4.z, q[4 * i + 2], x[4 * i + 2]); x[4 * i + 3] = fmaf(p4.w, q[4 * i + 3], x[4 * i + 3]);
+                }
+                fence_before();
+                mbar_arrive(su32(&bars.o_read[s]));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(su32(&bars.empty_p));
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    if (tok + i < a.T) raw[(size_t)(tok + i) * 128 + row] = x[i];
+            }
+            n = N;                                                       // nothing to poison: the finishing kernel reads the status
+        }
         for (; n < N; n++) {
-            const int s = n & 1, tok = n * C + 16 * grp;
+            const int s = n & 1, tok = (c0 + n) * C + 16 * grp;
             if (tid == 256) TR(2, n, 0);
             // the gate factors of this chunk, while the tensor core still works on it: norm weight x SiLU(z), in place
 #pragma unroll
@@ -765,6 +820,168 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
     if (warp == W_MMA) tmem_dealloc(tmem, TM_COLS);
 }
 
+// =============================================================================
+// segment-parallel form: carrying the state over the runs, and the finishing pass
+// =============================================================================
+// S_in of run j+1 = S_in of run j x Phi_j + S0_j, rows of the state independent of one another: one CTA per
+// (sequence, head, group of 8 rows), 128 threads = the 128 columns.  Leaves S_in of every run j >= 1 in its slot
+// of seg_state and the final state in the caller's S.
+__global__ void __launch_bounds__(128) k_delta_seg_carry(ScanArgs a) {
+    __shared__ float srow[8][128];
+    __shared__ __align__(16) float phi[32][128];                                  // 32 rows of Phi at a time
+    const int hv = blockIdx.x, b = blockIdx.y, r0 = 8 * blockIdx.z, c = threadIdx.x;
+    float *slots = a.seg_state + ((size_t)b * a.nv + hv) * 3 * a.n_seg * (128 * 128);
+    float s[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) s[r] = slots[(size_t)(r0 + r) * 128 + c];          // end state of run 0
+    for (int j = 1; j < a.n_seg; j++) {
+        const float *S0 = slots + (size_t)(3 * j) * (128 * 128), *Phi = S0 + 128 * 128;
+        float *Sin = slots + (size_t)(3 * j + 2) * (128 * 128);
+        float acc[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) { Sin[(size_t)(r0 + r) * 128 + c] = s[r]; srow[r][c] = s[r]; acc[r] = S0[(size_t)(r0 + r) * 128 + c]; }
+        for (int l0 = 0; l0 < 128; l0 += 32) {
+            __syncthreads();                                                      // srow written / phi free again
+            float4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = reinterpret_cast<const float4 *>(Phi + (size_t)l0 * 128)[i * 128 + c];
+#pragma unroll
+            for (int i = 0; i < 8; i++) reinterpret_cast<float4 *>(&phi[0][0])[i * 128 + c] = v[i];
+            __syncthreads();
+#pragma unroll 8
+            for (int l = 0; l < 32; l++) {
+                const float p = phi[l][c];
+#pragma unroll
+                for (int r = 0; r < 8; r++) acc[r] = fmaf(srow[r][l0 + l], p, acc[r]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < 8; r++) s[r] = acc[r];
+    }
+    float *Sg = a.S + (size_t)b * a.S_stride + (size_t)hv * 128 * 128;
+#pragma unroll
+    for (int r = 0; r < 8; r++) Sg[(size_t)(r0 + r) * 128 + c] = s[r];
+}
+
+// o_t = o0_t + S_in qt_t for the tokens of the runs j >= 1, then the output scale, the per-head RMSNorm and the
+// SiLU(z) gate (reference: linear_finish, src/ornith_rforward.c:300-314).  One CTA per (256 tokens, head, sequence)
+// walks four tiles of 64 tokens with S_in of its run in shared memory: a 64 x 128 x 128 product on tf32 mma.sync
+// (A = the qt rows, B = S_in, both rounded to tf32), four warps of 16 tokens; the normalised tile then goes through
+// shared memory so that z is read and the output written in whole rows.
+constexpr int FIN_LD = 132, FIN_TOK = 256;
+struct FinSmem { float Sin[128 * FIN_LD]; float Qt[64 * FIN_LD]; };
+template <typename ACT>
+__global__ void __launch_bounds__(128, 2) k_delta_seg_finish(ScanArgs a) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    FinSmem &sm = *reinterpret_cast<FinSmem *>(smraw);
+    const int hv = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, j4 = lane & 3;
+    const int seg_tokens = a.seg_chunks * C;                                       // a multiple of FIN_TOK? no: of 64
+    const int tiles_per_seg = (seg_tokens + FIN_TOK - 1) / FIN_TOK;
+    const int seg = 1 + (int)blockIdx.x / tiles_per_seg;                           // run 0 is final already
+    const int tbeg = seg * seg_tokens + ((int)blockIdx.x % tiles_per_seg) * FIN_TOK;
+    const int tend = min(min(tbeg + FIN_TOK, (seg + 1) * seg_tokens), a.T);
+    if (tbeg >= tend) return;
+    const size_t hb = (size_t)b * a.nv + hv, planes = (size_t)gridDim.z * a.nv;
+    const float *Sin = a.seg_state + (hb * 3 * a.n_seg + 3 * seg + 2) * (128 * 128);
+    const float *o0 = a.seg_raw + hb * (size_t)a.T * 128, *qt = a.seg_raw + (planes + hb) * (size_t)a.T * 128;
+    const int vd = a.nv * 128;
+    const ACT *zp = (const ACT *)a.z;
+    ACT *op = (ACT *)a.out;
+    for (int e = tid; e < 128 * 32; e += 128) {
+        const int r = e >> 5, c4 = (e & 31) * 4;
+        float4 v = *reinterpret_cast<const float4 *>(Sin + (size_t)r * 128 + c4);
+        v.x = tf32r(v.x); v.y = tf32r(v.y); v.z = tf32r(v.z); v.w = tf32r(v.w);
+        *reinterpret_cast<float4 *>(&sm.Sin[r * FIN_LD + c4]) = v;
+    }
+    const float4 nw4 = *reinterpret_cast<const float4 *>(a.norm_w + 4 * lane);     // channels 4 lane .. of the store pass
+    for (int t0 = tbeg; t0 < tend; t0 += 64) {
+        __syncthreads();                                                          // the tile buffer is free (and S_in is in place)
+        for (int e = tid; e < 64 * 32; e += 128) {
+            const int i = e >> 5, c4 = (e & 31) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t0 + i < tend) v = *reinterpret_cast<const float4 *>(qt + (size_t)(t0 + i) * 128 + c4);
+            v.x = tf32r(v.x); v.y = tf32r(v.y); v.z = tf32r(v.z); v.w = tf32r(v.w);
+            *reinterpret_cast<float4 *>(&sm.Qt[i * FIN_LD + c4]) = v;
+        }
+        __syncthreads();
+        // acc[nt][x]: token 16 w + g + 8 (x >> 1), value row 8 nt + 2 j4 + (x & 1)
+        float acc[16][4];
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++)
+#pragma unroll
+            for (int x = 0; x < 4; x++) acc[nt][x] = 0.0f;
+        const float *A0 = sm.Qt + (16 * w) * FIN_LD;
+#pragma unroll 2
+        for (int k0 = 0; k0 < 128; k0 += 8) {
+            float af[4];
+            af[0] = A0[g * FIN_LD + k0 + j4];
+            af[1] = A0[(g + 8) * FIN_LD + k0 + j4];
+            af[2] = A0[g * FIN_LD + k0 + j4 + 4];
+            af[3] = A0[(g + 8) * FIN_LD + k0 + j4 + 4];
+#pragma unroll
+            for (int nt = 0; nt < 16; nt++) {
+                const float *br = sm.Sin + (8 * nt + g) * FIN_LD + k0 + j4;         // B[k][n] = S_in[n][k]
+                mma_tf32_sync(acc[nt], af, br[0], br[4]);
+            }
+        }
+        __syncthreads();                                                          // every warp is done reading the qt tile
+        // the correction goes over the qt tile (own rows only), then whole rows: + o0, scale, norm, gate, store
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++) {
+            const int r = 8 * nt + 2 * j4;
+            *reinterpret_cast<float2 *>(&sm.Qt[(16 * w + g) * FIN_LD + r]) = make_float2(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<float2 *>(&sm.Qt[(16 * w + g + 8) * FIN_LD + r]) = make_float2(acc[nt][2], acc[nt][3]);
+        }
+        __syncwarp();
+        // whole rows, 4 channels per lane; the loads of 8 tokens are issued together (memory latency, not arithmetic,
+        // bounds this pass)
+#pragma unroll
+        for (int i0 = 0; i0 < 16; i0 += 8) {
+            float4 b4[8], z4[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int t = min(t0 + 16 * w + i0 + i, tend - 1);               // rows past the end repeat the last row (never stored)
+                b4[i] = *reinterpret_cast<const float4 *>(o0 + (size_t)t * 128 + 4 * lane);
+                z4[i] = act_ld4(zp, ((size_t)b * a.T + t) * vd + (size_t)hv * 128 + 4 * lane);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int t = t0 + 16 * w + i0 + i;
+                const float4 c4 = *reinterpret_cast<const float4 *>(&sm.Qt[(16 * w + i0 + i) * FIN_LD + 4 * lane]);
+                float4 o = make_float4((c4.x + b4[i].x) * a.out_scale, (c4.y + b4[i].y) * a.out_scale,
+                                       (c4.z + b4[i].z) * a.out_scale, (c4.w + b4[i].w) * a.out_scale);
+                float ss = (o.x * o.x + o.y * o.y) + (o.z * o.z + o.w * o.w);
+                ss = warp_sum(ss);
+                const float inv = rsqrtf(ss * (1.0f / 128.0f) + a.eps);
+                if (t < tend)
+                    act_st4(op, ((size_t)b * a.T + t) * vd + (size_t)hv * 128 + 4 * lane,
+                            make_float4(o.x * inv * nw4.x * silu_fast(z4[i].x), o.y * inv * nw4.y * silu_fast(z4[i].y),
+                                        o.z * inv * nw4.z * silu_fast(z4[i].z), o.w * inv * nw4.w * silu_fast(z4[i].w)));
+            }
+        }
+    }
+}
+
+// How many runs the prompt is cut into: only when the heads alone would leave most SMs idle (2 P - 1 CTAs per
+// head), with at least 8 chunks per run.  ORNITH_CUDA_DELTA_SEGMENTS=<n> forces a count (1 = off).
+int delta_seg_plan(int nv, int n_seq, int n_chunks, int *seg_chunks) {
+    int p = 1;
+    const char *e = getenv("ORNITH_CUDA_DELTA_SEGMENTS");
+    if (e && e[0]) p = atoi(e);
+    else {
+        const int heads = nv * n_seq;
+        if (heads <= 37) p = (148 / heads + 1) / 2;                  // 2 p - 1 <= 148 / heads
+        if (p > 16) p = 16;
+    }
+    if (p > n_chunks / 8) p = n_chunks / 8;
+    if (p < 1) p = 1;
+    int sc = (n_chunks + p - 1) / p;
+    p = (n_chunks + sc - 1) / sc;                                     // no empty run
+    *seg_chunks = sc;
+    return p;
+}
+
 // [rows][cols] f32, boxes of box_cols columns x box_rows rows; swz 0: no swizzle, 1: 128-byte swizzle, 2: the same with 32-byte atoms
 ornith_status f32_rows_map(CUtensorMap *m, const void *basep, uint64_t cols, uint64_t rows, uint32_t box_rows, int swz, uint32_t box_cols = 32) {
     OrnTensorMapEncodeFn enc = orn_tensor_map_encoder();
@@ -786,10 +1003,15 @@ ornith_status f32_rows_map(CUtensorMap *m, const void *basep, uint64_t cols, uin
 static size_t ap_part(int nv, int n_seq, int n_chunks) { return align_up((size_t)n_seq * nv * n_chunks * AP_BYTES, 256); }
 static size_t aux_part(int nv, int n_seq, int n_chunks) { return align_up((size_t)n_seq * nv * n_chunks * AUX_BYTES, 256); }
 
+static size_t seg_state_part(int nv, int n_seq, int n_seg) { return n_seg > 1 ? align_up((size_t)n_seq * nv * 3 * n_seg * 128 * 128 * 4, 256) : 0; }
+static size_t seg_raw_part(int nv, int n_seq, int T, int n_seg) { return n_seg > 1 ? align_up((size_t)2 * n_seq * nv * T * 128 * 4, 256) : 0; }
+
 size_t linear_prefill_tc5_work_bytes(int nk, int nv, int n_seq, int T) {
     const int n_chunks = (T + C - 1) / C;
     (void)nk;
-    return ap_part(nv, n_seq, n_chunks) + aux_part(nv, n_seq, n_chunks);
+    int sc;
+    const int n_seg = delta_seg_plan(nv, n_seq, n_chunks, &sc);
+    return ap_part(nv, n_seq, n_chunks) + aux_part(nv, n_seq, n_chunks) + seg_state_part(nv, n_seq, n_seg) + seg_raw_part(nv, n_seq, T, n_seg);
 }
 size_t linear_prefill_tc5_dump_floats() { return DBG_FLOATS; }
 
@@ -812,10 +1034,18 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
                           "delta prep smem opt-in"));
         ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_prep64<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PrepSmem)),
                           "delta prep smem opt-in"));
-        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_scan_tc5<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM),
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_scan_tc5<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM),
                           "delta scan smem opt-in"));
-        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_scan_tc5<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM),
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_scan_tc5<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM),
                           "delta scan smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_scan_tc5<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM),
+                          "delta scan smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_scan_tc5<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM),
+                          "delta scan smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_seg_finish<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FinSmem)),
+                          "delta finish smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_delta_seg_finish<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FinSmem)),
+                          "delta finish smem opt-in"));
         configured = true;
     }
     const dim3 pgrid((unsigned)n_chunks, (unsigned)x.nk, (unsigned)n_seq);
@@ -832,8 +1062,26 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
     a.Y = Y; a.aux = aux; a.S = x.S; a.S_stride = x.S_stride; a.z = x.z; a.out = x.out; a.norm_w = x.norm_w;
     a.nk = x.nk; a.nv = x.nv; a.head_map = x.head_map; a.T = x.T; a.n_chunks = n_chunks;
     a.out_scale = x.out_scale; a.eps = x.eps; a.status = orn_status_word(); a.dbg = dbg; a.trace = g_delta_scan_trace;
-    dim3 grid((unsigned)x.nv, (unsigned)n_seq);
-    if (act_dtype == ORNITH_ACT_BF16) k_delta_scan_tc5<__nv_bfloat16><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);
-    else                              k_delta_scan_tc5<float><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);
-    return orn_check_launch("k_delta_scan_tc5");
+    a.n_seg = delta_seg_plan(x.nv, n_seq, n_chunks, &a.seg_chunks);
+    a.seg_state = (float *)((char *)aux + aux_part(x.nv, n_seq, n_chunks));
+    a.seg_raw = (float *)((char *)a.seg_state + seg_state_part(x.nv, n_seq, a.n_seg));
+    const bool bf = act_dtype == ORNITH_ACT_BF16;
+    if (a.n_seg <= 1) {
+        dim3 grid((unsigned)x.nv, (unsigned)n_seq);
+        if (bf) k_delta_scan_tc5<__nv_bfloat16, false><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);
+        else    k_delta_scan_tc5<float, false><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);
+        return orn_check_launch("k_delta_scan_tc5");
+    }
+    // few heads: the runs of the prompt side by side, then the carry over the runs and the finishing pass
+    dim3 grid((unsigned)x.nv, (unsigned)n_seq, (unsigned)(2 * a.n_seg - 1));
+    if (bf) k_delta_scan_tc5<__nv_bfloat16, true><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);
+    else    k_delta_scan_tc5<float, true><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);
+    ORN_TRY(orn_check_launch("k_delta_scan_tc5 (runs)"));
+    k_delta_seg_carry<<<dim3((unsigned)x.nv, (unsigned)n_seq, 16), 128, 0, s>>>(a);
+    ORN_TRY(orn_check_launch("k_delta_seg_carry"));
+    const int fin_tiles = (a.n_seg - 1) * ((a.seg_chunks * C + FIN_TOK - 1) / FIN_TOK);
+    dim3 fgrid((unsigned)fin_tiles, (unsigned)x.nv, (unsigned)n_seq);
+    if (bf) k_delta_seg_finish<__nv_bfloat16><<<fgrid, 128, sizeof(FinSmem), s>>>(a);
+    else    k_delta_seg_finish<float><<<fgrid, 128, sizeof(FinSmem), s>>>(a);
+    return orn_check_launch("k_delta_seg_finish");
 }

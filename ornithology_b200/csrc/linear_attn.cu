@@ -365,12 +365,6 @@ __global__ void __launch_bounds__(128) k_conv_silu_prefill(LinArgs a, float *Y) 
     }
 }
 
-__device__ __forceinline__ float4 act_ld4(const float *p, size_t i) { return *reinterpret_cast<const float4 *>(p + i); }
-__device__ __forceinline__ float4 act_ld4(const __nv_bfloat16 *p, size_t i) {
-    const uint2 u = *reinterpret_cast<const uint2 *>(p + i);
-    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
-                       __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
-}
 
 template <bool FAST>
 __device__ __forceinline__ float silu_sel(float x) { return FAST ? silu_fast(x) : silu_f(x); }

@@ -215,3 +215,31 @@ def test_tensor_core_scan_long_prompt_against_fp32_scan(monkeypatch):
     assert rel_err(o_tc, o_ref) < TOL and rel_err(S_tc, S_ref) < TOL
     assert rel_err(o_3, o_ref) < TOL and rel_err(S_3, S_ref) < TOL
     assert (c_tc == c_ref).all() and (c_3 == c_ref).all()
+
+
+@pytest.mark.parametrize("segments,bf16", [(4, False), (3, True), (0, False)])
+def test_segment_parallel_scan_against_oracle(oracle, monkeypatch, segments, bf16):
+    """Few heads: the prompt is cut into runs that are scanned side by side (from a zero state and from the identity),
+    stitched by a carry over the runs and a finishing product.  2000 tokens (a ragged last chunk), 4 key / 8 value
+    heads, two calls with the state carried; segments = 0 leaves the choice to the library (8 heads: 9 runs wanted,
+    3 possible at 8 chunks per run).  Outputs and final state against the CPU scan."""
+    import torch
+    from ornithology_b200 import device as D
+    if segments:
+        monkeypatch.setenv("ORNITH_CUDA_DELTA_SEGMENTS", str(segments))
+    layer, kw = linear_case(41, nk=4, nv=8)
+    dl = device_linear(layer, kw)
+    T1, T2 = 1500, 500
+    QKV, A, Bm, Z = linear_inputs(410, layer, T1 + T2, bf16)
+    S = np.zeros((layer.nv, 128, 128), np.float32); buf = np.zeros(3 * layer.cc, np.float32)
+    st = D.LinearState(dl, 1)
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dt = torch.bfloat16 if bf16 else torch.float32
+    tol = TOL_BF16_IO if bf16 else TOL
+    for t0, n in ((0, T1), (T1, T2)):
+        sl = slice(t0, t0 + n)
+        ref = oracle.linear_attn_prefill(layer, S, buf, QKV[sl], A[sl], Bm[sl], Z[sl], chunk=64)
+        out = D.linear_attn_prefill(dl, st, pos, _t(QKV[sl], dt)[None], _t(A[sl], dt)[None], _t(Bm[sl], dt)[None], _t(Z[sl], dt)[None], n, chunk=64)
+        assert rel_err(out.float().cpu().numpy()[0], ref) < tol, t0
+        assert rel_err(st.S.cpu().numpy()[0], S) < TOL, t0
+        D.advance(pos, n)
