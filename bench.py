@@ -100,28 +100,27 @@ class SlabGather:
         self.bufs = {}
 
     def run(self, layer_fn, T, slab, width, dtype):
-        """layer_fn(t0, n) -> [1, n, width] output of tokens t0..t0+n; returns the gathered [world][1][T][width]."""
+        """layer_fn(t0, n) -> [1, n, width] output of tokens t0..t0+n; returns the gathered blocks, one [world][1][n][width] per slab."""
         import torch
         import torch.distributed as dist
         if self.world == 1:
             for t0 in range(0, T, slab):
                 layer_fn(t0, min(slab, T - t0))
             return None
-        key = (T, width, dtype)
-        if key not in self.bufs:
-            self.bufs[key] = torch.empty((self.world, 1, T, width), dtype=dtype, device=self.dev)
+        key = (T, slab, width, dtype)
+        if key not in self.bufs:                        # one gathered block [world][1][n][width] per slab (slab-major, no re-layout copy)
+            self.bufs[key] = [torch.empty((self.world, 1, min(slab, T - t0), width), dtype=dtype, device=self.dev)
+                              for t0 in range(0, T, slab)]
         out = self.bufs[key]
         main = torch.cuda.current_stream(self.dev)
-        for t0 in range(0, T, slab):
+        for k, t0 in enumerate(range(0, T, slab)):
             n = min(slab, T - t0)
-            o = layer_fn(t0, n)
+            o = layer_fn(t0, n).contiguous()
             ev = torch.cuda.Event()
             ev.record(main)
             with torch.cuda.stream(self.comm):
                 self.comm.wait_event(ev)
-                piece = torch.empty((self.world, 1, n, width), dtype=dtype, device=self.dev)
-                dist.all_gather_into_tensor(piece, o.contiguous())
-                out[:, :, t0:t0 + n].copy_(piece)
+                dist.all_gather_into_tensor(out[k], o)
                 o.record_stream(self.comm)
         main.wait_stream(self.comm)
         return out
