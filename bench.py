@@ -126,20 +126,23 @@ class SlabGather:
         return out
 
 
-def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b", slab=8192):
+def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b", slab=8192, shard_of=1):
     """Long prefill: one 397B-shaped delta-net layer and one GQA layer over a T-token prompt, batch 1, bf16
     activations, head-sharded over the ranks (64/G value heads; 32/G query heads with the KV heads they read),
     head outputs all-gathered.  Returns per-layer times (max over ranks) and the figures derived from them;
     the stack has 45 delta-net and 15 GQA layers.  shape="35b" (32 value heads, 16 query heads) and a smaller T
-    give the small cases the profiles are taken on."""
+    give the small cases the profiles are taken on; shard_of=W on one rank runs the shard one rank of W would own
+    (no gather), which is how a shard's kernels are profiled on one GPU."""
     import torch
     from ornithology_b200 import device as D
     from ornithology_b200 import stack as S
 
     g = torch.Generator(device="cpu").manual_seed(2)
     NV, NH = (64, 32) if shape == "397b" else (32, 16)
-    nv, nk = NV // world, min(16, NV // world)
-    nh, nkv = NH // world, max(1, 2 // world)
+    sw = world if world > 1 else max(1, shard_of)       # how many ways the heads are split
+    NV_run, NH_run = (NV, NH) if world > 1 else (NV // sw, NH // sw)
+    nv, nk = NV // sw, min(16, NV // sw)
+    nh, nkv = NH // sw, max(1, 2 // sw)
     a = S.ARCHS[shape]
     w = S.linear_weights(dict(a, nk=nk, nv=nv), 0, 0)
     lin = D.LinearLayer(nk, nv, 128, 128, w["conv_w"], w["a_coef"], w["dt_bias"], w["norm_w"], device=dev)
@@ -178,13 +181,14 @@ def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b", slab=8192):
         ms_lin_k = _timed(lin_whole, dev, world, reps)
         ms_full_k = _timed(full_whole, dev, world, reps)
     # algorithmic work of the whole layer (all ranks): causal QK^T + PV; chunked scan of 64-token chunks
-    fl_full = 4.0 * 256 * NH * T * (T + 1) / 2
-    fl_lin = float(NV) * (T / 64) * (6 * 64 * 128 * 128 + 2 * 64 * 64 * 256)
+    fl_full = 4.0 * 256 * NH_run * T * (T + 1) / 2
+    fl_lin = float(NV_run) * (T / 64) * (6 * 64 * 128 * 128 + 2 * 64 * 64 * 256)
     burst, sustained, src = measured_tensor_peak()
     stack_ms = 45 * ms_lin + 15 * ms_full
     tf_full = fl_full / (ms_full_k * 1e-3) / 1e12
     tf_lin = fl_lin / (ms_lin_k * 1e-3) / 1e12
-    return {"workload": "%d-token prompt, %s-shaped layers, batch 1, bf16, head-sharded x%d" % (T, shape.upper(), world),
+    return {"workload": "%d-token prompt, %s-shaped layers, batch 1, bf16, head-sharded x%d%s"
+                        % (T, shape.upper(), sw, "" if world > 1 or sw == 1 else " (one shard timed on one GPU, no gather)"),
             "tokens": T, "delta_net_ms_per_layer": ms_lin, "gqa_ms_per_layer": ms_full,
             "delta_net_ms_no_gather": ms_lin_k, "gqa_ms_no_gather": ms_full_k,
             "gather": "none" if world == 1 else f"NCCL all-gather per {slab}-token slab on a second stream, under the next slab's compute",
@@ -765,6 +769,8 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill leg (1 GPU) and print its figures")
     ap.add_argument("--prefill-tokens", type=int, default=32768)
     ap.add_argument("--prefill-shape", default="397b", choices=["397b", "35b"])
+    ap.add_argument("--prefill-shard-of", type=int, default=1, choices=[1, 2, 4, 8],
+                    help="with --prefill-only: time the head shard one rank of this many would own")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -777,7 +783,7 @@ def main():
         import torch
         torch.cuda.set_device(local_rank)
         print(json.dumps(run_prefill(torch.device("cuda", local_rank), 0, 1, T=args.prefill_tokens, reps=1,
-                                     shape=args.prefill_shape)), flush=True)
+                                     shape=args.prefill_shape, shard_of=args.prefill_shard_of)), flush=True)
         return
     if world == 1 and args.gpus > 1:
         # launched without torchrun: re-launch one rank per GPU

@@ -61,7 +61,12 @@ int ornith_backend_cuda_available(void);
 /* ======================================================================== */
 #ifndef ORNITH_ATTN_H
 
-/* reference: src/ornith_attn.h:57-69 (field order and types are ABI) */
+/* reference: src/ornith_attn.h:57-69 (field order and types are ABI)
+ * The device copy of a cache is refreshed when `len` or the address of the host
+ * buffers differs from what the last call left.  A host that rewrites cached rows in
+ * place WITHOUT changing `len` must call ornith_kv_reset (and set `len` again) or
+ * ornith_kv_init_ex before the next ornith_gqa_step; the engine's own session load
+ * re-initialises the cache first (src/ornith_rforward.c:1129), so it needs nothing. */
 typedef struct {
     float  *K, *V;
     int8_t *Kq, *Vq;
@@ -202,9 +207,13 @@ typedef struct {
 
 /* scratch bytes ornith_cuda_full_attn_step asks for with n_seq sequences whose
  * longest context (after the append) is max_len: room for the split length that fills
- * the GPU at this batch (short splits for few sequences).  The step adapts to what it
- * is given: with less it uses longer splits, down to the need of the coarsest split
- * (2048 tokens above a 16k context); below that it fails with ORNITH_ERR_FORMAT. */
+ * the GPU at this batch (short splits for few sequences), for any cache mode and head
+ * size (the query does not see the cache, so it also covers the CUDA-core kernel's
+ * 512-token splits).  The step adapts to what it is given: with less it uses longer
+ * splits; when one of the tensor-core kernels serves the cache (head_dim 256, groups
+ * of up to 16 heads) the least it accepts is the need of the coarse split length
+ * (2048 tokens above a 16k context, 1024 above 8k, 512 above 1k, else 256), otherwise
+ * that of 512-token splits; below that it fails with ORNITH_ERR_FORMAT. */
 size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *layer, int n_seq, int max_len);
 
 /* One decode step of a full-attention layer for n_seq sequences, between the
@@ -323,9 +332,14 @@ size_t ornith_cuda_linear_attn_prefill_scratch(const ornith_cuda_linear_layer *l
  * exactly where T decode steps would leave them.
  * Replaces linear_attn_prefill() minus its matvecs (reference: src/ornith_rforward.c:571-616).
  *   qkv [n_seq][T][Cc], a,b [n_seq][T][nv], z,out [n_seq][T][nv*dv]
- *   scratch: 256-byte aligned.  With dk = dv = 128 the scan runs in 32-token chunks with tf32
- *   tensor-core products whatever `chunk` says; with ORNITH_CUDA_PREFILL_FP32=1 in the
- *   environment every product stays in fp32 and chunk >= 32 / < 32 selects 32 / 16 tokens. */
+ *   scratch: 256-byte aligned.  With dk = dv = 128 the scan runs in 64-token chunks on the
+ *   tcgen05 tensor cores (tf32 products, f32 accumulation; the state of a head stays in tensor
+ *   memory for the whole prompt) whatever `chunk` says.  When the batch has too few
+ *   (sequence, value head) units to fill the GPU the prompt is cut into runs of chunks that are
+ *   scanned side by side and stitched by their transition matrices; ORNITH_CUDA_DELTA_SEGMENTS=n
+ *   forces n runs (1 = off).  ORNITH_CUDA_DELTA_SCAN=mma selects the older mma.sync scan
+ *   (32-token chunks); ORNITH_CUDA_PREFILL_FP32=1 keeps every product in fp32 on the CUDA cores
+ *   (chunk >= 32 / < 32 selects 32 / 16 tokens). */
 ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *layer,
                                               const ornith_cuda_linear_state *st, const int32_t *pos,
                                               const void *qkv, const void *a, const void *b,

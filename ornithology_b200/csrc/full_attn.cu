@@ -532,12 +532,24 @@ static long long head_groups(const ornith_cuda_full_layer *l, int n_seq) {
     return (long long)n_seq * l->n_kv_heads * ((g + 7) / 8);
 }
 // Scratch of one decode step whose tensor-core kernels use splits of tps_mma tokens: query rows, one arrival
-// counter per (sequence, head), then the partials (the CUDA-core kernel's split count is covered too).
-static size_t step_need(const ornith_cuda_full_layer *l, int n_seq, int max_len, int tps_mma) {
-    const int ta = split_tokens(max_len), t = ta < tps_mma ? ta : tps_mma, nsplit = (max_len + t - 1) / t;
+// counter per (sequence, head), then the partials.  cuda_core: the step may be served by the CUDA-core kernel
+// (fixed 512- or 128-token splits), so its split count is covered too; the size query has to assume that, since
+// it does not see the cache; the step itself knows which kernel it dispatches.
+static size_t step_need(const ornith_cuda_full_layer *l, int n_seq, int max_len, int tps_mma, bool cuda_core) {
+    const int ta = split_tokens(max_len), t = cuda_core ? (ta < tps_mma ? ta : tps_mma) : tps_mma,
+              nsplit = (max_len + t - 1) / t;
     return align_up((size_t)n_seq * l->n_heads * l->head_dim * sizeof(float), 256) +
            align_up((size_t)n_seq * l->n_heads * sizeof(int), 256) +
            align_up((size_t)n_seq * l->n_heads * nsplit * (l->head_dim + 2) * sizeof(float), 256);
+}
+
+// Whether a decode step over this cache runs on one of the tensor-core kernels (the dispatch of
+// ornith_cuda_full_attn_step below follows the same order).
+static bool decode_on_tensor_cores(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv) {
+    if (force_generic_decode()) return false;
+    const KvView v = make_view(kv);
+    return gqa_decode_q8_mma_supported(v, l->n_heads) || gqa_decode_f32_tc_supported(v, l->n_heads) ||
+           gqa_decode_i8_raw_supported(v, l->n_heads);
 }
 
 template <typename ACT>
@@ -571,7 +583,7 @@ extern "C" {
 size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *l, int n_seq, int max_len) {
     if (!l || n_seq <= 0 || l->n_kv_heads <= 0) return 0;
     if (max_len < 1) max_len = 1;
-    return step_need(l, n_seq, max_len, split_tokens_fine(max_len, head_groups(l, n_seq)));
+    return step_need(l, n_seq, max_len, split_tokens_fine(max_len, head_groups(l, n_seq)), true);
 }
 
 ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
@@ -588,15 +600,16 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     // it fits, down to the coarse one (ornith_cuda_full_attn_step_scratch asks for the fine one; a caller with a
     // fixed budget may pass less).  ORNITH_CUDA_DECODE_SPLIT=<tokens> overrides it when that fits too.
     int tps_mma = split_tokens_fine(max_len, head_groups(l, B));
+    const bool cuda_core = !decode_on_tensor_cores(l, kv);
     {
         const int coarse = split_tokens_coarse(max_len), tps_max = tps_mma > coarse ? tps_mma : coarse;
-        while (step_need(l, B, max_len, tps_mma) > scratch_bytes && tps_mma < tps_max)
+        while (step_need(l, B, max_len, tps_mma, cuda_core) > scratch_bytes && tps_mma < tps_max)
             tps_mma = (2 * tps_mma < tps_max) ? 2 * tps_mma : tps_max;
         static int forced = -1;
         if (forced < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_SPLIT"); forced = e ? atoi(e) : 0; }
-        if (forced >= 64 && step_need(l, B, max_len, forced / 64 * 64) <= scratch_bytes) tps_mma = forced / 64 * 64;
+        if (forced >= 64 && step_need(l, B, max_len, forced / 64 * 64, cuda_core) <= scratch_bytes) tps_mma = forced / 64 * 64;
     }
-    if (!scratch || step_need(l, B, max_len, tps_mma) > scratch_bytes) {
+    if (!scratch || step_need(l, B, max_len, tps_mma, cuda_core) > scratch_bytes) {
         orn_record_error("full_attn_step: scratch too small (%zu bytes given)", scratch_bytes);
         return ORNITH_ERR_FORMAT;
     }
@@ -771,7 +784,7 @@ ornith_status ornith_cuda_full_attn_step_static(const ornith_cuda_full_layer *l,
     if (kv->n_seq <= 0) return ORNITH_OK;
     // the step adapts its split length to the scratch it is given: what must fit is the coarse split's need
     const int mlen = max_len < 1 ? 1 : max_len, fine = split_tokens_fine(mlen, head_groups(l, kv->n_seq)), coarse = split_tokens_coarse(mlen);
-    const size_t need = step_need(l, kv->n_seq, mlen, fine > coarse ? fine : coarse);
+    const size_t need = step_need(l, kv->n_seq, mlen, fine > coarse ? fine : coarse, !decode_on_tensor_cores(l, kv));
     if (need > (size_t)ORNITH_CUDA_STATIC_SCRATCH_BYTES) {
         orn_record_error("full_attn_step_static: %d sequences x context %d need %zu bytes of scratch, the built-in "
                          "array holds %u; use ornith_cuda_full_attn_step with caller scratch",

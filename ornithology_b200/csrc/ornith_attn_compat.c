@@ -267,7 +267,7 @@ void ornith_gqa_reference(const float *Q, const float *K, const float *V, int T,
         if (ornith_cuda_full_attn_prefill(&L, &kv, dlen, NULL, dq, dk, dv, dout, ORNITH_ACT_F32, T, T, ds, sb, NULL)
             != ORNITH_OK)
             goto done;
-        ornith_cuda_d2h(O, dout, qn);
+        if (ornith_cuda_d2h(O, dout, qn) != ORNITH_OK) ornith_set_error("gqa_reference: copy of the output back to the host failed");
     }
 done:
     pthread_mutex_unlock(&g_lock);
@@ -302,7 +302,7 @@ void ornith_delta_step(ornith_delta_state *s, const float *q, const float *k, co
                                    (float *)dg, (float *)dg + 1, (float *)dout, NULL) != ORNITH_OK)
             goto done;
         if (ornith_cuda_d2h(o, dout, vn) != ORNITH_OK) goto done;
-        ornith_cuda_d2h(s->S, dS, sn);
+        if (ornith_cuda_d2h(s->S, dS, sn) != ORNITH_OK) ornith_set_error("delta: copy of the state back to the host failed");
     }
 done:
     pthread_mutex_unlock(&g_lock);
@@ -327,7 +327,7 @@ void ornith_delta_prefill(ornith_delta_state *s, const float *Q, const float *K,
                                       (float *)db, T, chunk, (float *)dout, NULL) != ORNITH_OK)
             goto done;
         if (ornith_cuda_d2h(O, dout, vn) != ORNITH_OK) goto done;
-        ornith_cuda_d2h(s->S, dS, sn);
+        if (ornith_cuda_d2h(s->S, dS, sn) != ORNITH_OK) ornith_set_error("delta: copy of the state back to the host failed");
     }
 done:
     pthread_mutex_unlock(&g_lock);
@@ -363,7 +363,7 @@ void ornith_conv_prefill(ornith_conv_state *cs, const float *X, const float *wei
                                    (float *)dout, NULL) != ORNITH_OK)
             goto done;
         if (ornith_cuda_d2h(OUT, dout, xn) != ORNITH_OK) goto done;
-        ornith_cuda_d2h(cs->buf, di, in);
+        if (ornith_cuda_d2h(cs->buf, di, in) != ORNITH_OK) ornith_set_error("conv: copy of the history back to the host failed");
     }
 done:
     pthread_mutex_unlock(&g_lock);

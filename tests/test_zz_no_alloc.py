@@ -76,3 +76,36 @@ def test_static_scratch_entry_rejects_oversized_requests():
                                                _p(out), D.ACT_F32, L, None)
     assert st != 0
     assert b"built-in" in lib.ornith_cuda_last_error()
+
+
+def test_static_scratch_entry_fits_long_contexts_at_the_coarse_split():
+    """20 sequences x 16 heads with a 32768-token bound: the partials of 512-token splits (21 MB) do not fit the
+    built-in array, those of the 2048-token splits the tensor-core kernel accepts (5.6 MB) do, so the call must be
+    served, and must agree with the regular entry point given ample scratch."""
+    import torch
+    from ornithology_b200 import _lib, device as D
+    lib = _lib.load()
+    layer = full_case(33)
+    dl = device_full(layer)
+    B, bound = 20, 32768
+    ctx = [3000 + 97 * b for b in range(B)]
+    caps = [c + 1 for c in ctx]
+    g = torch.Generator(device="cuda").manual_seed(6)
+    T = max(ctx)
+    k = torch.randn(B, T, layer.nkv * layer.hd, generator=g, device="cuda")
+    v = torch.randn(B, T, layer.nkv * layer.hd, generator=g, device="cuda")
+    kvs = []
+    for _ in range(2):
+        kv = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, caps)
+        D.kv_append(dl, kv, torch.zeros(B, dtype=torch.int32, device="cuda"), k, v, T=T)
+        kvs.append(kv)
+    lens = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    QP, K, V = [torch.from_numpy(np.stack(x)).cuda() for x in
+                zip(*[[a[0] for a in full_inputs(950 + b, layer, 1)] for b in range(B)])]
+    ref = D.full_attn_step(dl, kvs[0], lens, QP, K, V, max_len=bound)
+    out = torch.full_like(ref, float("nan"))
+    st = lib.ornith_cuda_full_attn_step_static(C.byref(dl.c), C.byref(kvs[1].c), _p(lens), None, _p(QP), _p(K), _p(V),
+                                               _p(out), D.ACT_F32, bound, None)
+    assert st == 0, lib.ornith_cuda_last_error()
+    torch.cuda.synchronize()
+    assert rel_err(out.cpu().numpy(), ref.cpu().numpy()) < TOL
