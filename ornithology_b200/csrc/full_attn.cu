@@ -531,25 +531,33 @@ static long long head_groups(const ornith_cuda_full_layer *l, int n_seq) {
     const int g = l->n_heads / l->n_kv_heads;
     return (long long)n_seq * l->n_kv_heads * ((g + 7) / 8);
 }
-// Scratch of one decode step whose tensor-core kernels use splits of tps_mma tokens: query rows, one arrival
-// counter per (sequence, head), then the partials.  cuda_core: the step may be served by the CUDA-core kernel
-// (fixed 512- or 128-token splits), so its split count is covered too; the size query has to assume that, since
-// it does not see the cache; the step itself knows which kernel it dispatches.
-static size_t step_need(const ornith_cuda_full_layer *l, int n_seq, int max_len, int tps_mma, bool cuda_core) {
-    const int ta = split_tokens(max_len), t = cuda_core ? (ta < tps_mma ? ta : tps_mma) : tps_mma,
+// Scratch of one decode step: query rows, one arrival counter per (sequence, head), then the partials.
+//   SPLIT_TC  a tensor-core kernel with splits of tps_mma tokens serves the cache;
+//   BALANCED  the Q8_0 raw-fragment kernel with its own schedule: a fixed number of partial slots per head;
+//   ANY       the size query, which does not see the cache: the larger of the two, with the CUDA-core kernel's
+//             fixed 512- or 128-token splits covered as well.  A step served by the CUDA-core kernel needs this too.
+enum DecodePath { PATH_ANY, PATH_SPLIT_TC, PATH_BALANCED };
+static size_t step_need(const ornith_cuda_full_layer *l, int n_seq, int max_len, int tps_mma, DecodePath path) {
+    const int ta = split_tokens(max_len), t = path == PATH_ANY ? (ta < tps_mma ? ta : tps_mma) : tps_mma,
               nsplit = (max_len + t - 1) / t;
+    size_t rows = (size_t)n_seq * l->n_heads * nsplit;
+    if (path != PATH_SPLIT_TC && l->n_kv_heads > 0 && l->n_heads % l->n_kv_heads == 0) {
+        const size_t bal = (size_t)l->n_heads * gqa_decode_q8_raw_slots(l->n_kv_heads, l->n_heads, n_seq, max_len);
+        rows = path == PATH_BALANCED ? bal : (bal > rows ? bal : rows);
+    }
     return align_up((size_t)n_seq * l->n_heads * l->head_dim * sizeof(float), 256) +
            align_up((size_t)n_seq * l->n_heads * sizeof(int), 256) +
-           align_up((size_t)n_seq * l->n_heads * nsplit * (l->head_dim + 2) * sizeof(float), 256);
+           align_up(rows * (l->head_dim + 2) * sizeof(float), 256);
 }
 
 // Whether a decode step over this cache runs on one of the tensor-core kernels (the dispatch of
 // ornith_cuda_full_attn_step below follows the same order).
-static bool decode_on_tensor_cores(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv) {
-    if (force_generic_decode()) return false;
+static DecodePath decode_path(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv) {
+    if (force_generic_decode()) return PATH_ANY;
     const KvView v = make_view(kv);
-    return gqa_decode_q8_mma_supported(v, l->n_heads) || gqa_decode_f32_tc_supported(v, l->n_heads) ||
-           gqa_decode_i8_raw_supported(v, l->n_heads);
+    if (gqa_decode_q8_raw_balanced(v, l->n_heads)) return PATH_BALANCED;
+    return (gqa_decode_q8_mma_supported(v, l->n_heads) || gqa_decode_f32_tc_supported(v, l->n_heads) ||
+            gqa_decode_i8_raw_supported(v, l->n_heads)) ? PATH_SPLIT_TC : PATH_ANY;
 }
 
 template <typename ACT>
@@ -583,7 +591,7 @@ extern "C" {
 size_t ornith_cuda_full_attn_step_scratch(const ornith_cuda_full_layer *l, int n_seq, int max_len) {
     if (!l || n_seq <= 0 || l->n_kv_heads <= 0) return 0;
     if (max_len < 1) max_len = 1;
-    return step_need(l, n_seq, max_len, split_tokens_fine(max_len, head_groups(l, n_seq)), true);
+    return step_need(l, n_seq, max_len, split_tokens_fine(max_len, head_groups(l, n_seq)), PATH_ANY);
 }
 
 ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const ornith_cuda_kv *kv,
@@ -600,16 +608,16 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     // it fits, down to the coarse one (ornith_cuda_full_attn_step_scratch asks for the fine one; a caller with a
     // fixed budget may pass less).  ORNITH_CUDA_DECODE_SPLIT=<tokens> overrides it when that fits too.
     int tps_mma = split_tokens_fine(max_len, head_groups(l, B));
-    const bool cuda_core = !decode_on_tensor_cores(l, kv);
+    const DecodePath path = decode_path(l, kv);
     {
         const int coarse = split_tokens_coarse(max_len), tps_max = tps_mma > coarse ? tps_mma : coarse;
-        while (step_need(l, B, max_len, tps_mma, cuda_core) > scratch_bytes && tps_mma < tps_max)
+        while (step_need(l, B, max_len, tps_mma, path) > scratch_bytes && tps_mma < tps_max)
             tps_mma = (2 * tps_mma < tps_max) ? 2 * tps_mma : tps_max;
         static int forced = -1;
         if (forced < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_SPLIT"); forced = e ? atoi(e) : 0; }
-        if (forced >= 64 && step_need(l, B, max_len, forced / 64 * 64, cuda_core) <= scratch_bytes) tps_mma = forced / 64 * 64;
+        if (forced >= 64 && step_need(l, B, max_len, forced / 64 * 64, path) <= scratch_bytes) tps_mma = forced / 64 * 64;
     }
-    if (!scratch || step_need(l, B, max_len, tps_mma, cuda_core) > scratch_bytes) {
+    if (!scratch || step_need(l, B, max_len, tps_mma, path) > scratch_bytes) {
         orn_record_error("full_attn_step: scratch too small (%zu bytes given)", scratch_bytes);
         return ORNITH_ERR_FORMAT;
     }
@@ -631,10 +639,12 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     d.kv = make_view(kv); d.kv_len = kv_len; d.q_prep = q_prep; d.part = part;
     d.nh = nh; d.scale = attn_scale(l);
     d.group_ctr = group_ctr; d.qproj = qproj; d.out = out; d.gated = l->gated; d.act_dtype = act_dtype;
+    d.n_seq = B; d.max_len = max_len; d.status = nullptr; d.piece_cost = 0;
     bool merged = false;
     int nsplit_used;
     if (gqa_decode_q8_mma_supported(d.kv, nh) && !force_generic_decode()) {
         d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
+        if (path == PATH_BALANCED) d.nsplit = nsplit_used = gqa_decode_q8_raw_slots(l->n_kv_heads, nh, B, max_len);
         ORN_TRY(launch_gqa_decode_q8_mma(d, B, st, &merged));
     } else if (gqa_decode_f32_tc_supported(d.kv, nh) && !force_generic_decode()) {
         d.tokens_per_split = tps_mma; d.nsplit = nsplit_used = (max_len + tps_mma - 1) / tps_mma;
@@ -784,7 +794,7 @@ ornith_status ornith_cuda_full_attn_step_static(const ornith_cuda_full_layer *l,
     if (kv->n_seq <= 0) return ORNITH_OK;
     // the step adapts its split length to the scratch it is given: what must fit is the coarse split's need
     const int mlen = max_len < 1 ? 1 : max_len, fine = split_tokens_fine(mlen, head_groups(l, kv->n_seq)), coarse = split_tokens_coarse(mlen);
-    const size_t need = step_need(l, kv->n_seq, mlen, fine > coarse ? fine : coarse, !decode_on_tensor_cores(l, kv));
+    const size_t need = step_need(l, kv->n_seq, mlen, fine > coarse ? fine : coarse, decode_path(l, kv));
     if (need > (size_t)ORNITH_CUDA_STATIC_SCRATCH_BYTES) {
         orn_record_error("full_attn_step_static: %d sequences x context %d need %zu bytes of scratch, the built-in "
                          "array holds %u; use ornith_cuda_full_attn_step with caller scratch",

@@ -16,6 +16,9 @@ struct DecodeArgs {
     const void *qproj;                   // gate = second half of each head's projection row (gated != 0)
     void *out;
     int gated, act_dtype;
+    int n_seq, max_len;                  // batch size and the call's bound on any context after the append
+    int piece_cost;                      // balanced schedule: tiles charged per sequence for the fixed work of a piece
+    unsigned int *status;                // device status word (a bounded wait that gave up sets ORN_WAIT_DECODE), or NULL
 };
 
 // Tensor-core split-K decode over Q8_0 rows, head_dim 256, up to 16 query heads
@@ -27,6 +30,11 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
 // Variant for groups of up to 8 query heads that builds its MMA fragments straight
 // from the staged raw rows (gqa_decode_q8_raw.cu).
 ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged);
+// Whether a step over this cache is served by that kernel with its balanced schedule (token ranges of equal
+// length found on the device instead of a grid of fixed splits), and then how many partial slots per head its
+// scratch needs: a.nsplit = gqa_decode_q8_raw_slots(...) and a.part laid out [head][slot][hd + 2].
+bool gqa_decode_q8_raw_balanced(const KvView &kv, int nh);
+int gqa_decode_q8_raw_slots(int nkv, int nh, int n_seq, int max_len);
 
 // The same for int8-per-head rows (gqa_decode_i8_raw.cu), up to 8 query heads per KV head.
 bool gqa_decode_i8_raw_supported(const KvView &kv, int nh);

@@ -549,6 +549,22 @@ bool gqa_decode_q8_mma_supported(const KvView &kv, int nh) {
            ((uintptr_t)kv.K % 16) == 0 && ((uintptr_t)kv.V % 16) == 0;
 }
 
+// ORNITH_CUDA_DECODE_VARIANT=tile selects the variant that decodes V into an f16 tile, =raw the raw-fragment
+// kernel for groups of 9-16 heads too (two CTAs of 8 heads per KV head)
+static int decode_variant() {
+    static int variant = -1;
+    if (variant < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); variant = !e ? 0 : (e[0] == 't' ? 1 : (e[0] == 'r' ? 2 : 0)); }
+    return variant;
+}
+
+// ORNITH_CUDA_DECODE_SCHED=grid keeps the grid of fixed splits for the raw-fragment kernel (A/B comparison)
+bool gqa_decode_q8_raw_balanced(const KvView &kv, int nh) {
+    static int grid_sched = -1;
+    if (grid_sched < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_SCHED"); grid_sched = (e && e[0] == 'g') ? 1 : 0; }
+    if (grid_sched || !gqa_decode_q8_mma_supported(kv, nh)) return false;
+    return decode_variant() == 2 || (decode_variant() == 0 && nh / kv.nkv <= 8);
+}
+
 ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged) {
     *merged = false;
     static bool configured_dev[ORN_MAX_DEVICES] = {};
@@ -566,10 +582,7 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
         configured3 = true;
     }
     dim3 grid(a.nsplit, a.kv.nkv, n_seq);
-    // ORNITH_CUDA_DECODE_VARIANT=tile selects the variant that decodes V into an f16 tile, =raw the raw-fragment
-    // kernel for groups of 9-16 heads too (two CTAs of 8 heads per KV head)
-    static int variant = -1;
-    if (variant < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); variant = !e ? 0 : (e[0] == 't' ? 1 : (e[0] == 'r' ? 2 : 0)); }
+    const int variant = decode_variant();
     const int use_tile = variant == 1;
     if (a.nh / a.kv.nkv <= 8 || variant == 2) {          // larger groups: k_gqa_decode_q8_mma below (the raw kernel would convert every row twice)
         if (!use_tile) return launch_gqa_decode_q8_raw(a, n_seq, st, merged);

@@ -110,6 +110,12 @@ __device__ __forceinline__ void qk_chunk(uint32_t raw0, uint32_t raw1, const uin
     mma16816(acc, A, qv.x, qv.y);
 }
 
+__device__ __forceinline__ unsigned short lds_u16(uint32_t addr) {
+    unsigned short u;
+    asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(u) : "r"(addr));
+    return u;
+}
+
 // ---- one m-tile of O^T += V^T P^T from chunk C of the staged V rows ------------------------
 // raw0 / raw1: transposed-ldmatrix registers: element 8C+r for tokens (2j, 2j+1) and
 // (2j+8, 2j+9).  sc*: the f16 scale pairs of the two candidate blocks for those tokens.
@@ -162,22 +168,22 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 
 // Stage the 16 rows of one tile of K (or V).  A full tile is one tensor copy (map != nullptr;
 // tok_abs = the tile's first token counted from the start of the pool); otherwise lanes 0-15
-// copy one row each, and rows past the end of the split are not copied: the slot keeps
-// earlier (finite) contents and the token is masked in the softmax.
-__device__ __forceinline__ void issue_rows16(unsigned char *slot, uint32_t bar, const unsigned char *src_base,
-                                             size_t row_stride, int tok0, int t1, int lane, const CUtensorMap *map,
-                                             int head, int tok_abs) {
-    const int valid = min(TILE, t1 - tok0);
-    if (map != nullptr && valid == TILE) {
+// copy one row each, and rows past the end of the piece are not copied: the slot keeps
+// earlier (finite) contents and the token is masked in the softmax.  The row addresses of
+// that rare path are worked out here, from the pool, rather than carried through the tile loop.
+__device__ __forceinline__ void issue_rows16(uint32_t slot, uint32_t bar, const unsigned char *pool, int nkv,
+                                             int valid, int lane, const CUtensorMap *map, int head, int tok_abs) {
+    if (map != nullptr && valid >= TILE) {
         if (lane == 0) {
             mbar_expect_tx(bar, (uint32_t)RAW_TILE);
-            tensor_copy_tile(smem_u32(slot), map, head, tok_abs, bar);
+            tensor_copy_tile(slot, map, head, tok_abs, bar);
         }
         return;
     }
+    valid = min(valid, TILE);
     if (lane == 0) mbar_expect_tx(bar, (uint32_t)(valid * ROWB));
     __syncwarp();
-    if (lane < valid) bulk_copy_row(smem_u32(slot + lane * ROWB), src_base + (size_t)(tok0 + lane) * row_stride, bar);
+    if (lane < valid) bulk_copy_row(slot + lane * ROWB, pool + ((size_t)(tok_abs + lane) * nkv + head) * ROWB, bar);
 }
 
 template <int C>
@@ -191,346 +197,467 @@ __device__ __forceinline__ void store_chunk(float *Ow, const float (&acc)[4], in
     Ow[(2 * j + 1) * HD + dim + 1] = acc[3];
 }
 
+// Tiles (16 tokens) a decode step reads for sequence b: its context plus the token being appended; nothing for a
+// sequence whose cache is full (the step leaves it alone).
+__device__ __forceinline__ int seq_tiles(const DecodeArgs &a, int b) {
+    const int len0 = a.kv_len[b];
+    const int cap = (int)(a.kv.seq_off[b + 1] - a.kv.seq_off[b]);
+    return len0 >= cap ? 0 : (len0 + TILE) / TILE;
+}
+
+// Inclusive prefix sum of v over the 128 threads of the CTA; *total = the sum.  wt: 4 ints of shared memory.
+__device__ __forceinline__ int block_scan128(int v, int *wt, int *total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) wt[warp] = incl;
+    __syncthreads();
+    int add = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < NWARP; w++) { const int x = wt[w]; if (w < warp) add += x; tot += x; }
+    __syncthreads();
+    *total = tot;
+    return incl + add;
+}
+
+// BALANCED = false: one CTA per (head group, split of tokens_per_split tokens, sequence); grid (groups, nsplit, n_seq).
+// BALANCED = true:  grid (groups, ranges).  The 16-token tiles of all sequences, laid end to end, are cut into
+//   gridDim.y ranges of equal length (found on the device from kv_len: the host never learns the contexts), and a
+//   CTA walks the pieces of the sequences that fall into its range, one partial per piece.  Every CTA is resident
+//   at once and all of them stream the same number of rows, so no SM runs dry before the others; a sequence
+//   shorter than a range costs one partial, a longer one as many as the ranges it touches.  The CTAs of the head
+//   groups that share the same rows (blockIdx.x) walk the same range side by side.
+template <bool BALANCED>
 __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, const __grid_constant__ CUtensorMap map_k,
                                                               const __grid_constant__ CUtensorMap map_v, int tensor_copies) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ float m_s[NWARP][8], l_s[NWARP][8];
     __shared__ __align__(8) unsigned long long bars[NWARP][2];
-    __shared__ int pipe_failed;
+    __shared__ int pipe_failed, last_one, scan_s[NWARP], found_s[2];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     unsigned char *wbase = smem + QS_BYTES + warp * WARP_BYTES;
     uint2 *Q_s = reinterpret_cast<uint2 *>(smem);               // [k-step][lane]
     if (tid == 0) pipe_failed = 0;
+    if (lane == 0) {
+        mbar_init(smem_u32(&bars[warp][0]), 1);
+        mbar_init(smem_u32(&bars[warp][1]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
 
-    // KV head on the fastest grid axis: the CTAs that read the two interleaved halves of the
-    // same token rows are launched side by side and share DRAM pages while they are open
-    // a group of more than 8 query heads is walked by two CTAs of 8 heads each; they sit side by side on
-    // the fastest grid axis, so the second one finds the rows the first one fetched in L2
+    // a group of more than 8 query heads is walked by two CTAs of 8 heads each; they and the CTAs of the other KV
+    // heads sit side by side on the fastest grid axis: the rows of the KV heads interleave in memory, so these CTAs
+    // share DRAM pages while they are open, and the second CTA of a group finds the rows of the first one in L2
     const int nkv = a.kv.nkv, Gall = a.nh / nkv, sub = (Gall + 7) / 8;
-    const int kvh = (int)blockIdx.x / sub, hs = (int)blockIdx.x % sub, split = blockIdx.y, b = blockIdx.z;
+    const int kvh = (int)blockIdx.x / sub, hs = (int)blockIdx.x % sub;
     const int G = min(8, Gall - 8 * hs), head0 = kvh * Gall + 8 * hs;
-    const int64_t base = a.kv.seq_off[b];
-    const int cap = (int)(a.kv.seq_off[b + 1] - base);
-    const int len0 = a.kv_len[b];
-    // A CTA that leaves early still has to wait for the grid in front (programmatic dependent launch):
-    // a grid whose CTAs all returned without waiting would retire, and let the next kernel in the
-    // stream start, before the append kernel has finished.
-    if (len0 >= cap) { asm volatile("griddepcontrol.wait;\n" ::: "memory"); return; }
-    const int L = len0 + 1;
-    const int t0 = split * a.tokens_per_split, t1 = min(L, t0 + a.tokens_per_split);
-    float *part0 = a.part + (((size_t)b * a.nh + (size_t)head0) * a.nsplit + split) * (HD + 2);
-    const size_t part_stride = (size_t)a.nsplit * (HD + 2);
-    if (t0 >= L) {
-        asm volatile("griddepcontrol.wait;\n" ::: "memory");
-        if (tid < G) { part0[tid * part_stride] = -INFINITY; part0[tid * part_stride + 1] = 0.0f; }
-        return;
-    }
     const int r = lane >> 2, j = lane & 3;
-
-    const int ntiles = (t1 - t0 + TILE - 1) / TILE;
-    const size_t row_stride = (size_t)nkv * ROWB;
-    const unsigned char *Kbase = a.kv.K + ((size_t)base * nkv + kvh) * ROWB;
-    const unsigned char *Vbase = a.kv.V + ((size_t)base * nkv + kvh) * ROWB;
     const CUtensorMap *mk = tensor_copies ? &map_k : nullptr, *mv = tensor_copies ? &map_v : nullptr;
-    const int tok_pool = (int)base + t0;                        // first token of the split, counted from the start of the pool
-
-
-    // ---- per-warp staging slots (K rows, V rows): zero them once (skipped tail rows must stay
-    //      finite), one mbarrier each.  K of the next tile is requested as soon as the score
-    //      loop is done with the slot, V right after the value loop.  The first tile is requested
-    //      before anything else so that its latency hides behind the query prologue; under
-    //      programmatic dependent launch that happens while the append kernel of this call may
-    //      still be running, so only for tiles that end before the row it appends (token len0).
-    unsigned char *rawK = wbase, *rawV = wbase + RAW_TILE;
-    {
-        uint4 *z = reinterpret_cast<uint4 *>(wbase);
-        for (int i = lane; i < WARP_BYTES / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (lane == 0) {
-            mbar_init(smem_u32(&bars[warp][0]), 1);
-            mbar_init(smem_u32(&bars[warp][1]), 1);
-            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        }
-        fence_proxy_async();                                      // generic-proxy zeros before async-proxy copies
-        __syncwarp();
-    }
     const uint32_t barK = smem_u32(&bars[warp][0]), barV = smem_u32(&bars[warp][1]);
-    int it = warp;
-    const bool first_issued = it < ntiles && t0 + (it + 1) * TILE <= len0;
-    if (first_issued) {
-        issue_rows16(rawK, barK, Kbase, row_stride, t0 + it * TILE, t1, lane, mk, kvh, tok_pool + it * TILE);
-        issue_rows16(rawV, barV, Vbase, row_stride, t0 + it * TILE, t1, lane, mv, kvh, tok_pool + it * TILE);
-    }
-    // everything below reads what the append kernel of this call wrote (query rows, the new K/V row, zeroed counters)
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
-
-    // ---- query group -> B fragments in stream order: lane (head r, quarter j), k-step c
-    //      holds q at the dims of elements 8c+2j and 8c+2j+1 (zeros where the stream has a scale)
-    float rs_mine;
-    {
-        const float *q = a.q_prep + ((size_t)b * a.nh + (size_t)head0 + (r < G ? r : 0)) * HD;
-        float mx = 0.0f;
-        {   // 16 independent 128-bit loads: the prologue is per CTA, keep it off the latency path
-            const float4 *q4 = reinterpret_cast<const float4 *>(q + j * 64);
-            float4 t[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) t[i] = q4[i];
-#pragma unroll
-            for (int i = 0; i < 16; i++)
-                mx = fmaxf(mx, fmaxf(fmaxf(fabsf(t[i].x), fabsf(t[i].y)), fmaxf(fabsf(t[i].z), fabsf(t[i].w))));
-        }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        int e = 0;
-        if (mx > 0.0f && mx < INFINITY) (void)frexpf(mx, &e);
-        const float down = (r < G) ? exp2f((float)-e) : 0.0f;
-        for (int c = warp; c < NCHUNK; c += NWARP) {      // the four warps share the work; identical per warp otherwise
-            uint32_t pk[2];
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int el = 8 * c + 2 * j + h;
-                const int bl = el / 17, idx = el - 17 * bl;
-                // scale slots read dims 0,1 (any valid address) and are zeroed by the multiplier
-                const int d = (idx != 0) ? 32 * bl + 2 * (idx - 1) : 0;
-                const float2 v = *reinterpret_cast<const float2 *>(q + d);
-                const float mul = (idx != 0) ? down : 0.0f;
-                pk[h] = pack_h2(v.x * mul, v.y * mul);
-            }
-            Q_s[c * 32 + lane] = make_uint2(pk[0], pk[1]);
-        }
-        rs_mine = (r < G) ? a.scale * exp2f((float)e) * LOG2E : 0.0f;
-    }
-    const float rsA = __shfl_sync(0xffffffffu, rs_mine, (2 * j) * 4);
-    const float rsB = __shfl_sync(0xffffffffu, rs_mine, (2 * j + 1) * 4);
-
-    float o[NCHUNK][4];
-#pragma unroll
-    for (int i = 0; i < NCHUNK; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-    float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
+    const uint32_t rawK = smem_u32(wbase), rawV = rawK + RAW_TILE;      // staging slots, as shared-memory addresses
     // ldmatrix row address of this lane inside a staged tile: matrices 0,1 = chunk c (tokens 0-7, 8-15),
     // matrices 2,3 = chunk c + 1
     const uint32_t lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
 
-    __syncthreads();                                              // publishes Q_s
-    const uint2 *q_frag = Q_s + lane;
-    bool pipe_ok = true;
-    if (it < ntiles && !first_issued) {
-        issue_rows16(rawK, barK, Kbase, row_stride, t0 + it * TILE, t1, lane, mk, kvh, tok_pool + it * TILE);
-        issue_rows16(rawV, barV, Vbase, row_stride, t0 + it * TILE, t1, lane, mv, kvh, tok_pool + it * TILE);
+    // ---- the range of this CTA (kv_len and seq_off are not written by the kernel in front, so this runs before
+    //      the wait on it) ------------------------------------------------------------------------------------
+    // the walk's state lives in shared memory (the tile loop needs every register): sequence b, index of its first
+    // tile, next tile to read, end of the range, range length
+    __shared__ int walk_s[9];                                    // [5..8]: sequence, slot, first slot and partial count of the current piece
+    if (BALANCED) {
+        // Ranges are cut in units of cost: a tile costs 1, and every sequence is charged a.piece_cost extra units in
+        // front of its first tile for the fixed work of a piece (query fragments, restart of the copy pipeline,
+        // partial write), so a CTA that walks pieces of several sequences gets fewer tiles.
+        const int pad = a.piece_cost;
+        int pos, range_end, W, total = 0, mine_n = 0, mine_incl = 0;
+        for (int b0 = 0; b0 < a.n_seq; b0 += 128) {
+            const int n = b0 + tid < a.n_seq ? seq_tiles(a, b0 + tid) : 0;
+            int t;
+            const int incl = block_scan128(n ? n + pad : 0, scan_s, &t);
+            if (b0 == 0) { mine_n = n; mine_incl = incl; }           // kept for the search below when the batch is one pass
+            total += t;
+        }
+        // range length: an equal share, but no shorter than 16 tiles nor than 1/32 of the longest context the call
+        // allows (the last CTA of a sequence merges its partials alone; past ~32 of them that outweighs the gain)
+        const int floor_w = max(16, ((a.max_len + TILE - 1) / TILE + 31) / 32);
+        W = max((total + (int)gridDim.y - 1) / (int)gridDim.y, floor_w);
+        pos = (int)blockIdx.y * W;
+        range_end = min(total, pos + W);
+        if (pos >= total) { asm volatile("griddepcontrol.wait;\n" ::: "memory"); return; }
+        // the sequence whose units hold `pos`
+        if (a.n_seq <= 128) {
+            const int cost = mine_n ? mine_n + pad : 0;
+            if (mine_incl - cost <= pos && pos < mine_incl) { found_s[0] = tid; found_s[1] = mine_incl - cost; }
+        } else {
+            int running = 0;
+            for (int b0 = 0; b0 < a.n_seq; b0 += 128) {
+                const int n = b0 + tid < a.n_seq ? seq_tiles(a, b0 + tid) : 0, cost = n ? n + pad : 0;
+                int t;
+                const int incl = running + block_scan128(cost, scan_s, &t);
+                if (incl - cost <= pos && pos < incl) { found_s[0] = b0 + tid; found_s[1] = incl - cost; }
+                running += t;
+                if (running > pos) break;
+            }
+        }
+        __syncthreads();
+        if (tid == 0) { walk_s[0] = found_s[0]; walk_s[1] = found_s[1]; walk_s[2] = pos; walk_s[3] = range_end; walk_s[4] = W; }
+        __syncthreads();
     }
-    for (uint32_t n = 0; it < ntiles; it += NWARP, n++) {
-        const int tok0 = t0 + it * TILE;
-        const bool more = it + NWARP < ntiles;
-        if (!mbar_wait(barK, n & 1)) {
-            (void)mbar_wait(barV, n & 1);                         // bounded chance for the other copy to drain
-            pipe_ok = false;
-            break;
-        }
 
-        // ---- S^T = K Q^T: 17 k-steps in two accumulator chains -----------------------------
-        uint32_t dk0[8], dk1[8];
-#pragma unroll
-        for (int bb = 0; bb < 8; bb++) {
-            const unsigned short u0 = *reinterpret_cast<const unsigned short *>(rawK + r * ROWB + 34 * bb);
-            const unsigned short u1 = *reinterpret_cast<const unsigned short *>(rawK + (r + 8) * ROWB + 34 * bb);
-            dk0[bb] = (uint32_t)u0 | ((uint32_t)u0 << 16);
-            dk1[bb] = (uint32_t)u1 | ((uint32_t)u1 << 16);
+    uint32_t phase = 0;                                           // tiles this warp has consumed: parity of its two barriers
+    bool pipe_ok = true, waited = false;
+    for (bool first_piece = true;; first_piece = false) {
+        // ---- next piece: tiles [tile_lo, tile_hi) of sequence b --------------------------------------------------
+        int tile_lo, tile_hi, slot, slot0, nlive, len0, b;
+        if (BALANCED) {
+            if (!first_piece) __syncthreads();                    // everybody has read the state of the previous piece
+            b = walk_s[0];
+            int seq_first = walk_s[1], pos = walk_s[2];
+            const int range_end = walk_s[3], W = walk_s[4];
+            if (pos >= range_end) break;
+            const int pad = a.piece_cost;
+            int nb = seq_tiles(a, b);
+            // units of sequence b: [seq_first, seq_first + pad + nb); pos < total, so b stays inside the batch
+            while (nb == 0 || seq_first + pad + nb <= pos) { seq_first += nb ? nb + pad : 0; b++; nb = seq_tiles(a, b); }
+            const int real0 = seq_first + pad;                    // unit of the sequence's first tile
+            tile_lo = max(pos - real0, 0);
+            tile_hi = min(nb, range_end - real0);
+            if (tile_hi <= tile_lo) break;                        // the range ends inside the charge in front of sequence b
+            len0 = a.kv_len[b];
+            const int c_first = real0 / W;
+            slot0 = c_first + b;                                  // (range, sequence) pairs in walking order: range + sequence is unique
+            slot = (int)blockIdx.y + b;
+            nlive = (real0 + nb - 1) / W - c_first + 1;           // ranges that hold a piece of this sequence
+            __syncthreads();                                      // everybody has read the old state
+            if (tid == 0) {
+                walk_s[0] = b; walk_s[1] = seq_first; walk_s[2] = seq_first + a.piece_cost + tile_hi;
+                walk_s[5] = b; walk_s[6] = slot; walk_s[7] = slot0; walk_s[8] = nlive;
+            }
+        } else {
+            if (!first_piece) break;
+            b = blockIdx.z;
+            len0 = a.kv_len[b];
+            // A CTA that leaves early still has to wait for the grid in front (programmatic dependent launch):
+            // a grid whose CTAs all returned without waiting would retire, and let the next kernel in the
+            // stream start, before the append kernel has finished.
+            if (len0 >= (int)(a.kv.seq_off[b + 1] - a.kv.seq_off[b])) { asm volatile("griddepcontrol.wait;\n" ::: "memory"); return; }
+            const int tps_tiles = a.tokens_per_split / TILE, nb = (len0 + TILE) / TILE;
+            slot = blockIdx.y; slot0 = 0;
+            tile_lo = slot * tps_tiles;
+            tile_hi = min(nb, tile_lo + tps_tiles);
+            nlive = min(a.nsplit, (len0 + a.tokens_per_split) / a.tokens_per_split);     // splits with t0 < L
         }
-        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        const uint32_t k_addr = smem_u32(rawK) + lane_off;
+        const int64_t base = a.kv.seq_off[b];
+        const int L = len0 + 1;
+        const int t0 = tile_lo * TILE, t1 = min(L, tile_hi * TILE);
+        if (!BALANCED && t0 >= L) {
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");
+            float *pd = a.part + (((size_t)b * a.nh + (size_t)head0) * a.nsplit + slot) * (HD + 2);
+            const size_t part_stride = (size_t)a.nsplit * (HD + 2);
+            if (tid < G) { pd[tid * part_stride] = -INFINITY; pd[tid * part_stride + 1] = 0.0f; }
+            return;
+        }
+        // this warp's tiles: the piece's tiles warp, warp + 4, ...  rem = tokens from the start of the warp's current
+        // tile to the end of the piece (<= 0: no tile left); tok_abs = that tile's first token, counted from the
+        // start of the pool
+        int rem = t1 - t0 - warp * TILE, tok_abs = (int)base + t0 + warp * TILE;
+
+        // ---- per-warp staging slots (K rows, V rows): zero them (skipped tail rows must stay finite; the slots
+        //      also held the warp's output tile of the piece before).  K of the next tile is requested as soon as
+        //      the score loop is done with the slot, V right after the value loop.  The first tile is requested
+        //      before anything else so that its latency hides behind the query prologue; under programmatic
+        //      dependent launch that happens while the append kernel of this call may still be running, so only
+        //      for tiles that end before the row it appends (token len0).
+        if (!BALANCED && !first_piece) __syncthreads();           // (BALANCED: the barriers of the walk above already separate the pieces)
         {
-            uint32_t R[4];
-#define QK_PAIR(C)                                                \
-            ldsm_x4(R, k_addr + (C) * 16);                        \
-            qk_chunk<(C)>(R[0], R[1], dk0, dk1, j, q_frag, s);    \
-            qk_chunk<(C) + 1>(R[2], R[3], dk0, dk1, j, q_frag, s2);
-            QK_PAIR(0) QK_PAIR(2) QK_PAIR(4) QK_PAIR(6) QK_PAIR(8) QK_PAIR(10) QK_PAIR(12) QK_PAIR(14)
-#undef QK_PAIR
-            ldsm_x2(R, k_addr + 16 * 16);                         // lanes 0-15 address chunk 16
-            qk_chunk<16>(R[0], R[1], dk0, dk1, j, q_frag, s);
+            uint4 *z = reinterpret_cast<uint4 *>(wbase);
+            for (int i = lane; i < WARP_BYTES / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+            fence_proxy_async();                                  // generic-proxy zeros before async-proxy copies
+            __syncwarp();
         }
-        __syncwarp();                                             // every lane is done with the K slot
-        if (more) {
-            fence_proxy_async();
-            issue_rows16(rawK, barK, Kbase, row_stride, tok0 + NWARP * TILE, t1, lane, mk, kvh, tok_pool + (it + NWARP) * TILE);
+        const bool first_issued = pipe_ok && rem > 0 && (waited || t0 + (warp + 1) * TILE <= len0);
+        if (first_issued) {
+            issue_rows16(rawK, barK, a.kv.K, nkv, rem, lane, mk, kvh, tok_abs);
+            issue_rows16(rawV, barV, a.kv.V, nkv, rem, lane, mv, kvh, tok_abs);
         }
+        // everything below reads what the append kernel of this call wrote (query rows, the new K/V row, zeroed counters)
+        if (!waited) { asm volatile("griddepcontrol.wait;\n" ::: "memory"); waited = true; }
 
-        // ---- online softmax over tokens (rows r, r+8); columns = heads 2j, 2j+1 -------------
-        const bool ok0 = tok0 + r < t1, ok1 = tok0 + r + 8 < t1;
-        float x00 = ok0 ? (s[0] + s2[0]) * rsA : -INFINITY, x01 = ok0 ? (s[1] + s2[1]) * rsB : -INFINITY;
-        float x10 = ok1 ? (s[2] + s2[2]) * rsA : -INFINITY, x11 = ok1 ? (s[3] + s2[3]) * rsB : -INFINITY;
-        float cA = fmaxf(x00, x10), cB = fmaxf(x01, x11);
+        // ---- query group -> B fragments in stream order: lane (head r, quarter j), k-step c
+        //      holds q at the dims of elements 8c+2j and 8c+2j+1 (zeros where the stream has a scale)
+        float rs_mine;
+        {
+            const float *q = a.q_prep + ((size_t)b * a.nh + (size_t)head0 + (r < G ? r : 0)) * HD;
+            float mx = 0.0f;
+            {   // 16 independent 128-bit loads: the prologue is per piece, keep it off the latency path
+                const float4 *q4 = reinterpret_cast<const float4 *>(q + j * 64);
+                float4 t[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) t[i] = q4[i];
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    mx = fmaxf(mx, fmaxf(fmaxf(fabsf(t[i].x), fabsf(t[i].y)), fmaxf(fabsf(t[i].z), fabsf(t[i].w))));
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            int e = 0;
+            if (mx > 0.0f && mx < INFINITY) (void)frexpf(mx, &e);
+            const float down = (r < G) ? exp2f((float)-e) : 0.0f;
+            for (int c = warp; c < NCHUNK; c += NWARP) {      // the four warps share the work; identical per warp otherwise
+                uint32_t pk[2];
+    #pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int el = 8 * c + 2 * j + h;
+                    const int bl = el / 17, idx = el - 17 * bl;
+                    // scale slots read dims 0,1 (any valid address) and are zeroed by the multiplier
+                    const int d = (idx != 0) ? 32 * bl + 2 * (idx - 1) : 0;
+                    const float2 v = *reinterpret_cast<const float2 *>(q + d);
+                    const float mul = (idx != 0) ? down : 0.0f;
+                    pk[h] = pack_h2(v.x * mul, v.y * mul);
+                }
+                Q_s[c * 32 + lane] = make_uint2(pk[0], pk[1]);
+            }
+            rs_mine = (r < G) ? a.scale * exp2f((float)e) * LOG2E : 0.0f;
+        }
+        const float rsA = __shfl_sync(0xffffffffu, rs_mine, (2 * j) * 4);
+        const float rsB = __shfl_sync(0xffffffffu, rs_mine, (2 * j + 1) * 4);
+
+        float o[NCHUNK][4];
+#pragma unroll
+        for (int i = 0; i < NCHUNK; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+        float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
+
+        __syncthreads();                                          // publishes Q_s
+        const uint2 *q_frag = Q_s + lane;
+        if (pipe_ok && rem > 0 && !first_issued) {
+            issue_rows16(rawK, barK, a.kv.K, nkv, rem, lane, mk, kvh, tok_abs);
+            issue_rows16(rawV, barV, a.kv.V, nkv, rem, lane, mv, kvh, tok_abs);
+        }
+        for (; pipe_ok && rem > 0; rem -= NWARP * TILE, tok_abs += NWARP * TILE, phase++) {
+            const bool more = rem > NWARP * TILE;
+            if (!mbar_wait(barK, phase & 1)) {
+                (void)mbar_wait(barV, phase & 1);                 // bounded chance for the other copy to drain
+                pipe_ok = false;
+                break;
+            }
+
+            // ---- S^T = K Q^T: 17 k-steps in two accumulator chains -----------------------------
+            uint32_t dk0[8], dk1[8];
+    #pragma unroll
+            for (int bb = 0; bb < 8; bb++) {
+                const unsigned short u0 = lds_u16(rawK + r * ROWB + 34 * bb);
+                const unsigned short u1 = lds_u16(rawK + (r + 8) * ROWB + 34 * bb);
+                dk0[bb] = (uint32_t)u0 | ((uint32_t)u0 << 16);
+                dk1[bb] = (uint32_t)u1 | ((uint32_t)u1 << 16);
+            }
+            float s[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const uint32_t k_addr = rawK + lane_off;
+            {
+                uint32_t R[4];
+    #define QK_PAIR(C)                                                \
+                ldsm_x4(R, k_addr + (C) * 16);                        \
+                qk_chunk<(C)>(R[0], R[1], dk0, dk1, j, q_frag, s);    \
+                qk_chunk<(C) + 1>(R[2], R[3], dk0, dk1, j, q_frag, s2);
+                QK_PAIR(0) QK_PAIR(2) QK_PAIR(4) QK_PAIR(6) QK_PAIR(8) QK_PAIR(10) QK_PAIR(12) QK_PAIR(14)
+    #undef QK_PAIR
+                ldsm_x2(R, k_addr + 16 * 16);                         // lanes 0-15 address chunk 16
+                qk_chunk<16>(R[0], R[1], dk0, dk1, j, q_frag, s);
+            }
+            __syncwarp();                                             // every lane is done with the K slot
+            if (more) {
+                fence_proxy_async();
+                issue_rows16(rawK, barK, a.kv.K, nkv, rem - NWARP * TILE, lane, mk, kvh, tok_abs + NWARP * TILE);
+            }
+
+            // ---- online softmax over tokens (rows r, r+8); columns = heads 2j, 2j+1 -------------
+            const bool ok0 = r < rem, ok1 = r + 8 < rem;
+            float x00 = ok0 ? (s[0] + s2[0]) * rsA : -INFINITY, x01 = ok0 ? (s[1] + s2[1]) * rsB : -INFINITY;
+            float x10 = ok1 ? (s[2] + s2[2]) * rsA : -INFINITY, x11 = ok1 ? (s[3] + s2[3]) * rsB : -INFINITY;
+            float cA = fmaxf(x00, x10), cB = fmaxf(x01, x11);
+#pragma unroll
+            for (int sft = 4; sft <= 16; sft <<= 1) {
+                cA = fmaxf(cA, __shfl_xor_sync(0xffffffffu, cA, sft));
+                cB = fmaxf(cB, __shfl_xor_sync(0xffffffffu, cB, sft));
+            }
+            // The reference maximum only moves when the tile maximum exceeds it by more than 2^6: the
+            // probabilities then stay below 2^6 (times 2^8 still inside f16) and the 68 multiplies that
+            // rescale the output tile are skipped on almost every tile.  (m, l, o) stay consistent, so
+            // the merge of the partials is unchanged.
+            const float nA = (cA > mA + 6.0f) ? cA : mA, nB = (cB > mB + 6.0f) ? cB : mB;   // finite: the tile's first token is valid
+            const float corrA = exp2f(mA - nA), corrB = exp2f(mB - nB);
+            mA = nA; mB = nB;
+            x00 = exp2f(x00 - nA); x10 = exp2f(x10 - nA); x01 = exp2f(x01 - nB); x11 = exp2f(x11 - nB);
+            lA = lA * corrA + x00 + x10;
+            lB = lB * corrB + x01 + x11;
+            if (__any_sync(0xffffffffu, corrA != 1.0f || corrB != 1.0f)) {
+#pragma unroll
+                for (int i = 0; i < NCHUNK; i++) { o[i][0] *= corrA; o[i][1] *= corrB; o[i][2] *= corrA; o[i][3] *= corrB; }
+            }
+            const uint32_t pb0 = movmatrix_trans(pack_h2(x00 * 256.0f, x01 * 256.0f));
+            const uint32_t pb1 = movmatrix_trans(pack_h2(x10 * 256.0f, x11 * 256.0f));
+
+            // ---- O^T += V^T P^T: one m-tile per chunk; block scales arrive with chunk 2b ---------
+            if (!mbar_wait(barV, phase & 1)) {
+                if (more) (void)mbar_wait(barK, (phase + 1) & 1);
+                pipe_ok = false;
+                break;
+            }
+            const uint32_t v_addr = rawV + lane_off;
+            {
+                uint32_t R[4];
+                uint32_t lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;          // scale pairs of the current two blocks
+#define PV_PAIR(C)                                                                         \
+                ldsm_x4_trans(R, v_addr + (C) * 16);                                           \
+                lo0 = hi0; lo1 = hi1;                                                          \
+                hi0 = __shfl_sync(0xffffffffu, R[0], ((C) / 2) * 4 + j);   /* scale of block C/2 */ \
+                hi1 = __shfl_sync(0xffffffffu, R[1], ((C) / 2) * 4 + j);                        \
+                if ((C) == 0) { lo0 = hi0; lo1 = hi1; }                                         \
+                pv_chunk<(C)>(R[0], R[1], lo0, lo1, hi0, hi1, r, pb0, pb1, o[(C)]);             \
+                pv_chunk<(C) + 1>(R[2], R[3], hi0, hi1, hi0, hi1, r, pb0, pb1, o[(C) + 1]);
+                PV_PAIR(0) PV_PAIR(2) PV_PAIR(4) PV_PAIR(6) PV_PAIR(8) PV_PAIR(10) PV_PAIR(12) PV_PAIR(14)
+#undef PV_PAIR
+                ldsm_x2_trans(R, v_addr + 16 * 16);
+                pv_chunk<16>(R[0], R[1], hi0, hi1, hi0, hi1, r, pb0, pb1, o[16]);
+            }
+            __syncwarp();                                             // every lane is done with the V slot
+            if (more) {
+                fence_proxy_async();
+                issue_rows16(rawV, barV, a.kv.V, nkv, rem - NWARP * TILE, lane, mv, kvh, tok_abs + NWARP * TILE);
+            }
+        }
+        // a copy that never completed: this warp stops streaming for good (its barriers are in an unknown phase),
+        // the CTA poisons what it writes from here on, and the host learns of it at its next synchronisation
+        if (!pipe_ok && lane == 0 && !pipe_failed) { pipe_failed = 1; if (a.status) atomicOr(a.status, ORN_WAIT_DECODE); }
+        __syncwarp();
+
+        // ---- merge the four warps, one partial per (head, piece) ------------------------------------
 #pragma unroll
         for (int sft = 4; sft <= 16; sft <<= 1) {
-            cA = fmaxf(cA, __shfl_xor_sync(0xffffffffu, cA, sft));
-            cB = fmaxf(cB, __shfl_xor_sync(0xffffffffu, cB, sft));
+            lA += __shfl_xor_sync(0xffffffffu, lA, sft);
+            lB += __shfl_xor_sync(0xffffffffu, lB, sft);
         }
-        // The reference maximum only moves when the tile maximum exceeds it by more than 2^6: the
-        // probabilities then stay below 2^6 (times 2^8 still inside f16) and the 68 multiplies that
-        // rescale the output tile are skipped on almost every tile.  (m, l, o) stay consistent, so
-        // the merge of the partials is unchanged.
-        const float nA = (cA > mA + 6.0f) ? cA : mA, nB = (cB > mB + 6.0f) ? cB : mB;   // finite: token tok0 is valid
-        const float corrA = exp2f(mA - nA), corrB = exp2f(mB - nB);
-        mA = nA; mB = nB;
-        x00 = exp2f(x00 - nA); x10 = exp2f(x10 - nA); x01 = exp2f(x01 - nB); x11 = exp2f(x11 - nB);
-        lA = lA * corrA + x00 + x10;
-        lB = lB * corrB + x01 + x11;
-        if (__any_sync(0xffffffffu, corrA != 1.0f || corrB != 1.0f)) {
-#pragma unroll
-            for (int i = 0; i < NCHUNK; i++) { o[i][0] *= corrA; o[i][1] *= corrB; o[i][2] *= corrA; o[i][3] *= corrB; }
+        if (BALANCED) {                                               // (published by the barrier behind the query fragments)
+            const volatile int *w = walk_s;
+            b = w[5]; slot = w[6]; slot0 = w[7]; nlive = w[8];
         }
-        const uint32_t pb0 = movmatrix_trans(pack_h2(x00 * 256.0f, x01 * 256.0f));
-        const uint32_t pb1 = movmatrix_trans(pack_h2(x10 * 256.0f, x11 * 256.0f));
-
-        // ---- O^T += V^T P^T: one m-tile per chunk; block scales arrive with chunk 2b ---------
-        if (!mbar_wait(barV, n & 1)) {
-            if (more) (void)mbar_wait(barK, (n + 1) & 1);
-            pipe_ok = false;
-            break;
+        // partials: BALANCED [head][slot], else [sequence][head][split]; a.nsplit = partial slots per head
+        const size_t part_stride = (size_t)a.nsplit * (HD + 2);     // next head
+        float *part_g = a.part + (BALANCED ? (size_t)head0 * a.nsplit : ((size_t)b * a.nh + (size_t)head0) * a.nsplit) * (HD + 2);
+        float *part0 = part_g + (size_t)slot * (HD + 2);
+        float *Ow = reinterpret_cast<float *>(smem + QS_BYTES + warp * WARP_BYTES);   // [8 heads][256] f32 over this warp's slots
+        store_chunk<0>(Ow, o[0], r, j);   store_chunk<1>(Ow, o[1], r, j);   store_chunk<2>(Ow, o[2], r, j);
+        store_chunk<3>(Ow, o[3], r, j);   store_chunk<4>(Ow, o[4], r, j);   store_chunk<5>(Ow, o[5], r, j);
+        store_chunk<6>(Ow, o[6], r, j);   store_chunk<7>(Ow, o[7], r, j);   store_chunk<8>(Ow, o[8], r, j);
+        store_chunk<9>(Ow, o[9], r, j);   store_chunk<10>(Ow, o[10], r, j); store_chunk<11>(Ow, o[11], r, j);
+        store_chunk<12>(Ow, o[12], r, j); store_chunk<13>(Ow, o[13], r, j); store_chunk<14>(Ow, o[14], r, j);
+        store_chunk<15>(Ow, o[15], r, j); store_chunk<16>(Ow, o[16], r, j);
+        if (r == 0) {
+            m_s[warp][2 * j] = mA; m_s[warp][2 * j + 1] = mB;
+            l_s[warp][2 * j] = lA; l_s[warp][2 * j + 1] = lB;
         }
-        const uint32_t v_addr = smem_u32(rawV) + lane_off;
-        {
-            uint32_t R[4];
-            uint32_t lo0 = 0, lo1 = 0, hi0 = 0, hi1 = 0;          // scale pairs of the current two blocks
-#define PV_PAIR(C)                                                                         \
-            ldsm_x4_trans(R, v_addr + (C) * 16);                                           \
-            lo0 = hi0; lo1 = hi1;                                                          \
-            hi0 = __shfl_sync(0xffffffffu, R[0], ((C) / 2) * 4 + j);   /* scale of block C/2 */ \
-            hi1 = __shfl_sync(0xffffffffu, R[1], ((C) / 2) * 4 + j);                        \
-            if ((C) == 0) { lo0 = hi0; lo1 = hi1; }                                         \
-            pv_chunk<(C)>(R[0], R[1], lo0, lo1, hi0, hi1, r, pb0, pb1, o[(C)]);             \
-            pv_chunk<(C) + 1>(R[2], R[3], hi0, hi1, hi0, hi1, r, pb0, pb1, o[(C) + 1]);
-            PV_PAIR(0) PV_PAIR(2) PV_PAIR(4) PV_PAIR(6) PV_PAIR(8) PV_PAIR(10) PV_PAIR(12) PV_PAIR(14)
-#undef PV_PAIR
-            ldsm_x2_trans(R, v_addr + 16 * 16);
-            pv_chunk<16>(R[0], R[1], hi0, hi1, hi0, hi1, r, pb0, pb1, o[16]);
-        }
-        __syncwarp();                                             // every lane is done with the V slot
-        if (more) {
-            fence_proxy_async();
-            issue_rows16(rawV, barV, Vbase, row_stride, tok0 + NWARP * TILE, t1, lane, mv, kvh, tok_pool + (it + NWARP) * TILE);
-        }
-    }
-    if (!pipe_ok && lane == 0) pipe_failed = 1;
-    __syncwarp();
-
-    // ---- merge the four warps, one partial per (head, split) -----------------------------------
-#pragma unroll
-    for (int sft = 4; sft <= 16; sft <<= 1) {
-        lA += __shfl_xor_sync(0xffffffffu, lA, sft);
-        lB += __shfl_xor_sync(0xffffffffu, lB, sft);
-    }
-    float *Ow = reinterpret_cast<float *>(wbase);                 // [8 heads][256] f32 over this warp's slots
-    store_chunk<0>(Ow, o[0], r, j);   store_chunk<1>(Ow, o[1], r, j);   store_chunk<2>(Ow, o[2], r, j);
-    store_chunk<3>(Ow, o[3], r, j);   store_chunk<4>(Ow, o[4], r, j);   store_chunk<5>(Ow, o[5], r, j);
-    store_chunk<6>(Ow, o[6], r, j);   store_chunk<7>(Ow, o[7], r, j);   store_chunk<8>(Ow, o[8], r, j);
-    store_chunk<9>(Ow, o[9], r, j);   store_chunk<10>(Ow, o[10], r, j); store_chunk<11>(Ow, o[11], r, j);
-    store_chunk<12>(Ow, o[12], r, j); store_chunk<13>(Ow, o[13], r, j); store_chunk<14>(Ow, o[14], r, j);
-    store_chunk<15>(Ow, o[15], r, j); store_chunk<16>(Ow, o[16], r, j);
-    if (r == 0) {
-        m_s[warp][2 * j] = mA; m_s[warp][2 * j + 1] = mB;
-        l_s[warp][2 * j] = lA; l_s[warp][2 * j + 1] = lB;
-    }
-    __syncthreads();
+        __syncthreads();
 #pragma unroll                                                    // unrolled: the heads' loads and stores overlap
-    for (int h = 0; h < 8; h++) {
-        if (h >= G) break;
-        float M = -INFINITY;
+        for (int h = 0; h < 8; h++) {
+            if (h >= G) break;
+            float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NWARP; w++) if (l_s[w][h] > 0.0f) M = fmaxf(M, m_s[w][h]);
-        float ww[NWARP], Lt = 0.0f;
+            for (int w = 0; w < NWARP; w++) if (l_s[w][h] > 0.0f) M = fmaxf(M, m_s[w][h]);
+            float ww[NWARP], Lt = 0.0f;
 #pragma unroll
-        for (int w = 0; w < NWARP; w++) {
-            ww[w] = (l_s[w][h] > 0.0f) ? exp2f(m_s[w][h] - M) : 0.0f;
-            Lt += l_s[w][h] * ww[w];
+            for (int w = 0; w < NWARP; w++) {
+                ww[w] = (l_s[w][h] > 0.0f) ? exp2f(m_s[w][h] - M) : 0.0f;
+                Lt += l_s[w][h] * ww[w];
+            }
+            float *part = part0 + h * part_stride;
+            // a staging copy that never completed poisons the partial (the result becomes NaN, not silently wrong)
+            const float poison = pipe_failed ? NAN : 0.0f;
+            if (tid == 0) { part[0] = M * LN2; part[1] = pipe_failed ? 1.0f : Lt; }
+            for (int d = tid; d < HD; d += 128) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int w = 0; w < NWARP; w++)
+                    acc += ww[w] * reinterpret_cast<const float *>(smem + QS_BYTES + w * WARP_BYTES)[h * HD + d];
+                part[2 + d] = acc * (1.0f / 256.0f) + poison;
+            }
         }
-        float *part = part0 + h * part_stride;
-        // a staging copy that never completed poisons the partial (the result becomes NaN, not silently wrong)
-        const float poison = pipe_failed ? NAN : 0.0f;
-        if (tid == 0) { part[0] = M * LN2; part[1] = pipe_failed ? 1.0f : Lt; }
-        for (int d = tid; d < HD; d += 128) {
-            float acc = 0.0f;
-#pragma unroll
-            for (int w = 0; w < NWARP; w++)
-                acc += ww[w] * reinterpret_cast<const float *>(smem + QS_BYTES + w * WARP_BYTES)[h * HD + d];
-            part[2 + d] = acc * (1.0f / 256.0f) + poison;
-        }
-    }
-    if (a.group_ctr == nullptr) return;
+        if (a.group_ctr == nullptr) continue;                         // (only without BALANCED: the combine kernel merges)
 
-    // ---- fused merge: the last CTA of this (sequence, head group) to get here combines the partials of the
-    //      group's live splits (reference: src/ornith_attn.c:131-148 normalisation, src/ornith_rforward.c:450 gate).
-    //      Nobody waits: every CTA publishes its partials, counts itself, and only the one that counts last goes on.
-    __shared__ int last_one;
-    __threadfence();
-    __syncthreads();
-    const int nlive = min(a.nsplit, (len0 + a.tokens_per_split) / a.tokens_per_split);   // splits with t0 < L
-    if (tid == 0) {
-        int *ctr = a.group_ctr + (size_t)b * gridDim.x + blockIdx.x;
-        last_one = (atomicAdd(ctr, 1) == nlive - 1);
-    }
-    __syncthreads();
-    if (!last_one) return;
-    __threadfence();
-    // 16 threads per head, all heads at once: thread (h, q) owns the float2 columns q + 16 k of head h.
-    // Partials of other SMs are read past L1.  Four splits' rows are in flight per thread at a time.
-    const int h = tid >> 4, q = tid & 15;
-    if (h < G) {
-        const unsigned hm = 0xffffu << (lane & 16);           // this half-warp (the other half may belong to no head)
-        const float *ph = part0 - (size_t)split * (HD + 2) + h * part_stride;   // split 0 of head h
-        float M = -INFINITY;
-        for (int s = q; s < nlive; s += 16) {
-            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2)));
-            if (ml.y > 0.0f) M = fmaxf(M, ml.x);
+        // ---- fused merge: the last CTA of this (sequence, head group) to get here combines the group's partials
+        //      (reference: src/ornith_attn.c:131-148 normalisation, src/ornith_rforward.c:450 gate).  Nobody waits:
+        //      every CTA publishes its partials, counts itself, and only the one that counts last goes on.
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int *ctr = a.group_ctr + (size_t)b * gridDim.x + blockIdx.x;
+            last_one = (atomicAdd(ctr, 1) == nlive - 1);
         }
+        __syncthreads();
+        if (!last_one) continue;
+        __threadfence();
+        // 16 threads per head, all heads at once: thread (h, q) owns the float2 columns q + 16 k of head h.
+        // Partials of other SMs are read past L1.  Four partials' rows are in flight per thread at a time.
+        const int h = tid >> 4, q = tid & 15;
+        if (h < G) {
+            const unsigned hm = 0xffffu << (lane & 16);           // this half-warp (the other half may belong to no head)
+            const float *ph = part_g + (size_t)slot0 * (HD + 2) + h * part_stride;   // first partial of head h
+            float M = -INFINITY;
+            for (int s = q; s < nlive; s += 16) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2)));
+                if (ml.y > 0.0f) M = fmaxf(M, ml.x);
+            }
 #pragma unroll
-        for (int sft = 8; sft >= 1; sft >>= 1) M = fmaxf(M, __shfl_xor_sync(hm, M, sft, 16));
-        float lsum = 0.0f;
-        float2 acc[8];
+            for (int sft = 8; sft >= 1; sft >>= 1) M = fmaxf(M, __shfl_xor_sync(hm, M, sft, 16));
+            float lsum = 0.0f;
+            float2 acc[8];
 #pragma unroll
-        for (int k = 0; k < 8; k++) acc[k] = make_float2(0.0f, 0.0f);
-        for (int s0 = 0; s0 < nlive; s0 += 16) {
-            const int s = s0 + q;
-            const float2 ml = s < nlive ? __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2))) : make_float2(0.0f, 0.0f);
-            const float w = (ml.y > 0.0f) ? expf(ml.x - M) : 0.0f;
-            lsum += ml.y * w;
-            const int n = min(16, nlive - s0);
-            for (int i0 = 0; i0 < n; i0 += 4) {
-                float2 v[4][8];
-                float wi[4];
+            for (int k = 0; k < 8; k++) acc[k] = make_float2(0.0f, 0.0f);
+            for (int s0 = 0; s0 < nlive; s0 += 16) {
+                const int s = s0 + q;
+                const float2 ml = s < nlive ? __ldcg(reinterpret_cast<const float2 *>(ph + (size_t)s * (HD + 2))) : make_float2(0.0f, 0.0f);
+                const float w = (ml.y > 0.0f) ? expf(ml.x - M) : 0.0f;
+                lsum += ml.y * w;
+                const int n = min(16, nlive - s0);
+                for (int i0 = 0; i0 < n; i0 += 4) {
+                    float2 v[4][8];
+                    float wi[4];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    wi[u] = __shfl_sync(hm, w, (i0 + u) & 15, 16);
-                    if (i0 + u >= n) wi[u] = 0.0f;
-                    const float2 *o2 = reinterpret_cast<const float2 *>(ph + (size_t)(s0 + min(i0 + u, n - 1)) * (HD + 2) + 2);
+                    for (int u = 0; u < 4; u++) {
+                        wi[u] = __shfl_sync(hm, w, (i0 + u) & 15, 16);
+                        if (i0 + u >= n) wi[u] = 0.0f;
+                        const float2 *o2 = reinterpret_cast<const float2 *>(ph + (size_t)(s0 + min(i0 + u, n - 1)) * (HD + 2) + 2);
 #pragma unroll
-                    for (int k = 0; k < 8; k++) v[u][k] = __ldcg(o2 + q + 16 * k);       // dims 2 (q + 16 k), +1
-                }
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                    if (wi[u] != 0.0f) {
-#pragma unroll
-                        for (int k = 0; k < 8; k++) { acc[k].x += v[u][k].x * wi[u]; acc[k].y += v[u][k].y * wi[u]; }
+                        for (int k = 0; k < 8; k++) v[u][k] = __ldcg(o2 + q + 16 * k);       // dims 2 (q + 16 k), +1
                     }
-            }
-        }
 #pragma unroll
-        for (int sft = 8; sft >= 1; sft >>= 1) lsum += __shfl_xor_sync(hm, lsum, sft, 16);
-        const float inv = 1.0f / lsum;
-        const size_t head = (size_t)b * a.nh + (size_t)head0 + h;
+                    for (int u = 0; u < 4; u++)
+                        if (wi[u] != 0.0f) {
 #pragma unroll
-        for (int k = 0; k < 8; k++)
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                const int d = 2 * (q + 16 * k) + e;
-                float o = (e ? acc[k].y : acc[k].x) * inv;
-                if (a.act_dtype == ORNITH_ACT_BF16) {
-                    if (a.gated) o *= sigmoid_f(act_ld((const __nv_bfloat16 *)a.qproj, head * HD * 2 + HD + d));
-                    act_st((__nv_bfloat16 *)a.out, head * HD + d, o);
-                } else {
-                    if (a.gated) o *= sigmoid_f(act_ld((const float *)a.qproj, head * HD * 2 + HD + d));
-                    act_st((float *)a.out, head * HD + d, o);
+                            for (int k = 0; k < 8; k++) { acc[k].x += v[u][k].x * wi[u]; acc[k].y += v[u][k].y * wi[u]; }
+                        }
                 }
             }
+#pragma unroll
+            for (int sft = 8; sft >= 1; sft >>= 1) lsum += __shfl_xor_sync(hm, lsum, sft, 16);
+            const float inv = 1.0f / lsum;
+            const size_t head = (size_t)b * a.nh + (size_t)head0 + h;
+#pragma unroll
+            for (int k = 0; k < 8; k++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int d = 2 * (q + 16 * k) + e;
+                    float o = (e ? acc[k].y : acc[k].x) * inv;
+                    if (a.act_dtype == ORNITH_ACT_BF16) {
+                        if (a.gated) o *= sigmoid_f(act_ld((const __nv_bfloat16 *)a.qproj, head * HD * 2 + HD + d));
+                        act_st((__nv_bfloat16 *)a.out, head * HD + d, o);
+                    } else {
+                        if (a.gated) o *= sigmoid_f(act_ld((const float *)a.qproj, head * HD * 2 + HD + d));
+                        act_st((float *)a.out, head * HD + d, o);
+                    }
+                }
+        }
     }
 }
 
@@ -567,12 +694,32 @@ bool q8_rows_map(CUtensorMap *m, const void *pool, int nkv) {
 
 }  // namespace
 
-ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged) {
+// ranges of the balanced schedule: one per resident CTA of a head-group column (4 CTAs on each of 148 SMs), fewer when
+// the batch is too small for ranges of at least floor_w tiles (same rule as in the kernel)
+static int balanced_ranges(int nkv, int nh, int n_seq, int max_len) {
+    const int X = nkv * ((nh / nkv + 7) / 8);
+    const long long tiles = (max_len + TILE - 1) / TILE, floor_w = (tiles + 31) / 32 > 16 ? (tiles + 31) / 32 : 16;
+    const long long by_work = ((long long)n_seq * tiles + floor_w - 1) / floor_w, cap = 592 / X > 0 ? 592 / X : 1;
+    return (int)(by_work < cap ? (by_work > 0 ? by_work : 1) : cap);
+}
+int gqa_decode_q8_raw_slots(int nkv, int nh, int n_seq, int max_len) {
+    return balanced_ranges(nkv, nh, n_seq, max_len) + n_seq;
+}
+
+ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a_in, int n_seq, cudaStream_t st, bool *merged) {
+    DecodeArgs a = a_in;
     *merged = a.group_ctr != nullptr;
+    const bool balanced = gqa_decode_q8_raw_balanced(a.kv, a.nh);
+    if (balanced && !a.group_ctr) {
+        orn_record_error("k_gqa_decode_q8_raw: the balanced schedule merges its partials itself and needs the arrival counters");
+        return ORNITH_ERR_FORMAT;
+    }
     static bool configured_dev[ORN_MAX_DEVICES] = {};
     bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
-        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_raw, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_raw<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               SMEM_BYTES), "gqa decode smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_decode_q8_raw<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SMEM_BYTES), "gqa decode smem opt-in"));
         configured = true;
     }
@@ -582,7 +729,14 @@ ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStrea
     memset(&mv, 0, sizeof mv);
     const char *env = getenv("ORNITH_CUDA_DECODE_ROW_COPIES");
     const int tensor_copies = !(env && env[0] == '1') && q8_rows_map(&mk, a.kv.K, a.kv.nkv) && q8_rows_map(&mv, a.kv.V, a.kv.nkv);
-    dim3 grid(a.kv.nkv * ((a.nh / a.kv.nkv + 7) / 8), a.nsplit, n_seq);
+    const int X = a.kv.nkv * ((a.nh / a.kv.nkv + 7) / 8);
+    a.n_seq = n_seq;
+    a.status = orn_status_word();
+    static int piece_cost = -1;                                   // ORNITH_CUDA_DECODE_PIECE_COST=<tiles>: see the kernel
+    if (piece_cost < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_PIECE_COST"); piece_cost = e ? atoi(e) : 4; if (piece_cost < 0 || piece_cost > 15) piece_cost = 4; }
+    a.piece_cost = piece_cost;
+    dim3 grid(X, a.nsplit, n_seq);
+    if (balanced) grid = dim3(X, balanced_ranges(a.kv.nkv, a.nh, n_seq, a.max_len), 1);
     // may start while the append kernel in front of it still runs: it waits (griddepcontrol.wait) before it reads that kernel's output
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = st;
@@ -590,5 +744,6 @@ ornith_status launch_gqa_decode_q8_raw(const DecodeArgs &a, int n_seq, cudaStrea
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    return orn_check(cudaLaunchKernelEx(&cfg, k_gqa_decode_q8_raw, a, mk, mv, tensor_copies), "k_gqa_decode_q8_raw");
+    if (balanced) return orn_check(cudaLaunchKernelEx(&cfg, k_gqa_decode_q8_raw<true>, a, mk, mv, tensor_copies), "k_gqa_decode_q8_raw");
+    return orn_check(cudaLaunchKernelEx(&cfg, k_gqa_decode_q8_raw<false>, a, mk, mv, tensor_copies), "k_gqa_decode_q8_raw");
 }

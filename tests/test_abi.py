@@ -65,23 +65,29 @@ def test_no_cpu_fallback_without_a_gpu(lib):
 
 
 def test_decode_scratch_follows_the_batch(lib):
-    """Host-side sizing only (no GPU work): the decode scratch asks for finer splits, hence more
-    partials per head, when the batch is too small to fill the GPU, and for the coarse 2048-token
-    splits when it is not."""
+    """Host-side sizing only (no GPU work).  The size query does not see the cache, so it covers both schedules:
+    the grid of splits (finer splits, hence more partials per head, when the batch is too small to fill the GPU;
+    the CUDA-core kernel's 512-token splits as a floor) and the balanced ranges of the Q8_0 raw-fragment kernel
+    (one partial slot per head for each of at most 592 / head-group-columns ranges plus one per sequence)."""
     from ornithology_b200._lib import CudaFullLayer
     layer = CudaFullLayer(16, 2, 256, 64, 1, 1e-6, 0.0, None, None, None)
 
-    def splits(n_seq, max_len):
+    def rows(n_seq, max_len):
         total = lib.ornith_cuda_full_attn_step_scratch(C.byref(layer), n_seq, max_len)
         fixed = (n_seq * 16 * 256 * 4 + 255) // 256 * 256 + (n_seq * 16 * 4 + 255) // 256 * 256
-        return (total - fixed) / (n_seq * 16 * 258 * 4)
+        return (total - fixed) / (16 * 258 * 4)                          # partial rows per head
 
-    big = splits(64, 32832)            # 64 sequences of up to 32k tokens: 512-token splits of the CUDA-core path bound it
-    assert abs(big - 65) < 0.01
-    four = splits(4, 8256)             # 4 sequences x 8k: 320-token splits -> 26 partials per head (coarse: 9, CUDA-core path: 17)
-    assert abs(four - 26) < 0.5
-    eight = splits(8, 16448)           # 8 sequences x 16k: 576-token splits -> 29, below the CUDA-core path's 33
-    assert abs(eight - 33) < 0.5
+    def balanced(n_seq, max_len):
+        tiles = -(-max_len // 16)
+        floor_w = max(16, -(-tiles // 32))
+        return min(592 // 2, -(-n_seq * tiles // floor_w)) + n_seq
+
+    # 64 sequences of up to 32k tokens: the 512-token splits of the CUDA-core path (65 per sequence) bound it
+    assert abs(rows(64, 32832) - 64 * 65) < 0.1 and balanced(64, 32832) == 296 + 64
+    # 4 sequences x 8k: 320-token splits -> 26 partials per (sequence, head) = 104 rows; balanced: 122 ranges + 4
+    assert abs(rows(4, 8256) - max(4 * 26, balanced(4, 8256))) < 0.1 and balanced(4, 8256) == 126
+    # 8 sequences x 16k: 576-token splits -> 29, below the CUDA-core path's 33 -> 264 rows; balanced: 249 + 8
+    assert abs(rows(8, 16448) - max(8 * 33, balanced(8, 16448))) < 0.1
     assert lib.ornith_cuda_full_attn_step_scratch(C.byref(layer), 0, 100) == 0
 
 

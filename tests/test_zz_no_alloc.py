@@ -66,7 +66,7 @@ def test_static_scratch_entry_rejects_oversized_requests():
     lib = _lib.load()
     layer = full_case(32)
     dl = device_full(layer)
-    B, L = 64, 32768                                       # needs far more than the built-in 8 MiB
+    B, L = 640, 32768                                      # the query rows alone (10 MiB) exceed the built-in 8 MiB
     kv = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [8] * B)
     lens = torch.zeros(B, dtype=torch.int32, device="cuda")
     z = torch.zeros(B, layer.nh * 2 * layer.hd, device="cuda")
