@@ -21,6 +21,11 @@ pytestmark = pytest.mark.gpu
 TOL_BF16_IO = TOL + 2.0 ** -9 + 5e-4     # bf16-stored outputs: half an ulp on top of the bar
 
 
+def _note(case, **kw):
+    """Worst errors of a case, printed for the record (`pytest -s` shows them)."""
+    print("parity:", case, " ".join(f"{k}={v:.3g}" for k, v in kw.items()))
+
+
 def _t(x, dt=None):
     import torch
     t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
@@ -53,6 +58,7 @@ def test_delta_net_layer_prefill_512_then_128_steps(oracle):
         worst = max(worst, rel_err(out.cpu().numpy()[0], ref))
         D.advance(pos)
     assert worst < TOL, worst
+    _note("delta-net 512+128", out=worst, state=rel_err(st.S.cpu().numpy()[0], S))
     assert rel_err(st.S.cpu().numpy()[0], S) < TOL
     assert (st.conv_image(0, T + steps).cpu().numpy().ravel().view(np.uint32) == buf.view(np.uint32)).all()
 
@@ -85,6 +91,7 @@ def test_gqa_layer_prefill_4096_then_256_steps(oracle, mode):
         worst = max(worst, rel_err(out.cpu().numpy()[0], ref))
         D.advance(kv_len)
     assert worst < TOL, worst
+    _note("gqa 4096+256 " + mode, out=worst)
     n = T + steps
     Kg, Vg = kv.rows(0, n)
     Ko, Vo = okv.rows_q8_0() if mode == "q8_0" else okv.rows_f32()
@@ -101,6 +108,8 @@ def test_gqa_layer_prefill_4096_then_256_steps(oracle, mode):
         a, b = Kg[..., :rot].astype(np.float64), Ko[..., :rot].astype(np.float64)
         assert np.abs(a - b).max() <= 4e-7 * np.abs(b).max(), "rotated K dims differ by more than a few ulp"
         frac = float((Kg[..., :rot].view(np.uint32) != Ko[..., :rot].view(np.uint32)).mean())
+        _note("gqa f32 K rows, rotated dims", worst=float(np.abs(a - b).max() / np.abs(b).max()), fraction_differing=frac,
+              bytes_differing=float((Kg.view(np.uint8) != Ko.view(np.uint8)).sum()), bytes=float(Kg.view(np.uint8).size))
         assert frac < 0.2, f"{frac:.3f} of the rotated values differ in the last place"
 
 
@@ -123,6 +132,7 @@ def test_gqa_512_consecutive_decode_steps(oracle):
         worst = max(worst, rel_err(out.cpu().numpy()[0], ref))
         D.advance(kv_len)
     assert worst < TOL, worst
+    _note("gqa 512 decode steps", out=worst)
     Kg, Vg = kv.rows(0, steps)
     Ko, Vo = okv.rows_q8_0()
     assert (Kg == np.asarray(Ko)[:steps].reshape(Kg.shape)).all() and (Vg == np.asarray(Vo)[:steps].reshape(Vg.shape)).all()
@@ -145,6 +155,8 @@ def test_delta_net_32768_token_prompt_sampled_heads(oracle):
     bf = torch.bfloat16
     out = D.linear_attn_prefill(dl, st, pos, _t(QKV, bf)[None], _t(A, bf)[None], _t(Bm, bf)[None], _t(Z, bf)[None], T, chunk=64)
     out = out.float().cpu().numpy()[0]
+    _note("delta-net 32768 tokens bf16", out=rel_err(out, ref), tail=rel_err(out[-2048:], ref[-2048:]),
+          state=rel_err(st.S.cpu().numpy()[0], S), bar=TOL_BF16_IO)
     assert rel_err(out, ref) < TOL_BF16_IO
     # the tail of the prompt on its own scale (errors must not build up over 512 chunks)
     assert rel_err(out[-2048:], ref[-2048:]) < TOL_BF16_IO
@@ -178,6 +190,7 @@ def test_gqa_prefill_32768_tokens_sampled_positions(oracle):
     out = D.full_attn_prefill(dl, kv, kv_len, _t(QP, bf)[None], _t(K, bf)[None], _t(V, bf)[None], T).float().cpu().numpy()[0]
     Kb, Vb = kv.rows(0, T)                       # [T][1][8][34] bytes
     Kd, Vd = _q8_0_rows_to_f32(Kb.reshape(T, 1, 8, 34)), _q8_0_rows_to_f32(Vb.reshape(T, 1, 8, 34))
+    worst = 0.0
     for p in (0, 1, 127, 128, 4095, 16383, 32767):
         okv = oracle.kv(p + 1, layer.nkv, layer.hd, O.KV_Q8_0)
         if p:
@@ -189,7 +202,9 @@ def test_gqa_prefill_32768_tokens_sampled_positions(oracle):
         ref = oracle.full_attn_step(layer, okv, p, QP[p], K[p], V[p])
         Ko, _ = okv.rows_q8_0()
         assert (np.asarray(Ko)[p].reshape(-1) == Kb[p].reshape(-1)).all(), f"row {p}: the appended K row differs from the oracle's"
+        worst = max(worst, rel_err(out[p], ref))
         assert rel_err(out[p], ref) < TOL_BF16_IO, p
+    _note("gqa prefill 32768 tokens bf16, sampled rows", out=worst, bar=TOL_BF16_IO)
 
 
 def test_head_sharded_decode_shard_shapes(oracle):
@@ -224,11 +239,13 @@ def test_head_sharded_decode_shard_shapes(oracle):
         okvs.append(okv)
     kv_len = torch.tensor(ctx, dtype=torch.int32, device="cuda")
     data = [full_inputs(700 + b, layer, steps, bf16=True) for b in range(len(ctx))]
+    worst_full = worst_lin = 0.0
     for s in range(steps):
         qp, k, v = [np.stack([data[b][i][s] for b in range(len(ctx))]) for i in range(3)]
         out = D.full_attn_step(dl, kv, kv_len, _t(qp, bf), _t(k, bf), _t(v, bf), max_len=max(caps)).float().cpu().numpy()
         for b in range(len(ctx)):
             ref = oracle.full_attn_step(layer, okvs[b], ctx[b] + s, qp[b], k[b], v[b])
+            worst_full = max(worst_full, rel_err(out[b], ref))
             assert rel_err(out[b], ref) < TOL_BF16_IO, (s, b)
         D.advance(kv_len)
     # --- delta-net
@@ -245,7 +262,10 @@ def test_head_sharded_decode_shard_shapes(oracle):
         out = D.linear_attn_step(dlin, st, pos, *[_t(x, bf) for x in stack]).float().cpu().numpy()
         for b in range(B):
             ref = oracle.linear_attn_step(lin, S[b], buf[b], *[ins[b][i][t] for i in range(4)])
+            worst_lin = max(worst_lin, rel_err(out[b], ref))
             assert rel_err(out[b], ref) < TOL_BF16_IO, (t, b)
         D.advance(pos)
+    _note("397B shard shapes bf16", gqa_out=worst_full, delta_out=worst_lin,
+          delta_state=max(rel_err(st.S[b].cpu().numpy(), S[b]) for b in range(B)), bar=TOL_BF16_IO)
     for b in range(B):
         assert rel_err(st.S[b].cpu().numpy(), S[b]) < TOL
