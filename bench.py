@@ -560,7 +560,7 @@ def run_ours(args, rank, world, local_rank):
     all_ctx = draw_contexts(args.seqs * world, args.min_ctx, args.max_ctx, args.seed)
     # one draw for the whole job, dealt so that every rank gets the same count and the summed contexts balance
     contexts = all_ctx[sequence_shard(all_ctx, rank, world)]
-    total_steps = 2 * (args.warmup + args.steps) + 12
+    total_steps = 2 * (args.warmup + args.steps) + 14
     caps = [int(c) + total_steps + 8 for c in contexts]
     stack = AttnStack("35b", caps, kv_mode=D.KV_Q8_0, seed=args.seed, device=dev)
     stack.fill(contexts, seed=args.seed + 17)
@@ -578,20 +578,43 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()                   # runs from the warm-up to the end of the host-fed timed region
-    for _ in range(args.warmup):
-        stack.decode_step(ins, outs, max_len=max_len)
+    # The step is a fixed sequence of 81 launches on device-resident arguments (positions live on the device), so it
+    # is captured once into a CUDA graph and replayed: launch gaps between the kernels go.  Warm-up runs on the
+    # capture stream first (the library keeps its delta-net work buffer per stream and must not allocate under
+    # capture).  --no-graph times the plain launch loop instead.
     n_layers = len(stack.layers)
+    graph = None
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for _ in range(args.warmup):
+            stack.decode_step(ins, outs, max_len=max_len)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                stack.decode_step(ins, outs, max_len=max_len)
+            graph.replay()                # one untimed replay
+        except Exception as e:            # noqa: BLE001 - any capture problem: time the launch loop, say so
+            sys.stderr.write(f"bench: CUDA graph capture failed ({e}); timing the launch loop\n")
+            graph = None
     barrier()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     for s in range(args.steps):
-        stack.decode_step(ins, outs, max_len=max_len)
+        if graph is not None:
+            graph.replay()
+        else:
+            stack.decode_step(ins, outs, max_len=max_len)
     t_end.record()
     barrier()
     ms_total = t_start.elapsed_time(t_end)
     # per-family times: a separate pass with an event between the layers (events between the launches cost the
     # overlap of a kernel's prologue with its predecessor's tail, so they stay out of the timed region above)
     fam_steps = max(3, min(args.steps, 5))
+    stack.decode_step(ins, outs, max_len=max_len)      # untimed: this stream's first step sets up its own work buffer
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n_layers + 1)] for _ in range(fam_steps)]
     for s in range(fam_steps):
         for i, (kind, layer, state) in enumerate(stack.layers):
@@ -742,7 +765,9 @@ def run_ours(args, rank, world, local_rank):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": workload_config(args, contexts, world),
+                "config": dict(workload_config(args, contexts, world),
+                               launch="the step's launches replayed as one CUDA graph" if graph is not None
+                               else "a loop of launches (no CUDA graph)"),
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": ms_e2e / args.steps},
                 "gpu_launches": launches * args.steps,
@@ -764,6 +789,7 @@ def main():
     ap.add_argument("--max-ctx", type=int, default=32768)
     ap.add_argument("--seed", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="time the decode step as a loop of launches instead of a CUDA graph replay")
     ap.add_argument("--no-prefill", action="store_true", help="skip the long-prefill leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the strong-scaling, 397B-decode and single-layer legs")
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill leg (1 GPU) and print its figures")
