@@ -379,6 +379,40 @@ ornith_status ornith_cuda_head_shard(int nk, int nv, int nh, int nkv, int rank, 
 ornith_status ornith_cuda_gather_layout(const void *gathered, void *full, int world, size_t rows, int width,
                                         int elem_bytes, void *stream);
 
+/* ---- session records of device-resident state ------------------------------
+ * The engine's session file is a header, one record per layer, the token history and the
+ * last logits (writer: src/ornith_rforward.c:1020-1076, reader: :1078-1171).  These entry
+ * points produce and consume the per-layer records in HOST memory, from and into the device
+ * pools; the engine keeps writing its header, history and logits itself, and its layer loop
+ * becomes one fwrite / fread of a record per layer.  They are synchronous.
+ *
+ *   full-attention layer: int32 q, len, n_kv_heads, head_dim, then (:1042-1052)
+ *     q = 0  K, V f32 [len][n_kv_heads][head_dim]
+ *     q = 1  Kq, Vq int8 [len][n_kv_heads][head_dim], Ks, Vs f32 [len][n_kv_heads]
+ *     q = 2  K, V ggml Q8_0 rows [len][n_kv_heads][head_dim/32][34] — an extension for
+ *            ORNITH_KV_Q8_0 pools; the engine has no such mode and rejects the record by q
+ *   delta-net layer: S f32 [nv][dv][dk], int32 conv_k, Cc, history f32 [(conv_k-1)][Cc],
+ *     oldest token first (:1054-1063)
+ * Records with q = 0 / 1 and the delta-net records are byte for byte the engine's, so a
+ * snapshot taken on the device loads into the CPU engine and the other way round. */
+size_t ornith_cuda_kv_record_bytes(const ornith_cuda_kv *kv, int len);
+/* the first `len` positions of sequence `seq` */
+ornith_status ornith_cuda_kv_export(const ornith_cuda_kv *kv, int seq, int len, void *host_dst,
+                                    size_t dst_bytes, void *stream);
+/* checks q, n_kv_heads, head_dim and the capacity; *len_out (may be NULL) = positions loaded;
+ * dev_kv_len (may be NULL): the batch's device length array, entry `seq` is set too */
+ornith_status ornith_cuda_kv_import(const ornith_cuda_kv *kv, int seq, const void *host_src,
+                                    size_t src_bytes, int32_t *len_out, int32_t *dev_kv_len,
+                                    void *stream);
+size_t ornith_cuda_linear_record_bytes(const ornith_cuda_linear_layer *layer);
+/* pos = tokens the sequence has seen so far (it fixes where the conv ring starts) */
+ornith_status ornith_cuda_linear_export(const ornith_cuda_linear_layer *layer,
+                                        const ornith_cuda_linear_state *st, int seq, int pos,
+                                        void *host_dst, size_t dst_bytes, void *stream);
+ornith_status ornith_cuda_linear_import(const ornith_cuda_linear_layer *layer,
+                                        const ornith_cuda_linear_state *st, int seq, int pos,
+                                        const void *host_src, size_t src_bytes, void *stream);
+
 /* ---- per-head primitives on device pointers (what tier 1 is built from) ---- */
 
 /* reference: src/ornith_attn.c:198-213; n_heads independent states S [h][dv][dk],

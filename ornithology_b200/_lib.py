@@ -112,6 +112,12 @@ SYMBOLS = {
     "ornith_cuda_advance": (_I, [vp, _I, _I, vp]),
     "ornith_cuda_head_shard": (_I, [_I, _I, _I, _I, _I, _I, vp]),
     "ornith_cuda_gather_layout": (_I, [vp, vp, _I, _SZ, _I, _I, vp]),
+    "ornith_cuda_kv_record_bytes": (_SZ, [vp, _I]),
+    "ornith_cuda_kv_export": (_I, [vp, _I, _I, vp, _SZ, vp]),
+    "ornith_cuda_kv_import": (_I, [vp, _I, vp, _SZ, vp, vp, vp]),
+    "ornith_cuda_linear_record_bytes": (_SZ, [vp]),
+    "ornith_cuda_linear_export": (_I, [vp, vp, _I, _I, vp, _SZ, vp]),
+    "ornith_cuda_linear_import": (_I, [vp, vp, _I, _I, vp, _SZ, vp]),
     "ornith_cuda_linear_attn_step": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, vp]),
     "ornith_cuda_linear_attn_prefill_scratch": (_SZ, [vp, _I, _I]),
     "ornith_cuda_linear_attn_prefill": (_I, [vp, vp, vp, vp, vp, vp, vp, vp, _I, _I, _I, _I, vp, _SZ, vp]),

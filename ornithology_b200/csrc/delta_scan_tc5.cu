@@ -548,14 +548,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             if (dbg && n == 1) {                                         // the state after the first update (before this chunk's decay)
 #pragma unroll 1
                 for (int cc = 0; cc < 2; cc++) {
-                    tmem_ld32(lane_t + TM_S + 64 * half + 32 * cc, x);
-                    tmem_wait_ld();
+                    tmem_ld32_wait(lane_t + TM_S + 64 * half + 32 * cc, x);
 #pragma unroll
                     for (int i = 0; i < 32; i++) dbg[4 * 128 * 64 + row * 128 + 64 * half + 32 * cc + i] = x[i];
                 }
             }
-            tmem_ld32(lane_t + TM_KQ + 128 * s + 32 * half, x);          // KS^T
-            tmem_wait_ld();
+            tmem_ld32_wait(lane_t + TM_KQ + 128 * s + 32 * half, x);          // KS^T
             if (tid == 0) TR(4, n, 0);
             if (dbg && n == 0) {
 #pragma unroll
@@ -591,8 +589,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
                 const float pend = aux[4 * C];
 #pragma unroll 1
                 for (int cc = 0; cc < 2; cc++) {
-                    tmem_ld32(lane_t + TM_S + 64 * half + 32 * cc, x);
-                    tmem_wait_ld();
+                    tmem_ld32_wait(lane_t + TM_S + 64 * half + 32 * cc, x);
 #pragma unroll
                     for (int i = 0; i < 32; i++) x[i] *= pend;
                     tmem_st32(lane_t + TM_S + 64 * half + 32 * cc, x);
@@ -603,8 +600,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             if (!ok) break;
             if (tid == 0) TR(1, n, 4);
             fence_after();
-            tmem_ld32(lane_t + TM_U + 32 * half, x);                     // U^T
-            tmem_wait_ld();
+            tmem_ld32_wait(lane_t + TM_U + 32 * half, x);                     // U^T
             if (tid == 0) TR(4, n, 3);
             if (dbg && n == 0) {
 #pragma unroll
@@ -638,8 +634,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
 #pragma unroll 1
         for (int cc = 0; cc < 2; cc++) {                                 // the state goes home
             float x[32];
-            tmem_ld32(lane_t + TM_S + 64 * half + 32 * cc, x);
-            tmem_wait_ld();
+            tmem_ld32_wait(lane_t + TM_S + 64 * half + 32 * cc, x);
             float4 *dst = reinterpret_cast<float4 *>(Sout + (size_t)row * 128 + 64 * half + 32 * cc);
 #pragma unroll
             for (int i = 0; i < 8; i++)
@@ -671,9 +666,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
                 if (!ok) break;
                 fence_after();
                 float q[16], x[16];
-                tmem_ld16(t_qs + 128 * s, q);
-                tmem_ld16(t_pu + 128 * s, x);
-                tmem_wait_ld();
+                tmem_ld16x2_wait(t_qs + 128 * s, q, t_pu + 128 * s, x);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const float4 p4 = *reinterpret_cast<const float4 *>(aux + 4 * i);
@@ -704,11 +697,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             if (!ok) break;
             if (tid == 256) TR(2, n, 1);
             fence_after();
+#ifdef ORNITH_SCAN_CHECK
+            float chk_p[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) chk_p[i] = aux[i];
+#endif
             {
                 float q[16], x[16];
-                tmem_ld16(t_qs + 128 * s, q);                            // QS^T
-                tmem_ld16(t_pu + 128 * s, x);                            // (P U)^T
-                tmem_wait_ld();
+                tmem_ld16x2_wait(t_qs + 128 * s, q, t_pu + 128 * s, x);   // QS^T, (P U)^T
                 if (dbg && n == 0) {
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
@@ -752,15 +748,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
 #pragma unroll
             for (int ps = 0; ps < 2; ps++) {                             // 8 tokens at a time
                 float q[8], x[8];
-                tmem_ld8(t_qs + 128 * s + 8 * ps, q);
-                tmem_ld8(t_pu + 128 * s + 8 * ps, x);
-                tmem_wait_ld();
+                tmem_ld8x2_wait(t_qs + 128 * s + 8 * ps, q, t_pu + 128 * s + 8 * ps, x);
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                     const float4 p4 = *reinterpret_cast<const float4 *>(aux + 8 * ps + 4 * i);
                     x[4 * i] = fmaf(p4.x, q[4 * i], x[4 * i]); x[4 * i + 1] = fmaf(p4.y, q[4 * i + 1], x[4 * i + 1]);
                     x[4 * i + 2] = fmaf(p4.z, q[4 * i + 2], x[4 * i + 2]); x[4 * i + 3] = fmaf(p4.w, q[4 * i + 3], x[4 * i + 3]);
                 }
+#ifdef ORNITH_SCAN_CHECK
+                if (a.trace) {   // bring-up check: read the same columns and factors again, count what changed meanwhile
+                    float q2[8], x2[8];
+                    tmem_ld8x2_wait(t_qs + 128 * s + 8 * ps, q2, t_pu + 128 * s + 8 * ps, x2);
+                    int bad_q = 0, bad_x = 0, bad_p = 0;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float pf = aux[8 * ps + i];
+                        bad_q |= __float_as_uint(q2[i]) != __float_as_uint(q[i]);
+                        bad_x |= __float_as_uint(fmaf(pf, q2[i], x2[i])) != __float_as_uint(x[i]);
+                        bad_p |= __float_as_uint(pf) != __float_as_uint(chk_p[8 * ps + i]);
+                    }
+                    unsigned long long *tr = (unsigned long long *)a.trace;
+                    if (bad_q) atomicAdd(tr + 0, 1ull);
+                    if (bad_x) atomicAdd(tr + 1, 1ull);
+                    if (bad_p) atomicAdd(tr + 2, 1ull);
+                    if (bad_q | bad_x | bad_p) tr[4] = ((unsigned long long)hv << 32) | ((unsigned)n << 8) | (warp << 1) | ps;
+                }
+#endif
                 if (ps == 1) {                                           // both tiles and the factors have been read for the last time
                     fence_before();
                     mbar_arrive(su32(&bars.o_read[s]));

@@ -253,8 +253,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
             ok = ok && mbar_wait(su32(&bars.s_full[sb]), (uint32_t)(j / NB) & 1u);
             fence_after();
             float s[32];
-            tmem_ld32(lane_t + TM_S + sb * BN + 32 * half, s);
-            tmem_wait_ld();
+            tmem_ld32_wait(lane_t + TM_S + sb * BN + 32 * half, s);
             if (key0 + 31 > qpos) {                            // the tile reaches past this row's diagonal
 #pragma unroll
                 for (int c = 0; c < 32; c++)
@@ -297,8 +296,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
 #pragma unroll 1
                 for (int c = 0; c < HD / 2; c += 32) {         // this thread's half of the output row
                     float o[32];
-                    tmem_ld32(lane_t + TM_O + 128 * half + c, o);
-                    tmem_wait_ld();
+                    tmem_ld32_wait(lane_t + TM_O + 128 * half + c, o);
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] *= corr;
                     tmem_st32(lane_t + TM_O + 128 * half + c, o);
@@ -323,8 +321,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
 #pragma unroll 1
         for (int c = 128 * half; c < 128 * half + 128; c += 32) {
             float o[32];
-            tmem_ld32(lane_t + TM_O + c, o);
-            tmem_wait_ld();
+            tmem_ld32_wait(lane_t + TM_O + c, o);
             if (live) {
 #pragma unroll
                 for (int i = 0; i < 32; i++) {

@@ -120,6 +120,26 @@ class KvBatch:
                 self.Vs[o * self.nkv:(o + n) * self.nkv].cpu().numpy().reshape(n, self.nkv))
 
 
+def kv_export(kv: KvBatch, seq, length):
+    """Session record of the first `length` positions of sequence `seq` (bytes, the engine's layer record)."""
+    lib = _lib.load()
+    n = lib.ornith_cuda_kv_record_bytes(C.byref(kv.c), int(length))
+    buf = np.zeros(n, np.uint8)
+    check(lib.ornith_cuda_kv_export(C.byref(kv.c), int(seq), int(length), buf.ctypes.data_as(C.c_void_p), n, _stream()),
+          "kv_export")
+    return buf
+
+
+def kv_import(kv: KvBatch, seq, record, kv_len=None):
+    """Load a session record into sequence `seq`; returns its position count (and sets kv_len[seq] if given)."""
+    lib = _lib.load()
+    rec = np.ascontiguousarray(record, np.uint8)
+    n = C.c_int32(0)
+    check(lib.ornith_cuda_kv_import(C.byref(kv.c), int(seq), rec.ctypes.data_as(C.c_void_p), rec.size, C.byref(n),
+                                    _ptr(kv_len), _stream()), "kv_import")
+    return n.value
+
+
 class LinearLayer:
     """Weights and shape of one gated delta-net layer, resident on the device."""
 
@@ -161,6 +181,21 @@ class LinearState:
         check(_lib.load().ornith_cuda_conv_export(_ptr(self.conv[seq]), L.conv_k, L.cc, int(pos), _ptr(img),
                                                   _stream()), "conv_export")
         return img
+
+    def export_record(self, seq, pos):
+        """Session record of sequence `seq` after `pos` tokens: S, conv_k, Cc, history image (bytes)."""
+        lib = _lib.load()
+        n = lib.ornith_cuda_linear_record_bytes(C.byref(self.layer.c))
+        buf = np.zeros(n, np.uint8)
+        check(lib.ornith_cuda_linear_export(C.byref(self.layer.c), C.byref(self.c), int(seq), int(pos),
+                                            buf.ctypes.data_as(C.c_void_p), n, _stream()), "linear_export")
+        return buf
+
+    def import_record(self, seq, pos, record):
+        lib = _lib.load()
+        rec = np.ascontiguousarray(record, np.uint8)
+        check(lib.ornith_cuda_linear_import(C.byref(self.layer.c), C.byref(self.c), int(seq), int(pos),
+                                            rec.ctypes.data_as(C.c_void_p), rec.size, _stream()), "linear_import")
 
     def load_conv_image(self, seq, pos, image):
         L = self.layer

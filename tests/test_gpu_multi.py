@@ -141,4 +141,6 @@ def test_prefill_head_shards_one_after_the_other_on_one_gpu():
         a = torch.cat([outs[1 + r][i] for r in range(world)], dim=-1).float()
         b = outs[0][i].float()
         err = float((a - b).abs().max() / b.abs().max())
-        assert err < 2e-4, (kind, err)
+        # the delta-net shards (8 value heads) take the segment-parallel scan, whose stitching product is a
+        # different tf32 summation from the single scan of the unsharded layer: the parity bar applies, not equality
+        assert err < 1e-3, (kind, err)
