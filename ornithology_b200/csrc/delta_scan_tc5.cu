@@ -697,33 +697,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
             if (!ok) break;
             if (tid == 256) TR(2, n, 1);
             fence_after();
-#ifdef ORNITH_SCAN_CHECK
-            float chk_p[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) chk_p[i] = aux[i];
-#endif
             {
-                float q[16], x[16];
-                tmem_ld16x2_wait(t_qs + 128 * s, q, t_pu + 128 * s, x);   // QS^T, (P U)^T
-                if (dbg && n == 0) {
+                float x[16];
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        dbg[2 * 128 * 64 + row * 64 + 16 * grp + i] = q[i];
-                        dbg[3 * 128 * 64 + row * 64 + 16 * grp + i] = x[i];
+                for (int h8 = 0; h8 < 2; h8++) {                         // 8 tokens at a time: O = p rq QS + P U, squared
+                    float q[8], y[8];
+                    tmem_ld8x2_wait(t_qs + 128 * s + 8 * h8, q, t_pu + 128 * s + 8 * h8, y);   // QS^T, (P U)^T
+                    if (dbg && n == 0) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            dbg[2 * 128 * 64 + row * 64 + 16 * grp + 8 * h8 + i] = q[i];
+                            dbg[3 * 128 * 64 + row * 64 + 16 * grp + 8 * h8 + i] = y[i];
+                        }
                     }
-                }
 #pragma unroll
-                for (int i = 0; i < 4; i++) {                            // O = p rq QS + P U (the output scale comes later)
-                    const float4 p4 = *reinterpret_cast<const float4 *>(aux + 4 * i);
-                    x[4 * i] = fmaf(p4.x, q[4 * i], x[4 * i]); x[4 * i + 1] = fmaf(p4.y, q[4 * i + 1], x[4 * i + 1]);
-                    x[4 * i + 2] = fmaf(p4.z, q[4 * i + 2], x[4 * i + 2]); x[4 * i + 3] = fmaf(p4.w, q[4 * i + 3], x[4 * i + 3]);
+                    for (int i = 0; i < 2; i++) {
+                        const float4 p4 = *reinterpret_cast<const float4 *>(aux + 8 * h8 + 4 * i);
+                        y[4 * i] = fmaf(p4.x, q[4 * i], y[4 * i]); y[4 * i + 1] = fmaf(p4.y, q[4 * i + 1], y[4 * i + 1]);
+                        y[4 * i + 2] = fmaf(p4.z, q[4 * i + 2], y[4 * i + 2]); y[4 * i + 3] = fmaf(p4.w, q[4 * i + 3], y[4 * i + 3]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; i++) x[8 * h8 + i] = y[i] * y[i];
                 }
                 // sum of squares over the 32 rows of this warp: token t of the 16 ends up in lanes t and t + 16
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    x[i] *= x[i];
-                    x[i] += __shfl_xor_sync(0xffffffffu, x[i], 16);
-                }
+                for (int i = 0; i < 16; i++) x[i] += __shfl_xor_sync(0xffffffffu, x[i], 16);
 #pragma unroll
                 for (int off = 8; off >= 1; off >>= 1) {
                     const bool up = (lane & off) != 0;
@@ -755,25 +753,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
                     x[4 * i] = fmaf(p4.x, q[4 * i], x[4 * i]); x[4 * i + 1] = fmaf(p4.y, q[4 * i + 1], x[4 * i + 1]);
                     x[4 * i + 2] = fmaf(p4.z, q[4 * i + 2], x[4 * i + 2]); x[4 * i + 3] = fmaf(p4.w, q[4 * i + 3], x[4 * i + 3]);
                 }
-#ifdef ORNITH_SCAN_CHECK
-                if (a.trace) {   // bring-up check: read the same columns and factors again, count what changed meanwhile
-                    float q2[8], x2[8];
-                    tmem_ld8x2_wait(t_qs + 128 * s + 8 * ps, q2, t_pu + 128 * s + 8 * ps, x2);
-                    int bad_q = 0, bad_x = 0, bad_p = 0;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float pf = aux[8 * ps + i];
-                        bad_q |= __float_as_uint(q2[i]) != __float_as_uint(q[i]);
-                        bad_x |= __float_as_uint(fmaf(pf, q2[i], x2[i])) != __float_as_uint(x[i]);
-                        bad_p |= __float_as_uint(pf) != __float_as_uint(chk_p[8 * ps + i]);
-                    }
-                    unsigned long long *tr = (unsigned long long *)a.trace;
-                    if (bad_q) atomicAdd(tr + 0, 1ull);
-                    if (bad_x) atomicAdd(tr + 1, 1ull);
-                    if (bad_p) atomicAdd(tr + 2, 1ull);
-                    if (bad_q | bad_x | bad_p) tr[4] = ((unsigned long long)hv << 32) | ((unsigned)n << 8) | (warp << 1) | ps;
-                }
-#endif
                 if (ps == 1) {                                           // both tiles and the factors have been read for the last time
                     fence_before();
                     mbar_arrive(su32(&bars.o_read[s]));
