@@ -397,3 +397,22 @@ def test_groups_of_16_query_heads(oracle, mode):
             ref = oracle.full_attn_step(layer, okvs[b], ctx[b] + s, qp[b], k[b], v[b])
             assert rel_err(out[b], ref) < TOL, (s, b)
         D.advance(kv_len)
+
+
+def test_tensor_core_prefill_is_reproducible():
+    """Eight runs of the same 2048-token prompt through the tcgen05 prefill must agree bit for bit."""
+    import torch
+    from ornithology_b200 import device as D
+    layer = full_case(61)
+    dl = device_full(layer)
+    T = 2048
+    QP, K, V = [torch.from_numpy(x).cuda()[None] for x in full_inputs(62, layer, T)]
+    first = None
+    for rep in range(8):
+        kv = D.KvBatch(D.KV_Q8_0, layer.nkv, layer.hd, [T])
+        kv_len = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = D.full_attn_prefill(dl, kv, kv_len, QP, K, V, T).cpu().numpy()
+        if first is None:
+            first = out
+        else:
+            assert (out == first).all(), rep
