@@ -413,6 +413,44 @@ ornith_status ornith_cuda_linear_import(const ornith_cuda_linear_layer *layer,
                                         const ornith_cuda_linear_state *st, int seq, int pos,
                                         const void *host_src, size_t src_bytes, void *stream);
 
+/* ---- host-fed layer calls over device-resident state -------------------------
+ * For an engine whose projections still run on the host: one object holds the state of all
+ * layers of one sequence on the device (what rstate holds on the host, reference:
+ * src/ornith_rforward.c:212-264), and the four wiring functions (full_attn :419-455,
+ * linear_attn :457-503, full_attn_prefill :513-556, linear_attn_prefill :563-618) hand over
+ * their projection outputs (host f32) and get the attention output back (host f32).  T == 1
+ * runs the decode kernels, T > 1 the prefill kernels.  Synchronous.  Conventions of the
+ * real-weights engine (tiled head map, no conv bias, 1/sqrt(dk) output scale, gated q).
+ * kv_mode: ORNITH_KV_F32 / ORNITH_KV_INT8_HEAD (the engine's ORNITH_KV_Q8=1) / ORNITH_KV_Q8_0. */
+typedef struct ornith_cuda_engine ornith_cuda_engine;
+ornith_cuda_engine *ornith_cuda_engine_new(int num_layers, int capacity, int kv_mode, int n_heads,
+                                           int n_kv_heads, int head_dim, int rope_dim, float rope_theta,
+                                           float rms_eps, int nk, int nv, int dk, int dv, int conv_k);
+void ornith_cuda_engine_free(ornith_cuda_engine *e);
+/* weights the attention math needs, host pointers; uploaded on the first call for a layer
+ * (which also creates that layer's zeroed state), ignored afterwards */
+ornith_status ornith_cuda_engine_full_layer(ornith_cuda_engine *e, int layer, const float *q_norm_w,
+                                            const float *k_norm_w);
+ornith_status ornith_cuda_engine_linear_layer(ornith_cuda_engine *e, int layer, const float *conv_w,
+                                              const float *a_coef, const float *dt_bias,
+                                              const float *norm_w);
+/* qproj [T][n_heads][2*head_dim], k, v [T][n_kv_heads*head_dim], out [T][n_heads*head_dim];
+ * pos = rows already in the cache = position of the first token */
+ornith_status ornith_cuda_engine_full_attn(ornith_cuda_engine *e, int layer, int pos, int T,
+                                           const float *qproj, const float *k, const float *v, float *out);
+/* qkv [T][Cc] (before the conv), a, b [T][nv], z [T][nv*dv] (gate projection, before SiLU),
+ * out [T][nv*dv] (scaled, normalised, gated: what ssm_out multiplies) */
+ornith_status ornith_cuda_engine_linear_attn(ornith_cuda_engine *e, int layer, int pos, int T,
+                                             const float *qkv, const float *a, const float *b,
+                                             const float *z, float *out);
+/* the layer's session record after `pos` tokens (layouts: the session-record entry points above);
+ * import needs the layer's weights call first and, for a full layer, a record of `pos` positions */
+size_t ornith_cuda_engine_record_bytes(const ornith_cuda_engine *e, int layer, int pos);
+ornith_status ornith_cuda_engine_export(const ornith_cuda_engine *e, int layer, int pos, void *host_dst,
+                                        size_t dst_bytes);
+ornith_status ornith_cuda_engine_import(ornith_cuda_engine *e, int layer, int pos, const void *host_src,
+                                        size_t src_bytes);
+
 /* ---- per-head primitives on device pointers (what tier 1 is built from) ---- */
 
 /* reference: src/ornith_attn.c:198-213; n_heads independent states S [h][dv][dk],

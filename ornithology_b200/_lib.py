@@ -112,6 +112,15 @@ SYMBOLS = {
     "ornith_cuda_advance": (_I, [vp, _I, _I, vp]),
     "ornith_cuda_head_shard": (_I, [_I, _I, _I, _I, _I, _I, vp]),
     "ornith_cuda_gather_layout": (_I, [vp, vp, _I, _SZ, _I, _I, vp]),
+    "ornith_cuda_engine_new": (vp, [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _I]),
+    "ornith_cuda_engine_free": (None, [vp]),
+    "ornith_cuda_engine_full_layer": (_I, [vp, _I, vp, vp]),
+    "ornith_cuda_engine_linear_layer": (_I, [vp, _I, vp, vp, vp, vp]),
+    "ornith_cuda_engine_full_attn": (_I, [vp, _I, _I, _I, vp, vp, vp, vp]),
+    "ornith_cuda_engine_linear_attn": (_I, [vp, _I, _I, _I, vp, vp, vp, vp, vp]),
+    "ornith_cuda_engine_record_bytes": (_SZ, [vp, _I, _I]),
+    "ornith_cuda_engine_export": (_I, [vp, _I, _I, vp, _SZ]),
+    "ornith_cuda_engine_import": (_I, [vp, _I, _I, vp, _SZ]),
     "ornith_cuda_kv_record_bytes": (_SZ, [vp, _I]),
     "ornith_cuda_kv_export": (_I, [vp, _I, _I, vp, _SZ, vp]),
     "ornith_cuda_kv_import": (_I, [vp, _I, vp, _SZ, vp, vp, vp]),

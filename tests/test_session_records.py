@@ -98,7 +98,10 @@ def test_kv_records_against_the_engine_layout(oracle, mode):
         nb = rows * layer.hd
         kq, kq_ref = rec[16:16 + nb].view(np.int8).reshape(rows, layer.hd), ref[16:16 + nb].view(np.int8).reshape(rows, layer.hd)
         assert (rec[16 + nb:16 + 2 * nb] == ref[16 + nb:16 + 2 * nb]).all(), "V codes differ"
-        assert (rec[16 + 2 * nb:] == ref[16 + 2 * nb:]).all(), "scales differ"
+        ks, ks_ref = rec[16 + 2 * nb:16 + 2 * nb + 4 * rows].view(np.float32), ref[16 + 2 * nb:16 + 2 * nb + 4 * rows].view(np.float32)
+        assert (rec[16 + 2 * nb + 4 * rows:] == ref[16 + 2 * nb + 4 * rows:]).all(), "V scales differ"
+        # a K scale is amax / 127 of the rotated row: the last place may differ when the largest value is a rotated one
+        assert np.abs(ks - ks_ref).max() <= 2.4e-7 * np.abs(ks_ref).max() and (ks != ks_ref).mean() < 0.05
         d = np.abs(kq.astype(np.int32) - kq_ref.astype(np.int32))
         assert (d[:, layer.rope_dim:] == 0).all() and d.max() <= 1 and (d != 0).mean() < 1e-3, (int(d.max()), int((d != 0).sum()))
     else:
