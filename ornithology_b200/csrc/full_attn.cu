@@ -676,11 +676,19 @@ ornith_status ornith_cuda_full_attn_step(const ornith_cuda_full_layer *l, const 
     return orn_check_launch("k_gqa_combine");
 }
 
+// The f32 image of the prepared query rows is only read by the kernels other than the tcgen05 one: when that
+// kernel will run (head_dim 256, at least 256 rows so that the warp-per-row front end writes the f16 image itself)
+// it is not reserved.
+static size_t prefill_q_f32_bytes(const ornith_cuda_full_layer *l, int n_seq, int T) {
+    const bool f16_image_only = l->head_dim == 256 && !force_generic_decode() && (long long)n_seq * T >= 256 && gqa_prefill_tc_selected();
+    return f16_image_only ? 0 : align_up((size_t)n_seq * T * l->n_heads * l->head_dim * sizeof(float), 256);
+}
+
 size_t ornith_cuda_full_attn_prefill_scratch(const ornith_cuda_full_layer *l, int n_seq, int T, int max_len) {
     if (!l || n_seq <= 0 || T <= 0) return 0;
     if (max_len < T) max_len = T;
-    size_t q = align_up((size_t)n_seq * T * l->n_heads * l->head_dim * sizeof(float), 256);
-    // decoded f16 image of the visible cache rows, used by the tensor-core path
+    size_t q = prefill_q_f32_bytes(l, n_seq, T);
+    // decoded f16 image of the visible cache rows and the f16 query image, used by the tensor-core path
     if (l->head_dim == 256) q += gqa_prefill_mma_scratch(n_seq, l->n_kv_heads, l->n_heads, T, max_len);
     return q;
 }
@@ -720,16 +728,21 @@ ornith_status ornith_cuda_full_attn_prefill(const ornith_cuda_full_layer *l, con
     }
     cudaStream_t st = as_stream(stream);
     const int hd = l->head_dim, nh = l->n_heads, G = nh / l->n_kv_heads;
-    float *q_prep = (float *)scratch;
+    const size_t q_f32 = prefill_q_f32_bytes(l, B, T);
+    float *q_prep = q_f32 ? (float *)scratch : nullptr;
     const bool bf = act_dtype == ORNITH_ACT_BF16;
     const bool tensor_path = gqa_prefill_mma_supported(make_view(kv)) && !force_generic_decode();
-    void *kvh = (char *)scratch + align_up((size_t)B * T * nh * hd * sizeof(float), 256);
+    void *kvh = (char *)scratch + q_f32;
     __half *Qh = nullptr;
     float *rs = nullptr;
     // the warp-per-row front end (B * T >= 256) writes the f16 query image of the tcgen05 kernel itself
     const bool q_image = tensor_path && (long long)B * T >= 256 &&
                          gqa_prefill_q_image(kvh, B, l->n_kv_heads, nh, T, max_len, &Qh, &rs);
     if (!q_image) { Qh = nullptr; rs = nullptr; }
+    if (!q_image && !q_prep) {
+        orn_record_error("full_attn_prefill: the scratch must be 16-byte aligned");
+        return ORNITH_ERR_FORMAT;
+    }
     if (bf) ORN_TRY(launch_prep<__nv_bfloat16>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st, false, Qh, rs));
     else    ORN_TRY(launch_prep<float>(l, kv, kv_len, rope_pos, qproj, k, v, q_prep, B * T, T, st, false, Qh, rs));
 

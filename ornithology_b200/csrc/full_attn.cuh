@@ -60,6 +60,7 @@ ornith_status launch_gqa_prefill_mma(const KvView &kv, const int32_t *kv_len, co
 size_t gqa_prefill_tc_scratch(int n_seq, int nh, int T);
 // Where the f16 query image and its per-row factors live inside `kvh_scratch`, if the tcgen05 kernel is
 // going to run: the front end may then write them itself and pass q_prep = nullptr to the launchers below.
+bool gqa_prefill_tc_selected();
 bool gqa_prefill_q_image(void *kvh_scratch, int n_seq, int nkv, int nh, int T, int Lmax, __half **Qh, float **rs);
 ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, const float *q_prep, const __half *Kh,
                                     const __half *Vh, void *q_scratch, const void *qproj, void *out, int nh, int T,

@@ -549,11 +549,12 @@ bool gqa_decode_q8_mma_supported(const KvView &kv, int nh) {
            ((uintptr_t)kv.K % 16) == 0 && ((uintptr_t)kv.V % 16) == 0;
 }
 
-// ORNITH_CUDA_DECODE_VARIANT=tile selects the variant that decodes V into an f16 tile, =raw the raw-fragment
-// kernel for groups of 9-16 heads too (two CTAs of 8 heads per KV head)
+// ORNITH_CUDA_DECODE_VARIANT: unset = the raw-fragment kernel (groups of 9-16 heads as two CTAs of 8 heads per KV
+// head: 0.51 of HBM bandwidth at 32 query / 2 KV heads against 0.40 for the f16-tile kernel); tile = the variant
+// that decodes V into an f16 tile; mma = the f16-tile kernel for groups of 9-16 heads
 static int decode_variant() {
     static int variant = -1;
-    if (variant < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); variant = !e ? 0 : (e[0] == 't' ? 1 : (e[0] == 'r' ? 2 : 0)); }
+    if (variant < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_VARIANT"); variant = !e ? 0 : (e[0] == 't' ? 1 : (e[0] == 'm' ? 3 : 0)); }
     return variant;
 }
 
@@ -562,7 +563,7 @@ bool gqa_decode_q8_raw_balanced(const KvView &kv, int nh) {
     static int grid_sched = -1;
     if (grid_sched < 0) { const char *e = getenv("ORNITH_CUDA_DECODE_SCHED"); grid_sched = (e && e[0] == 'g') ? 1 : 0; }
     if (grid_sched || !gqa_decode_q8_mma_supported(kv, nh)) return false;
-    return decode_variant() == 2 || (decode_variant() == 0 && nh / kv.nkv <= 8);
+    return decode_variant() == 0 || (decode_variant() == 3 && nh / kv.nkv <= 8);
 }
 
 ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStream_t st, bool *merged) {
@@ -584,7 +585,7 @@ ornith_status launch_gqa_decode_q8_mma(const DecodeArgs &a, int n_seq, cudaStrea
     dim3 grid(a.nsplit, a.kv.nkv, n_seq);
     const int variant = decode_variant();
     const int use_tile = variant == 1;
-    if (a.nh / a.kv.nkv <= 8 || variant == 2) {          // larger groups: k_gqa_decode_q8_mma below (the raw kernel would convert every row twice)
+    if (a.nh / a.kv.nkv <= 8 || variant != 3) {          // (variant mma: groups of 9-16 heads on k_gqa_decode_q8_mma below)
         if (!use_tile) return launch_gqa_decode_q8_raw(a, n_seq, st, merged);
         k_gqa_decode_q8_tok<<<grid, 128, SMEM3_BYTES, st>>>(a);
         return orn_check_launch("k_gqa_decode_q8_tok");

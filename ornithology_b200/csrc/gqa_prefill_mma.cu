@@ -303,6 +303,10 @@ static bool prefer_mma_sync() {
     return v && v[0] == 'm';
 }
 
+// whether the tcgen05 kernel is the one launch_gqa_prefill_mma will use (then the front end writes the f16 query
+// image itself and no f32 query image is needed)
+bool gqa_prefill_tc_selected() { return !prefer_mma_sync(); }
+
 bool gqa_prefill_q_image(void *kvh_scratch, int n_seq, int nkv, int nh, int T, int Lmax, __half **Qh, float **rs) {
     if (prefer_mma_sync() || ((uintptr_t)kvh_scratch % 16) != 0) return false;
     char *q = (char *)kvh_scratch + 2 * image_bytes(n_seq, nkv, Lmax);

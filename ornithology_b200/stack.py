@@ -228,11 +228,11 @@ class AttnStack:
     def launches_per_step(self):
         """Kernel launches of one decode step, mirroring the library's dispatch: a full-attention layer is
         append + split-K decode (+ a merge kernel unless the decode kernel merges itself: Q8_0 rows, head_dim 256,
-        groups of at most 8 query heads); a delta-net layer is one kernel, or front-end + state kernel above 296
+        groups of at most 16 query heads); a delta-net layer is one kernel, or front-end + state kernel above 296
         (sequence, value head) units; one launch advances the positions."""
         n_full = sum(1 for k, _, _ in self.layers if k == "full")
         n_lin = len(self.layers) - n_full
-        fused_merge = self.kv_mode == D.KV_Q8_0 and self.arch["hd"] == 256 and self.nh // max(self.nkv, 1) <= 8
+        fused_merge = self.kv_mode == D.KV_Q8_0 and self.arch["hd"] == 256 and self.nh // max(self.nkv, 1) <= 16
         two_kernels = self.arch["dk"] == 128 and self.arch["dv"] == 128 and self.n_seq * self.nv > 296
         return (2 if fused_merge else 3) * n_full + (2 if two_kernels else 1) * n_lin + 1
 
