@@ -413,6 +413,25 @@ ornith_status ornith_cuda_linear_import(const ornith_cuda_linear_layer *layer,
                                         const ornith_cuda_linear_state *st, int seq, int pos,
                                         const void *host_src, size_t src_bytes, void *stream);
 
+/* ---- quantised projections around the attention core ---------------------------
+ * Q8_0 weights x Q8_K activations, the engine's integer path for attn_qkv, ssm_alpha/beta,
+ * attn_gate, ssm_out, attn_q/k/v/output (matmul_batch_q, reference: src/ornith_rforward.c:138-192;
+ * qdot_quantize_row_q8_K src/ornith_qdot.c:38-70; vec_dot_q8_0 :144-163).  Decode-sized batches:
+ * more than 64 tokens are walked 64 at a time, re-reading the weights. */
+size_t ornith_cuda_qproj_scratch(int T, int n_in);       /* n_in: a multiple of 256 */
+/* x [T][n_in] -> Q8_K.  The codes and scales are the engine's bit for bit.  blocks: device
+ * [T][n_in/256][292 bytes] in the engine's block layout (f32 d, 256 int8, 16 int16 sums), or NULL;
+ * scratch: ornith_cuda_qproj_scratch bytes, 256-byte aligned (the form the product reads). */
+ornith_status ornith_cuda_q8k_quantize(const void *x, int act_dtype, int T, int n_in, void *blocks,
+                                       void *scratch, size_t scratch_bytes, void *stream);
+/* y [T][n_out] = x [T][n_in] through W = device Q8_0 rows [n_out][n_in/32][34] (the GGUF tensor bytes,
+ * 16-byte aligned).  Quantises x into scratch, then the product on the tensor cores: integer codes of
+ * both operands exact, a weight (code x f16 block scale) rounded once to f16, f32 sums, the activation's
+ * scale applied per block of 256 in f32.  out_dtype: ORNITH_ACT_F32 or ORNITH_ACT_BF16. */
+ornith_status ornith_cuda_matmul_q8_0(const void *W, int n_in, int n_out, const void *x, int act_dtype,
+                                      int T, void *y, int out_dtype, void *scratch, size_t scratch_bytes,
+                                      void *stream);
+
 /* ---- host-fed layer calls over device-resident state -------------------------
  * For an engine whose projections still run on the host: one object holds the state of all
  * layers of one sequence on the device (what rstate holds on the host, reference:

@@ -230,6 +230,26 @@ class Oracle:
         self.lib.orc_rope_partial(_fp(v), v.size, rotary_dim, pos, theta)
         return v
 
+    # -- quantised projections ----------------------------------------------
+    def q8k_quantize(self, x):
+        """f32 [..., k] (k a multiple of 256) -> Q8_K blocks as bytes [..., k/256, 292]."""
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[:-1] + (x.shape[-1] // 256, 292), np.uint8)
+        self.lib.orc_q8k_quantize.argtypes = [_f32p, C.c_void_p, C.c_int64]
+        self.lib.orc_q8k_quantize(_fp(x), out.ctypes.data, x.size)
+        return out
+
+    def matmul_q8_0(self, W, n_in, X):
+        """Y [T][out] = X [T][n_in] through Q8_0 weight rows W (bytes [out][n_in/32*34]), the engine's integer path."""
+        W = np.ascontiguousarray(W, np.uint8)
+        X = np.ascontiguousarray(X, np.float32).reshape(-1, n_in)
+        n_out = W.size // (n_in // 32 * 34)
+        Y = np.empty((X.shape[0], n_out), np.float32)
+        self.lib.orc_matmul_q8_0.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, _f32p]
+        if self.lib.orc_matmul_q8_0(W.ctypes.data, n_in, n_out, _fp(X), X.shape[0], _fp(Y)) != 0:
+            raise ValueError("the input width must be a multiple of 256")
+        return Y
+
     # -- codecs ----------------------------------------------------------
     def q8_0_encode(self, x):
         x = np.ascontiguousarray(x, np.float32)
@@ -390,6 +410,22 @@ class Ref:
         out = np.empty(x.size // 32 * 34, np.uint8)
         assert self.lib.oq_quantize(OGGML_Q8_0, _fp(x), out.ctypes.data, x.size) == 0
         return out
+
+    def q8k_quantize(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[:-1] + (x.shape[-1] // 256, 292), np.uint8)
+        self.lib.refdrv_q8k_quantize.argtypes = [_f32p, C.c_void_p, C.c_longlong]
+        self.lib.refdrv_q8k_quantize(_fp(x), out.ctypes.data, x.size)
+        return out
+
+    def matmul_q8_0(self, W, n_in, X):
+        W = np.ascontiguousarray(W, np.uint8)
+        X = np.ascontiguousarray(X, np.float32).reshape(-1, n_in)
+        n_out = W.size // (n_in // 32 * 34)
+        Y = np.empty((X.shape[0], n_out), np.float32)
+        self.lib.refdrv_matmul_q8_0.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, _f32p]
+        assert self.lib.refdrv_matmul_q8_0(W.ctypes.data, n_in, n_out, _fp(X), X.shape[0], _fp(Y)) == 0
+        return Y
 
     def q8_0_decode(self, b):
         n = b.size // 34 * 32

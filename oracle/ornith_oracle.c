@@ -556,3 +556,72 @@ void orc_full_attn_prefill(const orc_full_params *p, orc_kv *c, int base, int T,
     for (int t = 0; t < T; t++)
         orc_full_attn_step(p, c, base + t, QP + t * qp, K + t * kvd, V + t * kvd, OUT + t * qd);
 }
+
+/* ======================================================================== */
+/* quantised projections                                                     */
+/* ======================================================================== */
+
+/* src/ornith_qdot.c:38-70: the element of largest magnitude (first one on ties) fixes the scale
+ * -127/max, values are rounded to nearest even, d = 1/iscale; an all-zero block stays zero. */
+void orc_q8k_quantize(const float *x, orc_q8k_block *y, int64_t k) {
+    const int64_t nb = k / 256;
+    for (int64_t b = 0; b < nb; b++, x += 256) {
+        float amax = 0.0f, max = 0.0f;
+        for (int j = 0; j < 256; j++) {
+            const float ax = fabsf(x[j]);
+            if (ax > amax) { amax = ax; max = x[j]; }
+        }
+        if (amax == 0.0f) {
+            y[b].d = 0.0f;
+            memset(y[b].qs, 0, sizeof y[b].qs);
+            memset(y[b].bsums, 0, sizeof y[b].bsums);
+            continue;
+        }
+        const float iscale = -127.0f / max;
+        for (int j = 0; j < 256; j++) {
+            int v = (int)lrintf(iscale * x[j]);
+            v = v > 127 ? 127 : (v < -128 ? -128 : v);
+            y[b].qs[j] = (int8_t)v;
+        }
+        for (int g = 0; g < 16; g++) {
+            int sum = 0;
+            for (int i = 0; i < 16; i++) sum += y[b].qs[16 * g + i];
+            y[b].bsums[g] = (int16_t)sum;
+        }
+        y[b].d = 1.0f / iscale;
+    }
+}
+
+/* src/ornith_qdot.c:144-163: per super-block of 256 the eight Q8_0 blocks give wd * (float)isum, summed in
+ * order; the super-block sum is scaled by the activation's d and added to the running total, in order. */
+float orc_vec_dot_q8_0(int n, const uint8_t *wrow, const orc_q8k_block *y) {
+    const int nb = n / 256;
+    float sumf = 0.0f;
+    for (int i = 0; i < nb; i++) {
+        const uint8_t *w = wrow + (size_t)i * 8 * 34;
+        float blk_sum = 0.0f;
+        for (int sb = 0; sb < 8; sb++) {
+            const uint8_t *wb = w + (size_t)sb * 34;
+            const float wd = orc_f16_to_f32((uint16_t)(wb[0] | ((uint16_t)wb[1] << 8)));
+            const int8_t *wq = (const int8_t *)(wb + 2), *yq = y[i].qs + 32 * sb;
+            int isum = 0;
+            for (int l = 0; l < 32; l++) isum += (int)wq[l] * (int)yq[l];
+            blk_sum += wd * (float)isum;
+        }
+        sumf += y[i].d * blk_sum;
+    }
+    return sumf;
+}
+
+int orc_matmul_q8_0(const uint8_t *W, int n_in, int n_out, const float *X, int T, float *Y) {
+    if (n_in % 256 != 0) return -1;
+    const size_t nblk = (size_t)n_in / 256, rb = (size_t)n_in / 32 * 34;
+    orc_q8k_block *xq = malloc((size_t)T * nblk * sizeof *xq);
+    if (!xq) return -1;
+    for (int t = 0; t < T; t++) orc_q8k_quantize(X + (size_t)t * n_in, xq + (size_t)t * nblk, n_in);
+    for (int o = 0; o < n_out; o++)
+        for (int t = 0; t < T; t++)
+            Y[(size_t)t * n_out + o] = orc_vec_dot_q8_0(n_in, W + (size_t)o * rb, xq + (size_t)t * nblk);
+    free(xq);
+    return 0;
+}

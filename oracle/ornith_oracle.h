@@ -133,6 +133,21 @@ void orc_full_attn_step(const orc_full_params *p, orc_kv *c, int pos,
 void orc_full_attn_prefill(const orc_full_params *p, orc_kv *c, int base, int T,
                            const float *QP, const float *K, const float *V, float *OUT);
 
+/* ---- quantised projections (src/ornith_qdot.c, src/ornith_rforward.c:138-196) ---- */
+/* Q8_K activation super-block, 292 bytes (src/ornith_qdot.h:30-34) */
+typedef struct {
+    float   d;
+    int8_t  qs[256];
+    int16_t bsums[16];
+} orc_q8k_block;
+/* k f32 values (multiple of 256) -> k/256 blocks (src/ornith_qdot.c:38-70) */
+void orc_q8k_quantize(const float *x, orc_q8k_block *y, int64_t k);
+/* one Q8_0 weight row (n/32 blocks of 34 bytes) . one Q8_K activation row (src/ornith_qdot.c:144-163) */
+float orc_vec_dot_q8_0(int n, const uint8_t *wrow, const orc_q8k_block *y);
+/* Y[t][o] = W[o] . X[t] for T activation rows: every row quantised to Q8_K once, then the integer dot per
+ * (row of W, token) (matmul_batch_q, src/ornith_rforward.c:138-192).  W: [out] rows of n_in/32 Q8_0 blocks. */
+int orc_matmul_q8_0(const uint8_t *W, int n_in, int n_out, const float *X, int T, float *Y);
+
 #ifdef __cplusplus
 }
 #endif

@@ -95,3 +95,23 @@ void refdrv_full_step(const refdrv_full *p, ornith_kv_cache *c, int pos, const f
     for (int i = 0; i < qd; i++) out[i] *= ot_sigmoid(g[i]);
     free(q); free(g); free(kk); free(vv);
 }
+
+/* ---- quantised projections: the reference's own quantiser and integer dot (src/ornith_qdot.c), driven the way
+ *      matmul_batch_q drives them (src/ornith_rforward.c:165-175, :108-115) ---- */
+#include "ornith_qdot.h"
+#include "ornith_quant.h"
+
+void refdrv_q8k_quantize(const float *x, void *y, long long k) { qdot_quantize_row_q8_K(x, (oq8k_block *)y, k); }
+
+int refdrv_matmul_q8_0(const unsigned char *W, int n_in, int n_out, const float *X, int T, float *Y) {
+    if (!qdot_can(OGGML_Q8_0, n_in)) return -1;
+    const size_t nblk = (size_t)n_in / OQDOT_QK_K, rb = oq_row_bytes(OGGML_Q8_0, (size_t)n_in);
+    oq8k_block *xq = malloc((size_t)T * nblk * sizeof *xq);
+    if (!xq) return -1;
+    for (int t = 0; t < T; t++) qdot_quantize_row_q8_K(X + (size_t)t * n_in, xq + (size_t)t * nblk, n_in);
+    for (int o = 0; o < n_out; o++)
+        for (int t = 0; t < T; t++)
+            qdot_vec_dot(OGGML_Q8_0, n_in, &Y[(size_t)t * n_out + o], W + (size_t)o * rb, xq + (size_t)t * nblk);
+    free(xq);
+    return 0;
+}

@@ -120,6 +120,46 @@ class KvBatch:
                 self.Vs[o * self.nkv:(o + n) * self.nkv].cpu().numpy().reshape(n, self.nkv))
 
 
+class Q8_0Weight:
+    """A projection weight on the device as the GGUF tensor's Q8_0 rows, [n_out][n_in/32][34] bytes."""
+
+    def __init__(self, rows_bytes, n_in, device="cuda:0"):
+        rows = np.ascontiguousarray(rows_bytes, np.uint8).reshape(-1)
+        self.n_in = int(n_in)
+        self.n_out = rows.size // (self.n_in // 32 * 34)
+        self.bytes = torch.from_numpy(rows).to(device)
+        self._scratch = None
+
+    def scratch(self, T):
+        need = _lib.load().ornith_cuda_qproj_scratch(int(T), self.n_in)
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, dtype=torch.uint8, device=self.bytes.device)
+        return self._scratch
+
+
+def q8k_quantize(x, n_in):
+    """x [T][n_in] on the device -> the engine's Q8_K blocks, [T][n_in/256][292] bytes (host array)."""
+    lib = _lib.load()
+    T = x.numel() // n_in
+    blocks = torch.empty(T * (n_in // 256) * 292, dtype=torch.uint8, device=x.device)
+    need = lib.ornith_cuda_qproj_scratch(T, n_in)
+    scr = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(lib.ornith_cuda_q8k_quantize(_ptr(x), _act(x), T, n_in, _ptr(blocks), _ptr(scr), need, _stream()), "q8k_quantize")
+    return blocks.cpu().numpy().reshape(T, n_in // 256, 292)
+
+
+def matmul_q8_0(w: Q8_0Weight, x, out=None):
+    """y [T][n_out] = x [T][n_in] through Q8_0 weight rows (the engine's quantised projection)."""
+    lib = _lib.load()
+    T = x.numel() // w.n_in
+    if out is None:
+        out = torch.empty(T, w.n_out, dtype=x.dtype, device=x.device)
+    scr = w.scratch(T)
+    check(lib.ornith_cuda_matmul_q8_0(_ptr(w.bytes), w.n_in, w.n_out, _ptr(x), _act(x), T, _ptr(out), _act(out), _ptr(scr),
+                                      scr.numel(), _stream()), "matmul_q8_0")
+    return out
+
+
 def kv_export(kv: KvBatch, seq, length):
     """Session record of the first `length` positions of sequence `seq` (bytes, the engine's layer record)."""
     lib = _lib.load()

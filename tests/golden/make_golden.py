@@ -6,7 +6,7 @@ oracle/_ref/libornith_ref.so by oracle/Makefile):
     python tests/golden/make_golden.py
 
 Every array below is produced by calling the reference's functions
-(src/ornith_attn.c, src/ornith_tensor.c, src/ornith_quant.c) through ctypes; the
+(src/ornith_attn.c, src/ornith_tensor.c, src/ornith_quant.c, src/ornith_qdot.c) through ctypes; the
 seeds and shapes of the first four files are those of the reference's
 tests/test_attn.c (:28-192).  The layer-level files compose the reference
 primitives exactly as src/ornith_rforward.c:419-503 / src/ornith_forward.c:277-399
@@ -230,7 +230,25 @@ def full_layer(name, quantized, seed):
          q_norm_w=qw, k_norm_w=kw_, QP=QP, K=K, V=V, OUT=OUT, quantized=quantized)
 
 
+# ---- quantised projection: the reference's Q8_K quantiser and Q8_0 x Q8_K integer dot ------------
+def projection():
+    """src/ornith_qdot.c:38-70 (qdot_quantize_row_q8_K) and :144-163 (vec_dot_q8_0), driven as matmul_batch_q
+    drives them (src/ornith_rforward.c:165-175, :108-115): 6 activation rows of 768 through 33 Q8_0 weight rows,
+    with a zero block, ties for the maximum and values on rounding boundaries."""
+    g = np.random.default_rng(21)
+    n_in, n_out, T = 768, 33, 6
+    X = g.standard_normal((T, n_in)).astype(np.float32)
+    X[0, :256] = 0.0
+    X[1, 5] = 9.0; X[1, 100] = -9.0
+    X[2, 300] = -8.0; X[2, 290] = 8.0
+    X[3] = np.round(X[3] * 4) / 4
+    Wf = (g.standard_normal((n_out, n_in)) * 0.05).astype(np.float32)
+    W = np.stack([r.q8_0_encode(row) for row in Wf])
+    save("projection_q8_0.npz", X=X, W=W, n_in=n_in, blocks=r.q8k_quantize(X), Y=r.matmul_q8_0(W, n_in, X))
+
+
 if __name__ == "__main__":
+    projection()
     delta_parity()
     gqa(42, 4, 2, 8, 11, "attn_gqa.npz", 0)
     gqa(123, 4, 2, 16, 13, "attn_gqa_int8.npz", 1)

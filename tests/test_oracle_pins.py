@@ -212,3 +212,30 @@ def test_oracle_equals_reference_objects(oracle):
         for t in range(T):
             assert (oracle.gqa_step(kv, Qs[t], Ks[t], Vs[t], nh) == r.gqa_step(rc, Qs[t], Ks[t], Vs[t], nh)).all()
         r.kv_free(rc)
+
+
+@pytest.mark.skipif(not Ref.available(), reason="reference objects not built on this machine")
+def test_projection_oracle_equals_reference_objects(oracle):
+    """Q8_K quantiser and the Q8_0 x Q8_K integer dot: the restatement against the reference's own objects, bit
+    for bit, on rows with zero blocks, ties for the maximum and values on rounding boundaries."""
+    ref = Ref()
+    orc = oracle
+    g = np.random.default_rng(21)
+    n_in, n_out, T = 768, 33, 6
+    X = g.standard_normal((T, n_in)).astype(np.float32)
+    X[0, :256] = 0.0
+    X[1, 5] = 9.0; X[1, 100] = -9.0
+    X[2, 300] = -8.0; X[2, 290] = 8.0
+    X[3] = np.round(X[3] * 4) / 4
+    assert (orc.q8k_quantize(X) == ref.q8k_quantize(X)).all()
+    W = np.stack([orc.q8_0_encode(r) for r in (g.standard_normal((n_out, n_in)) * 0.05).astype(np.float32)])
+    a, b = orc.matmul_q8_0(W, n_in, X), ref.matmul_q8_0(W, n_in, X)
+    assert (a.view(np.uint32) == b.view(np.uint32)).all()
+
+
+def test_projection_golden_bit_exact(oracle, golden):
+    """The reference-made projection fixture (tests/golden/make_golden.py::projection): blocks and outputs."""
+    g = golden("projection_q8_0.npz")
+    assert (oracle.q8k_quantize(g["X"]) == g["blocks"]).all()
+    y = oracle.matmul_q8_0(g["W"], int(g["n_in"]), g["X"])
+    assert (bits(y) == bits(g["Y"])).all()
