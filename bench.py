@@ -354,6 +354,65 @@ def run_single_layer(dev, cpu=True):
     return res
 
 
+def run_projections(dev, n_tok=64, cpu=True):
+    """The quantised projections that bracket the attention kernels of one 35B-shaped delta-net layer and one
+    full-attention layer (hidden 2048): Q8_0 weights x Q8_K activations, 64 tokens (one decode step of the headline
+    batch), bf16 activations.  Each shape is timed over 16 distinct weight matrices used in turn (together larger
+    than L2 for the big shapes), activation quantisation included; the roofline figure is the weight bytes (what a
+    decode-sized batch has to stream) over the time.  The CPU figure is the engine's integer path on one host
+    thread over a sample of the output rows."""
+    import torch
+    from ornithology_b200 import device as D
+    from oracle import oracle as O
+    orc = O.Oracle()
+    shapes = [("attn_qkv", 2048, 8192), ("attn_gate", 2048, 4096), ("ssm_alpha", 2048, 32), ("ssm_beta", 2048, 32),
+              ("ssm_out", 4096, 2048), ("attn_q", 2048, 8192), ("attn_k", 2048, 512), ("attn_v", 2048, 512),
+              ("attn_output", 4096, 2048)]
+    g = np.random.default_rng(8)
+    peak, src = measured_peaks()
+    res, tot_bytes, tot_ms = {}, 0.0, 0.0
+    copies = 16
+    for name, n_in, n_out in shapes:
+        rows = np.stack([orc.q8_0_encode(r) for r in (g.standard_normal((min(n_out, 64), n_in)) * 0.04).astype(np.float32)])
+        W = np.tile(rows, (n_out // rows.shape[0], 1))                 # the timing does not depend on the values
+        ws = [D.Q8_0Weight(np.roll(W, c, axis=0), n_in, device=dev) for c in range(copies)]
+        x = torch.from_numpy(g.standard_normal((n_tok, n_in)).astype(np.float32)).to(dev).to(torch.bfloat16)
+        out = torch.empty(n_tok, n_out, dtype=torch.bfloat16, device=dev)
+
+        def loop():
+            for w in ws:
+                D.matmul_q8_0(w, x, out=out)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                loop()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()                 # the 32 launches of a pass replayed as one graph: the timing
+        with torch.cuda.graph(graph, stream=side):     # is then the kernels', not the Python call overhead
+            loop()
+        ms = _timed(graph.replay, dev, 1, 3) / copies
+        nbytes = float(n_out) * (n_in // 32 * 34)
+        res[name] = {"n_in": n_in, "n_out": n_out, "us": ms * 1e3, "weight_bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+        tot_bytes += nbytes; tot_ms += ms
+        if cpu and name == "attn_qkv":
+            sample = 256
+            t0 = time.perf_counter()
+            orc.matmul_q8_0(W[:sample], n_in, x.float().cpu().numpy())
+            dt = time.perf_counter() - t0
+            res["cpu"] = {"kind": "port", "cores": 1, "shape": name, "ms": dt * 1e3 * n_out / sample,
+                          "sample": f"{sample} of the {n_out} output rows, {n_tok} tokens, scaled by rows"}
+        del ws
+    return {"workload": f"Q8_0 x Q8_K projections of one delta-net and one full-attention layer, {n_tok} tokens, bf16",
+            "per_projection": res, "total_us": tot_ms * 1e3, "total_weight_bytes": tot_bytes,
+            "roofline": {"bound": "hbm", "kernel": "k_matmul_q8_0", "achieved": tot_bytes / (tot_ms * 1e-3) / 1e9, "peak": peak,
+                         "unit": "GB/s", "frac": tot_bytes / (tot_ms * 1e-3) / 1e9 / peak, "peak_source": f"of {src}"},
+            "note": "a decode-sized batch: each projection is a few microseconds of weight traffic, so launch latency "
+                    "(two kernels per projection) is a large part of the small ones"}
+
+
 def cpu_single_layer():
     """The CPU reference on the two single-layer workloads (one thread: the attention core is single-threaded in the
     engine).  The delta-net layer runs in full; of the GQA layer the decode steps run in full (64 of them, at the
@@ -734,9 +793,10 @@ def run_ours(args, rank, world, local_rank):
     decode_397b = None
     if world > 1 and not args.no_extras:
         decode_397b = run_decode_397b(dev, rank, world)
-    single = None
+    single = projections = None
     if world == 1 and not args.no_extras:
         single = run_single_layer(dev, cpu=not args.no_cpu)
+        projections = run_projections(dev, cpu=not args.no_cpu)
 
     if rank == 0:
         tokens = args.seqs * world * args.steps
@@ -772,7 +832,7 @@ def run_ours(args, rank, world, local_rank):
                         "ms_per_step": ms_e2e / args.steps},
                 "gpu_launches": launches * args.steps,
                 "roofline": roof, "cpu_baseline": cpu, "clocks": clocks, "ranks": ranks, "prefill": prefill,
-                "strong": strong, "decode_397b": decode_397b, "single_layer": single}
+                "strong": strong, "decode_397b": decode_397b, "single_layer": single, "projections": projections}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -37,9 +37,10 @@ constexpr int QK = 256;                       // inputs per super-block
 constexpr int SEGB = 272;                     // bytes of one weight row over a super-block: 8 x (f16 scale + 32 codes)
 constexpr int NCHUNK = 17;                    // 16-byte chunks per 272 bytes
 constexpr int ROWS = 16;                      // weight rows per warp
-constexpr int FRAG_BYTES = NCHUNK * 32 * 8;   // activation fragments of one (token tile of 8, super-block): 4352
+constexpr int FRAG_WORDS2 = NCHUNK * 32;       // uint2 entries of the activation fragments of one (token tile of 8, super-block)
+constexpr int FRAG_BYTES = FRAG_WORDS2 * 8 + 32; // the fragments (4352 bytes) followed by the 8 tokens' block scales (f32)
 constexpr int MAXNT = 8;                      // token tiles per pass (64 tokens)
-constexpr int WARPS = 2;
+constexpr int WARPS = 4;                      // warps that share the CTA's 64 weight rows (16 each)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -65,16 +66,8 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
-// bounded wait: gives up (returns false) after ~1 s instead of waiting for ever
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < (1 << 18); i++) {
-        uint32_t ok;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(10000u) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
+// bounded wait (poll limit and 2 s of wall time)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) { return tc5::mbar_wait(bar, parity); }
 __device__ __forceinline__ void tensor_copy_rows(uint32_t dst, const CUtensorMap *map, int word0, int row0, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(word0), "r"(row0) : "memory");
@@ -103,10 +96,10 @@ __device__ __forceinline__ void weights_chunk(uint32_t raw0, uint32_t raw1, cons
 
 // ---- activations -> Q8_K ------------------------------------------------------------------------------
 // grid (n_in / 256, T_pad), one warp each.  Tokens >= T are padding of the last tile of 8: zero fragments.
-// blocks: [T][n_in/256] engine blocks of 292 bytes, or NULL.  frags: [T_pad/8][n_in/256][17][32] uint2.
-// dplane: [T_pad][n_in/256] f32.
+// blocks: [T][n_in/256] engine blocks of 292 bytes, or NULL.  frags: [T_pad/8][n_in/256] images of FRAG_BYTES:
+// [17][32] uint2 fragments, then the 8 tokens' scales.
 template <typename ACT>
-__global__ void __launch_bounds__(32) k_q8k_quantize(const ACT *x, int T, int n_in, unsigned char *blocks, uint2 *frags, float *dplane) {
+__global__ void __launch_bounds__(32) k_q8k_quantize(const ACT *x, int T, int n_in, unsigned char *blocks, uint2 *frags) {
     const int seg = blockIdx.x, tok = blockIdx.y, lane = threadIdx.x, nseg = n_in / QK;
     float v[8];
     float amax = 0.0f, mx = 0.0f;
@@ -157,10 +150,11 @@ __global__ void __launch_bounds__(32) k_q8k_quantize(const ACT *x, int T, int n_
         *reinterpret_cast<uint32_t *>(blk + 8 + 8 * lane) = w1;
         if ((lane & 1) == 0) *reinterpret_cast<short *>(blk + 260 + lane) = (short)sum;
     }
-    if (lane == 0) dplane[(size_t)tok * nseg + seg] = d;
     // the product's image: pair p = inputs (2p, 2p+1) is stream element e = 17 (p / 16) + 1 + p % 16, which lies
     // in chunk e / 8 at position e % 8 = 2 j + h of lane (token % 8, j)
-    uint32_t *fr = reinterpret_cast<uint32_t *>(frags + ((size_t)(tok >> 3) * nseg + seg) * (NCHUNK * 32));
+    unsigned char *img = reinterpret_cast<unsigned char *>(frags) + ((size_t)(tok >> 3) * nseg + seg) * FRAG_BYTES;
+    uint32_t *fr = reinterpret_cast<uint32_t *>(img);
+    if (lane == 0) reinterpret_cast<float *>(img + FRAG_WORDS2 * 8)[tok & 7] = d;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int p = 4 * lane + i, e = 17 * (p >> 4) + 1 + (p & 15);
@@ -174,121 +168,140 @@ __global__ void __launch_bounds__(32) k_q8k_quantize(const ACT *x, int T, int n_
 }
 
 struct ProjArgs {
-    const uint2 *frags;                           // [token tiles][nseg][17][32]
-    const float *dplane;                          // [T_pad][nseg]
+    const unsigned char *frags;                   // [token tiles][nseg] images of FRAG_BYTES
     void *y;                                      // [T][n_out]
     int T, n_out, nseg, ntiles, out_dtype;
     unsigned int *status;
 };
 
-// grid: ceil(n_out / 32) CTAs of 2 warps; a warp owns 16 weight rows for all token tiles of the pass
-__global__ void __launch_bounds__(WARPS * 32) k_matmul_q8_0(ProjArgs a, const __grid_constant__ CUtensorMap map_w, int tok0) {
-    __shared__ __align__(128) unsigned char slots[WARPS][2][ROWS * SEGB];
-    __shared__ __align__(8) unsigned long long bars[WARPS][2];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = lane >> 2, j = lane & 3;
-    const int row0 = ((int)blockIdx.x * WARPS + warp) * ROWS;
-    if (row0 >= a.n_out) return;                  // whole warp
-    if (lane == 0) {
-        mbar_init(smem_u32(&bars[warp][0]), 1);
-        mbar_init(smem_u32(&bars[warp][1]), 1);
+// grid: ceil(n_out / 64) CTAs.  Warp w of group g owns weight rows 16 w .. 16 w + 15 of the CTA's 64 and the
+// token tiles of group g (NG groups split the pass's tiles: more warps per SM to hide the latencies of a k-step).
+// Per super-block one stage of shared memory holds the 64 weight rows (one tensor copy) and the activation images
+// of the pass's token tiles (one bulk copy each); NSTAGE stages on NSTAGE mbarriers.
+constexpr int CTA_ROWS = WARPS * ROWS;
+constexpr int STAGE_W = CTA_ROWS * SEGB;          // 17408
+constexpr int STAGE_X = MAXNT * FRAG_BYTES;       // 35072
+constexpr int STAGE = STAGE_W + STAGE_X;
+constexpr int NSTAGE = 3;
+constexpr int PROJ_SMEM = NSTAGE * STAGE + 128;
+
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+template <int NG>
+__global__ void __launch_bounds__(NG * WARPS * 32) k_matmul_q8_0(ProjArgs a, const __grid_constant__ CUtensorMap map_w, int tok0) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[NSTAGE];
+    __shared__ int failed;
+    unsigned char *smem = smem_raw + ((128 - (smem_u32(smem_raw) & 127)) & 127);
+    const int tid = threadIdx.x, lane = tid & 31, warp = (tid >> 5) & (WARPS - 1), grp = tid >> 7, r = lane >> 2, j = lane & 3;
+    const int cta_row0 = (int)blockIdx.x * CTA_ROWS, row0 = cta_row0 + warp * ROWS;
+    constexpr int MT = MAXNT / NG;                // token tiles of a group: tiles MT grp .. MT grp + MT - 1 of the pass
+    const int nt_all = a.ntiles, t_lo = grp * MT;
+    if (tid == 0) {
+        failed = 0;
+        for (int i = 0; i < NSTAGE; i++) mbar_init(smem_u32(&bars[i]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    __syncwarp();
+    __syncthreads();
     auto issue = [&](int seg) {                   // rows past n_out are outside the map: the copy fills them with zeros
-        if (lane == 0) {
-            const uint32_t bar = smem_u32(&bars[warp][seg & 1]);
-            mbar_expect_tx(bar, ROWS * SEGB);
-            tensor_copy_rows(smem_u32(slots[warp][seg & 1]), &map_w, seg * (SEGB / 4), row0, bar);
-        }
+        const uint32_t bar = smem_u32(&bars[seg % NSTAGE]), base = smem_u32(smem + (seg % NSTAGE) * STAGE);
+        mbar_expect_tx(bar, (uint32_t)(STAGE_W + nt_all * FRAG_BYTES));
+        tensor_copy_rows(base, &map_w, seg * (SEGB / 4), cta_row0, bar);
+        for (int t = 0; t < nt_all; t++)
+            bulk_copy(base + STAGE_W + t * FRAG_BYTES, a.frags + ((size_t)((tok0 >> 3) + t) * a.nseg + seg) * FRAG_BYTES, FRAG_BYTES, bar);
     };
-    issue(0);
-    if (a.nseg > 1) issue(1);
-    const int nt = a.ntiles;
-    float tot[MAXNT][4];
+    if (tid == 0)
+        for (int i = 0; i < NSTAGE - 1 && i < a.nseg; i++) issue(i);
+    // Tiles past the pass's last one are multiplied too (against whatever the stage holds there) and never stored:
+    // a test per tile would put every MMA into a basic block of its own and expose the latency of its fragment load.
+    float tot[MT][4];
 #pragma unroll
-    for (int t = 0; t < MAXNT; t++) tot[t][0] = tot[t][1] = tot[t][2] = tot[t][3] = 0.0f;
+    for (int t = 0; t < MT; t++) tot[t][0] = tot[t][1] = tot[t][2] = tot[t][3] = 0.0f;
     const uint32_t lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * SEGB + (lane >> 4) * 16;
+    const bool active = row0 < a.n_out && t_lo < nt_all;
     bool ok = true;
     for (int seg = 0; seg < a.nseg; seg++) {
-        const uint32_t slot = smem_u32(slots[warp][seg & 1]);
-        if (!mbar_wait(smem_u32(&bars[warp][seg & 1]), (uint32_t)(seg >> 1) & 1u)) { ok = false; break; }
-        uint32_t dk0[8], dk1[8];
+        const unsigned char *stage = smem + (seg % NSTAGE) * STAGE;
+        if (ok && !mbar_wait(smem_u32(&bars[seg % NSTAGE]), (uint32_t)(seg / NSTAGE) & 1u)) { ok = false; failed = 1; }
+        if (ok && active) {
+            const unsigned char *wrows = stage + warp * (ROWS * SEGB);
+            uint32_t dk0[8], dk1[8];
 #pragma unroll
-        for (int bb = 0; bb < 8; bb++) {
-            const unsigned short u0 = *reinterpret_cast<const unsigned short *>(slots[warp][seg & 1] + r * SEGB + 34 * bb);
-            const unsigned short u1 = *reinterpret_cast<const unsigned short *>(slots[warp][seg & 1] + (r + 8) * SEGB + 34 * bb);
-            dk0[bb] = (uint32_t)u0 | ((uint32_t)u0 << 16);
-            dk1[bb] = (uint32_t)u1 | ((uint32_t)u1 << 16);
-        }
-        float acc[MAXNT][4];
+            for (int bb = 0; bb < 8; bb++) {
+                const unsigned short u0 = *reinterpret_cast<const unsigned short *>(wrows + r * SEGB + 34 * bb);
+                const unsigned short u1 = *reinterpret_cast<const unsigned short *>(wrows + (r + 8) * SEGB + 34 * bb);
+                dk0[bb] = (uint32_t)u0 | ((uint32_t)u0 << 16);
+                dk1[bb] = (uint32_t)u1 | ((uint32_t)u1 << 16);
+            }
+            float acc[MT][4];
 #pragma unroll
-        for (int t = 0; t < MAXNT; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
-        // activation fragments of this super-block: tile t at frag0 + t * nseg * 17 * 32
-        const uint2 *frag0 = a.frags + ((size_t)(tok0 >> 3) * a.nseg + seg) * (NCHUNK * 32) + lane;
-        const size_t tile_stride = (size_t)a.nseg * (NCHUNK * 32);
-        const uint32_t w_addr = slot + lane_off;
-        uint32_t R[4], A[4];
+            for (int t = 0; t < MT; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+            const unsigned char *xst = stage + STAGE_W + t_lo * FRAG_BYTES;                   // this group's tile t at + t * FRAG_BYTES
+            const uint32_t w_addr = smem_u32(wrows) + lane_off;
+            uint32_t R[4], A[4];
 #define PROJ_STEP(C, R0, R1)                                                   \
-        weights_chunk<(C)>(R0, R1, dk0, dk1, j, A);                            \
-        _Pragma("unroll")                                                      \
-        for (int t = 0; t < MAXNT; t++)                                        \
-            if (t < nt) { const uint2 b = __ldg(frag0 + t * tile_stride + (C) * 32); mma16816(acc[t], A, b.x, b.y); }
+            weights_chunk<(C)>(R0, R1, dk0, dk1, j, A);                        \
+            _Pragma("unroll")                                                  \
+            for (int t = 0; t < MT; t++) {                                     \
+                const uint2 b = reinterpret_cast<const uint2 *>(xst + t * FRAG_BYTES)[(C) * 32 + lane];   \
+                mma16816(acc[t], A, b.x, b.y);                                 \
+            }
 #define PROJ_PAIR(C)                                                           \
-        ldsm_x4(R, w_addr + (C) * 16);                                         \
-        PROJ_STEP((C), R[0], R[1])                                             \
-        PROJ_STEP((C) + 1, R[2], R[3])
-        PROJ_PAIR(0) PROJ_PAIR(2) PROJ_PAIR(4) PROJ_PAIR(6) PROJ_PAIR(8) PROJ_PAIR(10) PROJ_PAIR(12) PROJ_PAIR(14)
-        ldsm_x2(R, w_addr + 16 * 16);
-        PROJ_STEP(16, R[0], R[1])
+            ldsm_x4(R, w_addr + (C) * 16);                                     \
+            PROJ_STEP((C), R[0], R[1])                                         \
+            PROJ_STEP((C) + 1, R[2], R[3])
+            PROJ_PAIR(0) PROJ_PAIR(2) PROJ_PAIR(4) PROJ_PAIR(6) PROJ_PAIR(8) PROJ_PAIR(10) PROJ_PAIR(12) PROJ_PAIR(14)
+            ldsm_x2(R, w_addr + 16 * 16);
+            PROJ_STEP(16, R[0], R[1])
 #undef PROJ_PAIR
 #undef PROJ_STEP
-        __syncwarp();                             // every lane is done with the slot
-        if (seg + 2 < a.nseg) {
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            issue(seg + 2);
-        }
-        // the super-block's sum times the activation's scale (tokens 2j, 2j+1 of each tile)
+            // the super-block's sum times the activation's scale (tokens 2j, 2j+1 of each tile)
 #pragma unroll
-        for (int t = 0; t < MAXNT; t++)
-            if (t < nt) {
-                const float d0 = a.dplane[(size_t)(tok0 + 8 * t + 2 * j) * a.nseg + seg];
-                const float d1 = a.dplane[(size_t)(tok0 + 8 * t + 2 * j + 1) * a.nseg + seg];
-                tot[t][0] = fmaf(d0, acc[t][0], tot[t][0]); tot[t][1] = fmaf(d1, acc[t][1], tot[t][1]);
-                tot[t][2] = fmaf(d0, acc[t][2], tot[t][2]); tot[t][3] = fmaf(d1, acc[t][3], tot[t][3]);
+            for (int t = 0; t < MT; t++) {
+                const float2 d2 = reinterpret_cast<const float2 *>(xst + t * FRAG_BYTES + FRAG_WORDS2 * 8)[j];
+                tot[t][0] = fmaf(d2.x, acc[t][0], tot[t][0]); tot[t][1] = fmaf(d2.y, acc[t][1], tot[t][1]);
+                tot[t][2] = fmaf(d2.x, acc[t][2], tot[t][2]); tot[t][3] = fmaf(d2.y, acc[t][3], tot[t][3]);
             }
+        }
+        __syncthreads();                          // every warp is done with stage seg (and so with stage seg - 1, refilled now)
+        if (tid == 0 && !failed && seg + NSTAGE - 1 < a.nseg) {
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            issue(seg + NSTAGE - 1);
+        }
+        if (failed) ok = false;
     }
-    if (!ok && lane == 0 && a.status) atomicOr(a.status, ORN_WAIT_DECODE);
+    if (!ok && tid == 0 && a.status) atomicOr(a.status, ORN_WAIT_DECODE);
     // y[token][row]: rows r, r + 8 of the warp's 16; tokens 2j, 2j+1 of each tile
 #pragma unroll
-    for (int t = 0; t < MAXNT; t++)
-        if (t < nt) {
+    for (int t = 0; t < MT; t++)
 #pragma unroll
-            for (int x = 0; x < 4; x++) {
-                const int row = row0 + r + 8 * (x >> 1), tok = tok0 + 8 * t + 2 * j + (x & 1);
-                if (row < a.n_out && tok < a.T) {
-                    const float val = ok ? tot[t][x] : NAN;
-                    if (a.out_dtype == ORNITH_ACT_BF16) act_st((__nv_bfloat16 *)a.y, (size_t)tok * a.n_out + row, val);
-                    else act_st((float *)a.y, (size_t)tok * a.n_out + row, val);
-                }
+        for (int x = 0; x < 4; x++) {
+            const int row = row0 + r + 8 * (x >> 1), tok = tok0 + 8 * (t_lo + t) + 2 * j + (x & 1);
+            if (row < a.n_out && t_lo + t < nt_all && tok < a.T) {
+                const float val = ok ? tot[t][x] : NAN;
+                if (a.out_dtype == ORNITH_ACT_BF16) act_st((__nv_bfloat16 *)a.y, (size_t)tok * a.n_out + row, val);
+                else act_st((float *)a.y, (size_t)tok * a.n_out + row, val);
             }
         }
 }
 
-// the weight matrix as [n_out rows][row_bytes / 4 words]; one box = 16 rows x 68 words (one super-block)
+// the weight matrix as [n_out rows][row_bytes / 4 words]; one box = 64 rows x 68 words (one super-block)
 bool weight_map(CUtensorMap *m, const void *W, int n_in, int n_out) {
     OrnTensorMapEncodeFn enc = orn_tensor_map_encoder();
     if (!enc || ((uintptr_t)W & 15) != 0) return false;
     const cuuint64_t row_bytes = (cuuint64_t)n_in / 32 * 34;
     cuuint64_t dims[2] = {row_bytes / 4, (cuuint64_t)n_out};
     cuuint64_t strides[1] = {row_bytes};
-    cuuint32_t box[2] = {SEGB / 4, ROWS};
+    cuuint32_t box[2] = {SEGB / 4, WARPS * ROWS};
     cuuint32_t es[2] = {1, 1};
     return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(W), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 size_t frag_bytes(int T, int n_in) { return align_up((size_t)((T + 7) / 8) * (n_in / QK) * FRAG_BYTES, 256); }
-size_t dplane_bytes(int T, int n_in) { return align_up((size_t)((T + 7) / 8 * 8) * (n_in / QK) * sizeof(float), 256); }
 
 }  // namespace
 
@@ -296,7 +309,7 @@ extern "C" {
 
 size_t ornith_cuda_qproj_scratch(int T, int n_in) {
     if (T <= 0 || n_in <= 0 || n_in % QK) return 0;
-    return frag_bytes(T, n_in) + dplane_bytes(T, n_in);
+    return frag_bytes(T, n_in);
 }
 
 // x [T][n_in] (act_dtype) -> Q8_K.  blocks: device [T][n_in/256][292] in the engine's layout, or NULL.
@@ -308,12 +321,11 @@ ornith_status ornith_cuda_q8k_quantize(const void *x, int act_dtype, int T, int 
     if (n_in <= 0 || n_in % QK) { orn_record_error("q8k_quantize: the row length must be a multiple of 256 (got %d)", n_in); return ORNITH_ERR_FORMAT; }
     if (!scratch || scratch_bytes < ornith_cuda_qproj_scratch(T, n_in)) { orn_record_error("q8k_quantize: scratch too small"); return ORNITH_ERR_FORMAT; }
     uint2 *frags = (uint2 *)scratch;
-    float *dplane = (float *)((char *)scratch + frag_bytes(T, n_in));
     dim3 grid(n_in / QK, (T + 7) / 8 * 8);
     if (act_dtype == ORNITH_ACT_BF16)
-        k_q8k_quantize<__nv_bfloat16><<<grid, 32, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x, T, n_in, (unsigned char *)blocks, frags, dplane);
+        k_q8k_quantize<__nv_bfloat16><<<grid, 32, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x, T, n_in, (unsigned char *)blocks, frags);
     else
-        k_q8k_quantize<float><<<grid, 32, 0, (cudaStream_t)stream>>>((const float *)x, T, n_in, (unsigned char *)blocks, frags, dplane);
+        k_q8k_quantize<float><<<grid, 32, 0, (cudaStream_t)stream>>>((const float *)x, T, n_in, (unsigned char *)blocks, frags);
     return orn_check_launch("k_q8k_quantize");
 }
 
@@ -327,13 +339,28 @@ ornith_status ornith_cuda_matmul_q8_0(const void *W, int n_in, int n_out, const 
     CUtensorMap map;
     if (!weight_map(&map, W, n_in, n_out)) { orn_record_error("matmul_q8_0: the weight rows must be 16-byte aligned"); return ORNITH_ERR_FORMAT; }
     ProjArgs a;
-    a.frags = (const uint2 *)scratch;
-    a.dplane = (const float *)((char *)scratch + frag_bytes(T, n_in));
+    a.frags = (const unsigned char *)scratch;
     a.y = y; a.T = T; a.n_out = n_out; a.nseg = n_in / QK; a.out_dtype = out_dtype; a.status = orn_status_word();
     const int grid = (n_out + WARPS * ROWS - 1) / (WARPS * ROWS);
+    static bool configured_dev[ORN_MAX_DEVICES] = {};
+    bool &configured = configured_dev[orn_device_index()];
+    if (!configured) {
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_matmul_q8_0<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PROJ_SMEM), "projection smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_matmul_q8_0<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PROJ_SMEM), "projection smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_matmul_q8_0<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, PROJ_SMEM), "projection smem opt-in"));
+        configured = true;
+    }
+    static int groups = -1;                       // ORNITH_CUDA_PROJ_GROUPS=1|2|4 caps the warp groups per CTA (default 4)
+    if (groups < 0) { const char *e = getenv("ORNITH_CUDA_PROJ_GROUPS"); groups = e ? atoi(e) : 4; }
     for (int tok0 = 0; tok0 < T; tok0 += 8 * MAXNT) {                 // 64 tokens per pass over the weights
         a.ntiles = ((T - tok0 < 8 * MAXNT ? T - tok0 : 8 * MAXNT) + 7) / 8;
-        k_matmul_q8_0<<<grid, WARPS * 32, 0, (cudaStream_t)stream>>>(a, map, tok0);
+        // a group handles MAXNT / NG consecutive tiles of the pass; groups without a tile idle (every group multiplies
+        // all of its MAXNT / NG tiles, so few groups would mean many wasted products for a small batch)
+        // (measured at 2048 -> 8192: 64 tokens 17.7 us with 2 groups, 20.5 with 4; 1-16 tokens 10.8-11.8 us with 4, 12.6-13.5 with 2)
+        const int want = a.ntiles > 4 ? 2 : 4, ng = groups >= want ? want : (groups >= 2 ? 2 : 1);
+        if (ng == 4)      k_matmul_q8_0<4><<<grid, 4 * WARPS * 32, PROJ_SMEM, (cudaStream_t)stream>>>(a, map, tok0);
+        else if (ng == 2) k_matmul_q8_0<2><<<grid, 2 * WARPS * 32, PROJ_SMEM, (cudaStream_t)stream>>>(a, map, tok0);
+        else              k_matmul_q8_0<1><<<grid, WARPS * 32, PROJ_SMEM, (cudaStream_t)stream>>>(a, map, tok0);
         ORN_TRY(orn_check_launch("k_matmul_q8_0"));
     }
     return ORNITH_OK;
