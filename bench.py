@@ -69,20 +69,21 @@ def measured_tensor_peak():
 
 
 def _timed(fn, dev, world, reps):
-    """Average device time of fn() in ms over `reps` calls after one warm-up call, max over ranks."""
+    """Device time of fn() in ms: the median of `reps` separately timed calls after one warm-up call (a one-off stall
+    of a collective or an allocation does not end up in the figure), max over ranks."""
     import torch
     import torch.distributed as dist
     fn()
     torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+    ev[0].record()
+    for i in range(reps):
         fn()
-    e1.record()
+        ev[i + 1].record()
     torch.cuda.synchronize(dev)
-    t = torch.tensor([e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+    t = torch.tensor([float(np.median([ev[i].elapsed_time(ev[i + 1]) for i in range(reps)]))], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t[0])
@@ -185,11 +186,14 @@ def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b", slab=8192, shar
     fl_lin = float(NV_run) * (T / 64) * (6 * 64 * 128 * 128 + 2 * 64 * 64 * 256)
     burst, sustained, src = measured_tensor_peak()
     stack_ms = 45 * ms_lin + 15 * ms_full
+    from ornithology_b200 import _lib
+    torch.cuda.synchronize(dev)
+    wait_status = int(_lib.load().ornith_cuda_poll_status())       # non-zero: a bounded wait inside a kernel gave up
     tf_full = fl_full / (ms_full_k * 1e-3) / 1e12
     tf_lin = fl_lin / (ms_lin_k * 1e-3) / 1e12
     return {"workload": "%d-token prompt, %s-shaped layers, batch 1, bf16, head-sharded x%d%s"
                         % (T, shape.upper(), sw, "" if world > 1 or sw == 1 else " (one shard timed on one GPU, no gather)"),
-            "tokens": T, "delta_net_ms_per_layer": ms_lin, "gqa_ms_per_layer": ms_full,
+            "tokens": T, "delta_net_ms_per_layer": ms_lin, "gqa_ms_per_layer": ms_full, "wait_status_rank0": wait_status,
             "delta_net_ms_no_gather": ms_lin_k, "gqa_ms_no_gather": ms_full_k,
             "gather": "none" if world == 1 else f"NCCL all-gather per {slab}-token slab on a second stream, under the next slab's compute",
             "stack_layers": "45 delta-net + 15 GQA", "stack_ms": stack_ms, "stack_tok_per_s": T / (stack_ms * 1e-3),
