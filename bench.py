@@ -15,6 +15,9 @@ Further legs on the same JSON line (each an object of its own):
               per-layer times with and without the all-gather (N > 1)
   single_layer  one delta-net layer (prefill 512 + 128 decode steps) and one GQA layer (prefill 4096 + 256
               decode steps, f32 and Q8_0 caches), f32 activations, batch 1, with the CPU reference beside them (N = 1)
+  projections   the nine Q8_0 x Q8_K projections of one delta-net and one GQA layer for the 64 tokens of a step (N = 1)
+
+The timed headline loop replays the step (81 launches) as one CUDA graph (--no-graph: a loop of launches).
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     torchrun ... bench.py --gpus N ...
