@@ -860,6 +860,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the long-prefill leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the strong-scaling, 397B-decode and single-layer legs")
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill leg (1 GPU) and print its figures")
+    ap.add_argument("--projections-only", action="store_true", help="run only the projections leg (1 GPU) and print its figures")
     ap.add_argument("--prefill-tokens", type=int, default=32768)
     ap.add_argument("--prefill-shape", default="397b", choices=["397b", "35b"])
     ap.add_argument("--prefill-shard-of", type=int, default=1, choices=[1, 2, 4, 8],
@@ -871,6 +872,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.projections_only:
+        import torch
+        torch.cuda.set_device(local_rank)
+        print(json.dumps(run_projections(torch.device("cuda", local_rank), cpu=not args.no_cpu)), flush=True)
         return
     if args.prefill_only:
         import torch
