@@ -372,7 +372,8 @@ __device__ __forceinline__ float silu_sel(float x) { return FAST ? silu_fast(x) 
 // conv_k = 4, Cc a multiple of 4: one thread owns 4 adjacent channels over CONV4_TOK
 // tokens and requests all its inputs before the first use.  Same products, sums and
 // rounding as k_conv_silu_prefill.  grid (ceil(Cc/512), ceil(T/CONV4_TOK), n_seq).
-constexpr int CONV4_TOK = 16;
+constexpr int CONV4_TOK = 8;                  // 8 tokens (+ 3 of history) per thread: ~80 registers, 24 warps per SM; 16 tokens took 128
+                                              // registers (16 warps per SM) and the kernel waited on its loads (200 us per 8192 tokens x 12288 channels)
 
 // nearest tf32 value (ties away from zero, finite inputs), in integer arithmetic
 __device__ __forceinline__ float tf32_rna(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
@@ -422,11 +423,14 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y,
     }
     if (NORMS && ch < 2 * qd) {                           // warp-uniform: a warp covers 128 channels = one head
         const int lane = threadIdx.x & 31;
-        // sums over the 32 lanes for 16 tokens: token t ends up in lanes t and t + 16
+        // sums over the 32 lanes for 8 tokens: token t ends up in lanes t, t + 8, t + 16, t + 24
 #pragma unroll
-        for (int i = 0; i < CONV4_TOK; i++) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], 16);
+        for (int i = 0; i < CONV4_TOK; i++) {
+            ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], 16);
+            ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], 8);
+        }
 #pragma unroll
-        for (int off = 8; off >= 1; off >>= 1) {
+        for (int off = CONV4_TOK / 2; off >= 1; off >>= 1) {
             const bool up = (lane & off) != 0;
 #pragma unroll
             for (int k = 0; k < off; k++) {
