@@ -860,6 +860,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the long-prefill leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the strong-scaling, 397B-decode and single-layer legs")
     ap.add_argument("--prefill-only", action="store_true", help="run only the prefill leg (1 GPU) and print its figures")
+    ap.add_argument("--prefill-reps", type=int, default=1, help="timed repetitions of each layer in --prefill-only (median reported)")
     ap.add_argument("--projections-only", action="store_true", help="run only the projections leg (1 GPU) and print its figures")
     ap.add_argument("--prefill-tokens", type=int, default=32768)
     ap.add_argument("--prefill-shape", default="397b", choices=["397b", "35b"])
@@ -881,7 +882,7 @@ def main():
     if args.prefill_only:
         import torch
         torch.cuda.set_device(local_rank)
-        print(json.dumps(run_prefill(torch.device("cuda", local_rank), 0, 1, T=args.prefill_tokens, reps=1,
+        print(json.dumps(run_prefill(torch.device("cuda", local_rank), 0, 1, T=args.prefill_tokens, reps=args.prefill_reps,
                                      shape=args.prefill_shape, shard_of=args.prefill_shard_of)), flush=True)
         return
     if world == 1 and args.gpus > 1:

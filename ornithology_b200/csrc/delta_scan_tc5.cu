@@ -43,6 +43,8 @@
 #include <cuda_runtime.h>
 #include <math.h>
 
+#include <mutex>
+
 #include "linear_attn.cuh"
 #include "tcgen05.cuh"
 
@@ -128,10 +130,10 @@ __device__ __forceinline__ void block_matvec16(const float *B, int row0, const f
 template <typename ACT>
 __global__ void __launch_bounds__(256, 2) k_delta_prep64(LinArgs a, const float *Y, const float *rqg, const float *rkg,
                                                       const float *la, const float *be, float *AP, float *aux,
-                                                      int n_chunks) {
+                                                      int n_chunks, int chunk0) {
     extern __shared__ __align__(16) unsigned char smraw[];
     PrepSmem &sm = *reinterpret_cast<PrepSmem *>(smraw);
-    const int chunk = blockIdx.x, kh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int chunk = chunk0 + blockIdx.x, kh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int g = lane >> 2, j = lane & 3;
     const int qd = a.nk * 128, Cc = 2 * qd + a.nv * 128;
     const int t0 = chunk * C, n = min(C, a.T - t0);
@@ -296,6 +298,7 @@ struct ScanArgs {
     void *out;
     const float *norm_w;
     int nk, nv, head_map, T, n_chunks;
+    int c_begin, c_count;                // the chunks one launch of the sequential form scans (a slab of the prompt)
     float out_scale, eps;
     // Segment-parallel form (n_seg > 1; for few heads): the prompt is cut into n_seg runs of seg_chunks chunks that
     // are scanned at the same time by different CTAs (grid.z = 2 n_seg - 1).  The state enters the recurrence
@@ -362,8 +365,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_delta_scan_tc5(const __grid_con
     // 2 = from the identity with V = 0, raw outputs
     int kind = 0, seg = 0;
     if (SEG && blockIdx.z > 0) { seg = 1 + ((int)blockIdx.z - 1) / 2; kind = 1 + ((int)blockIdx.z - 1) % 2; }
-    const int c0 = SEG ? seg * a.seg_chunks : 0;                               // first chunk
-    const int N = SEG ? min(a.seg_chunks, a.n_chunks - c0) : a.n_chunks;       // chunks of this CTA
+    const int c0 = SEG ? seg * a.seg_chunks : a.c_begin;                       // first chunk
+    const int N = SEG ? min(a.seg_chunks, a.n_chunks - c0) : a.c_count;        // chunks of this CTA
     const int kh = a.head_map == ORNITH_HEADMAP_GROUPED ? hv / (a.nv / a.nk) : hv % a.nk;
     const int qd = a.nk * 128, vd = a.nv * 128;
     const uint32_t base = (su32(smraw) + 1023u) & ~1023u; // swizzle atoms are 1 KiB aligned
@@ -1007,9 +1010,47 @@ size_t linear_prefill_tc5_work_bytes(int nk, int nv, int n_seq, int T) {
 }
 size_t linear_prefill_tc5_dump_floats() { return DBG_FLOATS; }
 
+namespace {
+
+// The second stream and the events of the slab pipeline, one set per device.  The lock covers one call's
+// launches: a wait takes the event's state at the moment it is enqueued, so the next call may re-record.
+constexpr int MAX_SLABS = 16;
+struct SlabPipe {
+    std::mutex lock;
+    cudaStream_t scan_stream = nullptr;
+    cudaEvent_t front_done[MAX_SLABS] = {}, scans_done = nullptr;
+};
+SlabPipe g_slab_pipe[ORN_MAX_DEVICES];
+
+ornith_status slab_pipe_ready(SlabPipe &p) {
+    if (p.scan_stream) return ORNITH_OK;
+    int least = 0, greatest = 0;
+    ORN_TRY(orn_check(cudaDeviceGetStreamPriorityRange(&least, &greatest), "stream priority range"));
+    cudaStream_t st = nullptr;
+    ORN_TRY(orn_check(cudaStreamCreateWithPriority(&st, cudaStreamNonBlocking, greatest), "delta scan stream"));
+    for (int i = 0; i < MAX_SLABS; i++) ORN_TRY(orn_check(cudaEventCreateWithFlags(&p.front_done[i], cudaEventDisableTiming), "slab event"));
+    ORN_TRY(orn_check(cudaEventCreateWithFlags(&p.scans_done, cudaEventDisableTiming), "slab event"));
+    p.scan_stream = st;
+    return ORNITH_OK;
+}
+
+// slabs of the prompt: 48 chunks or more each, at most 8; 1 = no pipeline (ORNITH_CUDA_DELTA_SLABS overrides)
+int slab_plan(int heads, int n_chunks, int n_seg) {
+    if (n_seg > 1 || heads > 148) return 1;
+    int n = n_chunks / 48;                                            // a slab costs about 25 us of start-up and hand-over
+    if (n > 8) n = 8;
+    const char *e = getenv("ORNITH_CUDA_DELTA_SLABS");
+    if (e && e[0]) n = atoi(e);
+    if (n > MAX_SLABS) n = MAX_SLABS;
+    if (n > n_chunks) n = n_chunks;
+    return n < 1 ? 1 : n;
+}
+
+}  // namespace
+
 ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dtype, const float *Y, const float *rq,
-                                        const float *rk, const float *la, const float *be, float *work, float *dbg,
-                                        cudaStream_t s) {
+                                        const float *rk, const float *la, const float *be, const TC5Front *front,
+                                        float *work, float *dbg, cudaStream_t s) {
     extern long long *g_delta_scan_trace;
     const int n_chunks = (x.T + C - 1) / C;
     const size_t n_blocks = (size_t)n_seq * x.nv * n_chunks;
@@ -1040,10 +1081,7 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
                           "delta finish smem opt-in"));
         configured = true;
     }
-    const dim3 pgrid((unsigned)n_chunks, (unsigned)x.nk, (unsigned)n_seq);
-    if (act_dtype == ORNITH_ACT_BF16) k_delta_prep64<__nv_bfloat16><<<pgrid, 256, sizeof(PrepSmem), s>>>(x, Y, rq, rk, la, be, AP, aux, n_chunks);
-    else                              k_delta_prep64<float><<<pgrid, 256, sizeof(PrepSmem), s>>>(x, Y, rq, rk, la, be, AP, aux, n_chunks);
-    ORN_TRY(orn_check_launch("k_delta_prep64"));
+    const bool bf = act_dtype == ORNITH_ACT_BF16;
     CUtensorMap my, mym, map_ap, map_ap32, map_v;
     ORN_TRY(f32_rows_map(&my, Y, (uint64_t)Cc, (uint64_t)n_seq * x.T, C, 1));
     ORN_TRY(f32_rows_map(&mym, Y, (uint64_t)Cc, (uint64_t)n_seq * x.T, C, 2));
@@ -1053,17 +1091,53 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
     ScanArgs a;
     a.Y = Y; a.aux = aux; a.S = x.S; a.S_stride = x.S_stride; a.z = x.z; a.out = x.out; a.norm_w = x.norm_w;
     a.nk = x.nk; a.nv = x.nv; a.head_map = x.head_map; a.T = x.T; a.n_chunks = n_chunks;
+    a.c_begin = 0; a.c_count = n_chunks;
     a.out_scale = x.out_scale; a.eps = x.eps; a.status = orn_status_word(); a.dbg = dbg; a.trace = g_delta_scan_trace;
     a.n_seg = delta_seg_plan(x.nv, n_seq, n_chunks, &a.seg_chunks);
     a.seg_state = (float *)((char *)aux + aux_part(x.nv, n_seq, n_chunks));
     a.seg_raw = (float *)((char *)a.seg_state + seg_state_part(x.nv, n_seq, a.n_seg));
-    const bool bf = act_dtype == ORNITH_ACT_BF16;
-    if (a.n_seg <= 1) {
+
+    auto prep = [&](int c_begin, int c_count, cudaStream_t ps) {
+        const dim3 pgrid((unsigned)c_count, (unsigned)x.nk, (unsigned)n_seq);
+        if (bf) k_delta_prep64<__nv_bfloat16><<<pgrid, 256, sizeof(PrepSmem), ps>>>(x, Y, rq, rk, la, be, AP, aux, n_chunks, c_begin);
+        else    k_delta_prep64<float><<<pgrid, 256, sizeof(PrepSmem), ps>>>(x, Y, rq, rk, la, be, AP, aux, n_chunks, c_begin);
+        return orn_check_launch("k_delta_prep64");
+    };
+    auto scan = [&](const ScanArgs &sa, cudaStream_t ss) {
         dim3 grid((unsigned)x.nv, (unsigned)n_seq);
-        if (bf) k_delta_scan_tc5<__nv_bfloat16, false><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);
-        else    k_delta_scan_tc5<float, false><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);
+        if (bf) k_delta_scan_tc5<__nv_bfloat16, false><<<grid, NTHREADS, SCAN_SMEM, ss>>>(my, mym, map_ap, map_ap32, map_v, sa);
+        else    k_delta_scan_tc5<float, false><<<grid, NTHREADS, SCAN_SMEM, ss>>>(my, mym, map_ap, map_ap32, map_v, sa);
         return orn_check_launch("k_delta_scan_tc5");
+    };
+
+    const int n_slabs = front ? slab_plan(x.nv * n_seq, n_chunks, a.n_seg) : 1;
+    if (n_slabs > 1) {
+        // front of slab k + 1 on the caller's stream beside the scan of slab k on the scan stream
+        SlabPipe &pipe = g_slab_pipe[orn_device_index()];
+        std::lock_guard<std::mutex> hold(pipe.lock);
+        ORN_TRY(slab_pipe_ready(pipe));
+        const int per = (n_chunks + n_slabs - 1) / n_slabs;
+        int k = 0;
+        for (int cb = 0; cb < n_chunks; cb += per, k++) {
+            const int cn = min(per, n_chunks - cb);
+            ORN_TRY(front->conv(cb * C, min(x.T, (cb + cn) * C), s));
+            ORN_TRY(prep(cb, cn, s));
+            ORN_TRY(orn_check(cudaEventRecord(pipe.front_done[k], s), "slab event record"));
+            ORN_TRY(orn_check(cudaStreamWaitEvent(pipe.scan_stream, pipe.front_done[k], 0), "slab event wait"));
+            ScanArgs sa = a;
+            sa.c_begin = cb; sa.c_count = cn;
+            ORN_TRY(scan(sa, pipe.scan_stream));
+        }
+        ORN_TRY(front->ring_refresh(s));                      // after the conv that reads the old history
+        ORN_TRY(orn_check(cudaEventRecord(pipe.scans_done, pipe.scan_stream), "slab event record"));
+        return orn_check(cudaStreamWaitEvent(s, pipe.scans_done, 0), "slab event wait");
     }
+    if (front) {
+        ORN_TRY(front->conv(0, x.T, s));
+        ORN_TRY(front->ring_refresh(s));
+    }
+    ORN_TRY(prep(0, n_chunks, s));
+    if (a.n_seg <= 1) return scan(a, s);
     // few heads: the runs of the prompt side by side, then the carry over the runs and the finishing pass
     dim3 grid((unsigned)x.nv, (unsigned)n_seq, (unsigned)(2 * a.n_seg - 1));
     if (bf) k_delta_scan_tc5<__nv_bfloat16, true><<<grid, NTHREADS, SCAN_SMEM, s>>>(my, mym, map_ap, map_ap32, map_v, a);

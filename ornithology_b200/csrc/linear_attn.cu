@@ -381,9 +381,10 @@ __device__ __forceinline__ float tf32_rna(float x) { return __uint_as_float((__f
 // inverse L2 norms 1/sqrt(sum x^2 + 1e-6) of the q and k rows it produces in rq / rk [token][key head], which saves
 // the pass of k_linear_prep over the image (reference: ot_l2norm_eps, src/ornith_tensor.c:155-160).
 template <typename ACT, bool FAST, bool NORMS>
-__global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y, float *rq, float *rk) {
+__global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y, float *rq, float *rk, int t_begin, int t_end) {
+    // tokens t_begin .. t_end - 1 of every sequence (the whole prompt, or one slab of it)
     const int qd = a.nk * a.dk, Cc = 2 * qd + a.nv * a.dv;
-    const int ch = (blockIdx.x * 128 + threadIdx.x) * 4, b = blockIdx.z, t0 = blockIdx.y * CONV4_TOK;
+    const int ch = (blockIdx.x * 128 + threadIdx.x) * 4, b = blockIdx.z, t0 = t_begin + blockIdx.y * CONV4_TOK;
     if (ch >= Cc) return;
     const int pos0 = a.pos[b];
     const float *ring = a.conv + (size_t)b * a.conv_stride;
@@ -406,7 +407,7 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y,
     for (int i = 0; i < CONV4_TOK; i++) ss[i] = 0.0f;
 #pragma unroll
     for (int i = 0; i < CONV4_TOK; i++) {
-        if (t0 + i >= a.T) break;
+        if (t0 + i >= t_end) break;
         float4 y;
 #define ORN_CONV4(F, WC, B)                                                                               \
         y.F = silu_sel<FAST>(__fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(B, __fmul_rn(WC.x, x[i].F)),                 \
@@ -438,7 +439,7 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y,
                 ss[k] = keep + __shfl_xor_sync(0xffffffffu, send, off);
             }
         }
-        if (lane < CONV4_TOK && t0 + lane < a.T) {
+        if (lane < CONV4_TOK && t0 + lane < t_end) {
             const bool is_k = ch >= qd;
             const int kh = (is_k ? ch - qd : ch) / 128;
             (is_k ? rk : rq)[((size_t)b * a.T + t0 + lane) * a.nk + kh] = 1.0f / sqrtf(ss[0] + 1e-6f);
@@ -836,19 +837,30 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     const bool tc = l->dk == 128 && l->dv == 128 && !(exact && exact[0] == '1');
     const char *variant = getenv("ORNITH_CUDA_DELTA_SCAN");
     const bool tc5 = tc && ((uintptr_t)st->S % 16) == 0 && (st->S_seq_stride % 4) == 0 && !(variant && variant[0] == 'm');
-    bool fused_norms = false;                            // the conv kernel has written rq / rk
     if (l->conv_k == 4 && Cc % 4 == 0 && st->conv_seq_stride % 4 == 0 && ((uintptr_t)qkv % 16) == 0 &&
         ((uintptr_t)st->conv % 16) == 0 && ((uintptr_t)l->conv_w % 16) == 0 && ((uintptr_t)l->conv_b % 16) == 0) {
         dim3 cgrid((unsigned)((Cc + 511) / 512), (T + CONV4_TOK - 1) / CONV4_TOK, n_seq);
         if (tc5) {
-            if (bf) k_conv4_silu_prefill<__nv_bfloat16, true, true><<<cgrid, 128, 0, s>>>(x, Y, rq, rk);
-            else    k_conv4_silu_prefill<float, true, true><<<cgrid, 128, 0, s>>>(x, Y, rq, rk);
-            fused_norms = true;
+            // the tcgen05 path: conv, chunk preparation and scan, slab by slab (see launch_linear_prefill_tc5)
+            TC5Front front;
+            front.conv = [=](int t_begin, int t_end, cudaStream_t cs) {
+                dim3 g((unsigned)((Cc + 511) / 512), (unsigned)((t_end - t_begin + CONV4_TOK - 1) / CONV4_TOK), (unsigned)n_seq);
+                if (bf) k_conv4_silu_prefill<__nv_bfloat16, true, true><<<g, 128, 0, cs>>>(x, Y, rq, rk, t_begin, t_end);
+                else    k_conv4_silu_prefill<float, true, true><<<g, 128, 0, cs>>>(x, Y, rq, rk, t_begin, t_end);
+                return orn_check_launch("k_conv4_silu_prefill");
+            };
+            front.ring_refresh = [=](cudaStream_t cs) {
+                dim3 rg((unsigned)((Cc + 255) / 256), n_seq);
+                if (bf) k_conv_ring_refresh<__nv_bfloat16><<<rg, 256, 0, cs>>>(x);
+                else    k_conv_ring_refresh<float><<<rg, 256, 0, cs>>>(x);
+                return orn_check_launch("k_conv_ring_refresh");
+            };
+            return launch_linear_prefill_tc5(x, n_seq, act_dtype, Y, rq, rk, nullptr, nullptr, &front, blocks, g_delta_scan_dump, s);
         }
-        else if (bf && tc)  k_conv4_silu_prefill<__nv_bfloat16, true, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr);
-        else if (bf)   k_conv4_silu_prefill<__nv_bfloat16, false, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr);
-        else if (tc)   k_conv4_silu_prefill<float, true, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr);
-        else           k_conv4_silu_prefill<float, false, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr);
+        else if (bf && tc)  k_conv4_silu_prefill<__nv_bfloat16, true, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr, 0, T);
+        else if (bf)   k_conv4_silu_prefill<__nv_bfloat16, false, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr, 0, T);
+        else if (tc)   k_conv4_silu_prefill<float, true, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr, 0, T);
+        else           k_conv4_silu_prefill<float, false, false><<<cgrid, 128, 0, s>>>(x, Y, nullptr, nullptr, 0, T);
         ORN_TRY(orn_check_launch("k_conv4_silu_prefill"));
     } else {
         dim3 cgrid((unsigned)((Cc + 127) / 128), (T + CONV_TOK - 1) / CONV_TOK, n_seq);
@@ -860,18 +872,14 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
     if (bf) k_conv_ring_refresh<__nv_bfloat16><<<rgrid, 256, 0, s>>>(x);
     else    k_conv_ring_refresh<float><<<rgrid, 256, 0, s>>>(x);
     ORN_TRY(orn_check_launch("k_conv_ring_refresh"));
-    // the tcgen05 path computes the gates in its own preparation kernel and takes the norms from the conv kernel
-    if (!(tc5 && fused_norms)) {
-        if (bf) k_linear_prep<__nv_bfloat16><<<(unsigned)n_tok, 128, 0, s>>>(x, Y, (int)n_tok, rq, rk, la, be);
-        else    k_linear_prep<float><<<(unsigned)n_tok, 128, 0, s>>>(x, Y, (int)n_tok, rq, rk, la, be);
-        ORN_TRY(orn_check_launch("k_linear_prep"));
-    }
+    if (bf) k_linear_prep<__nv_bfloat16><<<(unsigned)n_tok, 128, 0, s>>>(x, Y, (int)n_tok, rq, rk, la, be);
+    else    k_linear_prep<float><<<(unsigned)n_tok, 128, 0, s>>>(x, Y, (int)n_tok, rq, rk, la, be);
+    ORN_TRY(orn_check_launch("k_linear_prep"));
 
     dim3 grid(l->nv, n_seq);
     if (l->dk == 128 && l->dv == 128) {
         // default: tf32 tensor-core scan; ORNITH_CUDA_PREFILL_FP32=1 keeps every product in fp32
-        if (tc5) return launch_linear_prefill_tc5(x, n_seq, act_dtype, Y, rq, rk, fused_norms ? nullptr : la, fused_norms ? nullptr : be,
-                                                  blocks, g_delta_scan_dump, s);
+        if (tc5) return launch_linear_prefill_tc5(x, n_seq, act_dtype, Y, rq, rk, la, be, nullptr, blocks, g_delta_scan_dump, s);
         if (tc) return launch_linear_prefill_tc(x, n_seq, act_dtype, Y, rq, rk, la, be, blocks, s);
         if (chunk >= 32) return bf ? launch_chunk<32, __nv_bfloat16>(x, grid, Y, rq, rk, la, be, s)
                                    : launch_chunk<32, float>(x, grid, Y, rq, rk, la, be, s);

@@ -1,5 +1,7 @@
 // linear_attn.cuh — argument block shared by the gated delta-net kernels.
 #pragma once
+#include <functional>
+
 #include "common.cuh"
 
 struct LinArgs {
@@ -35,10 +37,20 @@ ornith_status launch_linear_prefill_tc(const LinArgs &x, int n_seq, int act_dtyp
 // state in tensor memory, operands staged by TMA, 64-token chunks.  Y must hold the q and k channels
 // rounded to tf32 (k_conv4_silu_prefill does that); work = linear_prefill_tc5_work_bytes() bytes;
 // la = be = nullptr: the gates are computed from the layer's a / b inputs.
+//
+// With a front (the causal conv of a token range and the refresh of the conv history, as launches the caller
+// provides) and one wave of heads or less, the prompt is cut into slabs and pipelined: conv + chunk preparation
+// of slab k + 1 run on the caller's stream while slab k is scanned on a second, high-priority stream, so the
+// SMs the scan leaves idle (one CTA per head) do the memory-bound passes.  Events order the slabs; the caller's
+// stream waits for the last scan before the call returns.  front = nullptr: Y, rq and rk are complete already.
+struct TC5Front {
+    std::function<ornith_status(int t_begin, int t_end, cudaStream_t)> conv;
+    std::function<ornith_status(cudaStream_t)> ring_refresh;
+};
 size_t linear_prefill_tc5_work_bytes(int nk, int nv, int n_seq, int T);
 ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dtype, const float *Y, const float *rq,
-                                        const float *rk, const float *la, const float *be, float *work, float *dbg,
-                                        cudaStream_t s);
+                                        const float *rk, const float *la, const float *be, const TC5Front *front,
+                                        float *work, float *dbg, cudaStream_t s);
 
 __device__ __forceinline__ float4 lds128(const float *p) {        // not hoisted: keeps k/q out of registers
     float4 v;

@@ -265,3 +265,40 @@ def test_64_head_prefill_is_reproducible():
             first = got
         else:
             assert (got[0] == first[0]).all() and (got[1] == first[1]).all(), rep
+
+
+@pytest.mark.parametrize("T,pos0", [(4096 + 37, 0), (8192, 2)])
+def test_slab_pipeline_matches_the_single_launch(monkeypatch, T, pos0):
+    """Long prompts with one wave of heads run conv + chunk preparation of the next slab beside the scan of
+    the current one (two streams, events).  The slabs hand the state over in f32 exactly as the chunks of a
+    single launch do, so outputs, state and conv history must be bit-identical to the unpipelined form, on a
+    ragged length, with a non-empty history, and when a second call follows at once on the same stream."""
+    import torch
+    from ornithology_b200 import device as D
+    layer, kw = linear_case(6, nk=16, nv=64)
+    dl = device_linear(layer, kw)
+    ins = linear_inputs(78, layer, T + 4)
+    dins = [torch.from_numpy(x).cuda()[None] for x in ins]
+
+    def run(slabs):
+        if slabs:
+            monkeypatch.setenv("ORNITH_CUDA_DELTA_SLABS", slabs)
+        else:
+            monkeypatch.delenv("ORNITH_CUDA_DELTA_SLABS", raising=False)
+        st = D.LinearState(dl, 1)
+        pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+        if pos0:                                                     # something in the conv history first
+            D.linear_attn_prefill(dl, st, pos, *[x[:, T:T + pos0] for x in dins], pos0, chunk=64)
+            D.advance(pos, pos0)
+        out = D.linear_attn_prefill(dl, st, pos, *[x[:, :T] for x in dins], T, chunk=64)
+        D.advance(pos, T)
+        nxt = D.linear_attn_prefill(dl, st, pos, *[x[:, T:T + 4] for x in dins], 4, chunk=64)   # reads S and the history at once
+        torch.cuda.synchronize()
+        return out.cpu().numpy(), nxt.cpu().numpy(), st.S.cpu().numpy(), st.conv_image(0, pos0 + T + 4).cpu().numpy()
+
+    single = run("1")
+    for slabs in (None, "3", "8"):
+        got = run(slabs)
+        for a, b in zip(got, single):
+            assert (a == b).all(), slabs
+    assert np.isfinite(single[0]).all() and np.abs(single[0]).max() > 0
