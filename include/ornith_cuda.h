@@ -432,6 +432,20 @@ ornith_status ornith_cuda_matmul_q8_0(const void *W, int n_in, int n_out, const 
                                       int T, void *y, int out_dtype, void *scratch, size_t scratch_bytes,
                                       void *stream);
 
+/* The engine's integer path for any weight type that has one (qdot_can, reference: src/ornith_qdot.c:167-177):
+ * Q8_0 (vec_dot_q8_0 :144-163), Q4_K (vec_dot_q4_K :75-105), Q6_K (vec_dot_q6_K :109-141), against Q8_K
+ * activations, bit for bit: int8 tensor-core products with int32 sums, integer sub-block scales, and the
+ * engine's f32 association per super-block.  W: the GGUF tensor bytes on the device, [n_out] rows of
+ * n_in/256 super-blocks (144 / 210 / 272 bytes); wtype: the GGUF type id.  Rows that start on 16-byte
+ * boundaries (always for Q4_K and Q8_0; Q6_K when n_in is a multiple of 2048) and a 16-byte-aligned W take the
+ * tensor-core kernel, any other shape a plain kernel with the same result.  scratch: 256-byte aligned,
+ * ornith_cuda_matmul_q_scratch bytes.  Any T; more than 64 tokens are walked 64 at a time. */
+enum { ORNITH_GGML_Q8_0 = 8, ORNITH_GGML_Q4_K = 12, ORNITH_GGML_Q6_K = 14 };   /* src/ornith_gguf.h:24-30 */
+size_t ornith_cuda_matmul_q_scratch(int wtype, int T, int n_in);
+ornith_status ornith_cuda_matmul_q(int wtype, const void *W, int n_in, int n_out, const void *x,
+                                   int act_dtype, int T, void *y, int out_dtype, void *scratch,
+                                   size_t scratch_bytes, void *stream);
+
 /* ---- host-fed layer calls over device-resident state -------------------------
  * For an engine whose projections still run on the host: one object holds the state of all
  * layers of one sequence on the device (what rstate holds on the host, reference:

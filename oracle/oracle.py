@@ -25,6 +25,9 @@ REF_SO = os.path.join(_HERE, "_ref", "libornith_ref.so")
 
 KV_F32, KV_INT8_HEAD, KV_Q8_0 = 0, 1, 2
 HEADMAP_TILED, HEADMAP_GROUPED = 0, 1
+# weight types with an integer dot against Q8_K activations (ids as in the GGUF file, src/ornith_gguf.h:24-30)
+GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 8, 12, 14
+QROW_BYTES = {GGML_Q8_0: lambda n: n // 32 * 34, GGML_Q4_K: lambda n: n // 256 * 144, GGML_Q6_K: lambda n: n // 256 * 210}
 
 _f32p = C.POINTER(C.c_float)
 
@@ -250,6 +253,20 @@ class Oracle:
             raise ValueError("the input width must be a multiple of 256")
         return Y
 
+    def matmul_q(self, wtype, W, n_in, X):
+        """The same for any weight type with an integer path: GGML_Q8_0, GGML_Q4_K, GGML_Q6_K."""
+        W = np.ascontiguousarray(W, np.uint8)
+        X = np.ascontiguousarray(X, np.float32).reshape(-1, n_in)
+        self.lib.orc_qrow_bytes.restype = C.c_size_t
+        rb = self.lib.orc_qrow_bytes(wtype, n_in)
+        if rb == 0 or n_in % 256:
+            raise ValueError("no integer path for this weight type / width")
+        n_out = W.size // rb
+        Y = np.empty((X.shape[0], n_out), np.float32)
+        self.lib.orc_matmul_q.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, _f32p]
+        assert self.lib.orc_matmul_q(wtype, W.ctypes.data, n_in, n_out, _fp(X), X.shape[0], _fp(Y)) == 0
+        return Y
+
     # -- codecs ----------------------------------------------------------
     def q8_0_encode(self, x):
         x = np.ascontiguousarray(x, np.float32)
@@ -426,6 +443,24 @@ class Ref:
         self.lib.refdrv_matmul_q8_0.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, _f32p]
         assert self.lib.refdrv_matmul_q8_0(W.ctypes.data, n_in, n_out, _fp(X), X.shape[0], _fp(Y)) == 0
         return Y
+
+    def matmul_q(self, wtype, W, n_in, X):
+        W = np.ascontiguousarray(W, np.uint8)
+        X = np.ascontiguousarray(X, np.float32).reshape(-1, n_in)
+        n_out = W.size // QROW_BYTES[wtype](n_in)
+        Y = np.empty((X.shape[0], n_out), np.float32)
+        self.lib.refdrv_matmul_q.argtypes = [C.c_uint, C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, _f32p]
+        assert self.lib.refdrv_matmul_q(wtype, W.ctypes.data, n_in, n_out, _fp(X), X.shape[0], _fp(Y)) == 0
+        return Y
+
+    def quantize_rows(self, wtype, x):
+        """f32 [rows][n] -> the reference encoder's bytes [rows][row bytes] (Q8_0, Q4_K, Q6_K)."""
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[:-1] + (QROW_BYTES[wtype](x.shape[-1]),), np.uint8)
+        self.lib.refdrv_quantize_rows.argtypes = [C.c_uint, _f32p, C.c_void_p, C.c_longlong]
+        self.lib.refdrv_quantize_rows.restype = C.c_longlong
+        assert self.lib.refdrv_quantize_rows(wtype, _fp(x), out.ctypes.data, x.size) == out.size
+        return out
 
     def q8_0_decode(self, b):
         n = b.size // 34 * 32

@@ -625,3 +625,101 @@ int orc_matmul_q8_0(const uint8_t *W, int n_in, int n_out, const float *X, int T
     free(xq);
     return 0;
 }
+
+/* ---- k-quant weights x Q8_K activations (src/ornith_qdot.c:63-141) ----------------------------------------
+ * Both formats hold 256 weights per super-block.  The dot over a super-block is an integer: codes times
+ * activation codes, weighted by small integer sub-block scales; one f32 product per super-block applies the
+ * weight's f16 scale and the activation's f32 scale.  The running total is f32, super-blocks in order. */
+
+/* Q4_K block, 144 bytes: f16 d, f16 dmin, 12 bytes of packed 6-bit (scale, min) pairs for 8 sub-blocks of 32,
+ * 128 bytes of 4-bit codes (sub-blocks 2p and 2p+1 share bytes 32p..32p+31: low and high nibbles).
+ * Sub-block j < 4 has its scale in the low 6 bits of byte j and its min in the low 6 bits of byte j + 4; for
+ * j >= 4 the low 4 bits come from the two nibbles of byte j + 4 and the top 2 bits from the top bits of bytes
+ * j - 4 (scale) and j (min) (src/ornith_qdot.c:65-71). */
+static void orc_q4k_scale_min(const uint8_t *sc12, int j, int *scale, int *min) {
+    if (j < 4) {
+        *scale = sc12[j] & 0x3F;
+        *min = sc12[j + 4] & 0x3F;
+    } else {
+        *scale = (sc12[j + 4] & 0x0F) | ((sc12[j - 4] >> 6) << 4);
+        *min = (sc12[j + 4] >> 4) | ((sc12[j] >> 6) << 4);
+    }
+}
+
+/* src/ornith_qdot.c:75-105: value of weight e = d * scale_j * code_e - dmin * min_j, so the dot splits into
+ * d * sum_j scale_j (codes . activation codes) and -dmin * sum_j min_j (sum of the sub-block's activation codes,
+ * taken from the block's 16-sums). */
+float orc_vec_dot_q4_K(int n, const uint8_t *wrow, const orc_q8k_block *y) {
+    float total = 0.0f;
+    for (int i = 0; i < n / 256; i++) {
+        const uint8_t *blk = wrow + (size_t)i * 144, *sc12 = blk + 4, *codes = blk + 16;
+        const float d = y[i].d * orc_f16_to_f32((uint16_t)(blk[0] | ((uint16_t)blk[1] << 8)));
+        const float dmin = -y[i].d * orc_f16_to_f32((uint16_t)(blk[2] | ((uint16_t)blk[3] << 8)));
+        int dots = 0, mins = 0;
+        for (int j = 0; j < 8; j++) {
+            int scale, min;
+            orc_q4k_scale_min(sc12, j, &scale, &min);
+            mins += min * ((int)y[i].bsums[2 * j] + (int)y[i].bsums[2 * j + 1]);
+            const uint8_t *src = codes + 32 * (j / 2);
+            int part = 0;
+            for (int l = 0; l < 32; l++) {
+                const int code = (j & 1) ? (src[l] >> 4) : (src[l] & 0x0F);
+                part += code * (int)y[i].qs[32 * j + l];
+            }
+            dots += part * scale;
+        }
+        total += d * (float)dots + dmin * (float)mins;
+    }
+    return total;
+}
+
+/* Q6_K block, 210 bytes: 128 bytes of low nibbles, 64 bytes of 2-bit high parts, 16 signed 8-bit scales (one per
+ * 16 weights), f16 d.  Weight e (0..255): half h = e / 128, quarter c = (e % 128) / 32, l = e % 32; low nibble =
+ * nibble (c / 2) of ql[64 h + 32 (c % 2) + l], high bits = bits 2c, 2c+1 of qh[32 h + l]; code - 32 is the value;
+ * its scale is sc[e / 16] (src/ornith_qdot.c:109-141). */
+float orc_vec_dot_q6_K(int n, const uint8_t *wrow, const orc_q8k_block *y) {
+    float total = 0.0f;
+    for (int i = 0; i < n / 256; i++) {
+        const uint8_t *blk = wrow + (size_t)i * 210, *ql = blk, *qh = blk + 128;
+        const int8_t *sc = (const int8_t *)(blk + 192);
+        const float d = y[i].d * orc_f16_to_f32((uint16_t)(blk[208] | ((uint16_t)blk[209] << 8)));
+        int dots = 0;
+        for (int e = 0; e < 256; e++) {
+            const int h = e / 128, c = (e % 128) / 32, l = e % 32;
+            const int lo = (ql[64 * h + 32 * (c % 2) + l] >> (4 * (c / 2))) & 0x0F;
+            const int hi = (qh[32 * h + l] >> (2 * c)) & 3;
+            dots += (int)y[i].qs[e] * ((lo | (hi << 4)) - 32) * (int)sc[e / 16];
+        }
+        total += d * (float)dots;
+    }
+    return total;
+}
+
+size_t orc_qrow_bytes(int wtype, int n_in) {
+    switch (wtype) {
+    case ORC_GGML_Q8_0: return (size_t)n_in / 32 * 34;
+    case ORC_GGML_Q4_K: return (size_t)n_in / 256 * 144;
+    case ORC_GGML_Q6_K: return (size_t)n_in / 256 * 210;
+    default: return 0;
+    }
+}
+
+/* matmul_batch_q (src/ornith_rforward.c:138-192) for any of the three integer paths (qdot_can, src/ornith_qdot.c:167-177) */
+int orc_matmul_q(int wtype, const uint8_t *W, int n_in, int n_out, const float *X, int T, float *Y) {
+    const size_t rb = orc_qrow_bytes(wtype, n_in);
+    if (n_in % 256 != 0 || rb == 0) return -1;
+    const size_t nblk = (size_t)n_in / 256;
+    orc_q8k_block *xq = malloc((size_t)T * nblk * sizeof *xq);
+    if (!xq) return -1;
+    for (int t = 0; t < T; t++) orc_q8k_quantize(X + (size_t)t * n_in, xq + (size_t)t * nblk, n_in);
+    for (int o = 0; o < n_out; o++)
+        for (int t = 0; t < T; t++) {
+            const uint8_t *w = W + (size_t)o * rb;
+            const orc_q8k_block *a = xq + (size_t)t * nblk;
+            Y[(size_t)t * n_out + o] = wtype == ORC_GGML_Q4_K ? orc_vec_dot_q4_K(n_in, w, a)
+                                     : wtype == ORC_GGML_Q6_K ? orc_vec_dot_q6_K(n_in, w, a)
+                                                              : orc_vec_dot_q8_0(n_in, w, a);
+        }
+    free(xq);
+    return 0;
+}

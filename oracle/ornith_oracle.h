@@ -147,6 +147,13 @@ float orc_vec_dot_q8_0(int n, const uint8_t *wrow, const orc_q8k_block *y);
 /* Y[t][o] = W[o] . X[t] for T activation rows: every row quantised to Q8_K once, then the integer dot per
  * (row of W, token) (matmul_batch_q, src/ornith_rforward.c:138-192).  W: [out] rows of n_in/32 Q8_0 blocks. */
 int orc_matmul_q8_0(const uint8_t *W, int n_in, int n_out, const float *X, int T, float *Y);
+/* the other two integer paths: Q4_K rows (144-byte super-blocks, src/ornith_qdot.c:75-105) and Q6_K rows
+ * (210-byte super-blocks, :109-141); weight type ids as in the GGUF file (src/ornith_gguf.h:24-30) */
+enum { ORC_GGML_Q8_0 = 8, ORC_GGML_Q4_K = 12, ORC_GGML_Q6_K = 14 };
+float orc_vec_dot_q4_K(int n, const uint8_t *wrow, const orc_q8k_block *y);
+float orc_vec_dot_q6_K(int n, const uint8_t *wrow, const orc_q8k_block *y);
+size_t orc_qrow_bytes(int wtype, int n_in);
+int orc_matmul_q(int wtype, const uint8_t *W, int n_in, int n_out, const float *X, int T, float *Y);
 
 #ifdef __cplusplus
 }

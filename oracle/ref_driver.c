@@ -103,6 +103,25 @@ void refdrv_full_step(const refdrv_full *p, ornith_kv_cache *c, int pos, const f
 
 void refdrv_q8k_quantize(const float *x, void *y, long long k) { qdot_quantize_row_q8_K(x, (oq8k_block *)y, k); }
 
+/* any weight type the reference has an integer dot for; rows quantised by the reference's own encoder */
+int refdrv_matmul_q(unsigned wtype, const unsigned char *W, int n_in, int n_out, const float *X, int T, float *Y) {
+    if (!qdot_can(wtype, n_in)) return -1;
+    const size_t nblk = (size_t)n_in / OQDOT_QK_K, rb = oq_row_bytes(wtype, (size_t)n_in);
+    oq8k_block *xq = malloc((size_t)T * nblk * sizeof *xq);
+    if (!xq) return -1;
+    for (int t = 0; t < T; t++) qdot_quantize_row_q8_K(X + (size_t)t * n_in, xq + (size_t)t * nblk, n_in);
+    for (int o = 0; o < n_out; o++)
+        for (int t = 0; t < T; t++)
+            qdot_vec_dot(wtype, n_in, &Y[(size_t)t * n_out + o], W + (size_t)o * rb, xq + (size_t)t * nblk);
+    free(xq);
+    return 0;
+}
+/* f32 rows -> quantised rows of `wtype` with the reference's encoder (src/ornith_quant.c oq_quantize) */
+long long refdrv_quantize_rows(unsigned wtype, const float *src, void *dst, long long n_elems) {
+    if (oq_quantize(wtype, src, dst, (size_t)n_elems) != 0) return -1;
+    return (long long)oq_row_bytes(wtype, (size_t)n_elems);
+}
+
 int refdrv_matmul_q8_0(const unsigned char *W, int n_in, int n_out, const float *X, int T, float *Y) {
     if (!qdot_can(OGGML_Q8_0, n_in)) return -1;
     const size_t nblk = (size_t)n_in / OQDOT_QK_K, rb = oq_row_bytes(OGGML_Q8_0, (size_t)n_in);

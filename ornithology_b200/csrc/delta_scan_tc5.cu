@@ -96,20 +96,21 @@ __device__ __forceinline__ void mma_tf32_sync(float (&d)[4], const float (&a)[4]
 }
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
-// (I + L)^-1 of a 32x32 strictly lower block by forward substitution; lane = column
+// (I + L)^-1 of a 32x32 strictly lower block by forward substitution; lane = column.  Four partial sums per
+// row: the rows form one dependent chain, and a single accumulator would make it 496 multiply-adds long.
 __device__ __forceinline__ void inv_unit_lower(const float *Mb, int lane, float (&x)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; i++) {
-        float acc = (i == lane) ? 1.0f : 0.0f;
+        float a0 = (i == lane) ? 1.0f : 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
         for (int l4 = 0; l4 < (i + 3) / 4; l4++) {
             const float4 m = *reinterpret_cast<const float4 *>(Mb + i * LDB + 4 * l4);
-            if (4 * l4 + 0 < i) acc -= m.x * x[4 * l4 + 0];
-            if (4 * l4 + 1 < i) acc -= m.y * x[4 * l4 + 1];
-            if (4 * l4 + 2 < i) acc -= m.z * x[4 * l4 + 2];
-            if (4 * l4 + 3 < i) acc -= m.w * x[4 * l4 + 3];
+            if (4 * l4 + 0 < i) a0 -= m.x * x[4 * l4 + 0];
+            if (4 * l4 + 1 < i) a1 -= m.y * x[4 * l4 + 1];
+            if (4 * l4 + 2 < i) a2 -= m.z * x[4 * l4 + 2];
+            if (4 * l4 + 3 < i) a3 -= m.w * x[4 * l4 + 3];
         }
-        x[i] = acc;
+        x[i] = (a0 + a1) + (a2 + a3);
     }
 }
 // y[i] = sum_l B[row0 + i][l] x[l] for 16 rows of a 32x32 block in shared memory, x in registers

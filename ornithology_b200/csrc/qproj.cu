@@ -29,6 +29,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "qproj.cuh"
 #include "tcgen05.cuh"          // the tensor-map encoder entry point
 
 namespace {
@@ -98,9 +99,16 @@ __device__ __forceinline__ void weights_chunk(uint32_t raw0, uint32_t raw1, cons
 // grid (n_in / 256, T_pad), one warp each.  Tokens >= T are padding of the last tile of 8: zero fragments.
 // blocks: [T][n_in/256] engine blocks of 292 bytes, or NULL.  frags: [T_pad/8][n_in/256] images of FRAG_BYTES:
 // [17][32] uint2 fragments, then the 8 tokens' scales.
+//
+// img (or NULL): the image the integer products read (kquant_matmul.cu), [T_pad/8][n_in/256] images of
+// ORN_Q8K_IMG_BYTES: the codes as int8 MMA B operands (16 k-steps of 16 inputs x [8 tokens][16 bytes]), the 8
+// tokens' scales, and the sums of the codes over each run of 32 inputs split into an unsigned low byte and a signed
+// high byte (two B operands of [8 tokens][16 bytes], bytes 8..15 zero).
 template <typename ACT>
-__global__ void __launch_bounds__(32) k_q8k_quantize(const ACT *x, int T, int n_in, unsigned char *blocks, uint2 *frags) {
+__global__ void __launch_bounds__(32) k_q8k_quantize(const ACT *x, int T, int n_in, unsigned char *blocks, uint2 *frags,
+                                                     unsigned char *img) {
     const int seg = blockIdx.x, tok = blockIdx.y, lane = threadIdx.x, nseg = n_in / QK;
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");     // a product launched as a dependent may start its weight copies
     float v[8];
     float amax = 0.0f, mx = 0.0f;
     int arg = 0;
@@ -150,11 +158,34 @@ __global__ void __launch_bounds__(32) k_q8k_quantize(const ACT *x, int T, int n_
         *reinterpret_cast<uint32_t *>(blk + 8 + 8 * lane) = w1;
         if ((lane & 1) == 0) *reinterpret_cast<short *>(blk + 260 + lane) = (short)sum;
     }
+    if (img) {
+        unsigned char *im = img + ((size_t)(tok >> 3) * nseg + seg) * ORN_Q8K_IMG_BYTES;
+        const int g = tok & 7;
+        uint2 w;
+        w.x = w.y = 0u;
+#pragma unroll
+        for (int i = 0; i < 4; i++) { w.x |= (uint32_t)(q[i] & 255) << (8 * i); w.y |= (uint32_t)(q[4 + i] & 255) << (8 * i); }
+        *reinterpret_cast<uint2 *>(im + (lane >> 1) * 128 + g * 16 + 8 * (lane & 1)) = w;      // inputs 8 lane .. 8 lane + 7
+        if (lane == 0) reinterpret_cast<float *>(im + ORN_Q8K_IMG_D)[g] = d;
+        int s32 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) s32 += q[i];
+        s32 += __shfl_xor_sync(0xffffffffu, s32, 1);
+        s32 += __shfl_xor_sync(0xffffffffu, s32, 2);                                           // inputs 32 (lane / 4) ..
+        if ((lane & 3) == 0) {
+            im[ORN_Q8K_IMG_LO + g * 16 + (lane >> 2)] = (unsigned char)(s32 & 255);
+            im[ORN_Q8K_IMG_HI + g * 16 + (lane >> 2)] = (unsigned char)((s32 >> 8) & 255);
+        } else if ((lane & 3) == 1) {
+            im[ORN_Q8K_IMG_LO + g * 16 + 8 + (lane >> 2)] = 0;
+            im[ORN_Q8K_IMG_HI + g * 16 + 8 + (lane >> 2)] = 0;
+        }
+    }
+    if (!frags) return;
     // the product's image: pair p = inputs (2p, 2p+1) is stream element e = 17 (p / 16) + 1 + p % 16, which lies
     // in chunk e / 8 at position e % 8 = 2 j + h of lane (token % 8, j)
-    unsigned char *img = reinterpret_cast<unsigned char *>(frags) + ((size_t)(tok >> 3) * nseg + seg) * FRAG_BYTES;
-    uint32_t *fr = reinterpret_cast<uint32_t *>(img);
-    if (lane == 0) reinterpret_cast<float *>(img + FRAG_WORDS2 * 8)[tok & 7] = d;
+    unsigned char *fimg = reinterpret_cast<unsigned char *>(frags) + ((size_t)(tok >> 3) * nseg + seg) * FRAG_BYTES;
+    uint32_t *fr = reinterpret_cast<uint32_t *>(fimg);
+    if (lane == 0) reinterpret_cast<float *>(fimg + FRAG_WORDS2 * 8)[tok & 7] = d;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int p = 4 * lane + i, e = 17 * (p >> 4) + 1 + (p & 15);
@@ -305,6 +336,17 @@ size_t frag_bytes(int T, int n_in) { return align_up((size_t)((T + 7) / 8) * (n_
 
 }  // namespace
 
+// x [T][n_in] -> the integer image of its Q8_K form (see k_q8k_quantize); img: orn_q8k_image_bytes(T, n_in) bytes
+size_t orn_q8k_image_bytes(int T, int n_in) { return align_up((size_t)((T + 7) / 8) * (n_in / QK) * ORN_Q8K_IMG_BYTES, 256); }
+ornith_status orn_q8k_quantize_image(const void *x, int act_dtype, int T, int n_in, void *img, cudaStream_t stream) {
+    dim3 grid(n_in / QK, (T + 7) / 8 * 8);
+    if (act_dtype == ORNITH_ACT_BF16)
+        k_q8k_quantize<__nv_bfloat16><<<grid, 32, 0, stream>>>((const __nv_bfloat16 *)x, T, n_in, nullptr, nullptr, (unsigned char *)img);
+    else
+        k_q8k_quantize<float><<<grid, 32, 0, stream>>>((const float *)x, T, n_in, nullptr, nullptr, (unsigned char *)img);
+    return orn_check_launch("k_q8k_quantize");
+}
+
 extern "C" {
 
 size_t ornith_cuda_qproj_scratch(int T, int n_in) {
@@ -323,9 +365,9 @@ ornith_status ornith_cuda_q8k_quantize(const void *x, int act_dtype, int T, int 
     uint2 *frags = (uint2 *)scratch;
     dim3 grid(n_in / QK, (T + 7) / 8 * 8);
     if (act_dtype == ORNITH_ACT_BF16)
-        k_q8k_quantize<__nv_bfloat16><<<grid, 32, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x, T, n_in, (unsigned char *)blocks, frags);
+        k_q8k_quantize<__nv_bfloat16><<<grid, 32, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x, T, n_in, (unsigned char *)blocks, frags, nullptr);
     else
-        k_q8k_quantize<float><<<grid, 32, 0, (cudaStream_t)stream>>>((const float *)x, T, n_in, (unsigned char *)blocks, frags);
+        k_q8k_quantize<float><<<grid, 32, 0, (cudaStream_t)stream>>>((const float *)x, T, n_in, (unsigned char *)blocks, frags, nullptr);
     return orn_check_launch("k_q8k_quantize");
 }
 

@@ -160,6 +160,39 @@ def matmul_q8_0(w: Q8_0Weight, x, out=None):
     return out
 
 
+GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 8, 12, 14          # GGUF tensor type ids (reference: src/ornith_gguf.h:24-30)
+_QROW_BYTES = {GGML_Q8_0: lambda n: n // 32 * 34, GGML_Q4_K: lambda n: n // 256 * 144, GGML_Q6_K: lambda n: n // 256 * 210}
+
+
+class QWeight:
+    """A projection weight on the device as the GGUF tensor's bytes: [n_out] rows of Q8_0, Q4_K or Q6_K blocks."""
+
+    def __init__(self, wtype, rows_bytes, n_in, device="cuda:0"):
+        rows = np.ascontiguousarray(rows_bytes, np.uint8).reshape(-1)
+        self.wtype, self.n_in = int(wtype), int(n_in)
+        self.n_out = rows.size // _QROW_BYTES[self.wtype](self.n_in)
+        self.bytes = torch.from_numpy(rows).to(device)
+        self._scratch = None
+
+    def scratch(self, T):
+        need = _lib.load().ornith_cuda_matmul_q_scratch(self.wtype, int(T), self.n_in)
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, dtype=torch.uint8, device=self.bytes.device)
+        return self._scratch
+
+
+def matmul_q(w: QWeight, x, out=None):
+    """y [T][n_out] = x [T][n_in] through quantised weight rows: the engine's integer path, bit for bit."""
+    lib = _lib.load()
+    T = x.numel() // w.n_in
+    if out is None:
+        out = torch.empty(T, w.n_out, dtype=x.dtype, device=x.device)
+    scr = w.scratch(T)
+    check(lib.ornith_cuda_matmul_q(w.wtype, _ptr(w.bytes), w.n_in, w.n_out, _ptr(x), _act(x), T, _ptr(out), _act(out),
+                                   _ptr(scr), scr.numel(), _stream()), "matmul_q")
+    return out
+
+
 def kv_export(kv: KvBatch, seq, length):
     """Session record of the first `length` positions of sequence `seq` (bytes, the engine's layer record)."""
     lib = _lib.load()

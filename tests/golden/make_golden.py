@@ -247,8 +247,25 @@ def projection():
     save("projection_q8_0.npz", X=X, W=W, n_in=n_in, blocks=r.q8k_quantize(X), Y=r.matmul_q8_0(W, n_in, X))
 
 
+def projection_kquant():
+    """The k-quant integer dots (src/ornith_qdot.c:75-105 vec_dot_q4_K, :109-141 vec_dot_q6_K) over rows from the
+    reference's own encoder (oq_quantize, src/ornith_quant.c): 5 activation rows of 2048 through 72 weight rows."""
+    from oracle.oracle import GGML_Q4_K, GGML_Q6_K
+    g = np.random.default_rng(22)
+    n_in, n_out, T = 2048, 72, 5
+    X = g.standard_normal((T, n_in)).astype(np.float32)
+    X[0, 256:512] = 0.0
+    X[1, 5] = 9.0; X[1, 100] = -9.0
+    Wf = (g.standard_normal((n_out, n_in)) * 0.05).astype(np.float32)
+    Wf[7] = 0.0
+    W4, W6 = r.quantize_rows(GGML_Q4_K, Wf), r.quantize_rows(GGML_Q6_K, Wf)
+    save("projection_kquant.npz", X=X, n_in=n_in, W_q4_k=W4, W_q6_k=W6,
+         Y_q4_k=r.matmul_q(GGML_Q4_K, W4, n_in, X), Y_q6_k=r.matmul_q(GGML_Q6_K, W6, n_in, X))
+
+
 if __name__ == "__main__":
     projection()
+    projection_kquant()
     delta_parity()
     gqa(42, 4, 2, 8, 11, "attn_gqa.npz", 0)
     gqa(123, 4, 2, 16, 13, "attn_gqa_int8.npz", 1)

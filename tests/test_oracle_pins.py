@@ -239,3 +239,36 @@ def test_projection_golden_bit_exact(oracle, golden):
     assert (oracle.q8k_quantize(g["X"]) == g["blocks"]).all()
     y = oracle.matmul_q8_0(g["W"], int(g["n_in"]), g["X"])
     assert (bits(y) == bits(g["Y"])).all()
+
+
+@pytest.mark.skipif(not Ref.available(), reason="reference objects not built on this machine")
+@pytest.mark.parametrize("wtype", ["q8_0", "q4_k", "q6_k"])
+def test_kquant_dots_equal_reference_objects(oracle, wtype):
+    """The integer dots of all three weight types (src/ornith_qdot.c:75-163) against the reference's own objects,
+    bit for bit: rows from the reference's encoder, and rows of random block bytes (every code, sub-block scale
+    and minimum occurs; finite f16 scales)."""
+    from oracle import oracle as O
+    ref = Ref()
+    wt = {"q8_0": O.GGML_Q8_0, "q4_k": O.GGML_Q4_K, "q6_k": O.GGML_Q6_K}[wtype]
+    g = np.random.default_rng(31 + wt)
+    n_in, n_out, T = 1024, 24, 5
+    X = g.standard_normal((T, n_in)).astype(np.float32)
+    X[0, :256] = 0.0
+    W = ref.quantize_rows(wt, (g.standard_normal((n_out, n_in)) * 0.05).astype(np.float32))
+    assert W.shape[1] == O.QROW_BYTES[wt](n_in)
+    assert (bits(oracle.matmul_q(wt, W, n_in, X)) == bits(ref.matmul_q(wt, W, n_in, X))).all()
+    Wr = g.integers(0, 256, W.shape, dtype=np.uint8)
+    blk = Wr.reshape(n_out, n_in // (32 if wt == O.GGML_Q8_0 else 256), -1)
+    for col in {O.GGML_Q8_0: (1,), O.GGML_Q4_K: (1, 3), O.GGML_Q6_K: (209,)}[wt]:
+        blk[:, :, col] &= 0x3B                                       # f16 exponent below 15: finite, |d| < 1
+    a, b = oracle.matmul_q(wt, Wr, n_in, X), ref.matmul_q(wt, Wr, n_in, X)
+    assert np.isfinite(a).all() and (bits(a) == bits(b)).all()
+
+
+def test_kquant_golden_bit_exact(oracle, golden):
+    """The reference-made k-quant fixture (tests/golden/make_golden.py::projection_kquant)."""
+    from oracle import oracle as O
+    g = golden("projection_kquant.npz")
+    for name, wt in (("q4_k", O.GGML_Q4_K), ("q6_k", O.GGML_Q6_K)):
+        y = oracle.matmul_q(wt, g["W_" + name], int(g["n_in"]), g["X"])
+        assert (bits(y) == bits(g["Y_" + name])).all(), name
