@@ -15,7 +15,8 @@ Further legs on the same JSON line (each an object of its own):
               per-layer times with and without the all-gather (N > 1)
   single_layer  one delta-net layer (prefill 512 + 128 decode steps) and one GQA layer (prefill 4096 + 256
               decode steps, f32 and Q8_0 caches), f32 activations, batch 1, with the CPU reference beside them (N = 1)
-  projections   the nine Q8_0 x Q8_K projections of one delta-net and one GQA layer for the 64 tokens of a step (N = 1)
+  projections   the nine integer-path projections (Q8_0 / Q6_K weights x Q8_K activations) of one delta-net and one GQA
+              layer for the 64 tokens of a step, and one prompt-sized product (N = 1)
 
 The timed headline loop replays the step (81 launches) as one CUDA graph (--no-graph: a loop of launches).
 
@@ -363,61 +364,118 @@ def run_single_layer(dev, cpu=True):
 
 def run_projections(dev, n_tok=64, cpu=True):
     """The quantised projections that bracket the attention kernels of one 35B-shaped delta-net layer and one
-    full-attention layer (hidden 2048): Q8_0 weights x Q8_K activations, 64 tokens (one decode step of the headline
-    batch), bf16 activations.  Each shape is timed over 16 distinct weight matrices used in turn (together larger
-    than L2 for the big shapes), activation quantisation included; the roofline figure is the weight bytes (what a
-    decode-sized batch has to stream) over the time.  The CPU figure is the engine's integer path on one host
-    thread over a sample of the output rows."""
+    full-attention layer (hidden 2048), through the engine's integer path (Q8_K activations; Q8_0 weights around the
+    delta-net core, Q6_K around the full-attention core), 64 tokens (one decode step of the headline batch), bf16
+    activations.  Projections that read the same input share one quantisation, as in the engine.  Each layer's
+    sequence is timed over 16 distinct weight sets used in turn (larger than L2 together), as one CUDA graph; the
+    roofline figure is the weight bytes (what a decode-sized batch has to stream) over the time.  Each projection is
+    also timed alone against a ready image.  `prompt` is attn_qkv over 4096 tokens (tensor-core bound).  The CPU
+    figure is the engine's integer path on one host thread over a sample of the output rows."""
     import torch
     from ornithology_b200 import device as D
     from oracle import oracle as O
     orc = O.Oracle()
-    shapes = [("attn_qkv", 2048, 8192), ("attn_gate", 2048, 4096), ("ssm_alpha", 2048, 32), ("ssm_beta", 2048, 32),
-              ("ssm_out", 4096, 2048), ("attn_q", 2048, 8192), ("attn_k", 2048, 512), ("attn_v", 2048, 512),
-              ("attn_output", 4096, 2048)]
+    Q8, Q6 = D.GGML_Q8_0, D.GGML_Q6_K
+    # (name, weight type, n_in, n_out, input): inputs "h" = the layer's normalised hidden state, "o" = the core's output
+    layers = {"delta_net": [("attn_qkv", Q8, 2048, 8192, "h"), ("attn_gate", Q8, 2048, 4096, "h"), ("ssm_alpha", Q8, 2048, 32, "h"),
+                            ("ssm_beta", Q8, 2048, 32, "h"), ("ssm_out", Q8, 4096, 2048, "o")],
+              "full_attn": [("attn_q", Q6, 2048, 8192, "h"), ("attn_k", Q6, 2048, 512, "h"), ("attn_v", Q6, 2048, 512, "h"),
+                            ("attn_output", Q6, 4096, 2048, "o")]}
     g = np.random.default_rng(8)
     peak, src = measured_peaks()
-    res, tot_bytes, tot_ms = {}, 0.0, 0.0
     copies = 16
-    for name, n_in, n_out in shapes:
-        rows = np.stack([orc.q8_0_encode(r) for r in (g.standard_normal((min(n_out, 64), n_in)) * 0.04).astype(np.float32)])
-        W = np.tile(rows, (n_out // rows.shape[0], 1))                 # the timing does not depend on the values
-        ws = [D.Q8_0Weight(np.roll(W, c, axis=0), n_in, device=dev) for c in range(copies)]
-        x = torch.from_numpy(g.standard_normal((n_tok, n_in)).astype(np.float32)).to(dev).to(torch.bfloat16)
-        out = torch.empty(n_tok, n_out, dtype=torch.bfloat16, device=dev)
 
-        def loop():
-            for w in ws:
-                D.matmul_q8_0(w, x, out=out)
+    def rows(wt, n_out, n_in):                         # random block bytes with finite scales: the timing does not depend on the values
+        rb = O.QROW_BYTES[wt](n_in)
+        W = g.integers(0, 256, (n_out, rb), dtype=np.uint8)
+        if wt == Q8:
+            W.reshape(n_out, -1, 34)[:, :, 1] &= 0x3B
+        else:
+            W.reshape(n_out, -1, 210)[:, :, 209] &= 0x3B
+        return W
+
+    def graph_ms(fn):
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             for _ in range(2):
-                loop()
+                fn()
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
-        graph = torch.cuda.CUDAGraph()                 # the 32 launches of a pass replayed as one graph: the timing
-        with torch.cuda.graph(graph, stream=side):     # is then the kernels', not the Python call overhead
-            loop()
-        ms = _timed(graph.replay, dev, 1, 3) / copies
-        nbytes = float(n_out) * (n_in // 32 * 34)
-        res[name] = {"n_in": n_in, "n_out": n_out, "us": ms * 1e3, "weight_bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
-                     "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
-        tot_bytes += nbytes; tot_ms += ms
-        if cpu and name == "attn_qkv":
-            sample = 256
-            t0 = time.perf_counter()
-            orc.matmul_q8_0(W[:sample], n_in, x.float().cpu().numpy())
-            dt = time.perf_counter() - t0
-            res["cpu"] = {"kind": "port", "cores": 1, "shape": name, "ms": dt * 1e3 * n_out / sample,
-                          "sample": f"{sample} of the {n_out} output rows, {n_tok} tokens, scaled by rows"}
-        del ws
-    return {"workload": f"Q8_0 x Q8_K projections of one delta-net and one full-attention layer, {n_tok} tokens, bf16",
-            "per_projection": res, "total_us": tot_ms * 1e3, "total_weight_bytes": tot_bytes,
-            "roofline": {"bound": "hbm", "kernel": "k_matmul_q8_0", "achieved": tot_bytes / (tot_ms * 1e-3) / 1e9, "peak": peak,
-                         "unit": "GB/s", "frac": tot_bytes / (tot_ms * 1e-3) / 1e9 / peak, "peak_source": f"of {src}"},
-            "note": "a decode-sized batch: each projection is a few microseconds of weight traffic, so launch latency "
-                    "(two kernels per projection) is a large part of the small ones"}
+        graph = torch.cuda.CUDAGraph()                 # the launches of a pass replayed as one graph: the timing is
+        with torch.cuda.graph(graph, stream=side):     # then the kernels', not the Python call overhead
+            fn()
+        return _timed(graph.replay, dev, 1, 3) / copies
+
+    res, per, tot_bytes, tot_ms, launches = {}, {}, 0.0, 0.0, 0
+    W_cpu = None
+    for lname, projs in layers.items():
+        xs = {"h": torch.from_numpy(g.standard_normal((n_tok, 2048)).astype(np.float32)).to(dev).to(torch.bfloat16),
+              "o": torch.from_numpy(g.standard_normal((n_tok, 4096)).astype(np.float32)).to(dev).to(torch.bfloat16)}
+        imgs = {k: D.q8k_image(v, v.shape[1]) for k, v in xs.items()}
+        sets, outs, nbytes = [], {}, 0.0
+        for c in range(copies):
+            ws = {}
+            for name, wt, n_in, n_out, _ in projs:
+                W = rows(wt, n_out, n_in)
+                if name == "attn_qkv" and c == 0:
+                    W_cpu = W
+                ws[name] = D.QWeight(wt, W, n_in, device=dev)
+            sets.append(ws)
+        for name, wt, n_in, n_out, _ in projs:
+            outs[name] = torch.empty(n_tok, n_out, dtype=torch.bfloat16, device=dev)
+            nbytes += float(n_out) * O.QROW_BYTES[wt](n_in)
+
+        def layer_pass():
+            for ws in sets:
+                done = set()
+                for name, wt, n_in, n_out, src_in in projs:
+                    if src_in not in done:             # one quantisation per distinct input
+                        D.q8k_image(xs[src_in], n_in, image=imgs[src_in]); done.add(src_in)
+                    D.matmul_q(ws[name], None, out=outs[name], image=imgs[src_in], T=n_tok)
+        ms = graph_ms(layer_pass)
+        res[lname] = {"us": ms * 1e3, "weight_bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak,
+                      "launches": len(projs) + 2}
+        tot_bytes += nbytes; tot_ms += ms; launches += len(projs) + 2
+        for name, wt, n_in, n_out, src_in in projs:
+            def one():
+                for ws in sets:
+                    D.matmul_q(ws[name], None, out=outs[name], image=imgs[src_in], T=n_tok)
+            m1 = graph_ms(one)
+            b1 = float(n_out) * O.QROW_BYTES[wt](n_in)
+            per[name] = {"type": {Q8: "q8_0", Q6: "q6_k"}[wt], "n_in": n_in, "n_out": n_out, "us": m1 * 1e3, "gbs": b1 / (m1 * 1e-3) / 1e9,
+                         "frac": b1 / (m1 * 1e-3) / 1e9 / peak}
+        del sets
+    # a prompt-sized batch of the largest projection
+    Tp = 4096
+    wp = [D.QWeight(Q8, rows(Q8, 8192, 2048), 2048, device=dev) for _ in range(copies)]
+    xp = torch.from_numpy(g.standard_normal((Tp, 2048)).astype(np.float32)).to(dev).to(torch.bfloat16)
+    ip = D.q8k_image(xp, 2048)
+    op = torch.empty(Tp, 8192, dtype=torch.bfloat16, device=dev)
+
+    def prompt_pass():
+        for w in wp:
+            D.q8k_image(xp, 2048, image=ip)
+            D.matmul_q(w, None, out=op, image=ip, T=Tp)
+    mp = graph_ms(prompt_pass)
+    prompt = {"shape": "attn_qkv 2048 -> 8192, q8_0", "tokens": Tp, "us": mp * 1e3, "tops": 2.0 * Tp * 2048 * 8192 / (mp * 1e-3) / 1e12,
+              "note": "int8 mma.sync with int32 sums (exact); integer multiply-adds per sub-block scale share the issue slots"}
+    out = {"workload": f"integer-path projections of one delta-net layer (Q8_0) and one full-attention layer (Q6_K), {n_tok} tokens, bf16",
+           "per_layer": res, "per_projection": per, "prompt": prompt, "total_us": tot_ms * 1e3, "total_weight_bytes": tot_bytes,
+           "launches": launches,
+           "roofline": {"bound": "hbm", "kernel": "k_matmul_kq", "achieved": tot_bytes / (tot_ms * 1e-3) / 1e9, "peak": peak,
+                        "unit": "GB/s", "frac": tot_bytes / (tot_ms * 1e-3) / 1e9 / peak, "peak_source": f"of {src}"},
+           "note": "a decode-sized batch: each projection is a few microseconds of weight traffic, so launch latency is a "
+                   "large part of the small ones; results are the engine's bit for bit"}
+    if cpu:
+        sample = 256
+        x = xs["h"].float().cpu().numpy()
+        t0 = time.perf_counter()
+        orc.matmul_q(Q8, W_cpu[:sample], 2048, x)
+        dt = time.perf_counter() - t0
+        out["cpu"] = {"kind": "port", "cores": 1, "shape": "attn_qkv", "ms": dt * 1e3 * 8192 / sample,
+                      "sample": f"{sample} of the 8192 output rows, {n_tok} tokens, scaled by rows"}
+    return out
 
 
 def cpu_single_layer():

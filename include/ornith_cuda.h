@@ -445,6 +445,16 @@ size_t ornith_cuda_matmul_q_scratch(int wtype, int T, int n_in);
 ornith_status ornith_cuda_matmul_q(int wtype, const void *W, int n_in, int n_out, const void *x,
                                    int act_dtype, int T, void *y, int out_dtype, void *scratch,
                                    size_t scratch_bytes, void *stream);
+/* The two halves of ornith_cuda_matmul_q, for projections that share an input (attn_qkv, attn_gate,
+ * ssm_alpha and ssm_beta all read the layer's normalised hidden state; the engine quantises it once,
+ * reference: src/ornith_rforward.c:165-170): quantise x [T][n_in] into an image of
+ * ornith_cuda_matmul_q_scratch bytes once, then any number of products against it.  The product starts
+ * its weight copies before the kernel launched in front of it on the stream has finished (it waits
+ * for that kernel only before it reads the image), so that kernel must not be one that writes W. */
+ornith_status ornith_cuda_q8k_image(const void *x, int act_dtype, int T, int n_in, void *image,
+                                    size_t image_bytes, void *stream);
+ornith_status ornith_cuda_matmul_q_image(int wtype, const void *W, int n_in, int n_out,
+                                         const void *image, int T, void *y, int out_dtype, void *stream);
 
 /* ---- host-fed layer calls over device-resident state -------------------------
  * For an engine whose projections still run on the host: one object holds the state of all

@@ -117,6 +117,8 @@ SYMBOLS = {
     "ornith_cuda_matmul_q8_0": (_I, [vp, _I, _I, vp, _I, _I, vp, _I, vp, _SZ, vp]),
     "ornith_cuda_matmul_q_scratch": (_SZ, [_I, _I, _I]),
     "ornith_cuda_matmul_q": (_I, [_I, vp, _I, _I, vp, _I, _I, vp, _I, vp, _SZ, vp]),
+    "ornith_cuda_q8k_image": (_I, [vp, _I, _I, _I, vp, _SZ, vp]),
+    "ornith_cuda_matmul_q_image": (_I, [_I, vp, _I, _I, vp, _I, vp, _I, vp]),
     "ornith_cuda_engine_new": (vp, [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _I]),
     "ornith_cuda_engine_free": (None, [vp]),
     "ornith_cuda_engine_full_layer": (_I, [vp, _I, vp, vp]),

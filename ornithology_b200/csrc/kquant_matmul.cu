@@ -469,6 +469,10 @@ ornith_status launch_tc(const void *W, int n_in, int n_out, int T, KqArgs a, cud
     int nstage = (SMEM_BUDGET - 128 - terms) / a.stage_bytes;
     if (nstage > MAX_STAGES) nstage = MAX_STAGES;
     if (nstage > a.nseg) nstage = a.nseg;
+    if (nstage < KS && nstage < a.nseg) {         // a round reads KS stages at once
+        orn_record_error("matmul_q: %d stages of %d bytes do not hold a round of %d super-blocks", nstage, a.stage_bytes, KS);
+        return (ornith_status)ORNITH_ERR_BACKEND;
+    }
     a.nstage = nstage;
     const int smem = nstage * a.stage_bytes + terms + 128;
     static bool opted[ORN_MAX_DEVICES] = {};
@@ -505,11 +509,12 @@ ornith_status launch_kq(const void *W, int n_in, int n_out, int T, KqArgs a, boo
         k_matmul_kq_plain<TYPE><<<dim3((unsigned)((n_out + 127) / 128), (unsigned)T), 128, 0, stream>>>((const unsigned char *)W, a);
         return orn_check_launch("k_matmul_kq_plain");
     }
-    if (T > 64) {                                 // prompts: passes of 128 tokens
-        const long passes = (T + 127) / 128;
-        if ((n_out + 63) / 64 * passes >= 100) return launch_tc<TYPE, 4, 1, 4>(W, n_in, n_out, T, a, stream);
-        if ((n_out + 31) / 32 * passes >= 100) return launch_tc<TYPE, 2, 2, 4>(W, n_in, n_out, T, a, stream);
-        return launch_tc<TYPE, 1, 4, 4>(W, n_in, n_out, T, a, stream);
+    if (T > 64) {                                 // prompts: passes of 128 tokens; of 64 with fewer rows per CTA for a small matrix
+        const long p128 = (T + 127) / 128, p64 = (T + 63) / 64;
+        if ((n_out + 63) / 64 * p128 >= 100) return launch_tc<TYPE, 4, 1, 4>(W, n_in, n_out, T, a, stream);
+        if ((n_out + 63) / 64 * p64 >= 100) return launch_tc<TYPE, 4, 1, 2>(W, n_in, n_out, T, a, stream);
+        if ((n_out + 31) / 32 * p64 >= 100) return launch_tc<TYPE, 2, 2, 2>(W, n_in, n_out, T, a, stream);
+        return launch_tc<TYPE, 1, 4, 2>(W, n_in, n_out, T, a, stream);
     }
     if (n_out >= 64 * 100) return launch_wr<TYPE, 4>(W, n_in, n_out, T, a, stream);
     if (n_out >= 32 * 100) return launch_wr<TYPE, 2>(W, n_in, n_out, T, a, stream);
@@ -523,32 +528,52 @@ extern "C" {
 size_t ornith_cuda_matmul_q_scratch(int wtype, int T, int n_in) {
     if (T <= 0 || n_in <= 0 || n_in % QK) return 0;
     if (wtype != ORNITH_GGML_Q4_K && wtype != ORNITH_GGML_Q6_K && wtype != ORNITH_GGML_Q8_0) return 0;
-    return orn_q8k_image_bytes(T, n_in);
+    return orn_q8k_image_bytes(T, n_in);       // the same for the three types: the image of the activations
 }
 
-ornith_status ornith_cuda_matmul_q(int wtype, const void *W, int n_in, int n_out, const void *x, int act_dtype, int T,
-                                   void *y, int out_dtype, void *scratch, size_t scratch_bytes, void *stream) {
+static bool kq_type_ok(int wtype) { return wtype == ORNITH_GGML_Q4_K || wtype == ORNITH_GGML_Q6_K || wtype == ORNITH_GGML_Q8_0; }
+
+ornith_status ornith_cuda_q8k_image(const void *x, int act_dtype, int T, int n_in, void *image, size_t image_bytes, void *stream) {
     ORN_TRY(orn_require_device());
-    if (wtype != ORNITH_GGML_Q4_K && wtype != ORNITH_GGML_Q6_K && wtype != ORNITH_GGML_Q8_0) {
+    if (n_in <= 0 || n_in % QK) { orn_record_error("q8k_image: the row length must be a multiple of 256 (got %d)", n_in); return ORNITH_ERR_FORMAT; }
+    if (T <= 0) return ORNITH_OK;
+    if (!image || image_bytes < orn_q8k_image_bytes(T, n_in) || ((uintptr_t)image & 255) != 0) {
+        orn_record_error("q8k_image: image buffer too small or not 256-byte aligned");
+        return ORNITH_ERR_FORMAT;
+    }
+    return orn_q8k_quantize_image(x, act_dtype, T, n_in, image, (cudaStream_t)stream);
+}
+
+ornith_status ornith_cuda_matmul_q_image(int wtype, const void *W, int n_in, int n_out, const void *image, int T, void *y,
+                                         int out_dtype, void *stream) {
+    ORN_TRY(orn_require_device());
+    if (!kq_type_ok(wtype)) {
         orn_record_error("matmul_q: no integer path for weight type %d (Q8_0 = 8, Q4_K = 12, Q6_K = 14)", wtype);
         return ORNITH_ERR_UNSUPPORTED;
     }
     if (n_in <= 0 || n_in % QK) { orn_record_error("matmul_q: the row length must be a multiple of 256 (got %d)", n_in); return ORNITH_ERR_FORMAT; }
     if (T <= 0 || n_out <= 0) return ORNITH_OK;
-    if (!scratch || scratch_bytes < ornith_cuda_matmul_q_scratch(wtype, T, n_in) || ((uintptr_t)scratch & 255) != 0) {
-        orn_record_error("matmul_q: scratch too small or not 256-byte aligned");
-        return ORNITH_ERR_FORMAT;
-    }
-    cudaStream_t s = (cudaStream_t)stream;
-    ORN_TRY(orn_q8k_quantize_image(x, act_dtype, T, n_in, scratch, s));
+    if (!image || ((uintptr_t)image & 255) != 0) { orn_record_error("matmul_q: the activation image must be 256-byte aligned"); return ORNITH_ERR_FORMAT; }
     KqArgs a;
-    a.img = (const unsigned char *)scratch;
+    a.img = (const unsigned char *)image;
     a.y = y; a.T = T; a.n_out = n_out; a.nseg = n_in / QK; a.out_dtype = out_dtype; a.nstage = 0; a.stage_bytes = 0; a.status = orn_status_word();
     const char *e = getenv("ORNITH_CUDA_PROJ_PLAIN");                 // =1: the plain kernel for every shape
     const bool plain = e && e[0] == '1';
+    cudaStream_t s = (cudaStream_t)stream;
     if (wtype == ORNITH_GGML_Q4_K) return launch_kq<T_Q4K>(W, n_in, n_out, T, a, plain, s);
     if (wtype == ORNITH_GGML_Q6_K) return launch_kq<T_Q6K>(W, n_in, n_out, T, a, plain, s);
     return launch_kq<T_Q80>(W, n_in, n_out, T, a, plain, s);
+}
+
+ornith_status ornith_cuda_matmul_q(int wtype, const void *W, int n_in, int n_out, const void *x, int act_dtype, int T,
+                                   void *y, int out_dtype, void *scratch, size_t scratch_bytes, void *stream) {
+    if (!kq_type_ok(wtype)) {
+        orn_record_error("matmul_q: no integer path for weight type %d (Q8_0 = 8, Q4_K = 12, Q6_K = 14)", wtype);
+        return ORNITH_ERR_UNSUPPORTED;
+    }
+    if (T <= 0 || n_out <= 0) return ORNITH_OK;
+    ORN_TRY(ornith_cuda_q8k_image(x, act_dtype, T, n_in, scratch, scratch_bytes, stream));
+    return ornith_cuda_matmul_q_image(wtype, W, n_in, n_out, scratch, T, y, out_dtype, stream);
 }
 
 }  // extern "C"

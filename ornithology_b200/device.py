@@ -181,9 +181,27 @@ class QWeight:
         return self._scratch
 
 
-def matmul_q(w: QWeight, x, out=None):
-    """y [T][n_out] = x [T][n_in] through quantised weight rows: the engine's integer path, bit for bit."""
+def q8k_image(x, n_in, image=None):
+    """x [T][n_in] -> the Q8_K image the integer products read; one image serves every projection of the same input."""
     lib = _lib.load()
+    T = x.numel() // n_in
+    need = lib.ornith_cuda_matmul_q_scratch(GGML_Q8_0, T, n_in)
+    if image is None or image.numel() < need:
+        image = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(lib.ornith_cuda_q8k_image(_ptr(x), _act(x), T, n_in, _ptr(image), image.numel(), _stream()), "q8k_image")
+    return image
+
+
+def matmul_q(w: QWeight, x, out=None, image=None, T=None, out_dtype=None):
+    """y [T][n_out] = x [T][n_in] through quantised weight rows: the engine's integer path, bit for bit.
+    With image= (from q8k_image) and T=, x is not read again."""
+    lib = _lib.load()
+    if image is not None:
+        if out is None:
+            out = torch.empty(T, w.n_out, dtype=out_dtype or torch.float32, device=image.device)
+        check(lib.ornith_cuda_matmul_q_image(w.wtype, _ptr(w.bytes), w.n_in, w.n_out, _ptr(image), int(T), _ptr(out), _act(out),
+                                             _stream()), "matmul_q_image")
+        return out
     T = x.numel() // w.n_in
     if out is None:
         out = torch.empty(T, w.n_out, dtype=x.dtype, device=x.device)

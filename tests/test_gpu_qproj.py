@@ -123,6 +123,21 @@ def test_integer_projection_is_bit_exact(oracle, monkeypatch, wtype, T, n_in, n_
             assert (plain.view(np.uint32) == ref.view(np.uint32)).all(), "plain kernel"
 
 
+def test_projections_sharing_one_image(oracle):
+    """One quantisation of the input, three products against it (what the engine does for attn_qkv / attn_gate /
+    ssm_alpha of a layer): each equals the integer path bit for bit."""
+    import torch
+    from oracle import oracle as O
+    from ornithology_b200 import device as D
+    T, n_in = 7, 2048
+    X = _acts(3, T, n_in)
+    img = D.q8k_image(torch.from_numpy(X).cuda(), n_in)
+    for wt, n_out in ((O.GGML_Q8_0, 8192), (O.GGML_Q6_K, 4096), (O.GGML_Q4_K, 96)):
+        W = _random_rows(wt + n_out, wt, n_out, n_in)
+        got = D.matmul_q(D.QWeight(wt, W, n_in), None, image=img, T=T).cpu().numpy()
+        assert (got.view(np.uint32) == oracle.matmul_q(wt, W, n_in, X).view(np.uint32)).all(), (wt, n_out)
+
+
 def test_integer_projection_golden(golden):
     """Weights from the reference's encoder and outputs from the reference's integer dot (tests/golden/make_golden.py)."""
     import torch
