@@ -337,7 +337,12 @@ size_t ornith_cuda_linear_attn_prefill_scratch(const ornith_cuda_linear_layer *l
  *   memory for the whole prompt) whatever `chunk` says.  When the batch has too few
  *   (sequence, value head) units to fill the GPU the prompt is cut into runs of chunks that are
  *   scanned side by side and stitched by their transition matrices; ORNITH_CUDA_DELTA_SEGMENTS=n
- *   forces n runs (1 = off).  ORNITH_CUDA_DELTA_SCAN=mma selects the older mma.sync scan
+ *   forces n runs (1 = off).  Long prompts with one wave of heads or less are cut into slabs:
+ *   conv and chunk preparation of the next slab run on `stream` while the current slab is
+ *   scanned on an internal second stream of the device; `stream` waits for the last scan before
+ *   the call returns, so the caller sees ordinary stream order (and may capture the call into a
+ *   graph).  Results do not depend on the slab count (ORNITH_CUDA_DELTA_SLABS=n, 1 = off).
+ *   ORNITH_CUDA_DELTA_SCAN=mma selects the older mma.sync scan
  *   (32-token chunks); ORNITH_CUDA_PREFILL_FP32=1 keeps every product in fp32 on the CUDA cores
  *   (chunk >= 32 / < 32 selects 32 / 16 tokens). */
 ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *layer,

@@ -372,7 +372,10 @@ __device__ __forceinline__ float silu_sel(float x) { return FAST ? silu_fast(x) 
 // conv_k = 4, Cc a multiple of 4: one thread owns 4 adjacent channels over CONV4_TOK
 // tokens and requests all its inputs before the first use.  Same products, sums and
 // rounding as k_conv_silu_prefill.  grid (ceil(Cc/512), ceil(T/CONV4_TOK), n_seq).
-constexpr int CONV4_TOK = 8;                  // 8 tokens (+ 3 of history) per thread: ~80 registers, 24 warps per SM; 16 tokens took 128
+#ifndef ORN_CONV4_TOK
+#define ORN_CONV4_TOK 8
+#endif
+constexpr int CONV4_TOK = ORN_CONV4_TOK;      // 8 tokens (+ 3 of history) per thread: ~80 registers, 24 warps per SM; 16 tokens took 128
                                               // registers (16 warps per SM) and the kernel waited on its loads (200 us per 8192 tokens x 12288 channels)
 
 // nearest tf32 value (ties away from zero, finite inputs), in integer arithmetic
@@ -409,8 +412,10 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y,
     for (int i = 0; i < CONV4_TOK; i++) {
         if (t0 + i >= t_end) break;
         float4 y;
+        // the tensor-core paths (FAST) round q, k to tf32 and take a hardware-exponential SiLU anyway: fused multiply-adds
 #define ORN_CONV4(F, WC, B)                                                                               \
-        y.F = silu_sel<FAST>(__fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(B, __fmul_rn(WC.x, x[i].F)),                 \
+        y.F = FAST ? silu_fast(fmaf(WC.w, x[i + 3].F, fmaf(WC.z, x[i + 2].F, fmaf(WC.y, x[i + 1].F, fmaf(WC.x, x[i].F, B)))))  \
+                   : silu_f(__fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(B, __fmul_rn(WC.x, x[i].F)),                  \
                                                              __fmul_rn(WC.y, x[i + 1].F)),                \
                                                    __fmul_rn(WC.z, x[i + 2].F)),                          \
                                          __fmul_rn(WC.w, x[i + 3].F)))
@@ -424,12 +429,11 @@ __global__ void __launch_bounds__(128) k_conv4_silu_prefill(LinArgs a, float *Y,
     }
     if (NORMS && ch < 2 * qd) {                           // warp-uniform: a warp covers 128 channels = one head
         const int lane = threadIdx.x & 31;
-        // sums over the 32 lanes for 8 tokens: token t ends up in lanes t, t + 8, t + 16, t + 24
+        // sums over the 32 lanes for CONV4_TOK tokens: token t ends up in the lanes that are t modulo CONV4_TOK
 #pragma unroll
-        for (int i = 0; i < CONV4_TOK; i++) {
-            ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], 16);
-            ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], 8);
-        }
+        for (int i = 0; i < CONV4_TOK; i++)
+#pragma unroll
+            for (int off = 16; off >= CONV4_TOK; off >>= 1) ss[i] += __shfl_xor_sync(0xffffffffu, ss[i], off);
 #pragma unroll
         for (int off = CONV4_TOK / 2; off >= 1; off >>= 1) {
             const bool up = (lane & off) != 0;
