@@ -195,6 +195,24 @@ def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b", slab=8192, shar
     wait_status = int(_lib.load().ornith_cuda_poll_status())       # non-zero: a bounded wait inside a kernel gave up
     tf_full = fl_full / (ms_full_k * 1e-3) / 1e12
     tf_lin = fl_lin / (ms_lin_k * 1e-3) / 1e12
+    sustained_leg = None
+    if world == 1 and rank == 0:
+        # the GQA layer back to back for about a second, clocks sampled: the figure to set against the sustained
+        # (power-capped) tensor peak, which is how a long prompt's 15 such layers actually run
+        n = max(3, min(200, int(1000.0 / max(ms_full_k, 0.05))))
+        sampler = ClockSampler(dev.index if dev.index is not None else 0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            full_whole()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        clk = sampler.stop()
+        ms_sus = e0.elapsed_time(e1) / n
+        tf_sus = fl_full / (ms_sus * 1e-3) / 1e12
+        sustained_leg = {"calls": n, "ms": ms_sus, "tflops": tf_sus, "peak": sustained, "frac": tf_sus / sustained,
+                         "peak_source": f"of {src} (bf16 sustained)", "clocks": clk}
     return {"workload": "%d-token prompt, %s-shaped layers, batch 1, bf16, head-sharded x%d%s"
                         % (T, shape.upper(), sw, "" if world > 1 or sw == 1 else " (one shard timed on one GPU, no gather)"),
             "tokens": T, "delta_net_ms_per_layer": ms_lin, "gqa_ms_per_layer": ms_full, "wait_status_rank0": wait_status,
@@ -209,6 +227,7 @@ def run_prefill(dev, rank, world, T=32768, reps=3, shape="397b", slab=8192, shar
                                    "achieved": tf_lin, "peak": burst * world, "unit": "TFLOP/s",
                                    "frac": tf_lin / (burst * world), "flop_per_layer": fl_lin, "ms": ms_lin_k,
                                    "note": "tf32 products run at half the bf16 rate; a sequential scan: chunks x chain latency bound it, not the pipe"},
+            "gqa_sustained": sustained_leg,
             "tensor_peak_tflops": burst * world, "tensor_peak_sustained_tflops": sustained * world,
             "gqa_frac_of_tensor_peak": tf_full / (burst * world), "peak_source": f"of {src}"}
 

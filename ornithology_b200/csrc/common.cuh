@@ -73,6 +73,20 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : lo
 // prefill paths, whose products are already rounded to tf32 / f16
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
+// Launch `kernel` as a programmatic dependent of the kernel in front of it on the stream: its CTAs may become resident
+// while that kernel still runs.  The kernel must execute griddepcontrol.wait in every CTA before it touches anything a
+// kernel in front of it may write or read, and before it exits.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t orn_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- reductions ---------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -43,7 +43,10 @@ __global__ void __launch_bounds__(128) k_full_prep(PrepArgs a) {
     __shared__ double redd[32];
     __shared__ float redf[32];
     const int hd = a.kv.hd, nkv = a.kv.nkv, nh = a.nh;
-    // a decode kernel launched behind this one may begin its prologue now; it waits for this grid before it reads its output
+    // Launched as a programmatic dependent of the kernel in front of it (the layer before): resident when that kernel
+    // ends, and waiting for its end before anything else.  After that a decode kernel launched behind this one may
+    // begin its prologue (it streams cache rows early, and waits for this grid before it reads its output).
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     if (a.group_ctr)
         for (int i = (blockIdx.y * gridDim.x + blockIdx.x) * 128 + threadIdx.x; i < a.n_ctr; i += gridDim.x * gridDim.y * 128)
@@ -582,8 +585,7 @@ static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_c
         return orn_check_launch("k_full_prep_warp");
     }
     dim3 grid(n_tok, rows_per_tok);
-    k_full_prep<ACT><<<grid, 128, l->head_dim * sizeof(float), st>>>(a);
-    return orn_check_launch("k_full_prep");
+    return orn_check(orn_launch_dependent(k_full_prep<ACT>, grid, dim3(128), l->head_dim * sizeof(float), st, a), "k_full_prep");
 }
 
 extern "C" {

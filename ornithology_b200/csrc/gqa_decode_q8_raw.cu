@@ -239,6 +239,8 @@ __global__ void __launch_bounds__(128, 4) k_gqa_decode_q8_raw(DecodeArgs a, cons
     __shared__ __align__(8) unsigned long long bars[NWARP][2];
     __shared__ int pipe_failed, last_one, scan_s[NWARP], found_s[2];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // the next layer's front-end kernel may become resident now; it waits for this grid before it does anything
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     unsigned char *wbase = smem + QS_BYTES + warp * WARP_BYTES;
     uint2 *Q_s = reinterpret_cast<uint2 *>(smem);               // [k-step][lane]
     if (tid == 0) pipe_failed = 0;

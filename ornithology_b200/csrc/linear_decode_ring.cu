@@ -47,7 +47,11 @@ __host__ __device__ inline size_t front_stride(int nk, int nv) { return (size_t)
 template <typename ACT>
 __global__ void __launch_bounds__(128) k_linear_decode_front(LinArgs a, float *front) {
     __shared__ double redd[8];
-    // the state kernel may start its prologue (it waits for this grid before it reads the blocks)
+    // This grid is launched as a programmatic dependent of the kernel in front of it (the layer before): its CTAs are
+    // resident when that kernel ends, and await its end before anything else.  Only then may the state kernel of this
+    // call start its prologue (it reads the recurrent state early, which the same layer's previous step may still be
+    // writing until this wait returns); it waits for this grid before it reads the blocks.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, b = blockIdx.y, j = blockIdx.x;
     const int qd = a.nk * 128, vd = a.nv * 128, Cc = 2 * qd + vd;
@@ -100,6 +104,8 @@ __global__ void __launch_bounds__(128) k_linear_decode_front(LinArgs a, float *f
 
 template <typename ACT>
 __global__ void __launch_bounds__(256, 2) k_linear_decode_ring(LinArgs a, const float *front, int n_units) {
+    // the next call's front-end kernel may become resident now; it waits for this grid before it does anything
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     extern __shared__ __align__(128) unsigned char smraw[];
     float *stage = reinterpret_cast<float *>(smraw);
     float *opnd = stage + STAGES * STAGE_FLOATS;       // per stage: the front-end blocks of the unit whose first half it holds
@@ -301,8 +307,8 @@ ornith_status launch_ring(const LinArgs &x, int n_seq, cudaStream_t s) {
     float *front = nullptr;
     ORN_TRY(front_blocks(s, (size_t)n_seq * front_stride(x.nk, x.nv) * sizeof(float), &front));
     const int n_units = n_seq * x.nv;
-    k_linear_decode_front<ACT><<<dim3(x.nk + (x.nv + 1) / 2, n_seq), 128, 0, s>>>(x, front);
-    ornith_status st = orn_check_launch("k_linear_decode_front");
+    ornith_status st = orn_check(orn_launch_dependent(k_linear_decode_front<ACT>, dim3(x.nk + (x.nv + 1) / 2, n_seq), dim3(128), 0, s, x, front),
+                                 "k_linear_decode_front");
     if (st == ORNITH_OK) {
         const int grid = n_units < 2 * n_sm ? n_units : 2 * n_sm;
         cudaLaunchConfig_t cfg = {};
