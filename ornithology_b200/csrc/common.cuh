@@ -71,7 +71,10 @@ __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 // SiLU with the hardware exponential and reciprocal (a few ulp); for the tensor-core
 // prefill paths, whose products are already rounded to tf32 / f16
-__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+// (the .ftz forms: without them the compiler wraps each special-function instruction in a denormal fix-up)
+__device__ __forceinline__ float ex2_fast(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float rcp_fast(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float silu_fast(float x) { return x * rcp_fast(1.0f + ex2_fast(-1.4426950408889634f * x)); }
 
 // Launch `kernel` as a programmatic dependent of the kernel in front of it on the stream: its CTAs may become resident
 // while that kernel still runs.  The kernel must execute griddepcontrol.wait in every CTA before it touches anything a

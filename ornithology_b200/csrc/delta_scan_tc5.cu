@@ -52,6 +52,7 @@ namespace {
 using namespace tc5;
 
 constexpr int C = 64;                                   // tokens per chunk
+constexpr float LOG2E_F = 1.4426950408889634f;
 constexpr int AUX_FLOATS = 5 * C;                       // beta | beta p rk | w rk | p rq | p_63 (first word)
 constexpr uint32_t AUX_BYTES = AUX_FLOATS * 4;
 // A and P are lower triangular.  Stored per block as four dense pieces of 32 columns: A columns 0..31 (64 rows),
@@ -225,7 +226,7 @@ __global__ void __launch_bounds__(256, 2) k_delta_prep64(LinArgs a, const float 
         // thread pt = column l of M and P
 #pragma unroll 4
         for (int i = 0; i < C; i++) {
-            const float gam = (pt <= i) ? __expf(ps.g[i] - gg) : 0.0f;
+            const float gam = (pt <= i) ? ex2_fast((ps.g[i] - gg) * LOG2E_F) : 0.0f;
             const float mv = (pt < i) ? ps.be[i] * gam * sm.GK[i * LDG + pt] : 0.0f;
             if (i < 32) { if (pt < 32) ps.M11[i * LDB + pt] = mv; }
             else if (pt < 32) ps.M21[(i - 32) * LDB + pt] = mv;
