@@ -166,7 +166,8 @@ ornith_status ornith_cuda_selftest_wait_timeout(int polls);
 typedef int (*ornith_cuda_alloc_hook)(size_t bytes, void *user);
 void ornith_cuda_set_alloc_hook(ornith_cuda_alloc_hook hook, void *user);
 /* Frees the work buffer the delta-net decode step keeps for `stream` on the current device (for every
- * stream of the device when all_streams != 0), after waiting for the work queued there.  Call it
+ * stream of the device when all_streams != 0, and then also the second stream and the events the
+ * delta-net prefill keeps per device), after waiting for the work queued there.  Call it
  * before destroying a stream that ran ornith_cuda_linear_attn_step. */
 ornith_status ornith_cuda_stream_release(void *stream, int all_streams);
 /* inverse RoPE frequencies theta^(-2i/rotary_dim), i < rotary_dim/2, computed on

@@ -1050,6 +1050,19 @@ int slab_plan(int heads, int n_chunks, int n_seg) {
 
 }  // namespace
 
+// frees the current device's scan stream and events (the next long prefill makes new ones); the device is idle
+ornith_status release_delta_slab_pipe() {
+    SlabPipe &p = g_slab_pipe[orn_device_index()];
+    std::lock_guard<std::mutex> hold(p.lock);
+    if (!p.scan_stream) return ORNITH_OK;
+    for (int i = 0; i < MAX_SLABS; i++) { if (p.front_done[i]) (void)cudaEventDestroy(p.front_done[i]); p.front_done[i] = nullptr; }
+    if (p.scans_done) (void)cudaEventDestroy(p.scans_done);
+    p.scans_done = nullptr;
+    const cudaError_t e = cudaStreamDestroy(p.scan_stream);
+    p.scan_stream = nullptr;
+    return orn_check(e, "delta scan stream destroy");
+}
+
 ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dtype, const float *Y, const float *rq,
                                         const float *rk, const float *la, const float *be, const TC5Front *front,
                                         float *work, float *dbg, cudaStream_t s) {
@@ -1112,6 +1125,11 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
         return orn_check_launch("k_delta_scan_tc5");
     };
 
+    // two runs per head (30-37 heads) lose to the slab pipeline on a long prompt: 2.41 against 2.07 ms for 32 heads x
+    // 32768 tokens (the finishing pass costs more than the halved chain saves); three runs or more win (16 heads: 1.72
+    // against 1.99 ms)
+    const char *seg_env = getenv("ORNITH_CUDA_DELTA_SEGMENTS");
+    if (front && a.n_seg == 2 && !(seg_env && seg_env[0]) && slab_plan(x.nv * n_seq, n_chunks, 1) >= 2) a.n_seg = 1;
     const int n_slabs = front ? slab_plan(x.nv * n_seq, n_chunks, a.n_seg) : 1;
     if (n_slabs > 1) {
         // front of slab k + 1 on the caller's stream beside the scan of slab k on the scan stream
@@ -1119,20 +1137,23 @@ ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dty
         std::lock_guard<std::mutex> hold(pipe.lock);
         ORN_TRY(slab_pipe_ready(pipe));
         const int per = (n_chunks + n_slabs - 1) / n_slabs;
-        int k = 0;
-        for (int cb = 0; cb < n_chunks; cb += per, k++) {
-            const int cn = min(per, n_chunks - cb);
+        auto slab = [&](int k, int cb, int cn) -> ornith_status {
             ORN_TRY(front->conv(cb * C, min(x.T, (cb + cn) * C), s));
             ORN_TRY(prep(cb, cn, s));
             ORN_TRY(orn_check(cudaEventRecord(pipe.front_done[k], s), "slab event record"));
             ORN_TRY(orn_check(cudaStreamWaitEvent(pipe.scan_stream, pipe.front_done[k], 0), "slab event wait"));
             ScanArgs sa = a;
             sa.c_begin = cb; sa.c_count = cn;
-            ORN_TRY(scan(sa, pipe.scan_stream));
-        }
-        ORN_TRY(front->ring_refresh(s));                      // after the conv that reads the old history
-        ORN_TRY(orn_check(cudaEventRecord(pipe.scans_done, pipe.scan_stream), "slab event record"));
-        return orn_check(cudaStreamWaitEvent(s, pipe.scans_done, 0), "slab event wait");
+            return scan(sa, pipe.scan_stream);
+        };
+        ornith_status st = ORNITH_OK;
+        int k = 0;
+        for (int cb = 0; cb < n_chunks && st == ORNITH_OK; cb += per, k++) st = slab(k, cb, min(per, n_chunks - cb));
+        if (st == ORNITH_OK) st = front->ring_refresh(s);     // after the conv that reads the old history
+        // the caller's stream always rejoins the scan stream, also when a launch failed on the way
+        ornith_status join = orn_check(cudaEventRecord(pipe.scans_done, pipe.scan_stream), "slab event record");
+        if (join == ORNITH_OK) join = orn_check(cudaStreamWaitEvent(s, pipe.scans_done, 0), "slab event wait");
+        return st != ORNITH_OK ? st : join;
     }
     if (front) {
         ORN_TRY(front->conv(0, x.T, s));

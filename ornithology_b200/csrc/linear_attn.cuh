@@ -48,6 +48,7 @@ struct TC5Front {
     std::function<ornith_status(cudaStream_t)> ring_refresh;
 };
 size_t linear_prefill_tc5_work_bytes(int nk, int nv, int n_seq, int T);
+ornith_status release_delta_slab_pipe();
 ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dtype, const float *Y, const float *rq,
                                         const float *rk, const float *la, const float *be, const TC5Front *front,
                                         float *work, float *dbg, cudaStream_t s);

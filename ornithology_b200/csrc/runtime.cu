@@ -153,6 +153,7 @@ __global__ void k_wait_selftest(unsigned int *status, int polls, int *gave_up) {
 }
 
 ornith_status release_linear_decode_buffers(cudaStream_t s, bool all);   // linear_decode_ring.cu
+ornith_status release_delta_slab_pipe();                                  // delta_scan_tc5.cu
 
 extern "C" {
 
@@ -173,6 +174,7 @@ ornith_status ornith_cuda_stream_release(void *stream, int all_streams) {
     ORN_TRY(orn_require_device());
     if (all_streams) ORN_TRY(orn_check(cudaDeviceSynchronize(), "device sync"));
     else ORN_TRY(orn_check(cudaStreamSynchronize(as_stream(stream)), "stream sync"));
+    if (all_streams) ORN_TRY(release_delta_slab_pipe());       // the prefill's second stream and its events (this device)
     return release_linear_decode_buffers(as_stream(stream), all_streams != 0);
 }
 

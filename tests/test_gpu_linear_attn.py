@@ -302,3 +302,8 @@ def test_slab_pipeline_matches_the_single_launch(monkeypatch, T, pos0):
         for a, b in zip(got, single):
             assert (a == b).all(), slabs
     assert np.isfinite(single[0]).all() and np.abs(single[0]).max() > 0
+    # the pipeline's second stream and events can be released and are made again on the next long prefill
+    from ornithology_b200 import _lib
+    assert _lib.load().ornith_cuda_stream_release(None, 1) == 0
+    for a, b in zip(run(None), single):
+        assert (a == b).all()
