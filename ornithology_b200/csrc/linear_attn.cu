@@ -847,7 +847,14 @@ ornith_status ornith_cuda_linear_attn_prefill(const ornith_cuda_linear_layer *l,
         if (tc5) {
             // the tcgen05 path: conv, chunk preparation and scan, slab by slab (see launch_linear_prefill_tc5)
             TC5Front front;
-            front.conv = [=](int t_begin, int t_end, cudaStream_t cs) {
+            const char *plain_conv = getenv("ORNITH_CUDA_CONV_PLAIN");       // =1: the plain-load conv kernel
+            const bool conv_tma = !(plain_conv && plain_conv[0] == '1');
+            front.conv = [=](int t_begin, int t_end, cudaStream_t cs) -> ornith_status {
+                if (conv_tma) {                                              // tensor-copy-fed kernel where the shape allows
+                    bool handled = false;
+                    ORN_TRY(launch_conv4_silu_prefill_tma(x, n_seq, act_dtype, Y, rq, rk, t_begin, t_end, cs, &handled));
+                    if (handled) return ORNITH_OK;
+                }
                 dim3 g((unsigned)((Cc + 511) / 512), (unsigned)((t_end - t_begin + CONV4_TOK - 1) / CONV4_TOK), (unsigned)n_seq);
                 if (bf) k_conv4_silu_prefill<__nv_bfloat16, true, true><<<g, 128, 0, cs>>>(x, Y, rq, rk, t_begin, t_end);
                 else    k_conv4_silu_prefill<float, true, true><<<g, 128, 0, cs>>>(x, Y, rq, rk, t_begin, t_end);

@@ -47,6 +47,9 @@ struct TC5Front {
     std::function<ornith_status(int t_begin, int t_end, cudaStream_t)> conv;
     std::function<ornith_status(cudaStream_t)> ring_refresh;
 };
+// conv_prefill_tma.cu: the conv + SiLU front of that path fed by tensor copies (see there)
+ornith_status launch_conv4_silu_prefill_tma(const LinArgs &x, int n_seq, int act_dtype, float *Y, float *rq, float *rk,
+                                            int t_begin, int t_end, cudaStream_t s, bool *handled);
 size_t linear_prefill_tc5_work_bytes(int nk, int nv, int n_seq, int T);
 ornith_status release_delta_slab_pipe();
 ornith_status launch_linear_prefill_tc5(const LinArgs &x, int n_seq, int act_dtype, const float *Y, const float *rq,

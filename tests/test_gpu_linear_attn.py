@@ -307,3 +307,38 @@ def test_slab_pipeline_matches_the_single_launch(monkeypatch, T, pos0):
     assert _lib.load().ornith_cuda_stream_release(None, 1) == 0
     for a, b in zip(run(None), single):
         assert (a == b).all()
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_tensor_copy_conv_matches_the_plain_conv(monkeypatch, bf16):
+    """The conv + SiLU front of the tensor-core prefill has two forms: plain loads, and tensor copies into shared
+    memory (the default).  Same products in the same order, so layer outputs, state and conv history must be
+    bit-identical: two sequences (the tile rows in front of the second one belong to the first), a ragged length,
+    a first call that starts from an empty history and a second one that continues from the ring."""
+    import torch
+    from ornithology_b200 import device as D
+    layer, kw = linear_case(8, nk=4, nv=8)
+    dl = device_linear(layer, kw)
+    B, T1, T2 = 2, 70, 133
+    dt = torch.bfloat16 if bf16 else torch.float32
+    ins = [linear_inputs(90 + b, layer, T1 + T2, bf16) for b in range(B)]
+    dins = [torch.stack([torch.from_numpy(ins[b][i]) for b in range(B)]).cuda().to(dt) for i in range(4)]
+
+    def run(plain):
+        if plain:
+            monkeypatch.setenv("ORNITH_CUDA_CONV_PLAIN", "1")
+        else:
+            monkeypatch.delenv("ORNITH_CUDA_CONV_PLAIN", raising=False)
+        st = D.LinearState(dl, B)
+        pos = torch.zeros(B, dtype=torch.int32, device="cuda")
+        o1 = D.linear_attn_prefill(dl, st, pos, *[x[:, :T1].contiguous() for x in dins], T1, chunk=64)
+        D.advance(pos, T1)
+        o2 = D.linear_attn_prefill(dl, st, pos, *[x[:, T1:].contiguous() for x in dins], T2, chunk=64)
+        torch.cuda.synchronize()
+        return (o1.float().cpu().numpy(), o2.float().cpu().numpy(), st.S.cpu().numpy(),
+                np.stack([st.conv_image(b, T1 + T2).cpu().numpy() for b in range(B)]))
+
+    got, ref = run(False), run(True)
+    for a, b in zip(got, ref):
+        assert (a == b).all()
+    assert np.isfinite(got[1]).all() and np.abs(got[1]).max() > 0
