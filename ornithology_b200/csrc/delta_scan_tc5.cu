@@ -223,16 +223,27 @@ __global__ void __launch_bounds__(256, 2) k_delta_prep64(LinArgs a, const float 
         ax[2 * C + pt] = expf(gend - gg) * sm.rk[pt];
         ax[3 * C + pt] = pp * sm.rq[pt];
         ax[4 * C + pt] = expf(gend);
-        // thread pt = column l of M and P
-#pragma unroll 4
-        for (int i = 0; i < C; i++) {
-            const float gam = (pt <= i) ? ex2_fast((ps.g[i] - gg) * LOG2E_F) : 0.0f;
-            const float mv = (pt < i) ? ps.be[i] * gam * sm.GK[i * LDG + pt] : 0.0f;
-            if (i < 32) { if (pt < 32) ps.M11[i * LDB + pt] = mv; }
-            else if (pt < 32) ps.M21[(i - 32) * LDB + pt] = mv;
-            else ps.M22[(i - 32) * LDB + pt - 32] = mv;
-            if (pt < 32) Ag[(AP_P0 + i) * 32 + pt] = (pt <= i) ? tf32r(gam * sm.GQ[i * LDG + pt]) : 0.0f;
-            else if (i >= 32) Ag[(AP_P1 + i - 32) * 32 + pt - 32] = (pt <= i) ? tf32r(gam * sm.GQ[i * LDG + pt]) : 0.0f;
+        // thread pt = column l of M and P; rows 0..31 concern the first warp of the pair only (columns 32.. are zero there)
+        if (wl == 0) {
+#pragma unroll 8
+            for (int i = 0; i < 32; i++) {
+                const float gam = (pt <= i) ? ex2_fast((ps.g[i] - gg) * LOG2E_F) : 0.0f;
+                ps.M11[i * LDB + pt] = (pt < i) ? ps.be[i] * gam * sm.GK[i * LDG + pt] : 0.0f;
+                Ag[(AP_P0 + i) * 32 + pt] = (pt <= i) ? tf32r(gam * sm.GQ[i * LDG + pt]) : 0.0f;
+            }
+#pragma unroll 8
+            for (int i = 32; i < C; i++) {                // pt < 32 <= i: below the diagonal throughout
+                const float gam = ex2_fast((ps.g[i] - gg) * LOG2E_F);
+                ps.M21[(i - 32) * LDB + pt] = ps.be[i] * gam * sm.GK[i * LDG + pt];
+                Ag[(AP_P0 + i) * 32 + pt] = tf32r(gam * sm.GQ[i * LDG + pt]);
+            }
+        } else {
+#pragma unroll 8
+            for (int i = 32; i < C; i++) {
+                const float gam = (pt <= i) ? ex2_fast((ps.g[i] - gg) * LOG2E_F) : 0.0f;
+                ps.M22[(i - 32) * LDB + pt - 32] = (pt < i) ? ps.be[i] * gam * sm.GK[i * LDG + pt] : 0.0f;
+                Ag[(AP_P1 + i - 32) * 32 + pt - 32] = (pt <= i) ? tf32r(gam * sm.GQ[i * LDG + pt]) : 0.0f;
+            }
         }
         pair_sync(1 + pr);
         // A = (I + M)^-1 = [[A11, 0], [-A22 M21 A11, A22]]; lane = column.  The two diagonal blocks are inverted by one
