@@ -230,6 +230,159 @@ __global__ void __launch_bounds__(128) k_full_prep_warp(PrepArgs a, long long n_
     }
 }
 
+// head_dim = 256, one warp per row, a lane owns 8 adjacent elements: one 16-byte (bf16) or two (f32) loads per lane
+// instead of eight 2-byte ones, everything but the rotation in registers, and a Q8_0 row leaves as 17 chunks of 16
+// bytes.  Same products and rounding as k_full_prep_warp; the f64 sum of squares adds a lane's 8 squares first.
+__device__ __forceinline__ void ld_row8(const __nv_bfloat16 *src, int lane, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4 *>(src + lane * 8);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+__device__ __forceinline__ void ld_row8(const float *src, int lane, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4 *>(src + lane * 8), b = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+template <typename ACT>
+__global__ void __launch_bounds__(128) k_full_prep_row8(PrepArgs a, long long n_rows, int rows_per_tok) {
+    constexpr int hd = 256;
+    __shared__ __align__(16) float rowbuf[4][hd];          // the rotation's exchange; then the encoded Q8_0 row (272 bytes)
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int nkv = a.kv.nkv, nh = a.nh;
+    if (a.group_ctr)
+        for (long long i = (long long)blockIdx.x * 128 + threadIdx.x; i < a.n_ctr; i += (long long)gridDim.x * 128)
+            a.group_ctr[i] = 0;
+    const long long R = (long long)blockIdx.x * 4 + wid;
+    if (R >= n_rows) return;
+    const int tt = (int)(R / rows_per_tok), j = (int)(R % rows_per_tok) + a.row0, b = tt / a.T, t = tt % a.T;
+    const int64_t base = a.kv.seq_off[b];
+    const int cap = (int)(a.kv.seq_off[b + 1] - base);
+    const int slot = a.kv_len[b] + t;
+    if (slot >= cap) return;                              // full cache: silent no-op
+    const int pos = (a.rope_pos ? a.rope_pos[b] : a.kv_len[b]) + t;
+    float *row = rowbuf[wid];
+
+    int kind, h;
+    const ACT *src;
+    const float *w;
+    if (j < nh) {
+        kind = 0; h = j; w = a.q_norm_w;
+        const size_t per_tok = (size_t)nh * hd * (a.gated ? 2 : 1);
+        src = (const ACT *)a.qproj + (size_t)tt * per_tok + (size_t)h * hd * (a.gated ? 2 : 1);
+    } else if (j < nh + nkv) {
+        kind = 1; h = j - nh; w = a.k_norm_w;
+        src = (const ACT *)a.k + ((size_t)tt * nkv + h) * hd;
+    } else {
+        kind = 2; h = j - nh - nkv; w = nullptr;
+        src = (const ACT *)a.v + ((size_t)tt * nkv + h) * hd;
+    }
+    float v[8];
+    ld_row8(src, lane, v);
+    if (w) {
+        double ss = 0.0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) ss += (double)v[i] * (double)v[i];
+        ss = warp_sum(ss);
+        const float inv = (float)(1.0 / sqrt(ss / (double)hd + (double)a.eps));
+        float wv[8];
+        ld_row8(w, lane, wv);
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __fmul_rn(__fmul_rn(v[i], inv), wv[i]);
+    }
+    if (kind != 2 && a.rope_dim > 0) {                    // pairs (i, i + half) sit in different lanes: through shared memory
+        const int half = a.rope_dim / 2;
+        if (lane * 8 < a.rope_dim) {
+            *reinterpret_cast<float4 *>(row + lane * 8) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4 *>(row + lane * 8 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+        __syncwarp();
+        for (int i = lane; i < half; i += 32) {
+            const float ang = __fmul_rn((float)pos, a.inv_freq[i]);
+            const float c = cosf(ang), sn = sinf(ang);
+            const float lo = row[i], hi = row[i + half];
+            row[i]        = __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, sn));
+            row[i + half] = __fadd_rn(__fmul_rn(lo, sn), __fmul_rn(hi, c));
+        }
+        __syncwarp();
+        if (lane * 8 < a.rope_dim) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = (lane * 8 + i < a.rope_dim) ? row[lane * 8 + i] : v[i];
+        }
+        __syncwarp();
+    }
+    if (kind == 0) {
+        if (a.Qh) {                                       // f16 image for the tensor-core kernel
+            float mx = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+            mx = warp_max(mx);
+            int e = 0;
+            if (mx > 0.0f && mx < INFINITY) (void)frexpf(mx, &e);
+            const float down = exp2f((float)-e);
+            const size_t orow = ((size_t)b * nh + h) * a.T + t;
+            __half2 p0 = __floats2half2_rn(v[0] * down, v[1] * down), p1 = __floats2half2_rn(v[2] * down, v[3] * down);
+            __half2 p2 = __floats2half2_rn(v[4] * down, v[5] * down), p3 = __floats2half2_rn(v[6] * down, v[7] * down);
+            *reinterpret_cast<uint4 *>(a.Qh + orow * hd + lane * 8) =
+                make_uint4(*reinterpret_cast<uint32_t *>(&p0), *reinterpret_cast<uint32_t *>(&p1),
+                           *reinterpret_cast<uint32_t *>(&p2), *reinterpret_cast<uint32_t *>(&p3));
+            if (lane == 0) a.rs[orow] = a.scale * exp2f((float)e) * 1.4426950408889634f;
+            return;
+        }
+        float *dst = a.q_prep + ((size_t)tt * nh + h) * hd + lane * 8;
+        *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        return;
+    }
+    const size_t r = (size_t)(base + slot) * nkv + h;
+    uint8_t *pool = (kind == 1) ? a.kv.K : a.kv.V;
+    if (a.kv.mode == ORNITH_KV_F32) {
+        float *dst = reinterpret_cast<float *>(pool) + r * hd + lane * 8;
+        *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else if (a.kv.mode == ORNITH_KV_Q8_0) {
+        // as encode_row_q8_0: a block of 32 = 4 lanes
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+        uint8_t *enc = reinterpret_cast<uint8_t *>(row);   // 272 bytes of this warp's buffer
+        uint8_t *o = enc + (lane >> 2) * 34;
+        if ((lane & 3) == 0) *reinterpret_cast<unsigned short *>(o) = __half_as_ushort(__float2half_rn(d));
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {                  // code pairs: the block's codes start 2 bytes into it
+            int q0 = (int)roundf(__fmul_rn(v[i], id)), q1 = (int)roundf(__fmul_rn(v[i + 1], id));
+            q0 = max(-127, min(127, q0)); q1 = max(-127, min(127, q1));
+            *reinterpret_cast<unsigned short *>(o + 2 + 8 * (lane & 3) + i) = (unsigned short)((q0 & 255) | ((q1 & 255) << 8));
+        }
+        __syncwarp();
+        if (lane < 17)
+            reinterpret_cast<uint4 *>(pool + r * kv_row_bytes(ORNITH_KV_Q8_0, hd))[lane] = reinterpret_cast<const uint4 *>(enc)[lane];
+    } else {                                              // as encode_row_int8
+        int8_t *codes = reinterpret_cast<int8_t *>(pool) + r * hd;
+        float *sc = ((kind == 1) ? a.kv.Ks : a.kv.Vs) + r;
+        float m = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) m = fmaxf(m, fabsf(v[i]));
+        const float amax = warp_max(m);
+        uint2 packed = make_uint2(0u, 0u);
+        if (amax != 0.0f) {
+            const float inv = __fdiv_rn(127.0f, amax);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int q = max(-127, min(127, __float2int_rn(__fmul_rn(v[i], inv))));
+                if (i < 4) packed.x |= (uint32_t)(q & 255) << (8 * i);
+                else packed.y |= (uint32_t)(q & 255) << (8 * (i - 4));
+            }
+        }
+        *reinterpret_cast<uint2 *>(codes + lane * 8) = packed;
+        if (lane == 0) *sc = amax != 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+    }
+}
+
 // =============================================================================
 // split-K decode, generic in head_dim and group size
 // =============================================================================
@@ -580,6 +733,14 @@ static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_c
     const int rows_per_tok = (kv_only ? 0 : l->n_heads) + 2 * l->n_kv_heads;
     if (n_tok >= 256) {                                   // prefill-sized: one warp per row
         const long long n_rows = (long long)n_tok * rows_per_tok;
+        // head_dim 256 with 16-byte-aligned rows: the vectorised form (rows of a token are multiples of 256 elements apart)
+        const bool aligned = (((uintptr_t)qproj | (uintptr_t)k | (uintptr_t)v | (uintptr_t)kv->K | (uintptr_t)kv->V |
+                               (uintptr_t)l->q_norm_w | (uintptr_t)l->k_norm_w) & 15) == 0 &&
+                             (!Qh || ((uintptr_t)Qh & 15) == 0) && (!q_prep || ((uintptr_t)q_prep & 15) == 0);
+        if (l->head_dim == 256 && aligned && l->rope_dim % 2 == 0 && l->rope_dim <= 256) {
+            k_full_prep_row8<ACT><<<(unsigned)((n_rows + 3) / 4), 128, 0, st>>>(a, n_rows, rows_per_tok);
+            return orn_check_launch("k_full_prep_row8");
+        }
         k_full_prep_warp<ACT><<<(unsigned)((n_rows + 3) / 4), 128, 4 * l->head_dim * sizeof(float), st>>>(a, n_rows,
                                                                                                       rows_per_tok);
         return orn_check_launch("k_full_prep_warp");
