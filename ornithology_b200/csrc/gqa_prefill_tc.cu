@@ -7,7 +7,7 @@
 // rows of the cache (k_kv_rows_to_f16), so quantised caches are attended over in their decoded
 // form, the current token included, exactly as the reference does.
 //
-// One CTA = 128 query tokens of one head, 14 warps:
+// One CTA = 128 query tokens of one head, 14 warps (22 with four softmax threads per row):
 //   warps 8,13  producers one lane each issues TMA loads (128B-swizzled boxes of 64 dims): warp 8
 //                         dims 128..255 of the query tile once, then the 64-key K tiles (3
 //                         stages); warp 13 the V tiles (2 stages)
@@ -97,17 +97,27 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// barrier among the two softmax warps that share 32 query rows
-__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+// barrier among the NQ softmax warps that share 32 query rows
+template <int NQ>
+__device__ __forceinline__ void row_sync(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(32 * NQ) : "memory"); }
+__device__ __forceinline__ void ld_scores(uint32_t t, float (&s)[32]) { tmem_ld32_wait(t, s); }
+__device__ __forceinline__ void ld_scores(uint32_t t, float (&s)[16]) { tmem_ld16_wait(t, s); }
+__device__ __forceinline__ void st_cols(uint32_t t, const float (&s)[32]) { tmem_st32(t, s); }
+__device__ __forceinline__ void st_cols(uint32_t t, const float (&s)[16]) { tmem_st16(t, s); }
+__device__ __forceinline__ void st_cols(uint32_t t, const float (&s)[8]) { tmem_st8(t, s); }
 
-template <typename ACT>
-__global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mq,
+// NQ = softmax threads per query row (2 or 4): warps 0 .. 4 NQ - 1 are the softmax warps, then the K producer, the three
+// score issuers, the value issuer and the V producer.  With 4 the per-tile softmax (its loads, the exchange of the row
+// maxima, 64 exponentials per row, the store) is spread over twice the warps; it measures no faster (see the launch).
+template <typename ACT, int NQ>
+__global__ void __launch_bounds__((4 * NQ + 6) * 32, 1) k_gqa_prefill_tc(const __grid_constant__ CUtensorMap mq,
                                                            const __grid_constant__ CUtensorMap mk,
                                                            const __grid_constant__ CUtensorMap mv, TcArgs a) {
     extern __shared__ unsigned char smraw[];
     __shared__ TcBars bars;
-    __shared__ float xch[NB][2][BM];                           // [score buffer][column half][row]: partial row maxima
-    __shared__ float lx[2][BM];                                // [column half][row]: partial row sums
+    constexpr int W_K = 4 * NQ, W_QK = W_K + 1, W_PV = W_K + 4, W_V = W_K + 5, COLS = BN / NQ, OCOLS = HD / NQ;
+    __shared__ float xch[NB][NQ][BM];                          // [score buffer][column part][row]: partial row maxima
+    __shared__ float lx[NQ][BM];                               // [column part][row]: partial row sums
     __shared__ uint32_t tmem_base_s;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / (a.nh / a.nkv);
@@ -123,14 +133,14 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
     const uint32_t base = (su32(smraw) + 1023u) & ~1023u;      // 128B-swizzle atoms are 1 KiB aligned
 
     if (tid == 0) {
-        mbar_init(su32(&bars.q_full), 257);                    // 256 rows stored to tensor memory + the TMA half
+        mbar_init(su32(&bars.q_full), 128 * NQ + 1);           // every softmax thread's share stored to tensor memory + the TMA half
         for (int s = 0; s < NSK; s++) { mbar_init(su32(&bars.k_full[s]), 1); mbar_init(su32(&bars.k_empty[s]), 1); }
         for (int s = 0; s < NSV; s++) { mbar_init(su32(&bars.v_full[s]), 1); mbar_init(su32(&bars.v_empty[s]), 1); }
         for (int s = 0; s < NB; s++) { mbar_init(su32(&bars.s_full[s]), 1); mbar_init(su32(&bars.pv_done[s]), 1); }
-        mbar_init(su32(&bars.p_full), 256);
+        mbar_init(su32(&bars.p_full), 128 * NQ);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 12) {
+    if (warp == W_PV) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(su32(&tmem_base_s)), "r"((uint32_t)TM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -141,7 +151,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
     const uint32_t tmem = tmem_base_s;
     bool ok = true;
 
-    if (warp == 8) {
+    if (warp == W_K) {
         // ================= producer =================
         if (lane == 0) {
             // dims 128..255 of the query tile stay in shared memory (two 64-dim slabs)
@@ -158,7 +168,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
                     tma_load_2d(base + SM_K + sk * 32768 + s * 8192, &mk, s * 64, krow + j * BN, su32(&bars.k_full[sk]));
             }
         }
-    } else if (warp == 13) {
+    } else if (warp == W_V) {
         // ================= producer of the V tiles =================
         // its own lane: a V stage is released late (after the value product of its tile), and
         // waiting for that must not hold back the K tiles, which the score MMAs need much earlier
@@ -173,7 +183,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
                     tma_load_2d(base + SM_V + sv * 32768 + s * 8192, &mv, s * 64, krow + j * BN, su32(&bars.v_full[sv]));
             }
         }
-    } else if (warp >= 9 && warp <= 11) {
+    } else if (warp >= W_QK && warp < W_QK + 3) {
         // ================= score MMAs: warp 9 + e issues the tiles j = e (mod 3) =================
         // One thread cannot issue tcgen05.mma faster than one per ~64-96 cycles, two to three times
         // the 32 cycles an M128 N64 K16 product occupies the pipe; several issuing threads overlap.
@@ -181,7 +191,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
         // buffer spans three tiles.  Dims 0..127 of Q are a tensor-memory operand, dims 128..255 a
         // shared-memory one (512 columns: output 256, scores 3 x 64, query 64).
         if (lane == 0) {
-            const int e = warp - 9;
+            const int e = warp - W_QK;
             const uint32_t idesc_qk = (1u << 4) | (8u << 17) | (8u << 24);                 // f16 x f16 -> f32, N 64, M 128
             ok = mbar_wait(su32(&bars.q_full), 0);
             const uint64_t qd = smem_desc(base + SM_Q, 16, 1024);
@@ -205,7 +215,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
                 mma_commit(su32(&bars.s_full[e]));
             }
         }
-    } else if (warp == 12) {
+    } else if (warp == W_PV) {
         // ================= value MMAs =================
         if (lane == 0) {
             const uint32_t idesc_pv = (1u << 4) | (1u << 16) | (32u << 17) | (8u << 24);   // B MN-major, N 256, M 128
@@ -225,50 +235,51 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
             }
         }
     } else {
-        // ======== softmax + epilogue: two threads per query row (= TMEM lane), 32 columns each ========
-        const int wq = warp & 3, half = warp >> 2;             // TMEM lane quarter, column half
+        // ======== softmax + epilogue: NQ threads per query row (= TMEM lane), 64 / NQ columns each ========
+        const int wq = warp & 3, part = warp >> 2;             // TMEM lane quarter, column part
         const int row = wq * 32 + lane;
         const bool live = row < rows_here;
         const int qpos = live ? len0 + q0 + row : 0x7fffffff;  // rows past the end mask nothing and are not stored
         const size_t qrow = ((size_t)b * a.nh + h) * a.T + q0 + row;
         const float rscale = live ? a.rs[qrow] : 0.0f;
         const uint32_t lane_t = tmem + ((uint32_t)(wq * 32) << 16);
-        {   // dims 0..127 of the query row -> tensor memory: 64 halves per thread, two per 32-bit column
-            const uint4 *src = reinterpret_cast<const uint4 *>(a.Qh + qrow * HD + 64 * half);
-            float q[32];
+        {   // dims 0..127 of the query row -> tensor memory: 128 / NQ halves per thread, two per 32-bit column
+            const uint4 *src = reinterpret_cast<const uint4 *>(a.Qh + qrow * HD + (128 / NQ) * part);
+            float q[COLS];
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
+            for (int i = 0; i < COLS / 4; i++) {
                 const uint4 v = live ? src[i] : make_uint4(0u, 0u, 0u, 0u);
                 q[4 * i] = __uint_as_float(v.x); q[4 * i + 1] = __uint_as_float(v.y);
                 q[4 * i + 2] = __uint_as_float(v.z); q[4 * i + 3] = __uint_as_float(v.w);
             }
-            tmem_st32(lane_t + TM_Q + 32 * half, q);
+            st_cols(lane_t + TM_Q + COLS * part, q);
             tmem_wait_st();
             fence_before();
             mbar_arrive(su32(&bars.q_full));
         }
         float m_ref = -INFINITY, l = 0.0f;
         for (int j = 0; j < n_tiles; j++) {
-            const int sb = j % NB, key0 = j * BN + 32 * half;
+            const int sb = j % NB, key0 = j * BN + COLS * part;
             ok = ok && mbar_wait(su32(&bars.s_full[sb]), (uint32_t)(j / NB) & 1u);
             fence_after();
-            float s[32];
-            tmem_ld32_wait(lane_t + TM_S + sb * BN + 32 * half, s);
-            if (key0 + 31 > qpos) {                            // the tile reaches past this row's diagonal
+            float s[COLS];
+            ld_scores(lane_t + TM_S + sb * BN + COLS * part, s);
+            if (key0 + COLS - 1 > qpos) {                      // the tile reaches past this row's diagonal
 #pragma unroll
-                for (int c = 0; c < 32; c++)
+                for (int c = 0; c < COLS; c++)
                     if (key0 + c > qpos) s[c] = -INFINITY;
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 32; c += 4) {
+            for (int c = 0; c < COLS; c += 4) {
                 m4[0] = fmaxf(m4[0], s[c]); m4[1] = fmaxf(m4[1], s[c + 1]);
                 m4[2] = fmaxf(m4[2], s[c + 2]); m4[3] = fmaxf(m4[3], s[c + 3]);
             }
             float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            xch[sb][half][row] = mx;
-            pair_sync(1 + wq);                                 // also: both halves hold their scores in registers now
-            mx = fmaxf(mx, xch[sb][half ^ 1][row]);
+            xch[sb][part][row] = mx;
+            row_sync<NQ>(1 + wq);                              // also: every part holds its scores in registers now
+#pragma unroll
+            for (int p = 1; p < NQ; p++) mx = fmaxf(mx, xch[sb][(part + p) % NQ][row]);
             mx = live ? mx * rscale : 0.0f;                    // rscale > 0 on live rows
             float corr = 1.0f;
             const bool grow = mx > m_ref + GROW || m_ref == -INFINITY;
@@ -278,10 +289,10 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
                 l *= corr;
             }
             const float msafe = (m_ref == -INFINITY) ? 0.0f : m_ref;
-            float pk[16];
+            float pk[COLS / 2];
             float p4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
+            for (int c = 0; c < COLS / 4; c++) {
                 const float e0 = ex2_approx(fmaf(s[4 * c], rscale, -msafe)), e1 = ex2_approx(fmaf(s[4 * c + 1], rscale, -msafe));
                 const float e2 = ex2_approx(fmaf(s[4 * c + 2], rscale, -msafe)), e3 = ex2_approx(fmaf(s[4 * c + 3], rscale, -msafe));
                 p4[0] += e0; p4[1] += e1; p4[2] += e2; p4[3] += e3;
@@ -294,24 +305,25 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
                 ok = ok && mbar_wait(su32(&bars.pv_done[(j - 1) % NB]), (uint32_t)((j - 1) / NB) & 1u);
                 fence_after();
 #pragma unroll 1
-                for (int c = 0; c < HD / 2; c += 32) {         // this thread's half of the output row
+                for (int c = 0; c < OCOLS; c += 32) {          // this thread's part of the output row
                     float o[32];
-                    tmem_ld32_wait(lane_t + TM_O + 128 * half + c, o);
+                    tmem_ld32_wait(lane_t + TM_O + OCOLS * part + c, o);
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] *= corr;
-                    tmem_st32(lane_t + TM_O + 128 * half + c, o);
+                    tmem_st32(lane_t + TM_O + OCOLS * part + c, o);
                 }
             }
             // probabilities over the scores: key k of the tile in the low / high half of column k / 2
-            tmem_st16(lane_t + TM_S + sb * BN + 16 * half, pk);
+            st_cols(lane_t + TM_S + sb * BN + (COLS / 2) * part, pk);
             tmem_wait_st();
             fence_before();
             mbar_arrive(su32(&bars.p_full));
         }
-        // row sum = the two halves' sums (both were rescaled by the same factors)
-        lx[half][row] = l;
-        pair_sync(1 + wq);
-        l += lx[half ^ 1][row];
+        // row sum = the parts' sums (all were rescaled by the same factors)
+        lx[part][row] = l;
+        row_sync<NQ>(1 + wq);
+#pragma unroll
+        for (int p = 1; p < NQ; p++) l += lx[(part + p) % NQ][row];
         ok = ok && mbar_wait(su32(&bars.pv_done[(n_tiles - 1) % NB]), (uint32_t)((n_tiles - 1) / NB) & 1u);
         fence_after();
         const float inv = ok ? 1.0f / l : NAN;
@@ -319,7 +331,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
         const ACT *gate = (a.gated && live) ? (const ACT *)a.qproj + tok * a.nh * HD * 2 + (size_t)h * HD * 2 + HD : nullptr;
         ACT *out = (ACT *)a.out + (tok * a.nh + h) * HD;
 #pragma unroll 1
-        for (int c = 128 * half; c < 128 * half + 128; c += 32) {
+        for (int c = OCOLS * part; c < OCOLS * part + OCOLS; c += 32) {
             float o[32];
             tmem_ld32_wait(lane_t + TM_O + c, o);
             if (live) {
@@ -335,7 +347,7 @@ __global__ void __launch_bounds__(448, 1) k_gqa_prefill_tc(const __grid_constant
     if (!ok) report_timeout(a.status, ORN_WAIT_GQA_PREFILL);
     fence_before();
     __syncthreads();
-    if (warp == 12) {
+    if (warp == W_PV) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TM_COLS) : "memory");
     }
 }
@@ -382,14 +394,28 @@ ornith_status launch_gqa_prefill_tc(const KvView &kv, const int32_t *kv_len, con
     static bool configured_dev[ORN_MAX_DEVICES] = {};
     bool &configured = configured_dev[orn_device_index()];
     if (!configured) {
-        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SM_BYTES + 1024), "tcgen05 prefill smem opt-in"));
-        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<__nv_bfloat16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               SM_BYTES + 1024), "tcgen05 prefill smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<float, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               SM_BYTES + 1024), "tcgen05 prefill smem opt-in"));
+        ORN_TRY(orn_check(cudaFuncSetAttribute(k_gqa_prefill_tc<__nv_bfloat16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                SM_BYTES + 1024), "tcgen05 prefill smem opt-in"));
         configured = true;
     }
     dim3 grid((T + BM - 1) / BM, nh, n_seq);
-    if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16><<<grid, 448, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
-    else          k_gqa_prefill_tc<float><<<grid, 448, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    // softmax threads per query row: 2 (default) or 4.  Measured at 32768 tokens x 32 heads: 19.1 ms with 2, 19.8 ms
+    // with 4 (back to back under the power cap): the softmax is not what bounds the kernel.  Every CTA pulls a 64 KB
+    // K + V tile pair from L2 per 128 query rows: 137 GB per layer, 7.2 TB/s over the 148 SMs, and that traffic is the bound.
+    const char *e = getenv("ORNITH_CUDA_PREFILL_SOFTMAX");
+    const int nq = (e && e[0] == '4') ? 4 : 2;
+    if (nq == 4) {
+        if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16, 4><<<grid, (4 * 4 + 6) * 32, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+        else          k_gqa_prefill_tc<float, 4><<<grid, (4 * 4 + 6) * 32, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    } else {
+        if (bf16_act) k_gqa_prefill_tc<__nv_bfloat16, 2><<<grid, (4 * 2 + 6) * 32, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+        else          k_gqa_prefill_tc<float, 2><<<grid, (4 * 2 + 6) * 32, SM_BYTES + 1024, st>>>(mq, mk, mv, a);
+    }
     return orn_check_launch("k_gqa_prefill_tc");
 }
