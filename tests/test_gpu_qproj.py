@@ -95,7 +95,7 @@ def _encoded_rows(seed, wtype, n_out, n_in):
 @pytest.mark.parametrize("wtype", ["q4_k", "q6_k", "q8_0"])
 @pytest.mark.parametrize("T,n_in,n_out", [(1, 2048, 8192), (64, 2048, 1024), (70, 2048, 520), (5, 512, 40), (8, 4096, 512),
                                            (33, 256, 64), (12, 2048, 4096), (24, 2048, 3300), (40, 4096, 6500), (20, 2304, 8192),
-                                           (300, 2048, 200)])
+                                           (300, 2048, 200), (50, 2048, 4000)])
 def test_integer_projection_is_bit_exact(oracle, monkeypatch, wtype, T, n_in, n_out):
     """Q4_K / Q6_K / Q8_0 rows x Q8_K activations: every output equals the engine's integer path bit for bit
     (tensor-core kernel; the plain kernel for Q6_K rows that do not start on 16-byte boundaries: n_in = 512, 256),
