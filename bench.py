@@ -385,7 +385,8 @@ def run_projections(dev, n_tok=64, cpu=True):
     """The quantised projections that bracket the attention kernels of one 35B-shaped delta-net layer and one
     full-attention layer (hidden 2048), through the engine's integer path (Q8_K activations; Q8_0 weights around the
     delta-net core, Q6_K around the full-attention core), 64 tokens (one decode step of the headline batch), bf16
-    activations.  Projections that read the same input share one quantisation, as in the engine.  Each layer's
+    activations.  Projections that read the same input share one quantisation, as in the engine, and go as one grouped
+    launch.  Each layer's
     sequence is timed over 16 distinct weight sets used in turn (larger than L2 together), as one CUDA graph; the
     roofline figure is the weight bytes (what a decode-sized batch has to stream) over the time.  Each projection is
     also timed alone against a ready image.  `prompt` is attn_qkv over 4096 tokens (tensor-core bound).  The CPU
@@ -446,16 +447,15 @@ def run_projections(dev, n_tok=64, cpu=True):
             nbytes += float(n_out) * O.QROW_BYTES[wt](n_in)
 
         def layer_pass():
-            for ws in sets:
-                done = set()
-                for name, wt, n_in, n_out, src_in in projs:
-                    if src_in not in done:             # one quantisation per distinct input
-                        D.q8k_image(xs[src_in], n_in, image=imgs[src_in]); done.add(src_in)
-                    D.matmul_q(ws[name], None, out=outs[name], image=imgs[src_in], T=n_tok)
+            for ws in sets:                            # per distinct input: one quantisation, one grouped launch of its projections
+                for src_in in ("h", "o"):
+                    names = [p[0] for p in projs if p[4] == src_in]
+                    D.q8k_image(xs[src_in], xs[src_in].shape[1], image=imgs[src_in])
+                    D.matmul_q_group([ws[nm] for nm in names], imgs[src_in], n_tok, outs=[outs[nm] for nm in names])
         ms = graph_ms(layer_pass)
         res[lname] = {"us": ms * 1e3, "weight_bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak,
-                      "launches": len(projs) + 2}
-        tot_bytes += nbytes; tot_ms += ms; launches += len(projs) + 2
+                      "launches": 4}
+        tot_bytes += nbytes; tot_ms += ms; launches += 4
         for name, wt, n_in, n_out, src_in in projs:
             def one():
                 for ws in sets:

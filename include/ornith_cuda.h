@@ -461,6 +461,17 @@ ornith_status ornith_cuda_q8k_image(const void *x, int act_dtype, int T, int n_i
                                     size_t image_bytes, void *stream);
 ornith_status ornith_cuda_matmul_q_image(int wtype, const void *W, int n_in, int n_out,
                                          const void *image, int T, void *y, int out_dtype, void *stream);
+/* Several projections of the same input in one launch (one per run of matrices of the same weight type):
+ * for a decode-sized batch the launches cost as much as the weight traffic, and a small matrix (ssm_alpha,
+ * ssm_beta: 32 rows) cannot fill the GPU alone.  y [T][n_out] per projection; results as the single call's. */
+typedef struct {
+    int         wtype;      /* ORNITH_GGML_Q8_0 / _Q4_K / _Q6_K */
+    const void *W;          /* device, [n_out] rows of n_in/256 super-blocks */
+    int         n_out;
+    void       *y;          /* device, [T][n_out] */
+} ornith_cuda_qproj;
+ornith_status ornith_cuda_matmul_q_group(const ornith_cuda_qproj *projs, int n, int n_in,
+                                         const void *image, int T, int out_dtype, void *stream);
 
 /* ---- host-fed layer calls over device-resident state -------------------------
  * For an engine whose projections still run on the host: one object holds the state of all

@@ -37,6 +37,11 @@ class ConvState(C.Structure):               # ornith_conv_state
     _fields_ = [("buf", f32p), ("K", C.c_int), ("C", C.c_int)]
 
 
+class CudaQproj(C.Structure):
+    """ornith_cuda_qproj: one projection of a grouped launch."""
+    _fields_ = [("wtype", C.c_int), ("W", C.c_void_p), ("n_out", C.c_int), ("y", C.c_void_p)]
+
+
 class CudaKv(C.Structure):                  # ornith_cuda_kv
     _fields_ = [("mode", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("n_seq", C.c_int32),
                 ("K", vp), ("V", vp), ("Ks", vp), ("Vs", vp), ("seq_off", vp)]
@@ -119,6 +124,7 @@ SYMBOLS = {
     "ornith_cuda_matmul_q": (_I, [_I, vp, _I, _I, vp, _I, _I, vp, _I, vp, _SZ, vp]),
     "ornith_cuda_q8k_image": (_I, [vp, _I, _I, _I, vp, _SZ, vp]),
     "ornith_cuda_matmul_q_image": (_I, [_I, vp, _I, _I, vp, _I, vp, _I, vp]),
+    "ornith_cuda_matmul_q_group": (_I, [vp, _I, _I, vp, _I, _I, vp]),
     "ornith_cuda_engine_new": (vp, [_I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _I, _I]),
     "ornith_cuda_engine_free": (None, [vp]),
     "ornith_cuda_engine_full_layer": (_I, [vp, _I, vp, vp]),

@@ -87,6 +87,18 @@ __device__ __forceinline__ uint32_t lds32_any(smem_ptr p) {
 __device__ __forceinline__ float f16_bits_to_f32(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 __device__ __forceinline__ int sbyte(uint32_t w, int k) { return (int)(w << (24 - 8 * k)) >> 24; }   // signed byte k of w
 
+// The weight matrices of one launch: projections that read the same activations (attn_qkv, attn_gate, ssm_alpha and
+// ssm_beta of a delta-net layer; attn_q / k / v of a full-attention layer) go as one grid, CTAs cta0[p] .. cta0[p+1]-1
+// belonging to matrix p.
+constexpr int MAX_GROUP = 8;
+struct KqGroup {
+    CUtensorMap map[MAX_GROUP];                   // [n_out rows][row bytes / 4 words] of each matrix
+    void *y[MAX_GROUP];                           // [T][n_out]
+    int n_out[MAX_GROUP];
+    int cta0[MAX_GROUP + 1];
+    int n;
+};
+
 struct KqArgs {
     const unsigned char *img;                     // [token tiles][nseg] Q8_K images
     void *y;                                      // [T][n_out]
@@ -281,7 +293,7 @@ __device__ __forceinline__ void superblock_q80(smem_ptr wrow0, smem_ptr xs, int 
 // (griddepcontrol.wait) only before the first copy of an activation image.
 constexpr int NWARP = 16, MAX_STAGES = 16;
 template <int TYPE, int WR, int KS, int MT>
-__global__ void __launch_bounds__(NWARP * 32, 1) k_matmul_kq(KqArgs a, const __grid_constant__ CUtensorMap map_w) {
+__global__ void __launch_bounds__(NWARP * 32, 1) k_matmul_kq(KqArgs a, const __grid_constant__ KqGroup grp) {
     constexpr int BLOCK = Fmt<TYPE>::BLOCK, BOX = Fmt<TYPE>::BOX, CTA_ROWS = 16 * WR, WBYTES = CTA_ROWS * BOX, TS = NWARP / (WR * KS);
     static_assert(WR * KS * TS == NWARP, "the warps split rows x super-blocks x token tiles");
     extern __shared__ unsigned char smem_raw[];
@@ -290,7 +302,10 @@ __global__ void __launch_bounds__(NWARP * 32, 1) k_matmul_kq(KqArgs a, const __g
     unsigned char *smem = smem_raw + ((128 - (smem_u32(smem_raw) & 127)) & 127);
     const int tid = threadIdx.x, lane = tid & 31, w16 = tid >> 5, g = lane >> 2, j = lane & 3;
     const int wr = w16 % WR, ks = (w16 / WR) % KS, ts = w16 / (WR * KS), t_lo = ts * MT;
-    const int cta_row0 = (int)blockIdx.x * CTA_ROWS, row0 = cta_row0 + wr * 16;
+    int pj = 0;                                                       // the matrix this CTA belongs to
+    while (pj + 1 < grp.n && (int)blockIdx.x >= grp.cta0[pj + 1]) pj++;
+    const int n_out = grp.n_out[pj];
+    const int cta_row0 = ((int)blockIdx.x - grp.cta0[pj]) * CTA_ROWS, row0 = cta_row0 + wr * 16;
     const int tok0 = (int)blockIdx.y * (8 * MT * TS);
     const int nt_all = min(MT * TS, (a.T - tok0 + 7) / 8);            // token tiles of this pass
     const int nstage = a.nstage, stage_bytes = a.stage_bytes;
@@ -306,7 +321,7 @@ __global__ void __launch_bounds__(NWARP * 32, 1) k_matmul_kq(KqArgs a, const __g
     auto issue_w = [&](int seg) {
         const uint32_t bar = smem_u32(&bars[seg % nstage]), base = smem_u32(smem + (size_t)(seg % nstage) * stage_bytes);
         tc5::mbar_expect_tx(bar, (uint32_t)(WBYTES + nt_all * ORN_Q8K_IMG_BYTES));
-        tensor_copy_rows(base, &map_w, ((seg * BLOCK) & ~15) / 4, cta_row0, bar);
+        tensor_copy_rows(base, &grp.map[pj], ((seg * BLOCK) & ~15) / 4, cta_row0, bar);
     };
     auto issue_x = [&](int seg) {
         const uint32_t bar = smem_u32(&bars[seg % nstage]), base = smem_u32(smem + (size_t)(seg % nstage) * stage_bytes);
@@ -325,7 +340,7 @@ __global__ void __launch_bounds__(NWARP * 32, 1) k_matmul_kq(KqArgs a, const __g
     float tot[MT][4];
 #pragma unroll
     for (int t = 0; t < MT; t++) tot[t][0] = tot[t][1] = tot[t][2] = tot[t][3] = 0.0f;
-    const bool active = row0 < a.n_out && t_lo < nt_all;
+    const bool active = row0 < n_out && t_lo < nt_all;
     bool ok = true;
     const int rounds = (a.nseg + KS - 1) / KS;
     for (int r = 0; r < rounds; r++) {
@@ -379,10 +394,10 @@ __global__ void __launch_bounds__(NWARP * 32, 1) k_matmul_kq(KqArgs a, const __g
 #pragma unroll
         for (int x = 0; x < 4; x++) {
             const int row = row0 + g + 8 * (x >> 1), tok = tok0 + 8 * (t_lo + t) + 2 * j + (x & 1);
-            if (row < a.n_out && t_lo + t < nt_all && tok < a.T) {
+            if (row < n_out && t_lo + t < nt_all && tok < a.T) {
                 const float val = ok ? tot[t][x] : NAN;
-                if (a.out_dtype == ORNITH_ACT_BF16) act_st((__nv_bfloat16 *)a.y, (size_t)tok * a.n_out + row, val);
-                else act_st((float *)a.y, (size_t)tok * a.n_out + row, val);
+                if (a.out_dtype == ORNITH_ACT_BF16) act_st((__nv_bfloat16 *)grp.y[pj], (size_t)tok * n_out + row, val);
+                else act_st((float *)grp.y[pj], (size_t)tok * n_out + row, val);
             }
         }
 }
@@ -456,11 +471,29 @@ bool weight_map(CUtensorMap *m, const void *W, int n_in, int n_out, int box_rows
 
 constexpr int SMEM_BUDGET = 200 * 1024;           // dynamic shared memory of one CTA (one CTA per SM: 512 threads)
 
+// what the host knows of a group: the matrices (all of one weight type, one n_in), their outputs
+struct HostGroup {
+    const void *W[MAX_GROUP];
+    void *y[MAX_GROUP];
+    int n_out[MAX_GROUP];
+    int n;
+    int rows_total() const { int r = 0; for (int i = 0; i < n; i++) r += n_out[i]; return r; }
+};
+
 template <int TYPE, int WR, int KS, int MT>
-ornith_status launch_tc(const void *W, int n_in, int n_out, int T, KqArgs a, cudaStream_t stream) {
+ornith_status launch_tc(const HostGroup &h, int n_in, int T, KqArgs a, cudaStream_t stream) {
     constexpr int TS = NWARP / (WR * KS), PASS_TOK = 8 * MT * TS, CTA_ROWS = 16 * WR;
-    CUtensorMap map;
-    if (!weight_map<TYPE>(&map, W, n_in, n_out, CTA_ROWS)) { orn_record_error("matmul_q: the weight tensor map could not be made"); return (ornith_status)ORNITH_ERR_BACKEND; }
+    KqGroup g;
+    g.n = h.n;
+    g.cta0[0] = 0;
+    for (int i = 0; i < h.n; i++) {
+        if (!weight_map<TYPE>(&g.map[i], h.W[i], n_in, h.n_out[i], CTA_ROWS)) {
+            orn_record_error("matmul_q: the weight tensor map could not be made");
+            return (ornith_status)ORNITH_ERR_BACKEND;
+        }
+        g.y[i] = h.y[i]; g.n_out[i] = h.n_out[i];
+        g.cta0[i + 1] = g.cta0[i] + (h.n_out[i] + CTA_ROWS - 1) / CTA_ROWS;
+    }
     // tiles of the fullest pass, rounded up to whole groups: a group multiplies all MT of its tiles, so the stage
     // must have room for them (the ones past the pass's last tile hold stale bytes and are never stored)
     const int nt_max = (((T < PASS_TOK ? T : PASS_TOK) + 7) / 8 + MT - 1) / MT * MT;
@@ -482,7 +515,7 @@ ornith_status launch_tc(const void *W, int n_in, int n_out, int T, KqArgs a, cud
         have = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((n_out + CTA_ROWS - 1) / CTA_ROWS), (unsigned)((T + PASS_TOK - 1) / PASS_TOK));
+    cfg.gridDim = dim3((unsigned)g.cta0[h.n], (unsigned)((T + PASS_TOK - 1) / PASS_TOK));
     cfg.blockDim = dim3(NWARP * 32);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
@@ -490,39 +523,57 @@ ornith_status launch_tc(const void *W, int n_in, int n_out, int T, KqArgs a, cud
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start while the quantiser in front of it still runs
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    return orn_check(cudaLaunchKernelEx(&cfg, k_matmul_kq<TYPE, WR, KS, MT>, a, map), "k_matmul_kq");
+    return orn_check(cudaLaunchKernelEx(&cfg, k_matmul_kq<TYPE, WR, KS, MT>, a, g), "k_matmul_kq");
 }
 
 // the split of the 16 warps: rows per CTA so that a few-token product has about one CTA per SM or more; the
 // rest over the super-blocks (few tokens) or the token tiles
 template <int TYPE, int WR>
-ornith_status launch_wr(const void *W, int n_in, int n_out, int T, KqArgs a, cudaStream_t stream) {
-    if (T <= 16) return launch_tc<TYPE, WR, 16 / WR, 2>(W, n_in, n_out, T, a, stream);
-    if (T <= 32) return launch_tc<TYPE, WR, 8 / WR, 2>(W, n_in, n_out, T, a, stream);
+ornith_status launch_wr(const HostGroup &h, int n_in, int T, KqArgs a, cudaStream_t stream) {
+    if (T <= 16) return launch_tc<TYPE, WR, 16 / WR, 2>(h, n_in, T, a, stream);
+    if (T <= 32) return launch_tc<TYPE, WR, 8 / WR, 2>(h, n_in, T, a, stream);
     // 33-64 tokens, k-quants: four tiles per warp where the stages still hold a round, so that an unpacked weight
     // operand (the expensive part for the packed 4- and 6-bit codes) feeds four MMAs instead of two: 2048 -> 8192 in
     // Q6_K 22.9 -> 19.8 us.  Q8_0 unpacks cheaply and pays per MMA for its exact f32 epilogue: 15.4 -> 16.4 us, not used.
-    if (TYPE != T_Q80 && WR >= 2) return launch_tc<TYPE, WR, 8 / WR, 4>(W, n_in, n_out, T, a, stream);
-    return launch_tc<TYPE, WR, 4 / WR, 2>(W, n_in, n_out, T, a, stream);
+    if (TYPE != T_Q80 && WR >= 2) return launch_tc<TYPE, WR, 8 / WR, 4>(h, n_in, T, a, stream);
+    return launch_tc<TYPE, WR, 4 / WR, 2>(h, n_in, T, a, stream);
 }
 
 template <int TYPE>
-ornith_status launch_kq(const void *W, int n_in, int n_out, int T, KqArgs a, bool plain, cudaStream_t stream) {
+ornith_status launch_kq(const HostGroup &h, int n_in, int T, KqArgs a, bool plain, cudaStream_t stream) {
     const size_t row_bytes = (size_t)n_in / QK * Fmt<TYPE>::BLOCK;
-    if (plain || ((uintptr_t)W & 15) != 0 || (row_bytes & 15) != 0 || !orn_tensor_map_encoder()) {
-        k_matmul_kq_plain<TYPE><<<dim3((unsigned)T, (unsigned)((n_out + 127) / 128)), 128, 0, stream>>>((const unsigned char *)W, a);
-        return orn_check_launch("k_matmul_kq_plain");
+    bool tc = !plain && (row_bytes & 15) == 0 && orn_tensor_map_encoder();
+    for (int i = 0; i < h.n; i++) tc = tc && ((uintptr_t)h.W[i] & 15) == 0;
+    if (!tc) {                                    // the plain kernel, matrix by matrix
+        for (int i = 0; i < h.n; i++) {
+            a.y = h.y[i]; a.n_out = h.n_out[i];
+            k_matmul_kq_plain<TYPE><<<dim3((unsigned)T, (unsigned)((h.n_out[i] + 127) / 128)), 128, 0, stream>>>((const unsigned char *)h.W[i], a);
+            ORN_TRY(orn_check_launch("k_matmul_kq_plain"));
+        }
+        return ORNITH_OK;
     }
+    const int n_out = h.rows_total();
     if (T > 64) {                                 // prompts: passes of 128 tokens; of 64 with fewer rows per CTA for a small matrix
         const long p128 = (T + 127) / 128, p64 = (T + 63) / 64;
-        if ((n_out + 63) / 64 * p128 >= 100) return launch_tc<TYPE, 4, 1, 4>(W, n_in, n_out, T, a, stream);
-        if ((n_out + 63) / 64 * p64 >= 100) return launch_tc<TYPE, 4, 1, 2>(W, n_in, n_out, T, a, stream);
-        if ((n_out + 31) / 32 * p64 >= 100) return launch_tc<TYPE, 2, 2, 2>(W, n_in, n_out, T, a, stream);
-        return launch_tc<TYPE, 1, 4, 2>(W, n_in, n_out, T, a, stream);
+        if ((n_out + 63) / 64 * p128 >= 100) return launch_tc<TYPE, 4, 1, 4>(h, n_in, T, a, stream);
+        if ((n_out + 63) / 64 * p64 >= 100) return launch_tc<TYPE, 4, 1, 2>(h, n_in, T, a, stream);
+        if ((n_out + 31) / 32 * p64 >= 100) return launch_tc<TYPE, 2, 2, 2>(h, n_in, T, a, stream);
+        return launch_tc<TYPE, 1, 4, 2>(h, n_in, T, a, stream);
     }
-    if (n_out >= 64 * 100) return launch_wr<TYPE, 4>(W, n_in, n_out, T, a, stream);
-    if (n_out >= 32 * 100) return launch_wr<TYPE, 2>(W, n_in, n_out, T, a, stream);
-    return launch_wr<TYPE, 1>(W, n_in, n_out, T, a, stream);
+    if (n_out >= 64 * 100) return launch_wr<TYPE, 4>(h, n_in, T, a, stream);
+    if (n_out >= 32 * 100) return launch_wr<TYPE, 2>(h, n_in, T, a, stream);
+    return launch_wr<TYPE, 1>(h, n_in, T, a, stream);
+}
+
+ornith_status run_group(int wtype, const HostGroup &h, int n_in, const void *image, int T, int out_dtype, cudaStream_t s) {
+    KqArgs a;
+    a.img = (const unsigned char *)image;
+    a.y = nullptr; a.T = T; a.n_out = 0; a.nseg = n_in / QK; a.out_dtype = out_dtype; a.nstage = 0; a.stage_bytes = 0; a.status = orn_status_word();
+    const char *e = getenv("ORNITH_CUDA_PROJ_PLAIN");                 // =1: the plain kernel for every shape
+    const bool plain = e && e[0] == '1';
+    if (wtype == ORNITH_GGML_Q4_K) return launch_kq<T_Q4K>(h, n_in, T, a, plain, s);
+    if (wtype == ORNITH_GGML_Q6_K) return launch_kq<T_Q6K>(h, n_in, T, a, plain, s);
+    return launch_kq<T_Q80>(h, n_in, T, a, plain, s);
 }
 
 }  // namespace
@@ -548,25 +599,37 @@ ornith_status ornith_cuda_q8k_image(const void *x, int act_dtype, int T, int n_i
     return orn_q8k_quantize_image(x, act_dtype, T, n_in, image, (cudaStream_t)stream);
 }
 
-ornith_status ornith_cuda_matmul_q_image(int wtype, const void *W, int n_in, int n_out, const void *image, int T, void *y,
+ornith_status ornith_cuda_matmul_q_group(const ornith_cuda_qproj *projs, int n, int n_in, const void *image, int T,
                                          int out_dtype, void *stream) {
     ORN_TRY(orn_require_device());
-    if (!kq_type_ok(wtype)) {
-        orn_record_error("matmul_q: no integer path for weight type %d (Q8_0 = 8, Q4_K = 12, Q6_K = 14)", wtype);
-        return ORNITH_ERR_UNSUPPORTED;
-    }
+    if (n <= 0 || T <= 0) return ORNITH_OK;
+    if (!projs) { orn_record_error("matmul_q: no projections given"); return ORNITH_ERR_FORMAT; }
     if (n_in <= 0 || n_in % QK) { orn_record_error("matmul_q: the row length must be a multiple of 256 (got %d)", n_in); return ORNITH_ERR_FORMAT; }
-    if (T <= 0 || n_out <= 0) return ORNITH_OK;
     if (!image || ((uintptr_t)image & 255) != 0) { orn_record_error("matmul_q: the activation image must be 256-byte aligned"); return ORNITH_ERR_FORMAT; }
-    KqArgs a;
-    a.img = (const unsigned char *)image;
-    a.y = y; a.T = T; a.n_out = n_out; a.nseg = n_in / QK; a.out_dtype = out_dtype; a.nstage = 0; a.stage_bytes = 0; a.status = orn_status_word();
-    const char *e = getenv("ORNITH_CUDA_PROJ_PLAIN");                 // =1: the plain kernel for every shape
-    const bool plain = e && e[0] == '1';
-    cudaStream_t s = (cudaStream_t)stream;
-    if (wtype == ORNITH_GGML_Q4_K) return launch_kq<T_Q4K>(W, n_in, n_out, T, a, plain, s);
-    if (wtype == ORNITH_GGML_Q6_K) return launch_kq<T_Q6K>(W, n_in, n_out, T, a, plain, s);
-    return launch_kq<T_Q80>(W, n_in, n_out, T, a, plain, s);
+    for (int i = 0; i < n; i++)
+        if (!kq_type_ok(projs[i].wtype)) {
+            orn_record_error("matmul_q: no integer path for weight type %d (Q8_0 = 8, Q4_K = 12, Q6_K = 14)", projs[i].wtype);
+            return ORNITH_ERR_UNSUPPORTED;
+        }
+    // one launch per run of matrices of the same weight type (at most MAX_GROUP of them)
+    for (int i = 0; i < n;) {
+        HostGroup h;
+        h.n = 0;
+        const int wtype = projs[i].wtype;
+        for (; i < n && projs[i].wtype == wtype && h.n < MAX_GROUP; i++) {
+            if (projs[i].n_out <= 0) continue;
+            h.W[h.n] = projs[i].W; h.y[h.n] = projs[i].y; h.n_out[h.n] = projs[i].n_out; h.n++;
+        }
+        if (h.n) ORN_TRY(run_group(wtype, h, n_in, image, T, out_dtype, (cudaStream_t)stream));
+    }
+    return ORNITH_OK;
+}
+
+ornith_status ornith_cuda_matmul_q_image(int wtype, const void *W, int n_in, int n_out, const void *image, int T, void *y,
+                                         int out_dtype, void *stream) {
+    ornith_cuda_qproj p;
+    p.wtype = wtype; p.W = W; p.n_out = n_out; p.y = y;
+    return ornith_cuda_matmul_q_group(&p, 1, n_in, image, T, out_dtype, stream);
 }
 
 ornith_status ornith_cuda_matmul_q(int wtype, const void *W, int n_in, int n_out, const void *x, int act_dtype, int T,

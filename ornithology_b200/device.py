@@ -211,6 +211,19 @@ def matmul_q(w: QWeight, x, out=None, image=None, T=None, out_dtype=None):
     return out
 
 
+def matmul_q_group(ws, image, T, outs=None, out_dtype=None):
+    """Several projections of the same (already quantised) input in one launch per weight type; returns the outputs."""
+    lib = _lib.load()
+    if outs is None:
+        outs = [torch.empty(T, w.n_out, dtype=out_dtype or torch.float32, device=image.device) for w in ws]
+    arr = (_lib.CudaQproj * len(ws))()
+    for i, (w, o) in enumerate(zip(ws, outs)):
+        arr[i].wtype, arr[i].W, arr[i].n_out, arr[i].y = w.wtype, _ptr(w.bytes), w.n_out, _ptr(o)
+    check(lib.ornith_cuda_matmul_q_group(C.cast(arr, C.c_void_p), len(ws), ws[0].n_in, _ptr(image), int(T), _act(outs[0]), _stream()),
+          "matmul_q_group")
+    return outs
+
+
 def kv_export(kv: KvBatch, seq, length):
     """Session record of the first `length` positions of sequence `seq` (bytes, the engine's layer record)."""
     lib = _lib.load()

@@ -138,6 +138,26 @@ def test_projections_sharing_one_image(oracle):
         assert (got.view(np.uint32) == oracle.matmul_q(wt, W, n_in, X).view(np.uint32)).all(), (wt, n_out)
 
 
+def test_grouped_projections(oracle):
+    """The projections of one input as one launch per weight type (attn_qkv, attn_gate, ssm_alpha, ssm_beta of a
+    delta-net layer; a mixed list falls into one launch per run of equal types): bit-exact like the single calls."""
+    import torch
+    from oracle import oracle as O
+    from ornithology_b200 import device as D
+    n_in = 2048
+    for T in (3, 64, 100):
+        X = _acts(40 + T, T, n_in)
+        img = D.q8k_image(torch.from_numpy(X).cuda(), n_in)
+        spec = [(O.GGML_Q8_0, 8192), (O.GGML_Q8_0, 4096), (O.GGML_Q8_0, 32), (O.GGML_Q8_0, 32), (O.GGML_Q6_K, 520), (O.GGML_Q6_K, 72),
+                (O.GGML_Q4_K, 40)]
+        Ws = [_random_rows(11 * i + T, wt, n_out, n_in) for i, (wt, n_out) in enumerate(spec)]
+        ws = [D.QWeight(wt, W, n_in) for (wt, _), W in zip(spec, Ws)]
+        outs = D.matmul_q_group(ws, img, T)
+        for (wt, n_out), W, y in zip(spec, Ws, outs):
+            ref = oracle.matmul_q(wt, W, n_in, X)
+            assert (y.cpu().numpy().view(np.uint32) == ref.view(np.uint32)).all(), (T, wt, n_out)
+
+
 def test_integer_projection_golden(golden):
     """Weights from the reference's encoder and outputs from the reference's integer dot (tests/golden/make_golden.py)."""
     import torch
