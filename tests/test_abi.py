@@ -101,3 +101,23 @@ def test_product_does_not_touch_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".c", ".h")):
                 text = open(os.path.join(dirpath, f), errors="replace").read()
                 assert "oracle" not in text.lower(), f"{f} mentions the oracle"
+
+
+def test_projection_sizing_and_no_gpu_behaviour(lib):
+    """Host-side: the scratch of the integer projections is the Q8_K image of the activations (one 2336-byte image
+    per 8 tokens x 256 inputs, the same for the three weight types), nothing for a type without an integer path or
+    a width that is not a multiple of 256; without a GPU the products fail with a status."""
+    import torch
+    from ornithology_b200 import _lib
+    img = lambda T, n_in: -(-(-(-T // 8) * (n_in // 256) * 2336) // 256) * 256
+    for wt in (8, 12, 14):
+        assert lib.ornith_cuda_matmul_q_scratch(wt, 1, 2048) == img(1, 2048)
+        assert lib.ornith_cuda_matmul_q_scratch(wt, 70, 4096) == img(70, 4096)
+    assert lib.ornith_cuda_matmul_q_scratch(13, 8, 2048) == 0          # Q5_K: the engine dequantises it
+    assert lib.ornith_cuda_matmul_q_scratch(8, 8, 300) == 0
+    assert lib.ornith_cuda_matmul_q_scratch(8, 0, 2048) == 0
+    assert C.sizeof(_lib.CudaQproj) == 32 and _lib.CudaQproj.n_out.offset == 16 and _lib.CudaQproj.y.offset == 24
+    if not torch.cuda.is_available():
+        p = _lib.CudaQproj(8, None, 64, None)
+        assert lib.ornith_cuda_matmul_q_group(C.byref(p), 1, 2048, None, 4, 0, None) != 0
+        assert lib.ornith_cuda_matmul_q(8, None, 2048, 64, None, 0, 4, None, 0, None, 0, None) != 0
