@@ -366,9 +366,6 @@ __global__ void __launch_bounds__(128) k_conv_silu_prefill(LinArgs a, float *Y) 
 }
 
 
-template <bool FAST>
-__device__ __forceinline__ float silu_sel(float x) { return FAST ? silu_fast(x) : silu_f(x); }
-
 // conv_k = 4, Cc a multiple of 4: one thread owns 4 adjacent channels over CONV4_TOK
 // tokens and requests all its inputs before the first use.  Same products, sums and
 // rounding as k_conv_silu_prefill.  grid (ceil(Cc/512), ceil(T/CONV4_TOK), n_seq).
