@@ -250,6 +250,11 @@ __global__ void __launch_bounds__(128) k_full_prep_row8(PrepArgs a, long long n_
     __shared__ __align__(16) float rowbuf[4][hd];          // the rotation's exchange; then the encoded Q8_0 row (272 bytes)
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int nkv = a.kv.nkv, nh = a.nh;
+    // Launched as a programmatic dependent of the kernel in front of it (in a decode step: the layer before): resident
+    // when that kernel ends, and waiting for its end before anything else.  After that a decode kernel launched behind
+    // this one may begin its prologue (it streams cache rows early, and waits for this grid before it reads its output).
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     if (a.group_ctr)
         for (long long i = (long long)blockIdx.x * 128 + threadIdx.x; i < a.n_ctr; i += (long long)gridDim.x * 128)
             a.group_ctr[i] = 0;
@@ -731,16 +736,21 @@ static ornith_status launch_prep(const ornith_cuda_full_layer *l, const ornith_c
     a.nh = l->n_heads; a.rope_dim = l->rope_dim; a.gated = l->gated; a.T = T; a.eps = l->eps;
     a.row0 = kv_only ? l->n_heads : 0;
     const int rows_per_tok = (kv_only ? 0 : l->n_heads) + 2 * l->n_kv_heads;
+    // prefill-sized batches of head_dim 256 with 16-byte-aligned rows: one warp per row, a lane owns 8 adjacent elements
+    // (rows of a token are multiples of 256 elements apart).  For a decode step it measures no faster than the
+    // one-CTA-per-row kernel below (3.796 against 3.785 ms per step: the front end hides behind the layer before it).
+    const bool aligned = (((uintptr_t)qproj | (uintptr_t)k | (uintptr_t)v | (uintptr_t)kv->K | (uintptr_t)kv->V |
+                           (uintptr_t)l->q_norm_w | (uintptr_t)l->k_norm_w) & 15) == 0 &&
+                         (!Qh || ((uintptr_t)Qh & 15) == 0) && (!q_prep || ((uintptr_t)q_prep & 15) == 0);
+    static int row8_ok = -1;
+    if (row8_ok < 0) { const char *e = getenv("ORNITH_CUDA_PREP_ROW8"); row8_ok = e ? atoi(e) : 1; }   // =0: the older kernels
+    if (row8_ok && n_tok >= 256 && l->head_dim == 256 && aligned && l->rope_dim % 2 == 0 && l->rope_dim <= 256) {
+        const long long n_rows = (long long)n_tok * rows_per_tok;
+        return orn_check(orn_launch_dependent(k_full_prep_row8<ACT>, dim3((unsigned)((n_rows + 3) / 4)), dim3(128), 0, st, a, n_rows,
+                                              rows_per_tok), "k_full_prep_row8");
+    }
     if (n_tok >= 256) {                                   // prefill-sized: one warp per row
         const long long n_rows = (long long)n_tok * rows_per_tok;
-        // head_dim 256 with 16-byte-aligned rows: the vectorised form (rows of a token are multiples of 256 elements apart)
-        const bool aligned = (((uintptr_t)qproj | (uintptr_t)k | (uintptr_t)v | (uintptr_t)kv->K | (uintptr_t)kv->V |
-                               (uintptr_t)l->q_norm_w | (uintptr_t)l->k_norm_w) & 15) == 0 &&
-                             (!Qh || ((uintptr_t)Qh & 15) == 0) && (!q_prep || ((uintptr_t)q_prep & 15) == 0);
-        if (l->head_dim == 256 && aligned && l->rope_dim % 2 == 0 && l->rope_dim <= 256) {
-            k_full_prep_row8<ACT><<<(unsigned)((n_rows + 3) / 4), 128, 0, st>>>(a, n_rows, rows_per_tok);
-            return orn_check_launch("k_full_prep_row8");
-        }
         k_full_prep_warp<ACT><<<(unsigned)((n_rows + 3) / 4), 128, 4 * l->head_dim * sizeof(float), st>>>(a, n_rows,
                                                                                                       rows_per_tok);
         return orn_check_launch("k_full_prep_warp");
