@@ -422,8 +422,9 @@ ornith_status ornith_cuda_linear_import(const ornith_cuda_linear_layer *layer,
 /* ---- quantised projections around the attention core ---------------------------
  * Q8_0 weights x Q8_K activations, the engine's integer path for attn_qkv, ssm_alpha/beta,
  * attn_gate, ssm_out, attn_q/k/v/output (matmul_batch_q, reference: src/ornith_rforward.c:138-192;
- * qdot_quantize_row_q8_K src/ornith_qdot.c:38-70; vec_dot_q8_0 :144-163).  Decode-sized batches:
- * more than 64 tokens are walked 64 at a time, re-reading the weights. */
+ * qdot_quantize_row_q8_K src/ornith_qdot.c:38-70; vec_dot_q8_0 :144-163).  This first pair is the
+ * f16-product form for Q8_0 (decode-sized batches: more than 64 tokens are walked 64 at a time,
+ * re-reading the weights); the bit-exact integer path for Q8_0, Q4_K and Q6_K follows below. */
 size_t ornith_cuda_qproj_scratch(int T, int n_in);       /* n_in: a multiple of 256 */
 /* x [T][n_in] -> Q8_K.  The codes and scales are the engine's bit for bit.  blocks: device
  * [T][n_in/256][292 bytes] in the engine's block layout (f32 d, 256 int8, 16 int16 sums), or NULL;
@@ -445,7 +446,7 @@ ornith_status ornith_cuda_matmul_q8_0(const void *W, int n_in, int n_out, const 
  * n_in/256 super-blocks (144 / 210 / 272 bytes); wtype: the GGUF type id.  Rows that start on 16-byte
  * boundaries (always for Q4_K and Q8_0; Q6_K when n_in is a multiple of 2048) and a 16-byte-aligned W take the
  * tensor-core kernel, any other shape a plain kernel with the same result.  scratch: 256-byte aligned,
- * ornith_cuda_matmul_q_scratch bytes.  Any T; more than 64 tokens are walked 64 at a time. */
+ * ornith_cuda_matmul_q_scratch bytes.  Any T: a prompt is walked in passes of 128 tokens inside one launch. */
 enum { ORNITH_GGML_Q8_0 = 8, ORNITH_GGML_Q4_K = 12, ORNITH_GGML_Q6_K = 14 };   /* src/ornith_gguf.h:24-30 */
 size_t ornith_cuda_matmul_q_scratch(int wtype, int T, int n_in);
 ornith_status ornith_cuda_matmul_q(int wtype, const void *W, int n_in, int n_out, const void *x,
