@@ -272,3 +272,63 @@ def test_kquant_golden_bit_exact(oracle, golden):
     for name, wt in (("q4_k", O.GGML_Q4_K), ("q6_k", O.GGML_Q6_K)):
         y = oracle.matmul_q(wt, g["W_" + name], int(g["n_in"]), g["X"])
         assert (bits(y) == bits(g["Y_" + name])).all(), name
+
+
+def _dequant_q4_k(rows, n):
+    """Q4_K rows -> f32 by the format's definition: value = d * scale_j * code - dmin * min_j (144-byte super-blocks:
+    f16 d, f16 dmin, 12 bytes of 6-bit (scale, min) pairs, 128 bytes of 4-bit codes)."""
+    blk = rows.reshape(rows.shape[0], n // 256, 144)
+    d = blk[:, :, 0:2].copy().view(np.float16).astype(np.float32)[..., 0]
+    dmin = blk[:, :, 2:4].copy().view(np.float16).astype(np.float32)[..., 0]
+    sc = blk[:, :, 4:16].astype(np.int32)
+    scale = np.empty(blk.shape[:2] + (8,), np.int32); mn = np.empty_like(scale)
+    for j in range(8):
+        if j < 4:
+            scale[..., j] = sc[..., j] & 63; mn[..., j] = sc[..., j + 4] & 63
+        else:
+            scale[..., j] = (sc[..., j + 4] & 15) | ((sc[..., j - 4] >> 6) << 4)
+            mn[..., j] = (sc[..., j + 4] >> 4) | ((sc[..., j] >> 6) << 4)
+    qs = blk[:, :, 16:144].astype(np.int32).reshape(blk.shape[0], blk.shape[1], 4, 32)
+    codes = np.stack([qs & 15, qs >> 4], axis=3).reshape(blk.shape[0], blk.shape[1], 8, 32)     # sub-blocks 2p, 2p+1
+    w = d[..., None, None] * scale[..., None] * codes - dmin[..., None, None] * mn[..., None]
+    return w.reshape(rows.shape[0], n).astype(np.float64)
+
+
+def _dequant_q6_k(rows, n):
+    """Q6_K rows -> f32: value = d * sc[e / 16] * (code - 32) (210-byte super-blocks: 128 low nibbles, 64 bytes of
+    2-bit high parts, 16 int8 scales, f16 d)."""
+    blk = rows.reshape(rows.shape[0], n // 256, 210)
+    ql = blk[:, :, 0:128].astype(np.int32); qh = blk[:, :, 128:192].astype(np.int32)
+    sc = blk[:, :, 192:208].copy().view(np.int8).astype(np.int32)
+    d = blk[:, :, 208:210].copy().view(np.float16).astype(np.float32)[..., 0]
+    w = np.empty(blk.shape[:2] + (256,), np.float64)
+    for e in range(256):
+        h, c, l = e // 128, (e % 128) // 32, e % 32
+        lo = (ql[..., 64 * h + 32 * (c % 2) + l] >> (4 * (c // 2))) & 15
+        hi = (qh[..., 32 * h + l] >> (2 * c)) & 3
+        w[..., e] = d * sc[..., e // 16] * ((lo | (hi << 4)) - 32)
+    return w.reshape(rows.shape[0], n)
+
+
+@pytest.mark.parametrize("wtype", ["q4_k", "q6_k"])
+def test_kquant_dots_against_the_format_definition(oracle, wtype):
+    """Independent of the reference's integer dot: dequantise random blocks by the format's definition in numpy,
+    dequantise the Q8_K activations (d * code), and compare the plain dot product with the oracle's integer path.
+    The two differ only by f32 rounding of the per-super-block terms."""
+    from oracle import oracle as O
+    wt = {"q4_k": O.GGML_Q4_K, "q6_k": O.GGML_Q6_K}[wtype]
+    g = np.random.default_rng(71 + wt)
+    n_in, n_out, T = 1024, 16, 4
+    W = g.integers(0, 256, (n_out, O.QROW_BYTES[wt](n_in)), dtype=np.uint8)
+    blk = W.reshape(n_out, n_in // 256, -1)
+    for col in {O.GGML_Q4_K: (1, 3), O.GGML_Q6_K: (209,)}[wt]:
+        blk[:, :, col] &= 0x3B
+    X = g.standard_normal((T, n_in)).astype(np.float32)
+    q = oracle.q8k_quantize(X)                                      # [T][n_in/256][292]
+    d = q[:, :, 0:4].copy().view(np.float32)[..., 0]
+    codes = q[:, :, 4:260].copy().view(np.int8).astype(np.float64)
+    act = (d[..., None].astype(np.float64) * codes).reshape(T, n_in)
+    w = (_dequant_q4_k if wt == O.GGML_Q4_K else _dequant_q6_k)(W, n_in)
+    want = act @ w.T
+    got = oracle.matmul_q(wt, W, n_in, X)
+    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max(), float(np.abs(got - want).max() / np.abs(want).max())
