@@ -153,6 +153,14 @@ def test_one_process_two_devices(lib, oracle):
             out = D.linear_attn_prefill(dlin, st, pos, *[to(x)[None] for x in li], T, chunk=64)
             assert rel_err(out.cpu().numpy()[0], ref_lin) < TOL, dev
             assert rel_err(st.S.cpu().numpy()[0], S) < TOL, dev
+            # the integer projections opt into their shared memory per device as well
+            from oracle import oracle as O
+            g = np.random.default_rng(16)
+            Wq = g.integers(0, 256, (96, O.QROW_BYTES[O.GGML_Q4_K](512)), dtype=np.uint8)
+            blk = Wq.reshape(96, 2, 144); blk[:, :, 1] &= 0x3B; blk[:, :, 3] &= 0x3B
+            Xq = g.standard_normal((5, 512)).astype(np.float32)
+            got = D.matmul_q(D.QWeight(O.GGML_Q4_K, Wq, 512, device=d), to(Xq)).cpu().numpy()
+            assert (got.view(np.uint32) == oracle.matmul_q(O.GGML_Q4_K, Wq, 512, Xq).view(np.uint32)).all(), dev
     finally:
         lib.ornith_cuda_set_device(0)
         torch.cuda.set_device(0)
